@@ -1,0 +1,167 @@
+/* picasso_b200.h — C ABI of libpicasso_b200.so: the mesh-convolution operators of
+ * PicassoPlus (vertex->facet, facet->facet, facet->vertex; forward and backward), the
+ * spherical-harmonic basis, and the adjacency they need, as CUDA kernels for sm_100a.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller; the library never allocates
+ *     or frees device memory.  Scratch memory is passed in as `workspace` and sized by the
+ *     matching `*_workspace_bytes` query.
+ *   - features are fp32, row-major, contiguous; indices are int32.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  All work
+ *     is enqueued on it; no call synchronises unless its comment says so.
+ *   - return value: PB200_OK (0) or a negative PB200_E* code; pb200_last_error() returns
+ *     a human-readable message for the calling thread's last failure.  Nothing throws,
+ *     prints or exits.
+ *   - output buffers are fully written by the call (no need to zero them first), with the
+ *     values the reference writes into its zero-initialised outputs.
+ *   - results are run-to-run deterministic: no floating-point atomics are used.
+ *
+ * Citations name files of the reference tree (EnyaHermite/PicassoPlus).
+ */
+#ifndef PICASSO_B200_H
+#define PICASSO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PB200_OK            0
+#define PB200_EINVAL       -1   /* bad size / null pointer / unsupported shape            */
+#define PB200_EWORKSPACE   -2   /* workspace missing or too small                          */
+#define PB200_ECUDA        -3   /* a CUDA runtime call or launch failed                    */
+#define PB200_EINDEX       -4   /* an index array holds an out-of-range value              */
+
+/* contraction precision for facet2facet (fp32 accumulation in every mode) */
+#define PB200_PREC_FP32     0   /* fp32-faithful: meets the 1e-4 relative gate             */
+#define PB200_PREC_TF32     1   /* tf32 operands on the tensor cores                       */
+#define PB200_PREC_BF16     2   /* bf16 operands on the tensor cores (2e-2 relative gate)  */
+
+int         pb200_version(void);
+const char* pb200_last_error(void);
+/* number of kernel launches issued by this library in this process so far */
+int64_t     pb200_launch_count(void);
+
+/* ---- per-kernel timing (for benchmarks) -------------------------------------------
+ * When enabled, every launch is bracketed by CUDA events on its stream.  pb200_prof_read
+ * synchronises those events and fills up to `cap` records sorted by total time; it
+ * returns the number of distinct kernels seen.  Off by default. */
+typedef struct { char name[48]; int64_t launches; double total_ms; } pb200_prof_record;
+void pb200_prof_enable(int on);
+void pb200_prof_reset(void);
+int  pb200_prof_read(pb200_prof_record* out, int cap);
+
+/* ---- adjacency ----------------------------------------------------------------------
+ * nfCount[vtMap[face[f][j]]] += 1 for every face corner whose mapped id is >= 0.
+ * Replaces count_vertex_adjface (picasso/mesh/pi_modules/source/decimate_gpu.cu:813-836,
+ * binding decimate.cpp:132-160).  vtMap may be NULL (identity).  nfCount: NvOut ints. */
+int pb200_count_vertex_adjface(int64_t Nf, int64_t NvIn, int64_t NvOut, const int32_t* face,
+                               const int32_t* vtMap, int32_t* nfCount, void* stream);
+
+/* Vertex -> incident face-corner lists in CSR form, keyed by the OUTPUT vertex
+ * vo = vtMap[face[f][j]] (corners with vo < 0 are dropped).  rowptr has NvOut+1 entries;
+ * entries[rowptr[v] .. rowptr[v+1]) hold (f << 2 | j) in ascending order, so every
+ * segmented reduction over a row has one fixed order.  rowptr[v+1]-rowptr[v] equals the
+ * reference's nfCount[v] bit for bit.  `entries` needs 3*Nf ints.  `status` (one int,
+ * device) is set to 0, or to PB200_EINDEX if a face id is outside [0,NvIn) or a vtMap
+ * value is outside [-1,NvOut) (such corners are skipped, never dereferenced).
+ * The reference has no such structure: it scatters with float atomics instead
+ * (picasso/mesh/pi_modules/source/mesh_conv3d_gpu.cu:215,326). */
+size_t pb200_vertex_csr_workspace_bytes(int64_t Nf, int64_t NvOut);
+int pb200_build_vertex_csr(int64_t Nf, int64_t NvIn, int64_t NvOut, const int32_t* face,
+                           const int32_t* vtMap, int32_t* rowptr, int32_t* entries,
+                           int32_t* status, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- vertex2facet -------------------------------------------------------------------
+ * output[f, c*r+m] = sum_{k<3} filter[k,c,m] * input[face[f,k], c]
+ * Replaces vertex2facetConv3dLauncher (mesh_conv3d_gpu.cu:176-195,261-266; binding
+ * mesh_conv3d.cpp:123-152).  input (Nv,C), filter (3,C,r), face (Nf,3), output (Nf,C*r). */
+int pb200_vertex2facet_forward(int64_t Nf, int64_t Nv, int C, int r, const float* input,
+                               const float* filter, const int32_t* face, float* output, void* stream);
+
+/* gradInput[v,c]  = sum_{(f,k): face[f,k]=v} sum_m gradOutput[f,c*r+m] * filter[k,c,m]
+ * gradFilter[k,c,m] = sum_f gradOutput[f,c*r+m] * input[face[f,k], c]
+ * Replaces vertex2facetConv3dGradLauncher (mesh_conv3d_gpu.cu:201-260,267-290; binding
+ * mesh_conv3d.cpp:153-188).  rowptr/entries: CSR built with vtMap = NULL over Nv vertices. */
+size_t pb200_vertex2facet_backward_workspace_bytes(int64_t Nf, int64_t Nv, int C, int r);
+int pb200_vertex2facet_backward(int64_t Nf, int64_t Nv, int C, int r, const float* gradOutput,
+                                const float* input, const float* filter, const int32_t* face,
+                                const int32_t* rowptr, const int32_t* entries,
+                                float* gradInput, float* gradFilter,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- facet2vertex -------------------------------------------------------------------
+ * w[f,co] = sum_k coeff[f,k]*filter[k,c,m];
+ * output[vo,co] = (sum over corners (f,j) with vtMap[face[f,j]] = vo of w[f,co]*input[f,c])
+ *                 / nfCount[vo];  rows no corner maps to are 0.
+ * Replaces facet2vertexConv3dLauncher (mesh_conv3d_gpu.cu:299-329,428-433; binding
+ * mesh_conv3d.cpp:33-74).  input (Nf,C), filter (K,C,r), coeff (Nf,K), nfCount (NvOut),
+ * output (NvOut,C*r); rowptr/entries: CSR built with the same face/vtMap.  The kernels
+ * never read vtMap or face here (the CSR carries them). */
+int pb200_facet2vertex_forward(int64_t Nf, int64_t NvOut, int C, int r, int K, const float* input,
+                               const float* filter, const float* coeff, const int32_t* nfCount,
+                               const int32_t* rowptr, const int32_t* entries, float* output, void* stream);
+
+/* gt[f,co] = sum_{j<3, vo_j>=0} gradOutput[vo_j,co] / nfCount[vo_j];
+ * gradInput[f,c] = sum_m gt[f,co]*w[f,co];  gradFilter[k,c,m] = sum_f coeff[f,k]*input[f,c]*gt[f,co]
+ * Replaces facet2vertexConv3dGradLauncher (mesh_conv3d_gpu.cu:338-426,434-458; binding
+ * mesh_conv3d.cpp:75-122).  vtMap may be NULL (identity). */
+size_t pb200_facet2vertex_backward_workspace_bytes(int64_t Nf, int C, int r, int K);
+int pb200_facet2vertex_backward(int64_t Nf, int64_t NvIn, int64_t NvOut, int C, int r, int K,
+                                const float* gradOutput, const float* input, const float* filter,
+                                const float* coeff, const int32_t* face, const int32_t* nfCount,
+                                const int32_t* vtMap, float* gradInput, float* gradFilter,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- facet2facet --------------------------------------------------------------------
+ * A[f,d,ci] = (1/T_f) sum_{k in samples(f)} bary[k,d]*input[k,ci];
+ * output[f,co] = sum_{d,ci} A[f,d,ci]*filter[co,ci,d];  samples(f) = rows
+ * numInterior[f-1] .. numInterior[f]-1 (numInterior = inclusive cumulative sample count).
+ * Replaces facet2facetConv3dLauncher (mesh_conv3d_gpu.cu:6-37,136-143; binding
+ * mesh_conv3d.cpp:192-228).  input (NiK,Cin), filter (Cout,Cin,F), bary (NiK,F),
+ * output (Nf,Cout).  F <= 50 as in the reference (mesh_conv3d.cpp:211). */
+size_t pb200_facet2facet_forward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision);
+int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input,
+                              const float* filter, const float* bary, const int32_t* numInterior,
+                              float* output, int precision,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* gradInput[k,ci] = (1/T_f) sum_d bary[k,d] * sum_co gradOutput[f,co]*filter[co,ci,d];
+ * gradFilter[co,ci,d] = sum_f gradOutput[f,co]*A[f,d,ci]
+ * Replaces facet2facetConv3dGradLauncher (mesh_conv3d_gpu.cu:45-135,144-168; binding
+ * mesh_conv3d.cpp:229-269). */
+size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision);
+int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
+                               const float* input, const float* filter, const float* bary,
+                               const int32_t* numInterior, float* gradInput, float* gradFilter,
+                               int precision, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- spherical-harmonic basis and triangle geometry -----------------------------------
+ * out[i, 0..(L+1)^2) = real/imaginary spherical-harmonic components of xyz[i] projected
+ * to the unit sphere, in the reference's column order, L <= 5.
+ * Replaces SphHarmCoeff.__call__ (picasso/mesh/layers.py:341-356) with
+ * torch_sph_harm_reorder (picasso/math_utils.py:10-62).  xyz (N,3) contiguous. */
+int pb200_sph_harm_coeff(int64_t N, int L, const float* xyz, float* out, void* stream);
+
+/* geometry[f] = [unit normal (3), plane intercept d, area].  Replaces
+ * compute_triangle_geometry_ (picasso/mesh/pi_modules/decimate.py:70-85).  `vertex` has
+ * `vstride` floats per row, of which the first three are xyz. */
+int pb200_triangle_geometry(int64_t Nf, int64_t Nv, int vstride, const float* vertex,
+                            const int32_t* face, float* geometry, void* stream);
+
+/* ---- row expansion (benchmark block glue) ----------------------------------------------
+ * forward:  out[k,:] = in[f,:] for every sample k of face f (numInterior as above);
+ * backward: gradIn[f,:] = sum over the samples k of f of gradOut[k,:] (fixed order).
+ * The reference does this with torch.repeat_interleave in user code; there is no
+ * counterpart inside its extension. */
+int pb200_expand_rows_forward(int64_t Nf, int64_t NiK, int C, const float* in, const int32_t* numInterior,
+                              float* out, void* stream);
+int pb200_expand_rows_backward(int64_t Nf, int64_t NiK, int C, const float* gradOut, const int32_t* numInterior,
+                               float* gradIn, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PICASSO_B200_H */

@@ -1,0 +1,133 @@
+"""ctypes doorway to oracle/_build/liboracle.so (the plain-C restatement in mesh_oracle.c).
+TEST INFRASTRUCTURE ONLY.  Arguments and results are numpy arrays; `acc64=True` selects the
+double-accumulator build of the same loops (the arbiter)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def build() -> str:
+    subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
+    return os.path.join(_HERE, "_build", "liboracle.so")
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "_build", "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        _LIB = C.CDLL(path)
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _fn(name, acc64):
+    return getattr(lib(), name + ("_f64acc" if acc64 else ""))
+
+
+def _scratch(n, acc64):
+    return np.zeros(max(int(n), 1), dtype=np.float64 if acc64 else np.float32)
+
+
+def v2f_forward(inp, filt, face, acc64=False):
+    inp, filt, face = _f32(inp), _f32(filt), _i32(face)
+    _, Cc, r = filt.shape
+    out = np.zeros((face.shape[0], Cc * r), np.float32)
+    _fn("oracle_v2f_forward", acc64)(C.c_int(face.shape[0]), C.c_int(Cc), C.c_int(r), _p(face), _p(inp),
+                                     _p(filt), _p(out))
+    return out
+
+
+def v2f_backward(gout, inp, filt, face, acc64=False):
+    gout, inp, filt, face = _f32(gout), _f32(inp), _f32(filt), _i32(face)
+    _, Cc, r = filt.shape
+    gin, gf = np.zeros_like(inp), np.zeros_like(filt)
+    s = _scratch(inp.size + filt.size, acc64)
+    _fn("oracle_v2f_backward", acc64)(C.c_int(face.shape[0]), C.c_int(inp.shape[0]), C.c_int(Cc), C.c_int(r),
+                                      _p(face), _p(inp), _p(filt), _p(gout), _p(gin), _p(gf), _p(s))
+    return gin, gf
+
+
+def f2v_forward(inp, filt, coeff, face, nf_count, vt_map, acc64=False):
+    inp, filt, coeff = _f32(inp), _f32(filt), _f32(coeff)
+    face, nf_count, vt_map = _i32(face), _i32(nf_count), _i32(vt_map)
+    K, Cc, r = filt.shape
+    nvo = nf_count.shape[0]
+    out = np.zeros((nvo, Cc * r), np.float32)
+    s = _scratch(out.size, acc64)
+    _fn("oracle_f2v_forward", acc64)(C.c_int(face.shape[0]), C.c_int(nvo), C.c_int(Cc), C.c_int(r), C.c_int(K),
+                                     _p(vt_map), _p(nf_count), _p(face), _p(coeff), _p(inp), _p(filt),
+                                     _p(out), _p(s))
+    return out
+
+
+def f2v_backward(gout, inp, filt, coeff, face, nf_count, vt_map, acc64=False):
+    gout, inp, filt, coeff = _f32(gout), _f32(inp), _f32(filt), _f32(coeff)
+    face, nf_count, vt_map = _i32(face), _i32(nf_count), _i32(vt_map)
+    K, Cc, r = filt.shape
+    gin, gf = np.zeros_like(inp), np.zeros_like(filt)
+    s = _scratch(inp.size + filt.size, acc64)
+    _fn("oracle_f2v_backward", acc64)(C.c_int(face.shape[0]), C.c_int(Cc), C.c_int(r), C.c_int(K), _p(vt_map),
+                                      _p(nf_count), _p(face), _p(coeff), _p(inp), _p(filt), _p(gout),
+                                      _p(gin), _p(gf), _p(s))
+    return gin, gf
+
+
+def f2f_forward(inp, filt, bary, cum, acc64=False):
+    inp, filt, bary, cum = _f32(inp), _f32(filt), _f32(bary), _i32(cum)
+    Cout, Cin, F = filt.shape
+    out = np.zeros((cum.shape[0], Cout), np.float32)
+    _fn("oracle_f2f_forward", acc64)(C.c_int(cum.shape[0]), C.c_int(F), C.c_int(Cin), C.c_int(Cout), _p(cum),
+                                     _p(bary), _p(inp), _p(filt), _p(out))
+    return out
+
+
+def f2f_backward(gout, inp, filt, bary, cum, acc64=False):
+    gout, inp, filt, bary, cum = _f32(gout), _f32(inp), _f32(filt), _f32(bary), _i32(cum)
+    Cout, Cin, F = filt.shape
+    gin, gf = np.zeros_like(inp), np.zeros_like(filt)
+    s = _scratch(inp.size + filt.size, acc64)
+    _fn("oracle_f2f_backward", acc64)(C.c_int(cum.shape[0]), C.c_int(inp.shape[0]), C.c_int(F), C.c_int(Cin),
+                                      C.c_int(Cout), _p(cum), _p(bary), _p(inp), _p(filt), _p(gout),
+                                      _p(gin), _p(gf), _p(s))
+    return gin, gf
+
+
+def count_vertex_adjface(face, vt_map, nv_out):
+    face, vt_map = _i32(face), _i32(vt_map)
+    out = np.zeros(nv_out, np.int32)
+    lib().oracle_count_vertex_adjface(C.c_int(face.shape[0]), _p(face), _p(vt_map), _p(out))
+    return out
+
+
+def sph_harm_coeff(L, xyz, consts):
+    xyz, consts = _f32(xyz), _f32(consts)
+    out = np.zeros((xyz.shape[0], (L + 1) ** 2), np.float32)
+    lib().oracle_sph_harm_coeff(C.c_int(xyz.shape[0]), C.c_int(L), _p(xyz), _p(consts), _p(out))
+    return out
+
+
+def triangle_geometry(vertex, face):
+    vertex, face = _f32(vertex), _i32(face)
+    out = np.zeros((face.shape[0], 5), np.float32)
+    lib().oracle_triangle_geometry(C.c_int(face.shape[0]), C.c_int(vertex.shape[1]), _p(vertex), _p(face), _p(out))
+    return out

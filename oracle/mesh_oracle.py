@@ -1,0 +1,335 @@
+"""CPU restatement (PyTorch, fp32 or fp64 by input dtype) of the reference's mesh
+convolution path.  TEST INFRASTRUCTURE ONLY: nothing in the product package imports this
+file; it exists to check the CUDA kernels and to serve as the timed CPU baseline.
+
+Parity status: the reference ships no tests, golden vectors or fixtures for this path, so
+the restatement is pinned against outputs of the reference's own CUDA operators run on a
+B200 (fixtures under tests/golden/, made by tests/golden/make_golden.py) and against the
+independent plain-C restatement in oracle/mesh_oracle.c.
+
+Each function cites the reference code it follows (paths relative to the reference root).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+
+# ------------------------------------------------------------------ spherical harmonics
+def _sph_constants(dtype: torch.dtype):
+    """Normalisation constants exactly as picasso/math_utils.py:6,17-59 evaluates them: a
+    python scalar combined with the fp32 CPU tensor TPI = tensor(pi), i.e. computed in fp32
+    (fp64 here when the fp64 arbiter is requested)."""
+    TPI = torch.tensor(math.pi, dtype=dtype)
+    s = torch.sqrt
+    c = {}
+    c[0] = 1 / 2. * s(1 / TPI)
+    c[1] = 1 / 2. * s(3 / 2 / TPI)
+    c[2] = 1 / 2. * s(3 / TPI)
+    c[3] = c[1]
+    c[4] = 1 / 4. * s(15 / 2 / TPI)
+    c[5] = 1 / 2. * s(15 / 2 / TPI)
+    c[6] = 1 / 4. * s(5 / TPI)
+    c[7] = c[4]
+    c[8] = c[5]
+    c[9] = 1 / 8. * s(35 / TPI)
+    c[10] = 1 / 4. * s(105 / 2 / TPI)
+    c[11] = 1 / 8. * s(21 / TPI)
+    c[12] = 1 / 4. * s(7 / TPI)
+    c[13], c[14], c[15] = c[9], c[10], c[11]
+    c[16] = 3 / 16. * s(35 / 2 / TPI)
+    c[17] = 3 / 8. * s(35 / TPI)
+    c[18] = 3 / 8. * s(5 / 2 / TPI)
+    c[19] = 3 / 8. * s(5 / TPI)
+    c[20] = 3 / 16. * s(1 / TPI)
+    c[21], c[22], c[23], c[24] = c[16], c[17], c[18], c[19]
+    c[25] = 3 / 32. * s(77 / TPI)
+    c[26] = 3 / 16. * s(385 / 2 / TPI)
+    c[27] = 1 / 32. * s(385 / TPI)
+    c[28] = 1 / 8. * s(1155 / 2 / TPI)
+    c[29] = 1 / 16. * s(165 / 2 / TPI)
+    c[30] = 1 / 16. * s(11 / TPI)
+    c[31], c[32], c[33], c[34], c[35] = c[25], c[26], c[27], c[28], c[29]
+    return c
+
+
+def sph_constants_f32() -> np.ndarray:
+    """The 36 fp32 normalisation constants (for handing to a kernel or a C routine)."""
+    c = _sph_constants(torch.float32)
+    return np.array([float(c[i]) for i in range(36)], dtype=np.float32)
+
+
+def sph_harm_reorder(L: int, phi: torch.Tensor, theta: torch.Tensor) -> torch.Tensor:
+    """picasso/math_utils.py:10-62 (torch_sph_harm_reorder): per degree l the columns are the
+    cos(m phi) terms for m = l..1, the m = 0 term, then the sin(m phi) terms for m = l..1."""
+    if L >= 6:
+        raise NotImplementedError
+    dt = phi.dtype
+    c = _sph_constants(dt)
+    st, ct = torch.sin(theta), torch.cos(theta)
+    out = torch.zeros(phi.shape[0], (L + 1) ** 2, dtype=dt)
+    cos, sin = torch.cos, torch.sin
+    if L >= 0:
+        out[:, 0] = c[0]
+    if L >= 1:
+        out[:, 1] = c[1] * st * cos(phi)
+        out[:, 2] = c[2] * ct
+        out[:, 3] = c[3] * st * sin(phi)
+    if L >= 2:
+        out[:, 4] = c[4] * (st ** 2) * cos(2 * phi)
+        out[:, 5] = c[5] * st * ct * cos(phi)
+        out[:, 6] = c[6] * (3 * (ct ** 2) - 1)
+        out[:, 7] = c[7] * (st ** 2) * sin(2 * phi)
+        out[:, 8] = c[8] * st * ct * sin(phi)
+    if L >= 3:
+        out[:, 9] = c[9] * (st ** 3) * cos(3 * phi)
+        out[:, 10] = c[10] * (st ** 2) * ct * cos(2 * phi)
+        out[:, 11] = c[11] * st * (5 * (ct ** 2) - 1) * cos(phi)
+        out[:, 12] = c[12] * (5 * (ct ** 3) - 3 * ct)
+        out[:, 13] = c[13] * (st ** 3) * sin(3 * phi)
+        out[:, 14] = c[14] * (st ** 2) * ct * sin(2 * phi)
+        out[:, 15] = c[15] * st * (5 * (ct ** 2) - 1) * sin(phi)
+    if L >= 4:
+        out[:, 16] = c[16] * (st ** 4) * cos(4 * phi)
+        out[:, 17] = c[17] * (st ** 3) * ct * cos(3 * phi)
+        out[:, 18] = c[18] * (st ** 2) * (7 * (ct ** 2) - 1) * cos(2 * phi)
+        out[:, 19] = c[19] * st * (7 * (ct ** 3) - 3 * ct) * cos(phi)
+        out[:, 20] = c[20] * (35 * ct ** 4 - 30 * (ct ** 2) + 3)
+        out[:, 21] = c[21] * (st ** 4) * sin(4 * phi)
+        out[:, 22] = c[22] * (st ** 3) * ct * sin(3 * phi)
+        out[:, 23] = c[23] * (st ** 2) * (7 * (ct ** 2) - 1) * sin(2 * phi)
+        out[:, 24] = c[24] * st * (7 * (ct ** 3) - 3 * ct) * sin(phi)
+    if L >= 5:
+        out[:, 25] = c[25] * (st ** 5) * cos(5 * phi)
+        out[:, 26] = c[26] * (st ** 4) * ct * cos(4 * phi)
+        out[:, 27] = c[27] * (st ** 3) * (9 * (ct ** 2) - 1) * cos(3 * phi)
+        out[:, 28] = c[28] * (st ** 2) * (3 * (ct ** 3) - ct) * cos(2 * phi)
+        out[:, 29] = c[29] * st * (21 * ct ** 4 - 14 * ct ** 2 + 1) * cos(phi)
+        out[:, 30] = c[30] * (63 * ct ** 5 - 70 * ct ** 3 + 15 * ct)
+        out[:, 31] = c[31] * (st ** 5) * sin(5 * phi)
+        out[:, 32] = c[32] * (st ** 4) * ct * sin(4 * phi)
+        out[:, 33] = c[33] * (st ** 3) * (9 * (ct ** 2) - 1) * sin(3 * phi)
+        out[:, 34] = c[34] * (st ** 2) * (3 * (ct ** 3) - ct) * sin(2 * phi)
+        out[:, 35] = c[35] * st * (21 * ct ** 4 - 14 * ct ** 2 + 1) * sin(phi)
+    return out
+
+
+def sph_harm_coeff(L: int, cart: torch.Tensor) -> torch.Tensor:
+    """picasso/mesh/layers.py:341-356 (SphHarmCoeff): project to the unit sphere with
+    +1e-10 in the denominator, azimuth phi in [0, 2pi), polar theta measured from +z."""
+    l2 = torch.sqrt(torch.sum(cart ** 2, dim=-1, keepdim=True))
+    p = cart / (l2 + 1e-10)
+    phi = torch.atan2(p[:, 1], p[:, 0])
+    theta = torch.atan2(p[:, 2], torch.linalg.norm(p[:, :2], dim=-1))
+    phi = torch.where(phi < 0, phi + 2 * np.pi, phi)
+    theta = np.pi / 2 - theta
+    return sph_harm_reorder(L, phi, theta)
+
+
+# ----------------------------------------------------------------- geometry / adjacency
+def triangle_geometry(vertex: torch.Tensor, face: torch.Tensor) -> torch.Tensor:
+    """picasso/mesh/pi_modules/decimate.py:70-85: [unit normal, plane intercept, area]."""
+    vertex = vertex[:, :3]
+    face = face.to(torch.long)
+    vec10 = vertex[face[:, 1]] - vertex[face[:, 0]]
+    vec20 = vertex[face[:, 2]] - vertex[face[:, 0]]
+    raw = torch.cross(vec10, vec20, dim=-1)
+    l2 = torch.sqrt(torch.sum(raw ** 2, dim=-1, keepdim=True))
+    area = l2 / 2
+    normal = raw / (l2 + 1e-10)
+    d = -torch.sum(normal * vertex[face[:, 0]], dim=-1, keepdim=True)
+    return torch.cat([normal, d, area], dim=-1)
+
+
+def count_vertex_adjface(face: torch.Tensor, vt_map: torch.Tensor, nv_out: int) -> torch.Tensor:
+    """picasso/mesh/pi_modules/source/decimate_gpu.cu:813-831: one count per face corner
+    whose mapped vertex id is non-negative."""
+    vo = vt_map.to(torch.long)[face.to(torch.long).reshape(-1)]
+    vo = vo[vo >= 0]
+    return torch.bincount(vo, minlength=nv_out).to(torch.int32)
+
+
+# ------------------------------------------------------------------------------ V2F
+def vertex2facet_forward(inp, filt, face):
+    """mesh_conv3d_gpu.cu:176-195: out[f, c*r+m] = sum_k filter[k,c,m] * in[face[f,k], c]."""
+    face = face.to(torch.long)
+    _, C, r = filt.shape
+    out = torch.zeros(face.shape[0], C, r, dtype=inp.dtype)
+    for k in range(3):
+        out += filt[k].unsqueeze(0) * inp[face[:, k]].unsqueeze(-1)
+    return out.reshape(face.shape[0], C * r)
+
+
+def vertex2facet_backward(gout, inp, filt, face):
+    """mesh_conv3d_gpu.cu:201-260: gIn[face[f,k], c] += sum_m gOut[f,c*r+m]*filter[k,c,m];
+    gF[k,c,m] = sum_f gOut[f,c*r+m] * in[face[f,k], c]."""
+    face = face.to(torch.long)
+    _, C, r = filt.shape
+    g = gout.reshape(-1, C, r)
+    gin = torch.zeros_like(inp)
+    gf = torch.zeros_like(filt)
+    for k in range(3):
+        gin.index_add_(0, face[:, k], (g * filt[k].unsqueeze(0)).sum(-1))
+        gf[k] = (g * inp[face[:, k]].unsqueeze(-1)).sum(0)
+    return gin, gf
+
+
+# ------------------------------------------------------------------------------ F2V
+def _f2v_terms(coeff, filt):
+    K, C, r = filt.shape
+    return (coeff @ filt.reshape(K, C * r)).reshape(-1, C, r)   # w[f, c, m]
+
+
+def facet2vertex_forward(inp, filt, coeff, face, nf_count, vt_map):
+    """mesh_conv3d_gpu.cu:299-329: w[f,co] = sum_k coeff[f,k]*filter[k,co];
+    out[vo,co] += w*in[f,c]/nfCount[vo] for the three corners with vo = vtMap[v] >= 0."""
+    face = face.to(torch.long)
+    K, C, r = filt.shape
+    nv_out = nf_count.shape[0]
+    wx = _f2v_terms(coeff, filt) * inp.unsqueeze(-1)          # (Nf, C, r)
+    out = torch.zeros(nv_out, C, r, dtype=inp.dtype)
+    vmap = vt_map.to(torch.long)
+    nf = nf_count.to(inp.dtype)
+    for j in range(3):
+        vo = vmap[face[:, j]]
+        ok = vo >= 0
+        vo_ok = vo[ok]
+        out.index_add_(0, vo_ok, wx[ok] / nf[vo_ok].reshape(-1, 1, 1))
+    return out.reshape(nv_out, C * r)
+
+
+def facet2vertex_backward(gout, inp, filt, coeff, face, nf_count, vt_map):
+    """mesh_conv3d_gpu.cu:338-426: gt[f,co] = sum_{corners, vo>=0} gOut[vo,co]/nfCount[vo];
+    gIn[f,c] = sum_m gt*w;  gF[k,c,m] = sum_f coeff[f,k]*in[f,c]*gt[f,c,m]."""
+    face = face.to(torch.long)
+    K, C, r = filt.shape
+    vmap = vt_map.to(torch.long)
+    nf = nf_count.to(inp.dtype)
+    g = gout.reshape(-1, C, r)
+    gt = torch.zeros(face.shape[0], C, r, dtype=inp.dtype)
+    for j in range(3):
+        vo = vmap[face[:, j]]
+        ok = vo >= 0
+        vo_c = vo.clamp(min=0)
+        term = g[vo_c] / nf[vo_c].clamp(min=1).reshape(-1, 1, 1)
+        gt += torch.where(ok.reshape(-1, 1, 1), term, torch.zeros_like(term))
+    w = _f2v_terms(coeff, filt)
+    gin = (gt * w).sum(-1)
+    gf = (coeff.t() @ (inp.unsqueeze(-1) * gt).reshape(-1, C * r)).reshape(K, C, r)
+    return gin, gf
+
+
+# ------------------------------------------------------------------------------ F2F
+def _f2f_segments(cum, n_samples):
+    cum = cum.to(torch.long)
+    counts = torch.diff(cum, prepend=torch.zeros(1, dtype=torch.long))
+    fid = torch.repeat_interleave(torch.arange(cum.shape[0]), counts, output_size=n_samples)
+    return counts, fid
+
+
+def _f2f_A(inp, bary, counts, fid, f0, f1, k0, k1):
+    """A[f,d,ci] = (1/T_f) sum_{k in f} bary[k,d]*in[k,ci] for faces [f0,f1)."""
+    F = bary.shape[1]
+    A = torch.zeros(f1 - f0, F, inp.shape[1], dtype=inp.dtype)
+    if k1 > k0:
+        A.index_add_(0, fid[k0:k1] - f0, bary[k0:k1].unsqueeze(-1) * inp[k0:k1].unsqueeze(1))
+    T = counts[f0:f1].to(inp.dtype).clamp(min=1).reshape(-1, 1, 1)
+    return A / T
+
+
+def _face_chunks(cum, chunk):
+    nf = cum.shape[0]
+    cl = cum.to(torch.long)
+    for f0 in range(0, nf, chunk):
+        f1 = min(nf, f0 + chunk)
+        k0 = int(cl[f0 - 1]) if f0 > 0 else 0
+        k1 = int(cl[f1 - 1])
+        yield f0, f1, k0, k1
+
+
+def facet2facet_forward(inp, filt, bary, cum, chunk=8192):
+    """mesh_conv3d_gpu.cu:6-37: out[f,co] = (1/T_f) sum_ci sum_{k in f} in[k,ci] *
+    sum_d bary[k,d]*filter[co,ci,d]; the samples of face f are rows cum[f-1]..cum[f]-1
+    (cum = inclusive cumulative sample count); a face with no samples gives 0."""
+    Cout = filt.shape[0]
+    counts, fid = _f2f_segments(cum, inp.shape[0])
+    out = torch.zeros(cum.shape[0], Cout, dtype=inp.dtype)
+    Wt = filt.permute(2, 1, 0).reshape(-1, Cout)             # [(d,ci), co]
+    for f0, f1, k0, k1 in _face_chunks(cum, chunk):
+        A = _f2f_A(inp, bary, counts, fid, f0, f1, k0, k1)
+        out[f0:f1] = A.reshape(f1 - f0, -1) @ Wt
+    return out
+
+
+def facet2facet_backward(gout, inp, filt, bary, cum, chunk=8192):
+    """mesh_conv3d_gpu.cu:45-135: gIn[k,ci] = (1/T_f) sum_co gOut[f,co] sum_d bary[k,d] *
+    filter[co,ci,d];  gF[co,ci,d] = sum_f gOut[f,co] * A[f,d,ci]."""
+    Cout, Cin, F = filt.shape
+    counts, fid = _f2f_segments(cum, inp.shape[0])
+    gin = torch.zeros_like(inp)
+    gfl = torch.zeros(F * Cin, Cout, dtype=inp.dtype)
+    Wt = filt.permute(2, 1, 0).reshape(-1, Cout)
+    for f0, f1, k0, k1 in _face_chunks(cum, chunk):
+        A = _f2f_A(inp, bary, counts, fid, f0, f1, k0, k1)
+        gfl += A.reshape(f1 - f0, -1).t() @ gout[f0:f1]
+        if k1 > k0:
+            gA = (gout[f0:f1] @ Wt.t()).reshape(f1 - f0, F, Cin)
+            gA = gA / counts[f0:f1].to(inp.dtype).clamp(min=1).reshape(-1, 1, 1)
+            gin[k0:k1] = (bary[k0:k1].unsqueeze(-1) * gA[fid[k0:k1] - f0]).sum(1)
+    gf = gfl.reshape(F, Cin, Cout).permute(2, 1, 0).contiguous()
+    return gin, gf
+
+
+# ------------------------------------------------------------- autograd wrappers (CPU)
+class _V2F(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, inp, filt, face):
+        ctx.save_for_backward(inp, filt, face)
+        return vertex2facet_forward(inp, filt, face)
+
+    @staticmethod
+    def backward(ctx, g):
+        gi, gf = vertex2facet_backward(g.contiguous(), *ctx.saved_tensors)
+        return gi, gf, None
+
+
+class _F2V(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, inp, filt, coeff, face, nf_count, vt_map):
+        ctx.save_for_backward(inp, filt, coeff, face, nf_count, vt_map)
+        return facet2vertex_forward(inp, filt, coeff, face, nf_count, vt_map)
+
+    @staticmethod
+    def backward(ctx, g):
+        gi, gf = facet2vertex_backward(g.contiguous(), *ctx.saved_tensors)
+        return gi, gf, None, None, None, None
+
+
+class _F2F(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, inp, filt, bary, cum):
+        ctx.save_for_backward(inp, filt, bary, cum)
+        return facet2facet_forward(inp, filt, bary, cum)
+
+    @staticmethod
+    def backward(ctx, g):
+        gi, gf = facet2facet_backward(g.contiguous(), *ctx.saved_tensors)
+        return gi, gf, None, None
+
+
+vertex2facet = _V2F.apply
+facet2vertex = _F2V.apply
+facet2facet = _F2F.apply
+
+
+def conv_block(x, Wv, Wf, Wo, face, counts, cum, bary_sh, coeff, nf_count, vt_map, sh_eye):
+    """The benchmark's V2F -> F2F -> F2V block: y = V2F(x, (SH(eye3) @ Wv) as (3,Cin,1));
+    texture rows repeat y[f] once per sample of f; z = F2F(tex, Wf, SH(bary), cum);
+    o = F2V(z, Wo, SH(normals), face, nfCount, vtMap)."""
+    cin = x.shape[1]
+    y = vertex2facet(x, (sh_eye @ Wv).reshape(3, cin, 1), face)
+    tex = torch.repeat_interleave(y, counts.to(torch.long), dim=0)
+    z = facet2facet(tex, Wf, bary_sh, cum)
+    return facet2vertex(z, Wo, coeff, face, nf_count, vt_map)

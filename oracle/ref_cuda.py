@@ -1,0 +1,105 @@
+"""ctypes doorway to oracle/_ref/libref_mesh_conv3d.so: the reference's own, unmodified
+CUDA kernels (compiled for sm_100a by oracle/Makefile, target `ref`), called on CUDA torch
+tensors.  TEST INFRASTRUCTURE ONLY; used as the live parity checker on a GPU and to make
+the fixtures under tests/golden/.  Output allocation follows the reference binding
+(picasso/mesh/pi_modules/source/mesh_conv3d.cpp:67,112-113,147,180-181,222,261-262):
+zero-initialised, dtype and device of `input`.
+
+The reference kernels read nfCount[vtMap[v]] before testing vtMap[v] >= 0
+(mesh_conv3d_gpu.cu:324-325), an out-of-bounds read when vtMap holds -1; callers here must
+pass a vtMap without negative entries."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PATH = os.path.join(_HERE, "_ref", "libref_mesh_conv3d.so")
+_LIB = None
+
+
+def available() -> bool:
+    return os.path.exists(_PATH) and torch.cuda.is_available()
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(_PATH)
+    return _LIB
+
+
+def _p(t):
+    assert t.is_cuda and t.is_contiguous()
+    return C.c_void_p(t.data_ptr())
+
+
+def _chk(code):
+    if code != 0:
+        raise RuntimeError(f"reference CUDA op failed with cudaError {code}")
+
+
+def _sync_in():
+    torch.cuda.synchronize()   # the reference uses the legacy default stream
+
+
+def v2f_forward(inp, filt, face):
+    _sync_in()
+    _, Cc, r = filt.shape
+    out = torch.zeros(face.shape[0], Cc * r, dtype=inp.dtype, device=inp.device)
+    _chk(lib().ref_v2f_forward(face.shape[0], Cc, r, _p(face), _p(inp), _p(filt), _p(out)))
+    return out
+
+
+def v2f_backward(gout, inp, filt, face):
+    _sync_in()
+    _, Cc, r = filt.shape
+    gin, gf = torch.zeros_like(inp), torch.zeros_like(filt)
+    _chk(lib().ref_v2f_backward(face.shape[0], Cc, r, _p(face), _p(inp), _p(filt), _p(gout), _p(gin), _p(gf)))
+    return gin, gf
+
+
+def f2v_forward(inp, filt, coeff, face, nf_count, vt_map):
+    assert int(vt_map.min()) >= 0, "reference kernel reads out of bounds for negative vtMap"
+    _sync_in()
+    K, Cc, r = filt.shape
+    out = torch.zeros(nf_count.shape[0], Cc * r, dtype=inp.dtype, device=inp.device)
+    _chk(lib().ref_f2v_forward(face.shape[0], Cc, r, K, _p(vt_map), _p(nf_count), _p(face), _p(coeff),
+                               _p(inp), _p(filt), _p(out)))
+    return out
+
+
+def f2v_backward(gout, inp, filt, coeff, face, nf_count, vt_map):
+    assert int(vt_map.min()) >= 0, "reference kernel reads out of bounds for negative vtMap"
+    _sync_in()
+    K, Cc, r = filt.shape
+    gin, gf = torch.zeros_like(inp), torch.zeros_like(filt)
+    _chk(lib().ref_f2v_backward(face.shape[0], Cc, r, K, _p(vt_map), _p(nf_count), _p(face), _p(coeff),
+                                _p(inp), _p(filt), _p(gout), _p(gin), _p(gf)))
+    return gin, gf
+
+
+def f2f_forward(inp, filt, bary, cum):
+    _sync_in()
+    Cout, Cin, F = filt.shape
+    out = torch.zeros(cum.shape[0], Cout, dtype=inp.dtype, device=inp.device)
+    _chk(lib().ref_f2f_forward(cum.shape[0], F, Cin, Cout, _p(cum), _p(bary), _p(inp), _p(filt), _p(out)))
+    return out
+
+
+def f2f_backward(gout, inp, filt, bary, cum):
+    _sync_in()
+    Cout, Cin, F = filt.shape
+    gin, gf = torch.zeros_like(inp), torch.zeros_like(filt)
+    _chk(lib().ref_f2f_backward(cum.shape[0], F, Cin, Cout, _p(cum), _p(bary), _p(inp), _p(filt), _p(gout),
+                                _p(gin), _p(gf)))
+    return gin, gf
+
+
+def count_vertex_adjface(face, vt_map, nv_out):
+    _sync_in()
+    out = torch.zeros(nv_out, dtype=torch.int32, device=face.device)
+    _chk(lib().ref_count_vertex_adjface(face.shape[0], _p(face), _p(vt_map), _p(out)))
+    return out

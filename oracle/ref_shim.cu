@@ -1,0 +1,71 @@
+// C-ABI doorway to the reference's own host launchers, so that the parity tests can call
+// the unmodified reference CUDA kernels through ctypes.  TEST INFRASTRUCTURE ONLY.
+// This file holds declarations and forwarding calls only; the kernels themselves are
+// compiled from the reference tree where it lies (see oracle/Makefile, target `ref`).
+// Launcher signatures: picasso/mesh/pi_modules/source/mesh_conv3d.cpp:9-23 and
+// picasso/mesh/pi_modules/source/decimate.cpp (countVertexAdjfaceLauncher).
+#include <cuda_runtime.h>
+
+void facet2vertexConv3dLauncher(int NfIn, int C, int r, int K, const int* vtMap, const int* nfCount, const int* face,
+                                const float* coeff, const float* input, const float* filter, float* output);
+void vertex2facetConv3dLauncher(int NfIn, int C, int r, const int* face,
+                                const float* input, const float* filter, float* output);
+void facet2facetConv3dLauncher(int NfIn, int F, int Cin, int Cout, const int* numInterior, const float* intrplWgts,
+                               const float* input, const float* filter, float* output);
+void facet2vertexConv3dGradLauncher(int NfIn, int C, int r, int K, const int* vtMap, const int* nfCount, const int* face,
+                                    const float* coeff, const float* input, const float* filter, const float* gradOutput,
+                                    float* gradInput, float* gradFilter);
+void vertex2facetConv3dGradLauncher(int NfIn, int C, int r, const int* face, const float* input, const float* filter,
+                                    const float* gradOutput, float* gradInput, float* gradFilter);
+void facet2facetConv3dGradLauncher(int NfIn, int F, int Cin, int Cout, const int* numInterior, const float* intrplWgts,
+                                   const float* input, const float* filter, const float* gradOutput,
+                                   float* gradInput, float* gradFilter);
+void countVertexAdjfaceLauncher(int NfIn, const int* face, const int* vtMap, int* nfCount);
+
+// The reference launches on the legacy default stream and never checks errors; each
+// doorway synchronises the device and returns the CUDA status so a test can assert on it.
+static int finish() {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaGetLastError();
+    return (int)e;
+}
+
+extern "C" {
+int ref_f2v_forward(int NfIn, int C, int r, int K, const int* vtMap, const int* nfCount, const int* face,
+                    const float* coeff, const float* input, const float* filter, float* output) {
+    facet2vertexConv3dLauncher(NfIn, C, r, K, vtMap, nfCount, face, coeff, input, filter, output);
+    return finish();
+}
+int ref_v2f_forward(int NfIn, int C, int r, const int* face, const float* input, const float* filter, float* output) {
+    vertex2facetConv3dLauncher(NfIn, C, r, face, input, filter, output);
+    return finish();
+}
+int ref_f2f_forward(int NfIn, int F, int Cin, int Cout, const int* numInterior, const float* bary,
+                    const float* input, const float* filter, float* output) {
+    facet2facetConv3dLauncher(NfIn, F, Cin, Cout, numInterior, bary, input, filter, output);
+    return finish();
+}
+int ref_f2v_backward(int NfIn, int C, int r, int K, const int* vtMap, const int* nfCount, const int* face,
+                     const float* coeff, const float* input, const float* filter, const float* gradOutput,
+                     float* gradInput, float* gradFilter) {
+    facet2vertexConv3dGradLauncher(NfIn, C, r, K, vtMap, nfCount, face, coeff, input, filter, gradOutput,
+                                   gradInput, gradFilter);
+    return finish();
+}
+int ref_v2f_backward(int NfIn, int C, int r, const int* face, const float* input, const float* filter,
+                     const float* gradOutput, float* gradInput, float* gradFilter) {
+    vertex2facetConv3dGradLauncher(NfIn, C, r, face, input, filter, gradOutput, gradInput, gradFilter);
+    return finish();
+}
+int ref_f2f_backward(int NfIn, int F, int Cin, int Cout, const int* numInterior, const float* bary,
+                     const float* input, const float* filter, const float* gradOutput,
+                     float* gradInput, float* gradFilter) {
+    facet2facetConv3dGradLauncher(NfIn, F, Cin, Cout, numInterior, bary, input, filter, gradOutput,
+                                  gradInput, gradFilter);
+    return finish();
+}
+int ref_count_vertex_adjface(int NfIn, const int* face, const int* vtMap, int* nfCount) {
+    countVertexAdjfaceLauncher(NfIn, face, vtMap, nfCount);
+    return finish();
+}
+}

@@ -1,0 +1,327 @@
+// Adjacency: per-vertex incident-face counts, the vertex -> (face, corner) CSR that every
+// scatter-shaped kernel pulls through, triangle geometry, and row expansion by sample
+// counts.  All integer work; results are bit-exact and independent of scheduling.
+#include "common.cuh"
+
+namespace pb {
+
+// ---------------------------------------------------------------- counting / validation
+// One thread per face corner.  Out-of-range ids are reported through `status` and the
+// corner is skipped, so no kernel downstream ever dereferences a bad index.
+__global__ void corner_count_kernel(int64_t ncorner, int64_t NvIn, int64_t NvOut,
+                                    const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap,
+                                    int32_t* __restrict__ cnt, int32_t* __restrict__ status) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ncorner) return;
+    int vi = face[i];
+    if (vi < 0 || vi >= NvIn) { if (status) *status = PB200_EINDEX; return; }
+    int vo = vtMap ? vtMap[vi] : vi;
+    if (vo >= NvOut || vo < -1) { if (status) *status = PB200_EINDEX; return; }
+    if (vo >= 0) atomicAdd(&cnt[vo], 1);
+}
+
+// ------------------------------------------------------------------------ exclusive scan
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_ITEMS = 8;
+constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;
+
+__global__ void scan_tiles_kernel(const int32_t* __restrict__ in, int64_t n, int32_t* __restrict__ out,
+                                  int32_t* __restrict__ tile_sum) {
+    __shared__ int32_t warp_tot[SCAN_THREADS / 32];
+    int64_t base = (int64_t)blockIdx.x * SCAN_TILE + (int64_t)threadIdx.x * SCAN_ITEMS;
+    int32_t v[SCAN_ITEMS];
+    int32_t run = 0;
+#pragma unroll
+    for (int j = 0; j < SCAN_ITEMS; ++j) {
+        int32_t x = (base + j < n) ? in[base + j] : 0;
+        v[j] = run;
+        run += x;
+    }
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int32_t inc = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) warp_tot[warp] = inc;
+    __syncthreads();
+    int32_t warp_off = 0;
+    for (int w = 0; w < warp; ++w) warp_off += warp_tot[w];
+    int32_t excl = warp_off + inc - run;
+#pragma unroll
+    for (int j = 0; j < SCAN_ITEMS; ++j)
+        if (base + j < n) out[base + j] = excl + v[j];
+    if (threadIdx.x == SCAN_THREADS - 1) tile_sum[blockIdx.x] = warp_off + inc;
+}
+
+__global__ void scan_tile_sums_kernel(int32_t* __restrict__ tile_sum, int ntiles, int32_t* __restrict__ total_out) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int32_t run = 0;
+    for (int t = 0; t < ntiles; ++t) { int32_t x = tile_sum[t]; tile_sum[t] = run; run += x; }
+    *total_out = run;
+}
+
+__global__ void scan_finish_kernel(int32_t* __restrict__ rowptr, int64_t n, const int32_t* __restrict__ tile_off,
+                                   int32_t* __restrict__ cursor) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int32_t v = rowptr[i] + tile_off[i / SCAN_TILE];
+    rowptr[i] = v;
+    cursor[i] = v;
+}
+
+// -------------------------------------------------------------------------------- fill
+__global__ void corner_fill_kernel(int64_t ncorner, int64_t NvIn, int64_t NvOut,
+                                   const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap,
+                                   int32_t* __restrict__ cursor, int32_t* __restrict__ entries) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ncorner) return;
+    int vi = face[i];
+    if (vi < 0 || vi >= NvIn) return;
+    int vo = vtMap ? vtMap[vi] : vi;
+    if (vo >= NvOut || vo < 0) return;
+    int32_t pos = atomicAdd(&cursor[vo], 1);
+    int64_t f = i / 3;
+    entries[pos] = (int32_t)((f << 2) | (i - 3 * f));
+}
+
+// Rows come out of the atomic fill in arbitrary order; sorting each row ascending makes
+// the CSR (and every reduction that walks it) independent of scheduling.
+constexpr int SHORT_ROW = 32;
+
+__global__ void sort_short_rows_kernel(int64_t nrows, const int32_t* __restrict__ rowptr,
+                                       int32_t* __restrict__ entries, int32_t* __restrict__ long_rows,
+                                       int32_t* __restrict__ n_long) {
+    int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= nrows) return;
+    int beg = rowptr[v], end = rowptr[v + 1];
+    int deg = end - beg;
+    if (deg <= 1) return;
+    if (deg > SHORT_ROW) { long_rows[atomicAdd(n_long, 1)] = (int32_t)v; return; }
+    int32_t a[SHORT_ROW];
+    for (int i = 0; i < deg; ++i) a[i] = entries[beg + i];
+    for (int i = 1; i < deg; ++i) {
+        int32_t x = a[i];
+        int j = i - 1;
+        while (j >= 0 && a[j] > x) { a[j + 1] = a[j]; --j; }
+        a[j + 1] = x;
+    }
+    for (int i = 0; i < deg; ++i) entries[beg + i] = a[i];
+}
+
+// One warp per long row: every element finds its rank by counting smaller elements
+// (all entries of a row are distinct), writes itself to that slot of `tmp`, then the
+// row is copied back.
+__global__ void sort_long_rows_kernel(const int32_t* __restrict__ rowptr, int32_t* __restrict__ entries,
+                                      const int32_t* __restrict__ long_rows, const int32_t* __restrict__ n_long,
+                                      int32_t* __restrict__ tmp) {
+    int lane = threadIdx.x & 31;
+    int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int nwarps = (gridDim.x * blockDim.x) >> 5;
+    int total = *n_long;
+    for (int r = warp; r < total; r += nwarps) {
+        int v = long_rows[r];
+        int beg = rowptr[v], end = rowptr[v + 1];
+        for (int i = beg + lane; i < end; i += 32) {
+            int32_t x = entries[i];
+            int rank = 0;
+            for (int j = beg; j < end; ++j) rank += (entries[j] < x);
+            tmp[beg + rank] = x;
+        }
+        __syncwarp();
+        for (int i = beg + lane; i < end; i += 32) entries[i] = tmp[i];
+        __syncwarp();
+    }
+}
+
+// ----------------------------------------------------------------------------- geometry
+__global__ void triangle_geometry_kernel(int64_t Nf, int64_t Nv, int vstride, const float* __restrict__ vertex,
+                                         const int32_t* __restrict__ face, float* __restrict__ geom) {
+    int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (f >= Nf) return;
+    int i0 = face[3 * f], i1 = face[3 * f + 1], i2 = face[3 * f + 2];
+    float* g = geom + f * 5;
+    if (i0 < 0 || i1 < 0 || i2 < 0 || i0 >= Nv || i1 >= Nv || i2 >= Nv) {
+        g[0] = g[1] = g[2] = g[3] = g[4] = 0.f;
+        return;
+    }
+    const float* a = vertex + (int64_t)i0 * vstride;
+    const float* b = vertex + (int64_t)i1 * vstride;
+    const float* c = vertex + (int64_t)i2 * vstride;
+    float ax = a[0], ay = a[1], az = a[2];
+    float ux = b[0] - ax, uy = b[1] - ay, uz = b[2] - az;
+    float vx = c[0] - ax, vy = c[1] - ay, vz = c[2] - az;
+    float nx = __fsub_rn(__fmul_rn(uy, vz), __fmul_rn(uz, vy));
+    float ny = __fsub_rn(__fmul_rn(uz, vx), __fmul_rn(ux, vz));
+    float nz = __fsub_rn(__fmul_rn(ux, vy), __fmul_rn(uy, vx));
+    float l2 = sqrtf(__fadd_rn(__fadd_rn(__fmul_rn(nx, nx), __fmul_rn(ny, ny)), __fmul_rn(nz, nz)));
+    float den = l2 + 1e-10f;
+    nx = nx / den; ny = ny / den; nz = nz / den;
+    g[0] = nx; g[1] = ny; g[2] = nz;
+    g[3] = -__fadd_rn(__fadd_rn(__fmul_rn(nx, ax), __fmul_rn(ny, ay)), __fmul_rn(nz, az));
+    g[4] = l2 / 2.f;
+}
+
+// ------------------------------------------------------------------------ row expansion
+// The samples of face f are rows cum[f-1] .. cum[f]-1 (cum = inclusive running count).
+__device__ __forceinline__ int64_t face_of_sample(const int32_t* __restrict__ cum, int64_t Nf, int64_t k) {
+    int64_t lo = 0, hi = Nf;            // first f with cum[f] > k
+    while (lo < hi) {
+        int64_t mid = (lo + hi) >> 1;
+        if (cum[mid] > k) hi = mid; else lo = mid + 1;
+    }
+    return lo;
+}
+
+template <int VEC>
+__global__ void expand_rows_fwd_kernel(int64_t Nf, int64_t NiK, int CVn, const float* __restrict__ in,
+                                       const int32_t* __restrict__ cum, float* __restrict__ out) {
+    int64_t total = NiK * CVn;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t k = i / CVn;
+        int c = (int)(i - k * CVn);
+        int64_t f = face_of_sample(cum, Nf, k);
+        if (f >= Nf) continue;
+        if (VEC == 4) {
+            float4 v = __ldg(reinterpret_cast<const float4*>(in) + f * CVn + c);
+            __stcs(reinterpret_cast<float4*>(out) + i, v);
+        } else {
+            out[i] = in[f * CVn + c];
+        }
+    }
+}
+
+template <int VEC>
+__global__ void expand_rows_bwd_kernel(int64_t Nf, int CVn, const float* __restrict__ gout,
+                                       const int32_t* __restrict__ cum, float* __restrict__ gin) {
+    int64_t total = Nf * CVn;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t f = i / CVn;
+        int c = (int)(i - f * CVn);
+        int k0 = f > 0 ? cum[f - 1] : 0, k1 = cum[f];
+        if (VEC == 4) {
+            float4 acc = zero4();
+            for (int k = k0; k < k1; ++k)
+                add4(acc, __ldcs(reinterpret_cast<const float4*>(gout) + (int64_t)k * CVn + c));
+            reinterpret_cast<float4*>(gin)[i] = acc;
+        } else {
+            float acc = 0.f;
+            for (int k = k0; k < k1; ++k) acc += gout[(int64_t)k * CVn + c];
+            gin[i] = acc;
+        }
+    }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace pb
+
+using namespace pb;
+
+extern "C" {
+
+int pb200_count_vertex_adjface(int64_t Nf, int64_t NvIn, int64_t NvOut, const int32_t* face,
+                               const int32_t* vtMap, int32_t* nfCount, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && NvIn >= 0 && NvOut >= 0 && Nf < (1LL << 29), PB200_EINVAL, "count_vertex_adjface: bad sizes");
+    if (NvOut == 0) return PB200_OK;
+    PB_REQUIRE(nfCount && (Nf == 0 || face), PB200_EINVAL, "count_vertex_adjface: null pointer");
+    PB_CUDA(cudaMemsetAsync(nfCount, 0, sizeof(int32_t) * NvOut, stream));
+    if (Nf == 0) return PB200_OK;
+    PB_LAUNCH("corner_count", corner_count_kernel, (unsigned)ceil_div(3 * Nf, 256), 256, 0, stream,
+              3 * Nf, NvIn, NvOut, face, vtMap, nfCount, (int32_t*)nullptr);
+    return PB200_OK;
+}
+
+size_t pb200_vertex_csr_workspace_bytes(int64_t Nf, int64_t NvOut) {
+    if (Nf < 0 || NvOut < 0) return 0;
+    size_t cursor = align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    size_t tiles = align_up(sizeof(int32_t) * (size_t)(ceil_div(NvOut + 1, SCAN_TILE) + 1), 256);
+    size_t longs = align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    size_t tmp = align_up(sizeof(int32_t) * (size_t)(3 * Nf + 1), 256);
+    return cursor + tiles + longs + tmp + 256;
+}
+
+int pb200_build_vertex_csr(int64_t Nf, int64_t NvIn, int64_t NvOut, const int32_t* face,
+                           const int32_t* vtMap, int32_t* rowptr, int32_t* entries, int32_t* status,
+                           void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && NvIn >= 0 && NvOut >= 0 && Nf < (1LL << 29) && NvOut < (1LL << 31) - 1, PB200_EINVAL,
+               "build_vertex_csr: bad sizes");
+    PB_REQUIRE(rowptr && status && (Nf == 0 || (face && entries)), PB200_EINVAL, "build_vertex_csr: null pointer");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_vertex_csr_workspace_bytes(Nf, NvOut), PB200_EWORKSPACE,
+               "build_vertex_csr: workspace too small");
+    char* w = (char*)workspace;
+    int32_t* cursor = (int32_t*)w;  w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int ntiles = (int)ceil_div(NvOut + 1, SCAN_TILE);
+    int32_t* tile_sum = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(ntiles + 1), 256);
+    int32_t* long_rows = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int32_t* tmp = (int32_t*)w;      w += align_up(sizeof(int32_t) * (size_t)(3 * Nf + 1), 256);
+    int32_t* n_long = (int32_t*)w;
+
+    PB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    PB_CUDA(cudaMemsetAsync(cursor, 0, sizeof(int32_t) * (NvOut + 1), stream));
+    PB_CUDA(cudaMemsetAsync(n_long, 0, sizeof(int32_t), stream));
+    if (Nf > 0)
+        PB_LAUNCH("corner_count", corner_count_kernel, (unsigned)ceil_div(3 * Nf, 256), 256, 0, stream,
+                  3 * Nf, NvIn, NvOut, face, vtMap, cursor, status);
+    // exclusive scan of cursor[0..NvOut] (last slot is 0) -> rowptr[0..NvOut]
+    PB_LAUNCH("scan_tiles", scan_tiles_kernel, ntiles, SCAN_THREADS, 0, stream,
+              (const int32_t*)cursor, NvOut + 1, rowptr, tile_sum);
+    PB_LAUNCH("scan_tile_sums", scan_tile_sums_kernel, 1, 32, 0, stream, tile_sum, ntiles, tile_sum + ntiles);
+    PB_LAUNCH("scan_finish", scan_finish_kernel, (unsigned)ceil_div(NvOut + 1, 256), 256, 0, stream,
+              rowptr, NvOut + 1, (const int32_t*)tile_sum, cursor);
+    if (Nf > 0 && NvOut > 0) {
+        PB_LAUNCH("corner_fill", corner_fill_kernel, (unsigned)ceil_div(3 * Nf, 256), 256, 0, stream,
+                  3 * Nf, NvIn, NvOut, face, vtMap, cursor, entries);
+        PB_LAUNCH("sort_short_rows", sort_short_rows_kernel, (unsigned)ceil_div(NvOut, 128), 128, 0, stream,
+                  NvOut, (const int32_t*)rowptr, entries, long_rows, n_long);
+        PB_LAUNCH("sort_long_rows", sort_long_rows_kernel, 2 * sm_count(), 256, 0, stream,
+                  (const int32_t*)rowptr, entries, (const int32_t*)long_rows, (const int32_t*)n_long, tmp);
+    }
+    return PB200_OK;
+}
+
+int pb200_triangle_geometry(int64_t Nf, int64_t Nv, int vstride, const float* vertex, const int32_t* face,
+                            float* geometry, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && Nv >= 0 && vstride >= 3, PB200_EINVAL, "triangle_geometry: bad sizes");
+    if (Nf == 0) return PB200_OK;
+    PB_REQUIRE(vertex && face && geometry, PB200_EINVAL, "triangle_geometry: null pointer");
+    PB_LAUNCH("triangle_geometry", triangle_geometry_kernel, (unsigned)ceil_div(Nf, 256), 256, 0, stream,
+              Nf, Nv, vstride, vertex, face, geometry);
+    return PB200_OK;
+}
+
+int pb200_expand_rows_forward(int64_t Nf, int64_t NiK, int C, const float* in, const int32_t* cum, float* out,
+                              void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && NiK >= 0 && C > 0, PB200_EINVAL, "expand_rows_forward: bad sizes");
+    if (NiK == 0) return PB200_OK;
+    PB_REQUIRE(in && cum && out, PB200_EINVAL, "expand_rows_forward: null pointer");
+    bool vec = (C % 4 == 0) && aligned16(in) && aligned16(out);
+    int CVn = vec ? C / 4 : C;
+    int grid = persistent_blocks(NiK * CVn, 256, 16);
+    if (vec) PB_LAUNCH("expand_rows_fwd", expand_rows_fwd_kernel<4>, grid, 256, 0, stream, Nf, NiK, CVn, in, cum, out);
+    else     PB_LAUNCH("expand_rows_fwd", expand_rows_fwd_kernel<1>, grid, 256, 0, stream, Nf, NiK, CVn, in, cum, out);
+    return PB200_OK;
+}
+
+int pb200_expand_rows_backward(int64_t Nf, int64_t NiK, int C, const float* gout, const int32_t* cum, float* gin,
+                               void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && NiK >= 0 && C > 0, PB200_EINVAL, "expand_rows_backward: bad sizes");
+    if (Nf == 0) return PB200_OK;
+    PB_REQUIRE(cum && gin && (NiK == 0 || gout), PB200_EINVAL, "expand_rows_backward: null pointer");
+    bool vec = (C % 4 == 0) && aligned16(gout) && aligned16(gin);
+    int CVn = vec ? C / 4 : C;
+    int grid = persistent_blocks(Nf * CVn, 256, 16);
+    if (vec) PB_LAUNCH("expand_rows_bwd", expand_rows_bwd_kernel<4>, grid, 256, 0, stream, Nf, CVn, gout, cum, gin);
+    else     PB_LAUNCH("expand_rows_bwd", expand_rows_bwd_kernel<1>, grid, 256, 0, stream, Nf, CVn, gout, cum, gin);
+    return PB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,73 @@
+// facet2facet entry points: argument checks and the choice between the fp32 FFMA path
+// (every shape, fp32-faithful) and the tensor-core path.
+#include "common.cuh"
+
+namespace pb {
+size_t f2f_simt_fwd_ws(int64_t Nf, int Cin, int Cout, int F);
+size_t f2f_simt_bwd_ws(int64_t Nf, int Cin, int Cout, int F);
+int f2f_simt_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input, const float* filter,
+                     const float* bary, const int32_t* cum, float* output, void* ws, cudaStream_t stream);
+int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
+                      const float* filter, const float* bary, const int32_t* cum, float* gin, float* gfilter,
+                      void* ws, cudaStream_t stream);
+}  // namespace pb
+
+using namespace pb;
+
+static bool f2f_sizes_ok(int64_t Nf, int64_t NiK, int Cin, int Cout, int F) {
+    return Nf >= 0 && NiK >= 0 && Cin > 0 && Cout > 0 && F > 0 && F <= 50 && NiK < (1LL << 31) && Nf < (1LL << 31);
+}
+
+extern "C" {
+
+size_t pb200_facet2facet_forward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
+    if (!f2f_sizes_ok(Nf, NiK, Cin, Cout, F)) return 0;
+    (void)precision;
+    return f2f_simt_fwd_ws(Nf, Cin, Cout, F);
+}
+
+int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input,
+                              const float* filter, const float* bary, const int32_t* numInterior, float* output,
+                              int precision, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(f2f_sizes_ok(Nf, NiK, Cin, Cout, F), PB200_EINVAL,
+               "facet2facet_forward: bad sizes (F must be in 1..50)");
+    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_BF16, PB200_EINVAL,
+               "facet2facet_forward: unknown precision %d", precision);
+    if (Nf == 0) return PB200_OK;
+    PB_REQUIRE(filter && numInterior && output && (NiK == 0 || (input && bary)), PB200_EINVAL,
+               "facet2facet_forward: null pointer");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_facet2facet_forward_workspace_bytes(Nf, NiK, Cin, Cout, F, precision),
+               PB200_EWORKSPACE, "facet2facet_forward: workspace too small");
+    return f2f_simt_forward(Nf, NiK, Cin, Cout, F, input, filter, bary, numInterior, output, workspace, stream);
+}
+
+size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
+    if (!f2f_sizes_ok(Nf, NiK, Cin, Cout, F)) return 0;
+    (void)precision;
+    return f2f_simt_bwd_ws(Nf, Cin, Cout, F);
+}
+
+int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
+                               const float* input, const float* filter, const float* bary,
+                               const int32_t* numInterior, float* gradInput, float* gradFilter, int precision,
+                               void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(f2f_sizes_ok(Nf, NiK, Cin, Cout, F), PB200_EINVAL,
+               "facet2facet_backward: bad sizes (F must be in 1..50)");
+    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_BF16, PB200_EINVAL,
+               "facet2facet_backward: unknown precision %d", precision);
+    PB_REQUIRE(gradFilter, PB200_EINVAL, "facet2facet_backward: null pointer");
+    if (Nf == 0) {
+        PB_CUDA(cudaMemsetAsync(gradFilter, 0, sizeof(float) * (size_t)Cout * Cin * F, stream));
+        return PB200_OK;
+    }
+    PB_REQUIRE(gradOutput && filter && numInterior && (NiK == 0 || (input && bary && gradInput)), PB200_EINVAL,
+               "facet2facet_backward: null pointer");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_facet2facet_backward_workspace_bytes(Nf, NiK, Cin, Cout, F, precision),
+               PB200_EWORKSPACE, "facet2facet_backward: workspace too small");
+    return f2f_simt_backward(Nf, NiK, Cin, Cout, F, gradOutput, input, filter, bary, numInterior, gradInput,
+                             gradFilter, workspace, stream);
+}
+
+}  // extern "C"

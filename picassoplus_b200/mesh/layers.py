@@ -1,0 +1,126 @@
+"""Layer modules of the mesh convolutions with the reference's class names, constructor
+arguments, parameter names and parameter shapes (picasso/mesh/layers.py:10-195,331-356),
+so reference checkpoints load unchanged.  Each module = one operator from
+pi_modules.conv3d followed by the pointwise stage: matmul -> + bias -> activation ->
+BatchNorm1d(eps=1e-3)  (batch norm AFTER the activation, as in the reference)."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+import torch.nn as nn
+
+from .pi_modules import conv3d
+from ..math_utils import sph_harm_coeff
+
+
+def _filter_variable_(shape, stddev=1.0, use_xavier=True):
+    w = nn.Parameter(torch.empty(shape))
+    return nn.init.xavier_normal_(w) if use_xavier else nn.init.trunc_normal_(w, mean=0, std=stddev)
+
+
+class SphHarmCoeff(nn.Module):
+    """Spherical-harmonic coefficients of cartesian directions, degree <= l."""
+
+    def __init__(self, l):
+        super().__init__()
+        self.l = l
+
+    def __call__(self, cart_coords):
+        return sph_harm_coeff(self.l, cart_coords)
+
+
+class _PointwiseTail(nn.Module):
+    """bias / activation / batch-norm stage shared by the three convolutions."""
+
+    def _init_tail(self, out_channels, activation_fn, with_bn, bn_momentum):
+        self.with_bn = with_bn
+        self.activation_fn = activation_fn
+        if with_bn:
+            self.BatchNorm = nn.BatchNorm1d(out_channels, eps=0.001, momentum=bn_momentum)
+        self.biases = nn.Parameter(torch.zeros(1, out_channels))
+
+    def _tail(self, x):
+        x = x + self.biases
+        if self.activation_fn is not None:
+            x = self.activation_fn(x)
+        if self.with_bn:
+            x = self.BatchNorm(x)
+        return x
+
+
+class F2FConv3d(_PointwiseTail):
+    """Facet-texture convolution; `weights` has shape (out_channels, in_channels, (L+1)^2)."""
+
+    def __init__(self, in_channels, out_channels, spharm_L, use_xavier=True, stddev=1e-3,
+                 activation_fn=nn.ReLU(), with_bn=True, bn_momentum=0.1):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.L = spharm_L
+        self.num_basis = (spharm_L + 1) ** 2
+        self.use_xavier, self.stddev = use_xavier, stddev
+        self.weights = _filter_variable_([out_channels, in_channels, self.num_basis], stddev, use_xavier)
+        self._init_tail(out_channels, activation_fn, with_bn, bn_momentum)
+
+    def forward(self, input_texture, bary_coeff, num_texture):
+        assert self.in_channels == input_texture.shape[-1]
+        assert self.num_basis == bary_coeff.shape[-1]
+        running = torch.cumsum(num_texture, dim=0, dtype=torch.int)   # the operator wants the running count
+        return self._tail(conv3d.facet2facet(input_texture, self.weights, bary_coeff, running))
+
+
+class V2FConv3d(_PointwiseTail):
+    """Vertex -> facet; the (3, Cin, mult) spatial filter is SH(eye(3)) @ spatial_weights."""
+
+    def __init__(self, in_channels, out_channels, spharm_L, depth_multiplier=1, use_xavier=True, stddev=1e-3,
+                 activation_fn=nn.ReLU(), with_bn=True, bn_momentum=0.1):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.L = spharm_L
+        self.num_basis = (spharm_L + 1) ** 2
+        self.multiplier = depth_multiplier
+        self.use_xavier, self.stddev = use_xavier, stddev
+        self.spatial_weights = _filter_variable_([self.num_basis, in_channels * depth_multiplier], stddev, use_xavier)
+        self.depth_weights = _filter_variable_([in_channels * depth_multiplier, out_channels], stddev, use_xavier)
+        self._init_tail(out_channels, activation_fn, with_bn, bn_momentum)
+
+    def forward(self, inputs, face):
+        corners = sph_harm_coeff(self.L, torch.eye(3, device=inputs.device))
+        spatial = (corners @ self.spatial_weights).reshape(3, self.in_channels, self.multiplier)
+        feats = conv3d.vertex2facet(inputs, spatial, face)
+        return self._tail(feats @ self.depth_weights)
+
+
+class F2VConv3d(_PointwiseTail):
+    """Facet -> vertex; `spatial_weights` has shape ((L+1)^2, Cin, mult)."""
+
+    def __init__(self, in_channels, out_channels, spharm_L, depth_multiplier=1, use_xavier=True, stddev=1e-3,
+                 activation_fn=nn.ReLU(), with_bn=True, bn_momentum=0.1):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.L = spharm_L
+        self.num_basis = (spharm_L + 1) ** 2
+        self.multiplier = depth_multiplier
+        self.use_xavier, self.stddev = use_xavier, stddev
+        self.spatial_weights = _filter_variable_([self.num_basis, in_channels, depth_multiplier], stddev, use_xavier)
+        self.depth_weights = _filter_variable_([in_channels * depth_multiplier, out_channels], stddev, use_xavier)
+        self._init_tail(out_channels, activation_fn, with_bn, bn_momentum)
+
+    def forward(self, inputs, face, nf_count, vt_map, filt_coeff):
+        feats = conv3d.facet2vertex(inputs, self.spatial_weights, filt_coeff, face, nf_count, vt_map)
+        return self._tail(feats @ self.depth_weights)
+
+
+class V2VConv3d(nn.Module):
+    """V2F then F2V; `dual_out_channels` and `dual_depth_multiplier` hold one value per stage."""
+
+    def __init__(self, in_channels, dual_out_channels, spharm_L, dual_depth_multiplier: List[int],
+                 use_xavier=True, stddev=1e-3, activation_fn=nn.ReLU(), with_bn=True, bn_momentum=0.1):
+        super().__init__()
+        self.V2F_conv3d = V2FConv3d(in_channels, dual_out_channels[0], spharm_L, dual_depth_multiplier[0],
+                                    use_xavier, stddev, activation_fn, with_bn, bn_momentum)
+        self.F2V_conv3d = F2VConv3d(dual_out_channels[0], dual_out_channels[1], spharm_L, dual_depth_multiplier[1],
+                                    use_xavier, stddev, activation_fn, with_bn, bn_momentum)
+
+    def forward(self, inputs, face, nf_count, vt_map, filt_coeff):
+        return self.F2V_conv3d(self.V2F_conv3d(inputs, face), face, nf_count, vt_map, filt_coeff)

@@ -1,0 +1,71 @@
+"""Seeded operator inputs shared by the parity tests and the golden-fixture generator."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from picassoplus_b200 import synth
+
+
+def topology(kind: str, seed: int):
+    """(vertex, face, vtMap, NvOut) as numpy; kinds: ico<level>x<batch>, grid<n>x<batch>,
+    and the suffix '+drop' that maps every 5th vertex to -1 and compacts the rest."""
+    drop = kind.endswith("+drop")
+    base = kind[:-5] if drop else kind
+    if base.startswith("ico"):
+        level, batch = base[3:].split("x")
+        mb = synth.icosphere_batch(int(batch), int(level), seed, "noise_rot")
+    elif base.startswith("grid"):
+        n, batch = base[4:].split("x")
+        mb = synth.heightfield_batch(int(batch), int(n), seed)
+    elif base == "tri":
+        mb = synth.concat_meshes([(np.eye(3, dtype=np.float32), np.array([[0, 1, 2]], np.int32))])
+    elif base == "tet+iso":   # a tetrahedron plus a vertex no face touches
+        v = np.array([[0, 0, 0], [1, 0, 0], [0, 1, 0], [0, 0, 1], [2, 2, 2]], np.float32)
+        f = np.array([[0, 2, 1], [0, 1, 3], [1, 2, 3], [0, 3, 2]], np.int32)
+        mb = synth.concat_meshes([(v, f)])
+    else:
+        raise ValueError(kind)
+    nv = mb.num_vertices
+    vt = np.arange(nv, dtype=np.int32)
+    nv_out = nv
+    if drop:
+        keep = (np.arange(nv) % 5) != 0
+        vt = np.where(keep, np.cumsum(keep) - 1, -1).astype(np.int32)
+        nv_out = int(keep.sum())
+    return mb.vertex, mb.face, vt, nv_out
+
+
+def conv_inputs(kind: str, C: int, r: int, K: int, cout: int, seed: int, zero_sample_faces: bool = True):
+    """All operator inputs for one case, as a dict of CPU torch tensors."""
+    g = torch.Generator().manual_seed(seed)
+    vertex, face, vt, nv_out = topology(kind, seed)
+    nv, nf = vertex.shape[0], face.shape[0]
+    counts, bary = synth.texture_samples(nf, seed + 7)
+    if zero_sample_faces and nf > 4:
+        counts[1] = 0
+        counts[nf - 1] = 0
+        bary = bary[: int(counts.sum())]
+    d = dict(
+        vertex=torch.from_numpy(vertex), face=torch.from_numpy(face), vt_map=torch.from_numpy(vt),
+        nv_out=nv_out,
+        x_v=torch.randn(nv, C, generator=g), filt_v2f=torch.randn(3, C, r, generator=g),
+        g_v2f=torch.randn(nf, C * r, generator=g),
+        x_f=torch.randn(nf, C, generator=g), filt_f2v=torch.randn(K, C, r, generator=g) / K ** 0.5,
+        coeff=torch.randn(nf, K, generator=g), g_f2v=torch.randn(nv_out, C * r, generator=g),
+        counts=torch.from_numpy(counts), cum=torch.cumsum(torch.from_numpy(counts), 0, dtype=torch.int32),
+        tex=torch.randn(int(counts.sum()), C, generator=g),
+        bary=torch.randn(int(counts.sum()), K, generator=g),
+        filt_f2f=torch.randn(cout, C, K, generator=g) / (C * K) ** 0.5,
+        g_f2f=torch.randn(nf, cout, generator=g),
+        bary_xyz=torch.from_numpy(bary),
+    )
+    return d
+
+
+GOLDEN_CASES = {
+    # name: (topology, C, r, K, Cout, seed)
+    "ico1x2_c8_r1_k16": ("ico1x2", 8, 1, 16, 12, 11),
+    "ico1x2_c5_r2_k9": ("ico1x2", 5, 2, 9, 7, 12),
+    "grid9x1_c4_r1_k25": ("grid9x1", 4, 1, 25, 4, 13),
+}

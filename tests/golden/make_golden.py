@@ -1,0 +1,52 @@
+"""Makes the fixtures in this folder by running the reference's own, unmodified CUDA
+operators (oracle/_ref, see oracle/Makefile target `ref`) on a CUDA device:
+
+    python tests/golden/make_golden.py [output_dir]
+
+For every case of tests/cases.py:GOLDEN_CASES it stores the inputs and the reference's
+outputs (all three operators forward and backward, and nfCount) in <case>.npz, plus
+sph_harm.npz: spherical-harmonic values computed with the reference's torch formulas is
+not possible without importing the reference (its imports need packages absent here), so
+that file is NOT produced here; the SH basis is pinned by analytic values instead.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from cases import GOLDEN_CASES, conv_inputs  # noqa: E402
+from oracle import ref_cuda  # noqa: E402
+
+
+def main(out_dir):
+    assert ref_cuda.available(), "needs oracle/_ref/libref_mesh_conv3d.so and a CUDA device"
+    os.makedirs(out_dir, exist_ok=True)
+    dev = torch.device("cuda:0")
+    for name, (kind, C, r, K, cout, seed) in GOLDEN_CASES.items():
+        d = conv_inputs(kind, C, r, K, cout, seed)
+        c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+        nf_count = ref_cuda.count_vertex_adjface(c["face"], c["vt_map"], d["nv_out"])
+        out = dict(nf_count=nf_count)
+        out["v2f_out"] = ref_cuda.v2f_forward(c["x_v"], c["filt_v2f"], c["face"])
+        out["v2f_gin"], out["v2f_gf"] = ref_cuda.v2f_backward(c["g_v2f"], c["x_v"], c["filt_v2f"], c["face"])
+        out["f2v_out"] = ref_cuda.f2v_forward(c["x_f"], c["filt_f2v"], c["coeff"], c["face"], nf_count, c["vt_map"])
+        out["f2v_gin"], out["f2v_gf"] = ref_cuda.f2v_backward(c["g_f2v"], c["x_f"], c["filt_f2v"], c["coeff"],
+                                                              c["face"], nf_count, c["vt_map"])
+        out["f2f_out"] = ref_cuda.f2f_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+        out["f2f_gin"], out["f2f_gf"] = ref_cuda.f2f_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+        arrays = {("in_" + k): v.numpy() for k, v in d.items() if isinstance(v, torch.Tensor)}
+        arrays.update({("ref_" + k): v.cpu().numpy() for k, v in out.items()})
+        arrays["nv_out"] = np.array(d["nv_out"])
+        np.savez_compressed(os.path.join(out_dir, name + ".npz"), **arrays)
+        print("wrote", name, {k: tuple(v.shape) for k, v in arrays.items() if k.startswith("ref_")})
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else os.path.dirname(os.path.abspath(__file__)))

@@ -1,0 +1,236 @@
+"""Parity of the CUDA operators, called through the C ABI (via the ctypes operator API),
+against the CPU oracle and, when its build is present, the reference's own CUDA kernels
+on identical seeded inputs.  Gate: max|a-b|/max|b| <= 1e-4 per fp32 tensor, index outputs
+bit-exact (north-star tolerances)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_err, max_abs
+from cases import conv_inputs
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4
+
+CASES = [
+    # topology, C, r, K, Cout
+    ("ico2x3", 32, 1, 16, 64),
+    ("ico2x3+drop", 32, 1, 16, 8),
+    ("ico1x2", 5, 2, 9, 7),
+    ("ico1x2+drop", 6, 3, 4, 3),
+    ("grid17x2", 128, 1, 25, 16),
+    ("grid17x2+drop", 64, 1, 25, 16),
+    ("grid9x1", 12, 1, 36, 5),
+    ("grid9x1", 8, 1, 7, 5),        # K without a register-resident variant
+    ("grid9x1", 160, 1, 16, 4),     # more than one 128-channel chunk
+    ("tri", 4, 1, 4, 2),
+    ("tet+iso", 3, 1, 1, 2),
+]
+
+
+def _dev(d):
+    return {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from picassoplus_b200.mesh.pi_modules import conv3d, decimate
+    from oracle import mesh_oracle, ref_cuda
+    return conv3d, decimate, mesh_oracle, ref_cuda
+
+
+@pytest.mark.parametrize("kind,C,r,K,cout", CASES)
+def test_adjacency_bit_exact(mods, kind, C, r, K, cout):
+    conv3d, decimate, mo, ref = mods
+    d = conv_inputs(kind, C, r, K, cout, seed=3)
+    c = _dev(d)
+    vout = torch.zeros(d["nv_out"], 3, device="cuda")
+    got = decimate.count_vertex_adjface_(c["face"], c["vt_map"], vout)
+    want = mo.count_vertex_adjface(d["face"], d["vt_map"], d["nv_out"])
+    assert got.dtype == torch.int32 and torch.equal(got.cpu(), want)
+    from picassoplus_b200.topology import build_vertex_csr
+    csr = build_vertex_csr(c["face"], c["vt_map"], d["vt_map"].shape[0], d["nv_out"])
+    rowptr = csr.rowptr.cpu()
+    assert torch.equal(rowptr[1:] - rowptr[:-1], want)          # row lengths == nfCount, bit for bit
+    ent = csr.entries.cpu()[: int(rowptr[-1])].long()
+    # every row ascending, and the multiset of entries equals all kept corners
+    for v in range(d["nv_out"]):
+        row = ent[rowptr[v]:rowptr[v + 1]]
+        assert torch.all(row[1:] > row[:-1])
+        f, j = row >> 2, row & 3
+        assert torch.all(d["vt_map"].long()[d["face"].long()[f, j]] == v)
+    if ref.available() and "+drop" not in kind:
+        assert torch.equal(ref.count_vertex_adjface(c["face"], c["vt_map"], d["nv_out"]).cpu(), want)
+
+
+@pytest.mark.parametrize("kind,C,r,K,cout", CASES)
+def test_vertex2facet(mods, kind, C, r, K, cout):
+    conv3d, _, mo, ref = mods
+    d = conv_inputs(kind, C, r, K, cout, seed=4)
+    c = _dev(d)
+    out = conv3d.vertex2facet_forward(c["x_v"], c["filt_v2f"], c["face"])
+    want = mo.vertex2facet_forward(d["x_v"], d["filt_v2f"], d["face"])
+    assert out.shape == want.shape and rel_err(out, want) <= TOL
+    gin, gf = conv3d.vertex2facet_backward(c["g_v2f"], c["x_v"], c["filt_v2f"], c["face"])
+    wgin, wgf = mo.vertex2facet_backward(d["g_v2f"].double(), d["x_v"].double(), d["filt_v2f"].double(), d["face"])
+    assert rel_err(gin, wgin) <= TOL and rel_err(gf, wgf) <= TOL
+    if ref.available():
+        r_out = ref.v2f_forward(c["x_v"], c["filt_v2f"], c["face"])
+        assert rel_err(out, r_out) <= TOL
+        r_gin, r_gf = ref.v2f_backward(c["g_v2f"], c["x_v"], c["filt_v2f"], c["face"])
+        assert rel_err(gin, r_gin) <= TOL and rel_err(gf, r_gf) <= TOL
+        # the fp64 oracle arbitrates: we must not be further from it than the reference is (plus slack)
+        assert max_abs(gf, wgf) <= max_abs(r_gf, wgf) * 4 + 1e-5 * float(wgf.abs().max())
+
+
+@pytest.mark.parametrize("kind,C,r,K,cout", CASES)
+def test_facet2vertex(mods, kind, C, r, K, cout):
+    conv3d, _, mo, ref = mods
+    d = conv_inputs(kind, C, r, K, cout, seed=5)
+    c = _dev(d)
+    nfc = mo.count_vertex_adjface(d["face"], d["vt_map"], d["nv_out"])
+    nfc_c = nfc.cuda()
+    out = conv3d.facet2vertex_forward(c["x_f"], c["filt_f2v"], c["coeff"], c["face"], nfc_c, c["vt_map"])
+    want = mo.facet2vertex_forward(d["x_f"].double(), d["filt_f2v"].double(), d["coeff"].double(), d["face"], nfc,
+                                   d["vt_map"])
+    assert out.shape == want.shape and rel_err(out, want) <= TOL
+    assert torch.all(out[nfc_c == 0] == 0)            # vertices no face maps to stay exactly zero
+    gin, gf = conv3d.facet2vertex_backward(c["g_f2v"], c["x_f"], c["filt_f2v"], c["coeff"], c["face"], nfc_c,
+                                           c["vt_map"])
+    wgin, wgf = mo.facet2vertex_backward(d["g_f2v"].double(), d["x_f"].double(), d["filt_f2v"].double(),
+                                         d["coeff"].double(), d["face"], nfc, d["vt_map"])
+    assert rel_err(gin, wgin) <= TOL and rel_err(gf, wgf) <= TOL
+    if ref.available() and "+drop" not in kind:       # the reference reads nfCount[-1] for dropped vertices
+        r_out = ref.f2v_forward(c["x_f"], c["filt_f2v"], c["coeff"], c["face"], nfc_c, c["vt_map"])
+        assert rel_err(out, r_out) <= TOL
+        r_gin, r_gf = ref.f2v_backward(c["g_f2v"], c["x_f"], c["filt_f2v"], c["coeff"], c["face"], nfc_c, c["vt_map"])
+        assert rel_err(gin, r_gin) <= TOL and rel_err(gf, r_gf) <= TOL
+
+
+@pytest.mark.parametrize("kind,C,r,K,cout", CASES)
+def test_facet2facet_fp32(mods, kind, C, r, K, cout):
+    conv3d, _, mo, ref = mods
+    d = conv_inputs(kind, C, r, K, cout, seed=6)
+    c = _dev(d)
+    conv3d.set_f2f_precision("fp32")
+    out = conv3d.facet2facet_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+    want = mo.facet2facet_forward(d["tex"].double(), d["filt_f2f"].double(), d["bary"].double(), d["cum"])
+    assert out.shape == want.shape and rel_err(out, want) <= TOL
+    zero_faces = (d["counts"] == 0).nonzero().flatten()
+    assert torch.all(out[zero_faces.cuda()] == 0)
+    gin, gf = conv3d.facet2facet_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+    wgin, wgf = mo.facet2facet_backward(d["g_f2f"].double(), d["tex"].double(), d["filt_f2f"].double(),
+                                        d["bary"].double(), d["cum"])
+    assert rel_err(gin, wgin) <= TOL and rel_err(gf, wgf) <= TOL
+    if ref.available() and d["tex"].shape[0] * C * cout < 5e7:
+        r_out = ref.f2f_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+        assert rel_err(out, r_out) <= TOL
+        r_gin, r_gf = ref.f2f_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+        assert rel_err(gin, r_gin) <= TOL and rel_err(gf, r_gf) <= TOL
+
+
+def test_autograd_functions_match_oracle_block(mods):
+    """The three autograd Functions chained as the benchmark block, against the oracle's
+    autograd over the same formula (fp64)."""
+    conv3d, _, mo, _ = mods
+    from picassoplus_b200.math_utils import sph_harm_coeff
+    d = conv_inputs("ico2x3", 16, 1, 16, 24, seed=9)
+    L, cin, cout = 3, 16, 24
+    g = torch.Generator().manual_seed(1)
+    Wv = torch.randn(16, cin, generator=g) * 0.2
+    Wf = d["filt_f2f"]
+    Wo = torch.randn(16, cout, 1, generator=g) * 0.2
+    geo = mo.triangle_geometry(d["vertex"], d["face"])
+    coeff = mo.sph_harm_coeff(L, geo[:, :3])
+    bary_sh = mo.sph_harm_coeff(L, d["bary_xyz"])
+    nfc = mo.count_vertex_adjface(d["face"], d["vt_map"], d["nv_out"])
+    G = torch.randn(d["nv_out"], cout, generator=g)
+
+    def run_oracle():
+        x = d["x_v"].double().requires_grad_()
+        ws = [w.double().requires_grad_() for w in (Wv, Wf, Wo)]
+        o = mo.conv_block(x, ws[0], ws[1], ws[2], d["face"], d["counts"], d["cum"], bary_sh.double(),
+                          coeff.double(), nfc, d["vt_map"], mo.sph_harm_coeff(L, torch.eye(3)).double())
+        (o * G.double()).sum().backward()
+        return o.detach(), x.grad, [w.grad for w in ws]
+
+    def run_gpu():
+        from picassoplus_b200.block import conv_block
+        x = d["x_v"].cuda().requires_grad_()
+        ws = [w.cuda().requires_grad_() for w in (Wv, Wf, Wo)]
+        o = conv_block(x, ws[0], ws[1], ws[2], d["face"].cuda(), d["cum"].cuda(), bary_sh.cuda(), coeff.cuda(),
+                       nfc.cuda(), d["vt_map"].cuda(), sph_harm_coeff(L, torch.eye(3, device="cuda")))
+        (o * G.cuda()).sum().backward()
+        return o.detach(), x.grad, [w.grad for w in ws]
+
+    o1, gx1, gw1 = run_oracle()
+    o2, gx2, gw2 = run_gpu()
+    assert rel_err(o2, o1) <= TOL and rel_err(gx2, gx1) <= TOL
+    for a, b in zip(gw2, gw1):
+        assert rel_err(a, b) <= TOL
+
+
+def test_run_to_run_deterministic(mods):
+    conv3d, _, mo, _ = mods
+    d = conv_inputs("grid33x2", 64, 1, 16, 32, seed=21)
+    c = _dev(d)
+    nfc = mo.count_vertex_adjface(d["face"], d["vt_map"], d["nv_out"]).cuda()
+
+    def once():
+        from picassoplus_b200.topology import clear_cache
+        clear_cache()
+        a = conv3d.vertex2facet_backward(c["g_v2f"], c["x_v"], c["filt_v2f"], c["face"])
+        b = conv3d.facet2vertex_forward(c["x_f"], c["filt_f2v"], c["coeff"], c["face"], nfc, c["vt_map"])
+        e = conv3d.facet2vertex_backward(c["g_f2v"], c["x_f"], c["filt_f2v"], c["coeff"], c["face"], nfc, c["vt_map"])
+        f = conv3d.facet2facet_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+        return [*a, b, *e, *f]
+
+    first = once()
+    for _ in range(3):
+        for x, y in zip(first, once()):
+            assert torch.equal(x, y)
+
+
+def test_sph_harm_and_geometry(mods):
+    _, decimate, mo, _ = mods
+    from picassoplus_b200.math_utils import sph_harm_coeff
+    g = torch.Generator().manual_seed(2)
+    xyz = torch.randn(5000, 3, generator=g)
+    xyz[:4] = torch.tensor([[1., 0, 0], [0, 1., 0], [0, 0, 1.], [0, 0, 0]])
+    for L in range(6):
+        got = sph_harm_coeff(L, xyz.cuda())
+        want = mo.sph_harm_coeff(L, xyz)
+        assert got.shape == want.shape
+        assert rel_err(got, mo.sph_harm_coeff(L, xyz.double())) <= 1e-5
+        assert max_abs(got, want) <= 2e-6
+    with pytest.raises(NotImplementedError):
+        sph_harm_coeff(6, xyz.cuda())
+    d = conv_inputs("grid17x2", 4, 1, 4, 2, seed=1)
+    geo = decimate.compute_triangle_geometry_(d["vertex"].cuda(), d["face"].cuda())
+    assert max_abs(geo, mo.triangle_geometry(d["vertex"], d["face"])) <= 1e-6
+
+
+def test_error_behaviour(mods):
+    conv3d, _, _, _ = mods
+    d = _dev(conv_inputs("ico1x2", 8, 1, 16, 4, seed=1))
+    with pytest.raises(RuntimeError):
+        conv3d.vertex2facet(d["x_v"].cpu(), d["filt_v2f"], d["face"])              # not CUDA
+    with pytest.raises(RuntimeError):
+        conv3d.vertex2facet(d["x_v"].t().contiguous().t(), d["filt_v2f"], d["face"])  # not contiguous
+    with pytest.raises(RuntimeError):
+        conv3d.vertex2facet(d["x_v"], d["filt_v2f"][:2].contiguous(), d["face"])    # needs 3 filters
+    with pytest.raises(RuntimeError):
+        conv3d.vertex2facet(d["x_v"], d["filt_v2f"], d["face"].long())              # int32 indices only
+    with pytest.raises(RuntimeError):
+        conv3d.facet2facet(d["tex"], torch.zeros(4, 8, 51, device="cuda"), torch.zeros(d["tex"].shape[0], 51,
+                           device="cuda"), d["cum"])                                 # F <= 50
+    with pytest.raises(RuntimeError):
+        conv3d.facet2vertex(d["x_f"], d["filt_f2v"][:, :4].contiguous(), d["coeff"], d["face"],
+                            torch.ones(d["nv_out"], dtype=torch.int32, device="cuda"), d["vt_map"])
+    bad = d["face"].clone()
+    bad[0, 0] = 10 ** 6                                                              # index out of range: reported, not dereferenced
+    with pytest.raises(RuntimeError):
+        conv3d.vertex2facet_backward(d["g_v2f"], d["x_v"], d["filt_v2f"], bad)
+    # the context is still usable afterwards
+    assert torch.isfinite(conv3d.vertex2facet(d["x_v"], d["filt_v2f"], d["face"])).all()
