@@ -1,0 +1,87 @@
+"""Mesh-level data parallelism: whole meshes per rank, one all-reduce of filter gradients.
+
+A batch is a concatenation of disjoint meshes (reference: picasso/mesh/dataset_shape.py:
+43-58); no operator couples faces or vertices of different meshes, so ranks take
+contiguous mesh ranges, re-base the vertex ids of their faces, and run the operators
+unchanged.  The only exchange is the sum of the filter gradients, sent as one flat buffer
+(NCCL on GPUs, gloo in the CPU tests).  For a fixed world size the result is
+deterministic; across world sizes it differs by fp32 re-association.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def partition_meshes(face_counts: Sequence[int], world_size: int) -> List[Tuple[int, int]]:
+    """Contiguous mesh ranges [(first, count)] per rank, balanced by face count: rank r ends
+    at the first mesh boundary whose cumulative face count reaches (r+1)/world of the total.
+    Every rank gets at least one mesh when there are enough meshes."""
+    n = len(face_counts)
+    total = float(sum(face_counts))
+    bounds = [0]
+    run = 0.0
+    i = 0
+    for r in range(1, world_size):
+        target = total * r / world_size
+        while i < n and run + face_counts[i] / 2.0 <= target:
+            run += face_counts[i]
+            i += 1
+        lo = bounds[-1] + (1 if n - bounds[-1] > world_size - r else 0)   # leave meshes for the ranks after
+        i = max(i, min(lo, n))
+        i = min(i, n - (world_size - r)) if n >= world_size else min(i, n)
+        i = max(i, bounds[-1])
+        run = float(sum(face_counts[:i]))
+        bounds.append(i)
+    bounds.append(n)
+    return [(bounds[r], bounds[r + 1] - bounds[r]) for r in range(world_size)]
+
+
+def shard_batch(vertex: torch.Tensor, face: torch.Tensor, nv: torch.Tensor, mf: torch.Tensor,
+                first: int, count: int):
+    """The sub-batch of meshes [first, first+count): vertex rows, faces with vertex ids
+    re-based to the shard, and the per-mesh counts."""
+    voff = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(nv.long().cpu(), 0)])
+    foff = torch.cat([torch.zeros(1, dtype=torch.long), torch.cumsum(mf.long().cpu(), 0)])
+    v0, v1 = int(voff[first]), int(voff[first + count])
+    f0, f1 = int(foff[first]), int(foff[first + count])
+    return vertex[v0:v1], (face[f0:f1] - v0).to(face.dtype), nv[first:first + count], mf[first:first + count], (v0, v1, f0, f1)
+
+
+class FilterGradAllReduce:
+    """Sums the gradients of a fixed list of (filter) parameters over the process group in
+    one collective on a flat buffer that is allocated once."""
+
+    def __init__(self, params: Sequence[torch.Tensor], group=None):
+        self.params = list(params)
+        self.group = group
+        self.sizes = [p.numel() for p in self.params]
+        p0 = self.params[0]
+        self.flat = torch.zeros(sum(self.sizes), dtype=p0.dtype, device=p0.device)
+        self.views = []
+        off = 0
+        for p, n in zip(self.params, self.sizes):
+            self.views.append(self.flat[off:off + n].view(p.shape))
+            off += n
+
+    @property
+    def nbytes(self) -> int:
+        return self.flat.numel() * self.flat.element_size()
+
+    def __call__(self) -> None:
+        """Replace every .grad by the sum over ranks (no-op for a single process)."""
+        if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(self.group) == 1:
+            return
+        for p, v in zip(self.params, self.views):
+            if p.grad is None:
+                v.zero_()
+            else:
+                v.copy_(p.grad)
+        dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+        for p, v in zip(self.params, self.views):
+            if p.grad is None:
+                p.grad = v.clone()
+            else:
+                p.grad.copy_(v)

@@ -4,10 +4,10 @@ operators (oracle/_ref, see oracle/Makefile target `ref`) on a CUDA device:
     python tests/golden/make_golden.py [output_dir]
 
 For every case of tests/cases.py:GOLDEN_CASES it stores the inputs and the reference's
-outputs (all three operators forward and backward, and nfCount) in <case>.npz, plus
-sph_harm.npz: spherical-harmonic values computed with the reference's torch formulas is
-not possible without importing the reference (its imports need packages absent here), so
-that file is NOT produced here; the SH basis is pinned by analytic values instead.
+outputs (all three operators forward and backward, and nfCount) in <case>.npz.  The
+spherical-harmonic basis has no fixture here: the reference's Python modules cannot be
+imported without packages that are absent (torch_scatter, scipy.special.sph_harm), so
+that function is pinned by analytic values in the CPU tests instead.
 """
 from __future__ import annotations
 
