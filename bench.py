@@ -1,0 +1,490 @@
+#!/usr/bin/env python
+"""Benchmark of the mesh-convolution block (vertex2facet -> facet2facet -> facet2vertex,
+forward + backward, + all-reduce of filter gradients when N > 1).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config c5] [--precision fp32|tf32|bf16] [--meshes M]
+
+Under torchrun (N > 1) one rank drives one GPU; rank 0 prints ONE JSON line.
+Metric: faces per second of one fwd+bwd pass of the block over the whole batch.
+  value     inputs resident in HBM, timed with CUDA events, max over ranks
+  e2e       the same step through the public operator API starting from pinned HOST buffers:
+            H2D of the batch (vertices, faces, features, texture samples), on-device
+            per-batch preparation (nfCount, normals, SH coefficients, CSR), fwd+bwd, D2H of
+            the loss
+  roofline  the dominant kernel of the step: algorithmic bytes (or flops) / measured duration
+  cpu_baseline  the CPU oracle (PyTorch composition of the same formulas) on a bounded sample
+`--impl reference` times that CPU composition alone (the reference has no CPU code path of
+its own; its operators are CUDA-only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from picassoplus_b200 import synth  # noqa: E402
+
+METRIC = "mesh_conv_block_fwd_bwd_faces_per_sec"
+UNIT = "faces/s"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
+    ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
+    return ap.parse_args()
+
+
+def workload_name(cfg, total_meshes):
+    if cfg["kind"] == "heightfield":
+        shape = f"{total_meshes} heightfield meshes {cfg['n']}x{cfg['n']} (10% faces deleted)"
+    else:
+        shape = f"{total_meshes} icospheres level {cfg['level']} ({cfg['mode']})"
+    return f"{shape}, V2F->F2F->F2V block, Cin={cfg['cin']} Cout={cfg['cout']} L={cfg['L']}"
+
+
+# ------------------------------------------------------------------------------ inputs
+def host_inputs(cfg, first, count, seed_shift=0):
+    """Host-side batch of meshes [first, first+count) with features, texture samples and
+    the upstream gradient, all seeded per mesh range."""
+    mb = synth.make_batch(cfg, count, first)
+    L = cfg["L"]
+    K = (L + 1) ** 2
+    counts, bary_xyz = synth.texture_samples(mb.num_faces, cfg["seed"] * 7919 + first)
+    g = torch.Generator().manual_seed(cfg["seed"] * 104729 + first + seed_shift)
+    x = torch.randn(mb.num_vertices, cfg["cin"], generator=g)
+    return dict(vertex=torch.from_numpy(mb.vertex), face=torch.from_numpy(mb.face),
+                counts=torch.from_numpy(counts), cum=torch.cumsum(torch.from_numpy(counts), 0, dtype=torch.int32),
+                bary_xyz=torch.from_numpy(bary_xyz), x=x, K=K, L=L,
+                Nv=mb.num_vertices, Nf=mb.num_faces, NiK=int(counts.sum()), nmesh=count)
+
+
+def make_params(cfg):
+    """Xavier-normal filters, identical on every rank."""
+    rng = np.random.default_rng(cfg["seed"] + 12345)
+    K = (cfg["L"] + 1) ** 2
+    Wv = torch.from_numpy(synth.xavier_normal((K, cfg["cin"]), rng))
+    Wf = torch.from_numpy(synth.xavier_normal((cfg["cout"], cfg["cin"], K), rng))
+    Wo = torch.from_numpy(synth.xavier_normal((K, cfg["cout"], 1), rng))
+    return Wv, Wf, Wo
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("uuid,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, uuid):
+        self.uuid = uuid
+        self.lines = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8 or (self.uuid and self.uuid not in parts[0]):
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[4:8]):
+                if v == "Active":
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def gpu_uuid(dev):
+    try:
+        return "GPU-" + str(torch.cuda.get_device_properties(dev).uuid)
+    except Exception:
+        return ""
+
+
+# ---------------------------------------------------------------------- kernel models
+def kernel_models(d):
+    """Algorithmic (compulsory) bytes and contraction flops of one launch set per step,
+    by kernel label: every operand read once, every result written once; fp32 / int32."""
+    Nv, Nf, NiK, Ci, Co, K = d["Nv"], d["Nf"], d["NiK"], d["cin"], d["cout"], d["K"]
+    Q = K * Ci
+    m = {
+        "v2f_fwd": dict(bytes=4 * Ci * Nv + 12 * Nf + 4 * Ci * Nf),
+        "v2f_bwd": dict(bytes=4 * Ci * Nf + 8 * Ci * Nv + 12 * Nf + 4 * Nv),
+        "expand_rows_fwd": dict(bytes=4 * Ci * Nf + 4 * Nf + 4 * Ci * NiK),
+        "expand_rows_bwd": dict(bytes=4 * Ci * Nf + 4 * Nf + 4 * Ci * NiK),
+        "f2v_fwd": dict(bytes=4 * Co * Nf + 4 * K * Nf + 12 * Nf + 8 * Nv + 4 * Co * Nv),
+        "f2v_bwd": dict(bytes=4 * Co * Nv + 8 * Co * Nf + 4 * K * Nf + 12 * Nf + 4 * Nv),
+        # fp32 FFMA path of facet2facet (chunked through workspace)
+        "f2f_build_A": dict(bytes=4 * Ci * NiK + 4 * K * NiK + 4 * Nf + 4 * Q * Nf),
+        "f2f_fwd_sgemm": dict(bytes=4 * Q * Nf + 4 * Co * Nf, flops=2 * Q * Co * Nf),
+        "f2f_gfilter_sgemm": dict(bytes=4 * Q * Nf + 4 * Co * Nf, flops=2 * Q * Co * Nf),
+        "f2f_gA_sgemm": dict(bytes=4 * Q * Nf + 4 * Co * Nf, flops=2 * Q * Co * Nf),
+        "f2f_gin_from_gA": dict(bytes=4 * Q * Nf + 4 * K * NiK + 4 * Ci * NiK),
+        # fused tensor-core path of facet2facet
+        "f2f_fwd_tc": dict(bytes=4 * Ci * NiK + 4 * K * NiK + 4 * Nf + 4 * Co * Nf,
+                           flops=2 * Q * NiK + 2 * Q * Co * Nf),
+        "f2f_bwd_gin_tc": dict(bytes=4 * Co * Nf + 4 * K * NiK + 4 * Nf + 4 * Ci * NiK,
+                               flops=2 * Q * NiK + 2 * Q * Co * Nf),
+        "f2f_bwd_gfilter_tc": dict(bytes=4 * Ci * NiK + 4 * K * NiK + 4 * Nf + 4 * Co * Nf,
+                                   flops=2 * Q * NiK + 2 * Q * Co * Nf),
+    }
+    return m
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return dict(hbm_gbs=float(j["hbm_gbs"]), tflops=float(j.get("bf16_tflops_sustained", j["bf16_tflops"])),
+                    source="measured (MEASURED_PEAKS.json; tensor = sustained bf16)")
+    return dict(hbm_gbs=6650.0, tflops=1400.0, source="fallback (6.65 TB/s, 1.4 PFLOP/s sustained bf16)")
+
+
+def roofline_from_profile(records, steps, dims):
+    """records: [(label, launches, total_ms)] over `steps` steps.  The dominant kernel label
+    (largest total time) gets: achieved = algorithmic bytes|flops per step / its time per step."""
+    models = kernel_models(dims)
+    peaks = load_peaks()
+    total = sum(r[2] for r in records) or 1.0
+    table = []
+    for name, launches, ms in records:
+        row = dict(kernel=name, launches_per_step=launches / steps, ms_per_step=ms / steps, share=ms / total)
+        mdl = models.get(name)
+        if mdl:
+            sec = ms / steps / 1e3
+            gbs = mdl["bytes"] / sec / 1e9
+            row["hbm_gbs"] = gbs
+            row["hbm_frac"] = gbs / peaks["hbm_gbs"]
+            if "flops" in mdl:
+                tf = mdl["flops"] / sec / 1e12
+                row["tflops"] = tf
+                row["tensor_frac"] = tf / peaks["tflops"]
+        table.append(row)
+    top = table[0] if table else None
+    roof = None
+    if top and top["kernel"] in models:
+        mdl = models[top["kernel"]]
+        t_hbm = mdl["bytes"] / (peaks["hbm_gbs"] * 1e9)
+        t_tc = mdl.get("flops", 0) / (peaks["tflops"] * 1e12)
+        if t_tc > t_hbm:
+            roof = dict(bound="tensor", achieved=top["tflops"], peak=peaks["tflops"], unit="TFLOP/s",
+                        frac=top["tensor_frac"], traffic=None)
+        else:
+            roof = dict(bound="hbm", achieved=top["hbm_gbs"], peak=peaks["hbm_gbs"], unit="GB/s",
+                        frac=top["hbm_frac"], traffic=None)
+        roof.update(kernel=top["kernel"], peak_source=peaks["source"], ms_per_launch_set=top["ms_per_step"],
+                    share_of_step=top["share"])
+    return roof, table
+
+
+# ------------------------------------------------------------------------------- ours
+def run_ours(args):
+    import torch.distributed as dist
+    from picassoplus_b200 import _lib
+    from picassoplus_b200.block import conv_block
+    from picassoplus_b200.math_utils import sph_harm_coeff
+    from picassoplus_b200.mesh import utils as mesh_utils
+    from picassoplus_b200.mesh.pi_modules import conv3d
+    from picassoplus_b200.parallel import FilterGradAllReduce, partition_meshes
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for --impl ours)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus or world == 1, f"WORLD_SIZE={world} but --gpus {args.gpus}"
+
+    cfg = dict(synth.CONFIGS[args.config])
+    total_meshes = args.meshes or cfg["batch"]
+    cfg["batch"] = total_meshes
+    first, count = partition_meshes([1] * total_meshes, world)[rank]
+    conv3d.set_f2f_precision(args.precision)
+
+    h = host_inputs(cfg, first, count)
+    L, K = h["L"], h["K"]
+    Wv, Wf, Wo = make_params(cfg)
+    pin = {k: h[k].pin_memory() for k in ("vertex", "face", "x", "cum", "bary_xyz")}
+    d = {k: v.to(dev) for k, v in pin.items()}
+    vt_map = torch.arange(h["Nv"], dtype=torch.int32, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(cfg["seed"] * 31 + first)
+    G = torch.randn(h["Nv"], cfg["cout"], generator=gen, device=dev)
+    params = [w.to(dev).requires_grad_() for w in (Wv, Wf, Wo)]
+    allreduce = FilterGradAllReduce(params)
+    sh_eye = sph_harm_coeff(L, torch.eye(3, device=dev))
+
+    def prepare():
+        nfc = mesh_utils.count_vertex_adjface(d["face"], vt_map, d["vertex"])
+        geo = mesh_utils.compute_triangle_geometry(d["vertex"], d["face"])
+        coeff = sph_harm_coeff(L, geo[:, :3].contiguous())
+        bary_sh = sph_harm_coeff(L, d["bary_xyz"])
+        return nfc, coeff, bary_sh
+
+    nfc, coeff, bary_sh = prepare()
+    xd = d["x"].requires_grad_()
+
+    def step_resident():
+        for p in params:
+            p.grad = None
+        xd.grad = None
+        o = conv_block(xd, params[0], params[1], params[2], d["face"], d["cum"], bary_sh, coeff, nfc, vt_map, sh_eye)
+        o.backward(G)
+        allreduce()
+
+    h2d_bytes = sum(pin[k].numel() * pin[k].element_size() for k in pin)
+
+    def step_e2e():
+        for p in params:
+            p.grad = None
+        with torch.no_grad():
+            for k in pin:
+                d[k].copy_(pin[k], non_blocking=True)      # bumps the version: topology is rebuilt
+        xe = d["x"].detach().requires_grad_()
+        nfc_, coeff_, bary_ = prepare()
+        o = conv_block(xe, params[0], params[1], params[2], d["face"], d["cum"], bary_, coeff_, nfc_, vt_map, sh_eye)
+        loss = (o * G).sum()
+        loss.backward()
+        allreduce()
+        return float(loss.item())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0 = _lib.launch_count()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), _lib.launch_count() - n0
+
+    # total faces over all ranks
+    nf_all = torch.tensor([h["Nf"], h["Nv"], h["NiK"]], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(nf_all)
+    faces_total = float(nf_all[0].item())
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    with ClockSampler(gpu_uuid(dev)) as clk:
+        ms, launches = timed(step_resident, args.steps)
+    clocks = clk.summary()
+    ms_per_step = ms / args.steps
+    value = faces_total / (ms_per_step / 1e3)
+
+    # per-kernel durations of the same step, measured live with CUDA events on the launch stream
+    prof_steps = min(args.steps, 3)
+    _lib.prof_reset()
+    _lib.prof_enable(True)
+    for _ in range(prof_steps):
+        step_resident()
+    torch.cuda.synchronize()
+    _lib.prof_enable(False)
+    records = _lib.prof_read(64)
+    _lib.prof_reset()
+    dims = dict(Nv=h["Nv"], Nf=h["Nf"], NiK=h["NiK"], cin=cfg["cin"], cout=cfg["cout"], K=K)
+    roof, table = roofline_from_profile(records, prof_steps, dims)
+
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(2):
+            step_e2e()
+        e_steps = max(2, min(args.steps, 5))
+        ems, _ = timed(step_e2e, e_steps)
+        e2e = dict(value=faces_total / (ems / e_steps / 1e3), unit=UNIT, ms_per_step=ems / e_steps,
+                   h2d_bytes_per_step=int(h2d_bytes), d2h_bytes_per_step=4, steps=e_steps,
+                   includes="H2D of vertices/faces/features/texture samples, nfCount + normals + SH + CSR "
+                            "rebuild, fwd+bwd, loss D2H")
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(cfg, args.cpu_seconds)
+
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(cfg, total_meshes), "name": args.config,
+                       "faces": int(faces_total), "vertices": int(nf_all[1].item()),
+                       "texture_samples": int(nf_all[2].item()), "f2f_precision": args.precision,
+                       "parallelism": f"mesh-dp{world}", "meshes_per_gpu": count,
+                       "l2_policy": "inputs larger than L2 (no flush)" if h["Nf"] * cfg["cin"] * 4 > 256e6
+                       else "inputs smaller than L2, no flush"},
+            "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
+            "clocks": clocks, "kernels": table[:12],
+            "allreduce_bytes": allreduce.nbytes if world > 1 else 0,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------- CPU oracle timing
+def _oracle_step_fn(cfg, n_or_level, seed_shift=0):
+    """One mesh of the configuration's kind (heightfield n x n or icosphere level) and a
+    closure that runs fwd+bwd of the block with the CPU oracle."""
+    from oracle import mesh_oracle as mo
+    c = dict(cfg)
+    c["batch"] = 1
+    if c["kind"] == "heightfield":
+        c["n"] = n_or_level
+    else:
+        c["level"] = n_or_level
+    h = host_inputs(c, 0, 1, seed_shift)
+    L = h["L"]
+    Wv, Wf, Wo = make_params(cfg)
+    vt = torch.arange(h["Nv"], dtype=torch.int32)
+    nfc = mo.count_vertex_adjface(h["face"], vt, h["Nv"])
+    geo = mo.triangle_geometry(h["vertex"], h["face"])
+    coeff = mo.sph_harm_coeff(L, geo[:, :3])
+    bary_sh = mo.sph_harm_coeff(L, h["bary_xyz"])
+    sh_eye = mo.sph_harm_coeff(L, torch.eye(3))
+    G = torch.randn(h["Nv"], cfg["cout"], generator=torch.Generator().manual_seed(1))
+    params = [w.clone().requires_grad_() for w in (Wv, Wf, Wo)]
+    x = h["x"].clone().requires_grad_()
+
+    def step():
+        for p in params:
+            p.grad = None
+        x.grad = None
+        o = mo.conv_block(x, params[0], params[1], params[2], h["face"], h["counts"], h["cum"], bary_sh, coeff, nfc,
+                          vt, sh_eye)
+        o.backward(G)
+
+    return step, h["Nf"]
+
+
+def _calibrated_sample(cfg, target_seconds):
+    """Pick the sample mesh so that one CPU step takes about `target_seconds` (at most one
+    full mesh of the configuration)."""
+    if cfg["kind"] == "heightfield":
+        small, full = 48, cfg["n"]
+    else:
+        small, full = 1, cfg["level"]
+    step, nf = _oracle_step_fn(cfg, small)
+    step()
+    t0 = time.perf_counter()
+    step()
+    per_face = (time.perf_counter() - t0) / nf
+    if cfg["kind"] == "heightfield":
+        n = int((target_seconds / per_face / 1.8) ** 0.5) + 1
+        return max(small, min(full, n))
+    lvl = small
+    while lvl < full and per_face * 20 * 4 ** (lvl + 1) <= target_seconds:
+        lvl += 1
+    return lvl
+
+
+def cpu_baseline(cfg, target_seconds):
+    torch.set_num_threads(os.cpu_count() or 1)
+    size = _calibrated_sample(cfg, target_seconds)
+    step, nf = _oracle_step_fn(cfg, size)
+    t0 = time.perf_counter()
+    step()
+    dt = time.perf_counter() - t0
+    what = f"one {size}x{size} heightfield mesh" if cfg["kind"] == "heightfield" else f"one icosphere level {size}"
+    return dict(value=nf / dt, unit=UNIT, cores=torch.get_num_threads(), kind="port",
+                sample=f"{what} of the workload ({nf} faces), 1 fwd+bwd step of the CPU oracle "
+                       f"(PyTorch index_add_/matmul composition, fp32), {dt:.2f} s")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = dict(synth.CONFIGS[args.config])
+    total_meshes = args.meshes or cfg["batch"]
+    torch.set_num_threads(os.cpu_count() or 1)
+    n_steps = args.steps + args.warmup
+    size = _calibrated_sample(cfg, min(args.cpu_seconds, 120.0 / max(n_steps, 1)))
+    step, nf = _oracle_step_fn(cfg, size)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = nf / dt
+    what = f"one {size}x{size} heightfield mesh" if cfg["kind"] == "heightfield" else f"one icosphere level {size}"
+    sample = (f"{what} ({nf} faces) per step; CPU oracle = PyTorch index_add_/matmul composition of the "
+              "reference formulas, fp32 (the reference's own operators are CUDA-only)")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(cfg, total_meshes), "name": args.config},
+        "cpu_baseline": dict(value=value, unit=UNIT, cores=torch.get_num_threads(), kind="port", sample=sample),
+        "e2e": dict(value=value, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+    }))
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)
