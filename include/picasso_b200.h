@@ -92,6 +92,31 @@ int pb200_vertex2facet_backward(int64_t Nf, int64_t Nv, int C, int r, const floa
                                 float* gradInput, float* gradFilter,
                                 void* workspace, size_t workspace_bytes, void* stream);
 
+/* Allocation-free variant of pb200_vertex2facet_backward.  It has no counterpart in the
+ * reference.  It is for callers that cannot obtain device memory at call time: code that
+ * runs where the embedding framework's allocator is frozen or off limits, callbacks with a
+ * fixed memory budget, hosts that may not call cudaMalloc after start-up.  The scratch the
+ * backward pass needs (per-block filter-gradient partials) is a fixed array inside the
+ * library image, pb200_vertex2facet_backward_static_max_bytes() = 4 MiB, resident on every
+ * GPU that loads the library until the process exits.  The caller still passes all inputs
+ * and outputs.
+ *   - limit: shapes whose pb200_vertex2facet_backward_workspace_bytes() exceed the array
+ *     are refused with PB200_EWORKSPACE and a message that names both sizes (e.g.
+ *     C*r = 128 needs 1.8 MB on a 148-SM part; C*r above ~290 does not fit).
+ *   - the first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress, with that device current); make that first call outside any
+ *     stream capture.  No call allocates or frees memory.
+ *   - all calls on one device share the array: two calls that overlap on the GPU (different
+ *     streams, or different threads without ordering) race on it.  Calls that are ordered
+ *     on one stream are safe.  Nothing in the array needs clearing between calls: each call
+ *     writes every partial before it reads it; the array keeps the last call's partials.
+ *   - results are bit-identical to pb200_vertex2facet_backward for the same shape. */
+size_t pb200_vertex2facet_backward_static_max_bytes(void);
+int pb200_vertex2facet_backward_static(int64_t Nf, int64_t Nv, int C, int r, const float* gradOutput,
+                                       const float* input, const float* filter, const int32_t* face,
+                                       const int32_t* rowptr, const int32_t* entries,
+                                       float* gradInput, float* gradFilter, void* stream);
+
 /* ---- facet2vertex -------------------------------------------------------------------
  * w[f,co] = sum_k coeff[f,k]*filter[k,c,m];
  * output[vo,co] = (sum over corners (f,j) with vtMap[face[f,j]] = vo of w[f,co]*input[f,c])

@@ -2,6 +2,8 @@
 // yields the input gradient and the filter gradient in one pass, no float atomics).
 #include "common.cuh"
 
+#include <mutex>
+
 namespace pb {
 
 // ------------------------------------------------------------------- forward, vectorised
@@ -243,6 +245,67 @@ int pb200_vertex2facet_backward(int64_t Nf, int64_t Nv, int C, int r, const floa
     PB_LAUNCH("v2f_bwd_filter_generic", v2f_bwd_filter_generic_kernel, gridf, 128, 0, stream, Nf, C, r,
               q.faces_per_chunk, face, input, gradOutput, partial);
     return reduce_partials(partial, q.grid_x, 3 * Cr, gradFilter, stream);
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------- allocation-free variant
+// Some hosts of this library may not allocate device memory at the moment they call it:
+// a plugin invoked inside a region the embedding framework has frozen (its allocator is
+// locked or its pool already handed out), a real-time or signal-adjacent callback, or a
+// process whose memory budget was fixed at start-up.  For them the filter-gradient
+// partials of vertex2facet_backward live in a fixed array that is part of the loaded
+// library image on every GPU (it costs PB200_STATIC_SCRATCH_BYTES of device memory per
+// GPU from load until exit).
+//
+// In host code `g_v2f_bwd_static_scratch` is only a handle for the runtime; the device
+// address must be asked for with cudaGetSymbolAddress, once per device, with that device
+// current.
+#define PB200_STATIC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char g_v2f_bwd_static_scratch[PB200_STATIC_SCRATCH_BYTES];
+
+namespace pb {
+static int static_scratch_for_current_device(void** out) {
+    static void* cached[64] = {nullptr};
+    static std::mutex mu;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    PB_REQUIRE(dev >= 0 && dev < 64, PB200_EINVAL, "vertex2facet_backward_static: device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_v2f_bwd_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_v2f_bwd_static_scratch)");
+        PB_REQUIRE(p != nullptr, PB200_ECUDA, "vertex2facet_backward_static: null scratch address");
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return PB200_OK;
+}
+}  // namespace pb
+
+extern "C" {
+
+size_t pb200_vertex2facet_backward_static_max_bytes(void) { return PB200_STATIC_SCRATCH_BYTES; }
+
+int pb200_vertex2facet_backward_static(int64_t Nf, int64_t Nv, int C, int r, const float* gradOutput,
+                                       const float* input, const float* filter, const int32_t* face,
+                                       const int32_t* rowptr, const int32_t* entries, float* gradInput,
+                                       float* gradFilter, void* stream_) {
+    PB_REQUIRE(Nf >= 0 && Nv >= 0 && C > 0 && r > 0, PB200_EINVAL, "vertex2facet_backward_static: bad sizes");
+    size_t need = pb200_vertex2facet_backward_workspace_bytes(Nf, Nv, C, r);
+    PB_REQUIRE(need <= PB200_STATIC_SCRATCH_BYTES, PB200_EWORKSPACE,
+               "vertex2facet_backward_static: this shape needs %zu bytes of scratch, the built-in array holds %u; "
+               "use pb200_vertex2facet_backward with a caller-provided workspace",
+               need, (unsigned)PB200_STATIC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    int rc = static_scratch_for_current_device(&scratch);
+    if (rc != PB200_OK) return rc;
+    // Every partial the second stage reads is written by the first stage of the same call,
+    // so nothing in the array has to start at zero.
+    return pb200_vertex2facet_backward(Nf, Nv, C, r, gradOutput, input, filter, face, rowptr, entries, gradInput,
+                                       gradFilter, scratch, PB200_STATIC_SCRATCH_BYTES, stream_);
 }
 
 }  // extern "C"
