@@ -35,9 +35,11 @@ extern "C" {
 #define PB200_EINDEX       -4   /* an index array holds an out-of-range value              */
 
 /* contraction precision for facet2facet (fp32 accumulation in every mode) */
-#define PB200_PREC_FP32     0   /* fp32-faithful: meets the 1e-4 relative gate             */
+#define PB200_PREC_FP32     0   /* fp32-faithful (tf32 hi+lo split on the tensor cores where the
+                                   shape allows, FFMA otherwise): meets the 1e-4 relative gate */
 #define PB200_PREC_TF32     1   /* tf32 operands on the tensor cores                       */
 #define PB200_PREC_BF16     2   /* bf16 operands on the tensor cores (2e-2 relative gate)  */
+#define PB200_PREC_FP32_FFMA 3  /* fp32 FFMA path (no tensor cores), every shape            */
 
 int         pb200_version(void);
 const char* pb200_last_error(void);

@@ -13,8 +13,8 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libpicasso_b200.so")
 
 OK, EINVAL, EWORKSPACE, ECUDA, EINDEX = 0, -1, -2, -3, -4
-PREC_FP32, PREC_TF32, PREC_BF16 = 0, 1, 2
-PRECISIONS = {"fp32": PREC_FP32, "tf32": PREC_TF32, "bf16": PREC_BF16}
+PREC_FP32, PREC_TF32, PREC_BF16, PREC_FP32_FFMA = 0, 1, 2, 3
+PRECISIONS = {"fp32": PREC_FP32, "tf32": PREC_TF32, "bf16": PREC_BF16, "fp32_ffma": PREC_FP32_FFMA}
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(

@@ -10,9 +10,21 @@ int f2f_simt_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const fl
 int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
                       const float* filter, const float* bary, const int32_t* cum, float* gin, float* gfilter,
                       void* ws, cudaStream_t stream);
+namespace tc {
+bool fwd_supported(int Cin, int Cout, int F);
+size_t fwd_workspace_bytes(int Cin, int Cout, int F, int precision);
+int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input, const float* filter,
+            const float* bary, const int32_t* cum, float* output, int precision, void* ws, cudaStream_t stream);
+int check_async_error(const char* where);
+}  // namespace tc
 }  // namespace pb
 
 using namespace pb;
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+static bool use_tc_fwd(int Cin, int Cout, int F, int precision) {
+    return precision != PB200_PREC_FP32_FFMA && tc::fwd_supported(Cin, Cout, F);
+}
 
 static bool f2f_sizes_ok(int64_t Nf, int64_t NiK, int Cin, int Cout, int F) {
     return Nf >= 0 && NiK >= 0 && Cin > 0 && Cout > 0 && F > 0 && F <= 50 && NiK < (1LL << 31) && Nf < (1LL << 31);
@@ -22,7 +34,7 @@ extern "C" {
 
 size_t pb200_facet2facet_forward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
     if (!f2f_sizes_ok(Nf, NiK, Cin, Cout, F)) return 0;
-    (void)precision;
+    if (use_tc_fwd(Cin, Cout, F, precision)) return tc::fwd_workspace_bytes(Cin, Cout, F, precision);
     return f2f_simt_fwd_ws(Nf, Cin, Cout, F);
 }
 
@@ -32,13 +44,19 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
     cudaStream_t stream = (cudaStream_t)stream_;
     PB_REQUIRE(f2f_sizes_ok(Nf, NiK, Cin, Cout, F), PB200_EINVAL,
                "facet2facet_forward: bad sizes (F must be in 1..50)");
-    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_BF16, PB200_EINVAL,
+    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_FFMA, PB200_EINVAL,
                "facet2facet_forward: unknown precision %d", precision);
     if (Nf == 0) return PB200_OK;
     PB_REQUIRE(filter && numInterior && output && (NiK == 0 || (input && bary)), PB200_EINVAL,
                "facet2facet_forward: null pointer");
     PB_REQUIRE(workspace && workspace_bytes >= pb200_facet2facet_forward_workspace_bytes(Nf, NiK, Cin, Cout, F, precision),
                PB200_EWORKSPACE, "facet2facet_forward: workspace too small");
+    if (use_tc_fwd(Cin, Cout, F, precision)) {
+        PB_REQUIRE(NiK == 0 || aligned16(input), PB200_EINVAL, "facet2facet_forward: input must be 16-byte aligned");
+        PB_REQUIRE(aligned16(workspace), PB200_EINVAL, "facet2facet_forward: workspace must be 16-byte aligned");
+        return tc::forward(Nf, NiK, Cin, Cout, F, input, filter, bary, numInterior, output, precision, workspace,
+                           stream);
+    }
     return f2f_simt_forward(Nf, NiK, Cin, Cout, F, input, filter, bary, numInterior, output, workspace, stream);
 }
 
@@ -55,7 +73,7 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
     cudaStream_t stream = (cudaStream_t)stream_;
     PB_REQUIRE(f2f_sizes_ok(Nf, NiK, Cin, Cout, F), PB200_EINVAL,
                "facet2facet_backward: bad sizes (F must be in 1..50)");
-    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_BF16, PB200_EINVAL,
+    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_FFMA, PB200_EINVAL,
                "facet2facet_backward: unknown precision %d", precision);
     PB_REQUIRE(gradFilter, PB200_EINVAL, "facet2facet_backward: null pointer");
     if (Nf == 0) {

@@ -1,0 +1,387 @@
+// facet2facet forward on the 5th-generation tensor cores (tcgen05 + TMEM), one fused kernel:
+//
+//   out^T[co, f] = sum_{q=(c16,d,kk)}  W[co, q] * A[f, q],   A[f,(d,ci)] = (1/T_f) sum_k bary[k,d]*in[k,ci]
+//
+// Per CTA (persistent, one per SM) and per tile of 256 faces:
+//   * 16 producer warps build the A operand on the fly: a thread keeps the (pre-scaled)
+//     input values of its face for 8 channels in registers, walks the F bases, and writes
+//     one 64-byte swizzled K-major row segment per stage straight into shared memory
+//     (A is never materialised in HBM: at 128 channels x 25 bases it would be 12.8 KB/face);
+//   * one thread streams the pre-swizzled filter blocks (8 KB, or hi+lo 16 KB) with 1-D bulk
+//     copies of the TMA engine, completion counted on the stage's mbarrier;
+//   * one thread issues tcgen05.mma (M = 128 filter rows, N = 256 faces, K = 8 per
+//     instruction, tf32 operands, fp32 accumulation in TMEM) and commits stages back;
+//   * the producer warps drain the 128 x 256 accumulator with tcgen05.ld and store
+//     out[f, co] coalesced along co.
+// Precision modes: 1 split  = operands rounded to tf32;
+//                  2 splits = every operand as tf32 hi + tf32 lo, three MMAs per k-step
+//                             (hi*hi + hi*lo + lo*hi): fp32-faithful products.
+// All waits are bounded (tc_ptx.cuh); on a time-out the block unwinds, frees its TMEM and
+// raises the library's asynchronous error word.
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+#include <mutex>
+
+namespace pb {
+namespace tc {
+
+using namespace ptx;
+
+constexpr int TILE_F = 256;                 // faces per tile  (UMMA N)
+constexpr int UM = 128;                     // filter rows     (UMMA M), Cout zero-padded to it
+constexpr int KS = 16;                      // floats per operand row per stage (64 B)
+constexpr int PWARPS = 16;                  // producer / epilogue warps, 16 faces each
+constexpr int NTHREADS = (PWARPS + 2) * 32; // + bulk-copy warp + MMA warp
+constexpr int FACE_TILE_BYTES = TILE_F * 64;
+constexpr int FILT_TILE_BYTES = UM * 64;
+constexpr int TREG = 4;                     // samples per face whose inputs stay in registers
+constexpr int TMEM_COLS = 256;
+
+// ---- asynchronous error word (pinned, mapped host memory; written by a kernel that gave up)
+static int* g_async_err_host = nullptr;
+static std::mutex g_async_mu;
+
+int* async_error_word() {
+    std::lock_guard<std::mutex> lk(g_async_mu);
+    if (!g_async_err_host) {
+        int* p = nullptr;
+        if (cudaHostAlloc((void**)&p, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        *p = 0;
+        g_async_err_host = p;
+    }
+    return g_async_err_host;
+}
+
+int check_async_error(const char* where) {
+    int* p = g_async_err_host;
+    if (p && *(volatile int*)p != 0) {
+        set_error("%s: an earlier tensor-core kernel of this library gave up waiting (code %d); results of that "
+                  "call are invalid", where, *(volatile int*)p);
+        return PB200_ECUDA;
+    }
+    return PB200_OK;
+}
+
+// ---- filter image: Wimg[kb][split][co 0..127][16 floats, 64B-swizzled], kb = c16*F + d,
+//      element (co, kk) = filter[co][c16*16 + kk][d]
+__global__ void f2f_tc_prep_filter_kernel(int F, int Cin, int Cout, int nsplit, const float* __restrict__ filter,
+                                          uint8_t* __restrict__ wimg) {
+    const int nkb = (Cin / KS) * F;
+    int64_t total = (int64_t)nkb * UM * 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int c = (int)(i & 3);
+        int co = (int)((i >> 2) % UM);
+        int kb = (int)(i / (4 * UM));
+        int c16 = kb / F, d = kb - c16 * F;
+        float v[4], hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            v[j] = co < Cout ? __ldg(filter + ((int64_t)co * Cin + c16 * KS + c * 4 + j) * F + d) : 0.f;
+            if (nsplit == 1) { hi[j] = to_tf32_rna(v[j]); lo[j] = 0.f; }
+            else { hi[j] = tf32_hi(v[j]); lo[j] = v[j] - hi[j]; }
+        }
+        uint8_t* base = wimg + (int64_t)kb * nsplit * FILT_TILE_BYTES;
+        uint32_t off = swz64_offset((uint32_t)co, (uint32_t)c);
+        *reinterpret_cast<float4*>(base + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        if (nsplit == 2)
+            *reinterpret_cast<float4*>(base + FILT_TILE_BYTES + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+struct FwdParams {
+    int64_t Nf;
+    int Cin, Cout, F;
+    int nstages;          // pipeline depth
+    int smaxw;            // bary rows staged per producer warp
+    const float* in;
+    const float* bary;
+    const int32_t* cum;
+    const uint8_t* wimg;
+    float* out;
+    int* async_err;
+};
+
+__host__ __device__ inline size_t fwd_stage_bytes(int nsplit) {
+    return (size_t)nsplit * (FACE_TILE_BYTES + FILT_TILE_BYTES);
+}
+
+template <int NSPLIT>
+__global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = p.nstages;
+    const int F = p.F, Cin = p.Cin, Cout = p.Cout;
+    const int FP = F | 1;                                     // odd row pitch: conflict-free column reads
+    const size_t stage_bytes = fwd_stage_bytes(NSPLIT);
+    // stage layout: [face hi][face lo?][filter hi][filter lo?]
+    uint8_t* stages = smem;
+    float* bary_s = reinterpret_cast<float*>(smem + (size_t)S * stage_bytes);
+    uint8_t* tail = reinterpret_cast<uint8_t*>(bary_s + (size_t)PWARPS * p.smaxw * FP);
+    uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(tail) + 15) & ~(uintptr_t)15);
+    uint64_t* full = bars;                 // [S]  producers (16 warps) + filter bytes
+    uint64_t* empty = bars + S;            // [S]  MMA done with the stage
+    uint64_t* acc_full = bars + 2 * S;     // [1]  accumulator of the tile complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], PWARPS + 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == PWARPS) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t ntiles = (p.Nf + TILE_F - 1) / TILE_F;
+    const int nkb = (Cin / KS) * F;
+
+    if (warp < PWARPS) {
+        // ================================ producers + epilogue ================================
+        const int ml = lane >> 1, h = lane & 1;               // face within the warp's 16, 8-channel half
+        const int m = warp * 16 + ml;                         // row of the face operand tile
+        float* wb = bary_s + (size_t)warp * p.smaxw * FP;     // this warp's staged bary rows
+        const uint32_t off0 = swz64_offset((uint32_t)m, (uint32_t)(2 * h));
+        const uint32_t off1 = swz64_offset((uint32_t)m, (uint32_t)(2 * h + 1));
+        uint32_t it = 0, tcount = 0;
+        bool alive = true;
+        for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
+            const int64_t f0 = tile * TILE_F;
+            const int64_t fw0 = f0 + warp * 16;               // first face of this warp
+            const int64_t f = fw0 + ml;
+            const bool valid = f < p.Nf;
+            int k0 = 0, k1 = 0;
+            if (valid) { k0 = f > 0 ? __ldg(p.cum + f - 1) : 0; k1 = __ldg(p.cum + f); }
+            const int T = k1 - k0;
+            // sample range of the warp's faces, staged (as far as it fits) in the warp's region
+            int kw0 = 0, kw1 = 0;
+            if (fw0 < p.Nf) {
+                int64_t fl = fw0 + 16 < p.Nf ? fw0 + 16 : p.Nf;
+                kw0 = fw0 > 0 ? __ldg(p.cum + fw0 - 1) : 0;
+                kw1 = __ldg(p.cum + fl - 1);
+            }
+            int nS = kw1 - kw0;
+            if (nS > p.smaxw) nS = p.smaxw;
+            __syncwarp();
+            {
+                const float* src = p.bary + (int64_t)kw0 * F;
+                for (int i = lane; i < nS * F; i += 32) {
+                    int s = i / F;
+                    wb[s * FP + (i - s * F)] = __ldg(src + i);
+                }
+            }
+            __syncwarp();
+            const float invT = T > 0 ? 1.f / (float)T : 0.f;
+            const int kloc = k0 - kw0;                        // row of the face's first sample in wb
+            for (int c16 = 0; c16 < Cin / KS && alive; ++c16) {
+                float4 x[TREG][2];
+#pragma unroll
+                for (int t = 0; t < TREG; ++t) {
+                    if (t < T) {
+                        const float4* src = reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + c16 * KS + h * 8);
+                        x[t][0] = scale4(ldg4(src), invT);
+                        x[t][1] = scale4(ldg4(src + 1), invT);
+                    } else {
+                        x[t][0] = zero4(); x[t][1] = zero4();
+                    }
+                }
+                for (int d = 0; d < F; ++d, ++it) {
+                    const int s = (int)(it % (uint32_t)S);
+                    const uint32_t ph = (it / (uint32_t)S) & 1u;
+                    int ok = 1;
+                    if (lane == 0) ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) { alive = false; break; }
+                    float4 a0 = zero4(), a1 = zero4();
+#pragma unroll
+                    for (int t = 0; t < TREG; ++t) {
+                        if (t < T) {
+                            int row = kloc + t;
+                            float b = row < p.smaxw ? wb[row * FP + d] : __ldg(p.bary + (int64_t)(k0 + t) * F + d);
+                            fma4s(a0, b, x[t][0]);
+                            fma4s(a1, b, x[t][1]);
+                        }
+                    }
+                    for (int t = TREG; t < T; ++t) {          // faces with many samples: re-read from global
+                        float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
+                        const float4* src = reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + c16 * KS + h * 8);
+                        fma4s(a0, b, ldg4(src));
+                        fma4s(a1, b, ldg4(src + 1));
+                    }
+                    uint8_t* st = stages + (size_t)s * stage_bytes;
+                    if (NSPLIT == 1) {
+                        *reinterpret_cast<float4*>(st + off0) =
+                            make_float4(to_tf32_rna(a0.x), to_tf32_rna(a0.y), to_tf32_rna(a0.z), to_tf32_rna(a0.w));
+                        *reinterpret_cast<float4*>(st + off1) =
+                            make_float4(to_tf32_rna(a1.x), to_tf32_rna(a1.y), to_tf32_rna(a1.z), to_tf32_rna(a1.w));
+                    } else {
+                        float4 h0 = make_float4(tf32_hi(a0.x), tf32_hi(a0.y), tf32_hi(a0.z), tf32_hi(a0.w));
+                        float4 h1 = make_float4(tf32_hi(a1.x), tf32_hi(a1.y), tf32_hi(a1.z), tf32_hi(a1.w));
+                        *reinterpret_cast<float4*>(st + off0) = h0;
+                        *reinterpret_cast<float4*>(st + off1) = h1;
+                        *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off0) =
+                            make_float4(a0.x - h0.x, a0.y - h0.y, a0.z - h0.z, a0.w - h0.w);
+                        *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off1) =
+                            make_float4(a1.x - h1.x, a1.y - h1.y, a1.z - h1.z, a1.w - h1.w);
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&full[s]);
+                }
+            }
+            if (!alive) break;
+            // ---- epilogue: drain the accumulator (rows = co, columns = faces of the tile)
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(acc_full, tcount & 1u, abort_flag) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { alive = false; break; }
+            tc_fence_after();
+            const int q = warp & 3, g = warp >> 2;
+            const int co = q * 32 + lane;
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                const int col = g * 64 + half * 32;
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)col, r);
+                tmem_ld_wait();
+                if (co < Cout) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        int64_t fo = f0 + col + j;
+                        if (fo < p.Nf) __stcs(p.out + fo * Cout + co, __uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    } else if (warp == PWARPS) {
+        // ================================ filter loader (TMA engine) ==========================
+        if (lane == 0) {
+            const uint32_t bytes = (uint32_t)(NSPLIT * FILT_TILE_BYTES);
+            uint32_t it = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % (uint32_t)S);
+                    const uint32_t ph = (it / (uint32_t)S) & 1u;
+                    if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { alive = false; break; }
+                    mbar_arrive_expect_tx(&full[s], bytes);
+                    bulk_g2s(stages + (size_t)s * stage_bytes + (size_t)NSPLIT * FACE_TILE_BYTES,
+                             p.wimg + (size_t)kb * bytes, bytes, &full[s]);
+                }
+            }
+            if (!alive) {                       // let copies in flight land before shared memory is released
+                long long t0 = clock64();
+                while (clock64() - t0 < 2000000) { }
+            }
+        }
+    } else {
+        // ================================ MMA issuer =========================================
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(FMT_TF32, UM, TILE_F);
+            uint32_t it = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % (uint32_t)S);
+                    const uint32_t ph = (it / (uint32_t)S) & 1u;
+                    if (!mbar_wait(&full[s], ph, abort_flag)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(stages + (size_t)s * stage_bytes);
+                    const uint64_t face_hi = smem_desc_kmajor(st, 64, SWZ_64B);
+                    const uint64_t filt_hi = smem_desc_kmajor(st + NSPLIT * FACE_TILE_BYTES, 64, SWZ_64B);
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks) {          // 2 x (K = 8 tf32 = 32 bytes)
+                        const uint64_t adv = (uint64_t)(ks * 2);
+                        const uint32_t first = (kb | ks) != 0;
+                        if (NSPLIT == 1) {
+                            mma_tf32(tmem_base, filt_hi + adv, face_hi + adv, idesc, first);
+                        } else {
+                            const uint64_t face_lo = smem_desc_kmajor(st + FACE_TILE_BYTES, 64, SWZ_64B);
+                            const uint64_t filt_lo =
+                                smem_desc_kmajor(st + NSPLIT * FACE_TILE_BYTES + FILT_TILE_BYTES, 64, SWZ_64B);
+                            mma_tf32(tmem_base, filt_lo + adv, face_hi + adv, idesc, first);
+                            mma_tf32(tmem_base, filt_hi + adv, face_lo + adv, idesc, 1u);
+                            mma_tf32(tmem_base, filt_hi + adv, face_hi + adv, idesc, 1u);
+                        }
+                    }
+                    tc_commit(&empty[s]);
+                }
+                if (alive) tc_commit(acc_full);
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == PWARPS) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (tid == 0 && *abort_flag && p.async_err) {
+        *p.async_err = 1;
+        __threadfence_system();
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+struct FwdPlan { int nsplit, nstages, smaxw; size_t smem; size_t wimg_bytes; };
+
+bool fwd_supported(int Cin, int Cout, int F) { return Cin % KS == 0 && Cout >= 1 && Cout <= UM && F >= 1 && F <= 50; }
+
+FwdPlan fwd_plan(int Cin, int Cout, int F, int precision) {
+    FwdPlan pl;
+    pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
+    pl.nstages = pl.nsplit == 2 ? 2 : 4;
+    const int FP = F | 1;
+    const size_t budget = 220 * 1024;
+    size_t fixed = (size_t)pl.nstages * fwd_stage_bytes(pl.nsplit) + 1024 /*alignment*/ + 256 /*barriers*/;
+    int smaxw = (int)((budget - fixed) / ((size_t)PWARPS * FP * 4));
+    if (smaxw > 64) smaxw = 64;             // 16 faces x 4 samples
+    if (smaxw < 0) smaxw = 0;
+    pl.smaxw = smaxw;
+    pl.smem = fixed + (size_t)PWARPS * smaxw * FP * 4;
+    pl.wimg_bytes = (size_t)(Cin / KS) * F * pl.nsplit * FILT_TILE_BYTES;
+    return pl;
+}
+
+size_t fwd_workspace_bytes(int Cin, int Cout, int F, int precision) {
+    return align_up(fwd_plan(Cin, Cout, F, precision).wimg_bytes, 256);
+}
+
+int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input, const float* filter,
+            const float* bary, const int32_t* cum, float* output, int precision, void* ws, cudaStream_t stream) {
+    (void)NiK;
+    int rc = check_async_error("facet2facet_forward");
+    if (rc) return rc;
+    FwdPlan pl = fwd_plan(Cin, Cout, F, precision);
+    uint8_t* wimg = (uint8_t*)ws;
+    int64_t prep_items = (int64_t)(Cin / KS) * F * UM * 4;
+    PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_kernel, persistent_blocks(prep_items, 256, 8), 256, 0, stream,
+              F, Cin, Cout, pl.nsplit, filter, wimg);
+    FwdParams p;
+    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F;
+    p.nstages = pl.nstages; p.smaxw = pl.smaxw;
+    p.in = input; p.bary = bary; p.cum = cum; p.wimg = wimg; p.out = output;
+    p.async_err = async_error_word();
+    int64_t ntiles = ceil_div(Nf, TILE_F);
+    int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
+    if (pl.nsplit == 2) {
+        PB_CUDA(cudaFuncSetAttribute(f2f_fwd_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+        PB_LAUNCH("f2f_fwd_tc", f2f_fwd_tc_kernel<2>, grid, NTHREADS, pl.smem, stream, p);
+    } else {
+        PB_CUDA(cudaFuncSetAttribute(f2f_fwd_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
+        PB_LAUNCH("f2f_fwd_tc", f2f_fwd_tc_kernel<1>, grid, NTHREADS, pl.smem, stream, p);
+    }
+    return PB200_OK;
+}
+
+}  // namespace tc
+}  // namespace pb

@@ -36,12 +36,13 @@ def topology(kind: str, seed: int):
     return mb.vertex, mb.face, vt, nv_out
 
 
-def conv_inputs(kind: str, C: int, r: int, K: int, cout: int, seed: int, zero_sample_faces: bool = True):
+def conv_inputs(kind: str, C: int, r: int, K: int, cout: int, seed: int, zero_sample_faces: bool = True,
+                max_per_face: int = 4):
     """All operator inputs for one case, as a dict of CPU torch tensors."""
     g = torch.Generator().manual_seed(seed)
     vertex, face, vt, nv_out = topology(kind, seed)
     nv, nf = vertex.shape[0], face.shape[0]
-    counts, bary = synth.texture_samples(nf, seed + 7)
+    counts, bary = synth.texture_samples(nf, seed + 7, max_per_face)
     if zero_sample_faces and nf > 4:
         counts[1] = 0
         counts[nf - 1] = 0

@@ -1,0 +1,78 @@
+"""facet2facet on the tcgen05 tensor-core path (through the C ABI) against the fp64 oracle
+and against the library's own fp32 FFMA path.  Gates: 'fp32' mode (tf32 hi+lo split)
+<= 1e-4 relative like every fp32 feature tensor; 'tf32' mode <= 2e-3; 'bf16' mode <= 2e-2
+(the stated tolerance of bf16-operand variants)."""
+import pytest
+import torch
+
+from conftest import rel_err
+from cases import conv_inputs
+
+pytestmark = pytest.mark.gpu
+
+GATE = {"fp32": 1e-4, "tf32": 2e-3, "bf16": 2e-2}
+
+SHAPES = [
+    # topology, Cin, K(=F), Cout, max samples per face
+    ("ico2x3", 16, 16, 8, 4),          # 960 faces: 4 tiles, one k-group
+    ("grid33x2", 32, 16, 64, 4),       # c1-like channels, ~3.7k faces
+    ("grid33x2", 128, 25, 128, 4),     # c5-like channels
+    ("grid17x2", 64, 9, 128, 9),       # faces with more samples than stay in registers / staged rows
+    ("ico1x2", 48, 4, 100, 2),         # Cout not a multiple of 32, Cin = 3 groups
+    ("tri", 16, 16, 16, 3),            # a single face
+]
+
+
+def _dev(d):
+    return {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from picassoplus_b200.mesh.pi_modules import conv3d
+    from oracle import mesh_oracle
+    yield conv3d, mesh_oracle
+    conv3d.set_f2f_precision("fp32")
+
+
+@pytest.mark.parametrize("mode", ["fp32", "tf32", "bf16"])
+@pytest.mark.parametrize("kind,C,K,cout,tmax", SHAPES)
+def test_forward_matches_oracle(mods, kind, C, K, cout, tmax, mode):
+    conv3d, mo = mods
+    d = conv_inputs(kind, C, 1, K, cout, seed=41, max_per_face=tmax)
+    c = _dev(d)
+    want = mo.facet2facet_forward(d["tex"].double(), d["filt_f2f"].double(), d["bary"].double(), d["cum"])
+    conv3d.set_f2f_precision(mode)
+    out = conv3d.facet2facet_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+    torch.cuda.synchronize()
+    assert out.shape == want.shape
+    assert rel_err(out, want) <= GATE[mode], (mode, rel_err(out, want))
+    zero_faces = (d["counts"] == 0).nonzero().flatten()
+    assert torch.all(out[zero_faces.cuda()] == 0)
+    # deterministic
+    again = conv3d.facet2facet_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+    assert torch.equal(out, again)
+
+
+def test_forward_many_tiles_vs_ffma_path(mods):
+    """One full 360x360 heightfield mesh at the benchmark's channel widths: ~900 tiles, so
+    every CTA walks several tiles and every barrier wraps its phase many times."""
+    conv3d, _ = mods
+    from picassoplus_b200 import synth
+    mb = synth.heightfield_batch(1, 360, seed=9)
+    nf = mb.num_faces
+    counts, _ = synth.texture_samples(nf, 3)
+    g = torch.Generator().manual_seed(5)
+    cum = torch.cumsum(torch.from_numpy(counts), 0, dtype=torch.int32).cuda()
+    nik = int(counts.sum())
+    C, F, cout = 128, 25, 128
+    tex = torch.randn(nik, C, generator=g).cuda()
+    bary = torch.randn(nik, F, generator=g).cuda()
+    W = (torch.randn(cout, C, F, generator=g) / (C * F) ** 0.5).cuda()
+    conv3d.set_f2f_precision("fp32_ffma")
+    want = conv3d.facet2facet_forward(tex, W, bary, cum)
+    for mode in ("fp32", "tf32"):
+        conv3d.set_f2f_precision(mode)
+        out = conv3d.facet2facet_forward(tex, W, bary, cum)
+        torch.cuda.synchronize()
+        assert rel_err(out, want) <= GATE[mode], (mode, rel_err(out, want))
