@@ -98,6 +98,7 @@ struct FwdParams {
     int Cin, Cout, F;
     int nstages;          // pipeline depth
     int smaxw;            // bary rows staged per producer warp
+    int bpitch;           // floats per staged bary row: multiple of 4 and = 4 (mod 8) -> aligned, conflict-free
     const float* in;
     const float* bary;
     const int32_t* cum;
@@ -117,7 +118,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = p.nstages;
     const int F = p.F, Cin = p.Cin, Cout = p.Cout;
-    const int FP = F | 1;                                     // odd row pitch: conflict-free column reads
+    const int FP = p.bpitch;
     const size_t stage_bytes = fwd_stage_bytes(NSPLIT);
     // stage layout: [face hi][face lo?][filter hi][filter lo?]
     uint8_t* stages = smem;
@@ -150,10 +151,45 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
         const int ml = lane >> 1, h = lane & 1;               // face within the warp's 16, 8-channel half
         const int m = warp * 16 + ml;                         // row of the face operand tile
         float* wb = bary_s + (size_t)warp * p.smaxw * FP;     // this warp's staged bary rows
+        for (int i = lane; i < p.smaxw * FP; i += 32) wb[i] = 0.f;
         const uint32_t off0 = swz64_offset((uint32_t)m, (uint32_t)(2 * h));
         const uint32_t off1 = swz64_offset((uint32_t)m, (uint32_t)(2 * h + 1));
-        uint32_t it = 0, tcount = 0;
+        int st_i = 0;                                         // running stage index and phase
+        uint32_t st_ph = 0;
+        uint32_t tcount = 0;
         bool alive = true;
+
+        // publish one operand row segment (a0, a1 = 8 channels of A[f, d, :]) into the current stage
+        auto publish = [&](const float4& a0, const float4& a1) -> bool {
+            if (!mbar_try_wait(&empty[st_i], st_ph ^ 1u)) {
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(&empty[st_i], st_ph ^ 1u, abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) return false;
+            }
+            uint8_t* st = stages + (size_t)st_i * stage_bytes;
+            if (NSPLIT == 1) {
+                *reinterpret_cast<float4*>(st + off0) =
+                    make_float4(to_tf32_rna(a0.x), to_tf32_rna(a0.y), to_tf32_rna(a0.z), to_tf32_rna(a0.w));
+                *reinterpret_cast<float4*>(st + off1) =
+                    make_float4(to_tf32_rna(a1.x), to_tf32_rna(a1.y), to_tf32_rna(a1.z), to_tf32_rna(a1.w));
+            } else {
+                float4 h0 = make_float4(tf32_hi(a0.x), tf32_hi(a0.y), tf32_hi(a0.z), tf32_hi(a0.w));
+                float4 h1 = make_float4(tf32_hi(a1.x), tf32_hi(a1.y), tf32_hi(a1.z), tf32_hi(a1.w));
+                *reinterpret_cast<float4*>(st + off0) = h0;
+                *reinterpret_cast<float4*>(st + off1) = h1;
+                *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off0) =
+                    make_float4(a0.x - h0.x, a0.y - h0.y, a0.z - h0.z, a0.w - h0.w);
+                *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off1) =
+                    make_float4(a1.x - h1.x, a1.y - h1.y, a1.z - h1.z, a1.w - h1.w);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[st_i]);
+            if (++st_i == S) { st_i = 0; st_ph ^= 1u; }
+            return true;
+        };
+
         for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t f0 = tile * TILE_F;
             const int64_t fw0 = f0 + warp * 16;               // first face of this warp
@@ -171,71 +207,74 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
             }
             int nS = kw1 - kw0;
             if (nS > p.smaxw) nS = p.smaxw;
+            // a warp whose faces all have <= TREG samples and fit the staged rows takes the lean path
+            const bool slow = __any_sync(0xffffffffu, (T > TREG) || (kw1 - kw0 > p.smaxw));
             __syncwarp();
             {
                 const float* src = p.bary + (int64_t)kw0 * F;
                 for (int i = lane; i < nS * F; i += 32) {
-                    int s = i / F;
-                    wb[s * FP + (i - s * F)] = __ldg(src + i);
+                    int sr = i / F;
+                    wb[sr * FP + (i - sr * F)] = __ldg(src + i);
                 }
             }
             __syncwarp();
             const float invT = T > 0 ? 1.f / (float)T : 0.f;
-            const int kloc = k0 - kw0;                        // row of the face's first sample in wb
-            for (int c16 = 0; c16 < Cin / KS && alive; ++c16) {
-                float4 x[TREG][2];
+            const int kloc = valid ? k0 - kw0 : 0;            // row of the face's first sample in wb
+            if (!slow) {
+                // rows of the face's samples; unused slots point at a valid row and meet x == 0
+                const float* bp[TREG];
 #pragma unroll
                 for (int t = 0; t < TREG; ++t) {
-                    if (t < T) {
-                        const float4* src = reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + c16 * KS + h * 8);
-                        x[t][0] = scale4(ldg4(src), invT);
-                        x[t][1] = scale4(ldg4(src + 1), invT);
-                    } else {
-                        x[t][0] = zero4(); x[t][1] = zero4();
-                    }
+                    int row = kloc + (t < T ? t : (T > 0 ? T - 1 : 0));
+                    if (row >= p.smaxw) row = 0;
+                    bp[t] = wb + row * FP;
                 }
-                for (int d = 0; d < F; ++d, ++it) {
-                    const int s = (int)(it % (uint32_t)S);
-                    const uint32_t ph = (it / (uint32_t)S) & 1u;
-                    int ok = 1;
-                    if (lane == 0) ok = mbar_wait(&empty[s], ph ^ 1u, abort_flag) ? 1 : 0;
-                    ok = __shfl_sync(0xffffffffu, ok, 0);
-                    if (!ok) { alive = false; break; }
-                    float4 a0 = zero4(), a1 = zero4();
+                for (int c16 = 0; c16 < Cin / KS && alive; ++c16) {
+                    float4 x[TREG][2];
 #pragma unroll
                     for (int t = 0; t < TREG; ++t) {
                         if (t < T) {
-                            int row = kloc + t;
-                            float b = row < p.smaxw ? wb[row * FP + d] : __ldg(p.bary + (int64_t)(k0 + t) * F + d);
-                            fma4s(a0, b, x[t][0]);
-                            fma4s(a1, b, x[t][1]);
+                            const float4* src =
+                                reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + c16 * KS + h * 8);
+                            x[t][0] = scale4(ldg4(src), invT);
+                            x[t][1] = scale4(ldg4(src + 1), invT);
+                        } else {
+                            x[t][0] = zero4(); x[t][1] = zero4();
                         }
                     }
-                    for (int t = TREG; t < T; ++t) {          // faces with many samples: re-read from global
-                        float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
-                        const float4* src = reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + c16 * KS + h * 8);
-                        fma4s(a0, b, ldg4(src));
-                        fma4s(a1, b, ldg4(src + 1));
+                    for (int d4 = 0; d4 < F && alive; d4 += 4) {
+                        float4 b[TREG];
+#pragma unroll
+                        for (int t = 0; t < TREG; ++t) b[t] = *reinterpret_cast<const float4*>(bp[t] + d4);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (d4 + j < F) {
+                                float4 a0 = zero4(), a1 = zero4();
+#pragma unroll
+                                for (int t = 0; t < TREG; ++t) {
+                                    float bj = j == 0 ? b[t].x : (j == 1 ? b[t].y : (j == 2 ? b[t].z : b[t].w));
+                                    fma4s(a0, bj, x[t][0]);
+                                    fma4s(a1, bj, x[t][1]);
+                                }
+                                if (!publish(a0, a1)) { alive = false; break; }
+                            }
+                        }
                     }
-                    uint8_t* st = stages + (size_t)s * stage_bytes;
-                    if (NSPLIT == 1) {
-                        *reinterpret_cast<float4*>(st + off0) =
-                            make_float4(to_tf32_rna(a0.x), to_tf32_rna(a0.y), to_tf32_rna(a0.z), to_tf32_rna(a0.w));
-                        *reinterpret_cast<float4*>(st + off1) =
-                            make_float4(to_tf32_rna(a1.x), to_tf32_rna(a1.y), to_tf32_rna(a1.z), to_tf32_rna(a1.w));
-                    } else {
-                        float4 h0 = make_float4(tf32_hi(a0.x), tf32_hi(a0.y), tf32_hi(a0.z), tf32_hi(a0.w));
-                        float4 h1 = make_float4(tf32_hi(a1.x), tf32_hi(a1.y), tf32_hi(a1.z), tf32_hi(a1.w));
-                        *reinterpret_cast<float4*>(st + off0) = h0;
-                        *reinterpret_cast<float4*>(st + off1) = h1;
-                        *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off0) =
-                            make_float4(a0.x - h0.x, a0.y - h0.y, a0.z - h0.z, a0.w - h0.w);
-                        *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off1) =
-                            make_float4(a1.x - h1.x, a1.y - h1.y, a1.z - h1.z, a1.w - h1.w);
+                }
+            } else {
+                for (int c16 = 0; c16 < Cin / KS && alive; ++c16) {
+                    for (int d = 0; d < F; ++d) {
+                        float4 a0 = zero4(), a1 = zero4();
+                        for (int t = 0; t < T; ++t) {
+                            int row = kloc + t;
+                            float b = (row < p.smaxw ? wb[row * FP + d] : __ldg(p.bary + (int64_t)(k0 + t) * F + d)) * invT;
+                            const float4* src =
+                                reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + c16 * KS + h * 8);
+                            fma4s(a0, b, ldg4(src));
+                            fma4s(a1, b, ldg4(src + 1));
+                        }
+                        if (!publish(a0, a1)) { alive = false; break; }
                     }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&full[s]);
                 }
             }
             if (!alive) break;
@@ -267,16 +306,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
         // ================================ filter loader (TMA engine) ==========================
         if (lane == 0) {
             const uint32_t bytes = (uint32_t)(NSPLIT * FILT_TILE_BYTES);
-            uint32_t it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool alive = true;
             for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = (int)(it % (uint32_t)S);
-                    const uint32_t ph = (it / (uint32_t)S) & 1u;
+                for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { alive = false; break; }
                     mbar_arrive_expect_tx(&full[s], bytes);
                     bulk_g2s(stages + (size_t)s * stage_bytes + (size_t)NSPLIT * FACE_TILE_BYTES,
                              p.wimg + (size_t)kb * bytes, bytes, &full[s]);
+                    if (++s == S) { s = 0; ph ^= 1u; }
                 }
             }
             if (!alive) {                       // let copies in flight land before shared memory is released
@@ -288,12 +327,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
         // ================================ MMA issuer =========================================
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(FMT_TF32, UM, TILE_F);
-            uint32_t it = 0;
+            int s = 0;
+            uint32_t ph = 0;
             bool alive = true;
             for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = (int)(it % (uint32_t)S);
-                    const uint32_t ph = (it / (uint32_t)S) & 1u;
+                for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(&full[s], ph, abort_flag)) { alive = false; break; }
                     tc_fence_after();
                     const uint32_t st = smem_u32(stages + (size_t)s * stage_bytes);
@@ -315,6 +353,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                         }
                     }
                     tc_commit(&empty[s]);
+                    if (++s == S) { s = 0; ph ^= 1u; }
                 }
                 if (alive) tc_commit(acc_full);
             }
@@ -332,7 +371,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
 }
 
 // ---------------------------------------------------------------------------- host side
-struct FwdPlan { int nsplit, nstages, smaxw; size_t smem; size_t wimg_bytes; };
+struct FwdPlan { int nsplit, nstages, smaxw, bpitch; size_t smem; size_t wimg_bytes; };
 
 bool fwd_supported(int Cin, int Cout, int F) { return Cin % KS == 0 && Cout >= 1 && Cout <= UM && F >= 1 && F <= 50; }
 
@@ -340,7 +379,8 @@ FwdPlan fwd_plan(int Cin, int Cout, int F, int precision) {
     FwdPlan pl;
     pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
     pl.nstages = pl.nsplit == 2 ? 2 : 4;
-    const int FP = F | 1;
+    const int FP = ((F + 3) / 4 * 4) | 4;
+    pl.bpitch = FP;
     const size_t budget = 220 * 1024;
     size_t fixed = (size_t)pl.nstages * fwd_stage_bytes(pl.nsplit) + 1024 /*alignment*/ + 256 /*barriers*/;
     int smaxw = (int)((budget - fixed) / ((size_t)PWARPS * FP * 4));
@@ -368,7 +408,7 @@ int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* inpu
               F, Cin, Cout, pl.nsplit, filter, wimg);
     FwdParams p;
     p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F;
-    p.nstages = pl.nstages; p.smaxw = pl.smaxw;
+    p.nstages = pl.nstages; p.smaxw = pl.smaxw; p.bpitch = pl.bpitch;
     p.in = input; p.bary = bary; p.cum = cum; p.wimg = wimg; p.out = output;
     p.async_err = async_error_word();
     int64_t ntiles = ceil_div(Nf, TILE_F);
