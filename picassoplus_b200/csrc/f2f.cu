@@ -9,13 +9,20 @@ int f2f_simt_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const fl
                      const float* bary, const int32_t* cum, float* output, void* ws, cudaStream_t stream);
 int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
                       const float* filter, const float* bary, const int32_t* cum, float* gin, float* gfilter,
-                      void* ws, cudaStream_t stream);
+                      void* ws, cudaStream_t stream, bool want_gin);
 namespace tc {
 bool fwd_supported(int Cin, int Cout, int F);
 size_t fwd_workspace_bytes(int Cin, int Cout, int F, int precision);
 int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input, const float* filter,
             const float* bary, const int32_t* cum, float* output, int precision, void* ws, cudaStream_t stream);
 int check_async_error(const char* where);
+namespace gin {
+bool supported(int Cin, int Cout, int F);
+bool fits(int Cin, int Cout, int F, int precision);
+size_t workspace_bytes(int Cin, int Cout, int F, int precision);
+int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* filter, const float* bary,
+                   const int32_t* cum, float* gin, int precision, void* ws, cudaStream_t stream);
+}  // namespace gin
 }  // namespace tc
 }  // namespace pb
 
@@ -24,6 +31,9 @@ using namespace pb;
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static bool use_tc_fwd(int Cin, int Cout, int F, int precision) {
     return precision != PB200_PREC_FP32_FFMA && tc::fwd_supported(Cin, Cout, F);
+}
+static bool use_tc_gin(int Cin, int Cout, int F, int precision) {
+    return precision != PB200_PREC_FP32_FFMA && tc::gin::supported(Cin, Cout, F) && tc::gin::fits(Cin, Cout, F, precision);
 }
 
 static bool f2f_sizes_ok(int64_t Nf, int64_t NiK, int Cin, int Cout, int F) {
@@ -62,8 +72,9 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
 
 size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
     if (!f2f_sizes_ok(Nf, NiK, Cin, Cout, F)) return 0;
-    (void)precision;
-    return f2f_simt_bwd_ws(Nf, Cin, Cout, F);
+    size_t n = f2f_simt_bwd_ws(Nf, Cin, Cout, F);
+    if (use_tc_gin(Cin, Cout, F, precision)) n += tc::gin::workspace_bytes(Cin, Cout, F, precision);
+    return n;
 }
 
 int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
@@ -84,8 +95,15 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
                "facet2facet_backward: null pointer");
     PB_REQUIRE(workspace && workspace_bytes >= pb200_facet2facet_backward_workspace_bytes(Nf, NiK, Cin, Cout, F, precision),
                PB200_EWORKSPACE, "facet2facet_backward: workspace too small");
+    const bool tc_gin = use_tc_gin(Cin, Cout, F, precision) && aligned16(gradOutput) && aligned16(workspace);
+    if (tc_gin && NiK > 0) {
+        void* wimg = (char*)workspace + f2f_simt_bwd_ws(Nf, Cin, Cout, F);
+        int rc = tc::gin::backward_input(Nf, Cin, Cout, F, gradOutput, filter, bary, numInterior, gradInput,
+                                         precision, wimg, stream);
+        if (rc) return rc;
+    }
     return f2f_simt_backward(Nf, NiK, Cin, Cout, F, gradOutput, input, filter, bary, numInterior, gradInput,
-                             gradFilter, workspace, stream);
+                             gradFilter, workspace, stream, !tc_gin);
 }
 
 }  // extern "C"

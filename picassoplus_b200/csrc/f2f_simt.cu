@@ -191,9 +191,10 @@ __global__ void f2f_gin_all_kernel(int64_t f0, int64_t nfaces, int64_t Nf, int F
     }
 }
 
+// want_gin = false skips the input-gradient half (the caller computes it elsewhere)
 int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
                       const float* filter, const float* bary, const int32_t* cum, float* gin, float* gfilter,
-                      void* ws, cudaStream_t stream) {
+                      void* ws, cudaStream_t stream, bool want_gin) {
     const int Q = F * Cin;
     char* w = (char*)ws;
     float* Wt = (float*)w;  w += align_up(sizeof(float) * (size_t)Q * Cout, 256);
@@ -211,6 +212,7 @@ int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const f
         // gWt[Q x Cout] += A^T[Q x nf] @ gout[nf x Cout]
         int rc = sgemm(stream, "f2f_gfilter_sgemm", Q, Cout, nf, A, 1, Q, gout + f0 * Cout, Cout, 1, gWt, Cout, 1);
         if (rc) return rc;
+        if (!want_gin) continue;
         // gA[nf x Q] = gout[nf x Cout] @ Wt^T[Cout x Q]
         rc = sgemm(stream, "f2f_gA_sgemm", nf, Q, Cout, gout + f0 * Cout, Cout, 1, Wt, 1, Cout, gA, Q, 0);
         if (rc) return rc;

@@ -1,0 +1,463 @@
+// facet2facet input gradient on tcgen05 + TMEM, one fused kernel:
+//
+//   gA[f, (ci,d)] = sum_co g[f,co] * W[co,ci,d]            (tensor cores, K = co)
+//   gradInput[k, ci] = (1/T_f) sum_d bary[k,d] * gA[f(k), (ci,d)]   (epilogue, straight from TMEM)
+//
+// gA (F*Cin floats per face, 12.8 KB at 128 channels x 25 bases) never leaves the SM.
+// Per CTA (persistent) and per tile of 128 faces (UMMA M = TMEM lanes = faces):
+//   * the epilogue warps copy the tile's gradOutput rows into shared memory once, as the
+//     K-major M-side operand (64-byte swizzled rows, one 8 KB block per 16 output channels);
+//   * one thread streams pre-swizzled filter blocks W'[(ci,d) rows][16 co] (N-side operand,
+//     N = up to 256 rows = NQ channels x F bases per slice) with 1-D bulk copies;
+//   * one thread issues tcgen05.mma into one of two 256-column accumulators;
+//   * 8 epilogue warps (thread = face) drain the other accumulator: for every channel pair
+//     they read the F columns of both channels, contract with the bary rows of the face's
+//     samples and store float2 results.
+// Modes: 1 split (tf32 operands) or 2 splits (tf32 hi+lo, three MMAs per k-step).
+// All waits are bounded; on a time-out the block unwinds and raises the async error word.
+#include "common.cuh"
+#include "tc_ptx.cuh"
+
+namespace pb {
+namespace tc {
+
+int* async_error_word();
+int check_async_error(const char* where);
+
+namespace gin {
+
+using namespace ptx;
+
+constexpr int TILE_M = 128;
+constexpr int NCOLS = 256;
+constexpr int KS = 16;
+constexpr int EWARPS = 8;
+constexpr int NTHREADS = (EWARPS + 2) * 32;
+constexpr int G_KTILE_BYTES = TILE_M * 64;      // one 16-channel block of the gradOutput tile
+constexpr int W_STAGE_BYTES = NCOLS * 64;       // one 16-channel block of a filter slice
+
+// ---- TMEM loads of 1/4/8/16/32 consecutive columns (lane = row)
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, float* v) {
+    uint32_t r0;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r0) : "r"(taddr) : "memory");
+    v[0] = __uint_as_float(r0);
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float* v) {
+    uint32_t r[4];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+                   "=r"(r[15])
+                 : "r"(taddr) : "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld32f(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    tmem_ld32(taddr, r);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// F consecutive columns -> v[0..F)
+template <int F>
+__device__ __forceinline__ void tmem_ld_row(uint32_t taddr, float* v) {
+    int o = 0;
+    if (F & 32) { tmem_ld32f(taddr + o, v + o); o += 32; }
+    if (F & 16) { tmem_ld16(taddr + o, v + o); o += 16; }
+    if (F & 8)  { tmem_ld8(taddr + o, v + o); o += 8; }
+    if (F & 4)  { tmem_ld4(taddr + o, v + o); o += 4; }
+    if (F & 2)  { tmem_ld1(taddr + o, v + o); tmem_ld1(taddr + o + 1, v + o + 1); o += 2; }
+    if (F & 1)  { tmem_ld1(taddr + o, v + o); }
+}
+
+// ---- filter image: Wimg[slice][kst][split][row 0..255][16 floats, 64B-swizzled];
+//      row = cil*F + d, element (row, kk) = filter[co = kst*16 + kk][ci = slice*NQ + cil][d]
+__global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int Cout, int nq, int nslices, int kst, int nsplit,
+                                              const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
+    int64_t total = (int64_t)nslices * kst * NCOLS * 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int c = (int)(i & 3);
+        int row = (int)((i >> 2) % NCOLS);
+        int64_t blk = i / (4 * NCOLS);
+        int ks = (int)(blk % kst);
+        int slice = (int)(blk / kst);
+        int cil = row / F, d = row - cil * F;
+        int ci = slice * nq + cil;
+        float hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int co = ks * KS + c * 4 + j;
+            float v = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)co * Cin + ci) * F + d) : 0.f;
+            if (nsplit == 1) { hi[j] = to_tf32_rna(v); lo[j] = 0.f; }
+            else { hi[j] = tf32_hi(v); lo[j] = v - hi[j]; }
+        }
+        uint8_t* base = wimg + blk * (int64_t)nsplit * W_STAGE_BYTES;
+        uint32_t off = swz64_offset((uint32_t)row, (uint32_t)c);
+        *reinterpret_cast<float4*>(base + off) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+        if (nsplit == 2)
+            *reinterpret_cast<float4*>(base + W_STAGE_BYTES + off) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
+struct Params {
+    int64_t Nf;
+    int Cin, Cout;
+    int nq, nslices, kst, nmma;      // channels per slice, slices, 16-channel K blocks, UMMA N
+    int nstages;                     // filter ring depth
+    int bary_rows, bpitch;           // staged bary rows per tile (0 = read from global), row pitch in floats
+    const float* gout;
+    const float* bary;
+    const int32_t* cum;
+    const uint8_t* wimg;
+    float* gin;
+    int* async_err;
+};
+
+template <int NSPLIT, int F>
+__global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int S = p.nstages, KST = p.kst;
+    const int Cin = p.Cin, Cout = p.Cout;
+    const size_t gtile_bytes = (size_t)NSPLIT * KST * G_KTILE_BYTES;       // [split][kst][8 KB]
+    const size_t wstage_bytes = (size_t)NSPLIT * W_STAGE_BYTES;           // [split][16 KB]
+    uint8_t* gtile = smem;
+    uint8_t* wst = smem + gtile_bytes;
+    float* bary_s = reinterpret_cast<float*>(wst + (size_t)S * wstage_bytes);
+    uint8_t* tail = reinterpret_cast<uint8_t*>(bary_s + (size_t)p.bary_rows * p.bpitch);
+    uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(tail) + 15) & ~(uintptr_t)15);
+    uint64_t* w_full = bars;                  // [S]
+    uint64_t* w_empty = bars + S;             // [S]
+    uint64_t* acc_full = bars + 2 * S;        // [2]
+    uint64_t* acc_empty = bars + 2 * S + 2;   // [2]
+    uint64_t* g_full = bars + 2 * S + 4;      // gradOutput tile written
+    uint64_t* g_empty = bars + 2 * S + 5;     // all MMAs of the tile done reading it
+    uint64_t* b_ready = bars + 2 * S + 6;     // bary rows of the tile staged
+    uint64_t* b_free = bars + 2 * S + 7;      // all warps done with the staged rows
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    if (tid == 0) {
+        for (int s = 0; s < S; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EWARPS); }
+        mbar_init(g_full, EWARPS);
+        mbar_init(g_empty, 1);
+        mbar_init(b_ready, EWARPS);
+        mbar_init(b_free, EWARPS);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == EWARPS) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const int64_t ntiles = (p.Nf + TILE_M - 1) / TILE_M;
+
+    if (warp < EWARPS) {
+        // ===================== gradOutput tile loader + epilogue (thread = face) =====================
+        const int q = warp & 3, half = warp >> 2;
+        const int r = q * 32 + lane;                            // face row of the tile = TMEM lane
+        const int npairs = (p.nq + 1) >> 1;
+        const int pair_lo = half == 0 ? 0 : (npairs + 1) >> 1;
+        const int pair_hi = half == 0 ? (npairs + 1) >> 1 : npairs;
+        uint32_t tcount = 0, sc = 0;
+        bool alive = true;
+        auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+            return __shfl_sync(0xffffffffu, ok, 0) != 0;
+        };
+        for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
+            const int64_t f0 = tile * TILE_M;
+            const int64_t f = f0 + r;
+            const bool valid = f < p.Nf;
+            int k0 = 0, k1 = 0;
+            if (valid) { k0 = f > 0 ? __ldg(p.cum + f - 1) : 0; k1 = __ldg(p.cum + f); }
+            const int T = k1 - k0;
+            const float invT = T > 0 ? 1.f / (float)T : 0.f;
+            // ---- 1. the tile's gradOutput rows -> K-major swizzled operand blocks
+            if (!warp_wait(g_empty, (tcount & 1u) ^ 1u)) { alive = false; break; }
+            {
+                const int rr = tid & 127, cg = tid >> 7;         // 256 threads: row, chunk parity
+                const int64_t fr = f0 + rr;
+                const float4* src = reinterpret_cast<const float4*>(p.gout + fr * Cout);
+                for (int c = cg; c < KST * 4; c += 2) {
+                    float4 v = zero4();
+                    if (fr < p.Nf && c * 4 < Cout) v = ldg4(src + c);
+                    uint8_t* dst = gtile + (size_t)(c >> 2) * G_KTILE_BYTES + swz64_offset((uint32_t)rr, (uint32_t)(c & 3));
+                    if (NSPLIT == 1) {
+                        *reinterpret_cast<float4*>(dst) =
+                            make_float4(to_tf32_rna(v.x), to_tf32_rna(v.y), to_tf32_rna(v.z), to_tf32_rna(v.w));
+                    } else {
+                        float4 hv = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+                        *reinterpret_cast<float4*>(dst) = hv;
+                        *reinterpret_cast<float4*>(dst + (size_t)KST * G_KTILE_BYTES) =
+                            make_float4(v.x - hv.x, v.y - hv.y, v.z - hv.z, v.w - hv.w);
+                    }
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(g_full);
+            // ---- 2. stage the bary rows of the tile's samples (as many as fit)
+            int kt0 = 0, kt1 = 0;
+            {
+                int64_t fl = f0 + TILE_M < p.Nf ? f0 + TILE_M : p.Nf;
+                kt0 = f0 > 0 ? __ldg(p.cum + f0 - 1) : 0;
+                kt1 = __ldg(p.cum + fl - 1);
+            }
+            int nrows = kt1 - kt0;
+            if (nrows > p.bary_rows) nrows = p.bary_rows;
+            if (p.bary_rows > 0) {
+                if (!warp_wait(b_free, (tcount & 1u) ^ 1u)) { alive = false; break; }
+                const float* src = p.bary + (int64_t)kt0 * F;
+                for (int i = tid; i < nrows * F; i += EWARPS * 32) {
+                    int sr = i / F;
+                    bary_s[sr * p.bpitch + (i - sr * F)] = __ldg(src + i);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_ready);
+                if (!warp_wait(b_ready, tcount & 1u)) { alive = false; break; }
+            }
+            const int kloc = k0 - kt0;
+            const bool staged = valid && (kloc + T <= nrows);
+            // ---- 3. per slice: drain the accumulator, contract with bary, store gradInput
+            for (int slice = 0; slice < p.nslices && alive; ++slice, ++sc) {
+                const uint32_t a = sc & 1u;
+                if (!warp_wait(&acc_full[a], (sc >> 1) & 1u)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + a * NCOLS;
+                for (int pr = pair_lo; pr < pair_hi; ++pr) {
+                    const int cil = 2 * pr;
+                    const int ci = slice * p.nq + cil;
+                    const bool has_b = (cil + 1 < p.nq) && (ci + 1 < Cin);
+                    float va[F], vb[F];
+                    tmem_ld_row<F>(tbase + (uint32_t)(cil * F), va);
+                    if (cil + 1 < p.nq) tmem_ld_row<F>(tbase + (uint32_t)((cil + 1) * F), vb);
+                    else {
+#pragma unroll
+                        for (int d = 0; d < F; ++d) vb[d] = 0.f;
+                    }
+                    tmem_ld_wait();
+                    if (ci < Cin) {
+                        for (int t = 0; t < T; ++t) {
+                            float ga = 0.f, gb = 0.f;
+                            if (staged) {
+                                const float* bp = bary_s + (kloc + t) * p.bpitch;
+#pragma unroll
+                                for (int d4 = 0; d4 + 4 <= F; d4 += 4) {
+                                    float4 b = *reinterpret_cast<const float4*>(bp + d4);
+                                    ga = fmaf(b.x, va[d4], ga); gb = fmaf(b.x, vb[d4], gb);
+                                    ga = fmaf(b.y, va[d4 + 1], ga); gb = fmaf(b.y, vb[d4 + 1], gb);
+                                    ga = fmaf(b.z, va[d4 + 2], ga); gb = fmaf(b.z, vb[d4 + 2], gb);
+                                    ga = fmaf(b.w, va[d4 + 3], ga); gb = fmaf(b.w, vb[d4 + 3], gb);
+                                }
+#pragma unroll
+                                for (int d = F & ~3; d < F; ++d) {
+                                    float b = bp[d];
+                                    ga = fmaf(b, va[d], ga); gb = fmaf(b, vb[d], gb);
+                                }
+                            } else {
+                                const float* bp = p.bary + (int64_t)(k0 + t) * F;
+#pragma unroll
+                                for (int d = 0; d < F; ++d) {
+                                    float b = __ldg(bp + d);
+                                    ga = fmaf(b, va[d], ga); gb = fmaf(b, vb[d], gb);
+                                }
+                            }
+                            const int64_t idx = (int64_t)(k0 + t) * Cin + ci;
+                            float* dst = p.gin + idx;
+                            if (has_b && ((idx & 1) == 0)) *reinterpret_cast<float2*>(dst) = make_float2(ga * invT, gb * invT);
+                            else { dst[0] = ga * invT; if (has_b) dst[1] = gb * invT; }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[a]);
+            }
+            if (!alive) break;
+            if (p.bary_rows > 0) { __syncwarp(); if (lane == 0) mbar_arrive(b_free); }
+        }
+    } else if (warp == EWARPS) {
+        // ===================== filter loader (TMA engine) =====================
+        if (lane == 0) {
+            const uint32_t bytes = (uint32_t)wstage_bytes;
+            int s = 0;
+            uint32_t ph = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
+                for (int blk = 0; blk < p.nslices * KST; ++blk) {
+                    if (!mbar_wait(&w_empty[s], ph ^ 1u, abort_flag)) { alive = false; break; }
+                    mbar_arrive_expect_tx(&w_full[s], bytes);
+                    bulk_g2s(wst + (size_t)s * wstage_bytes, p.wimg + (size_t)blk * bytes, bytes, &w_full[s]);
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (!alive) {
+                long long t0 = clock64();
+                while (clock64() - t0 < 2000000) { }
+            }
+        }
+    } else {
+        // ===================== MMA issuer =====================
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(FMT_TF32, TILE_M, (uint32_t)p.nmma);
+            int s = 0;
+            uint32_t ph = 0, tcount = 0, sc = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
+                if (!mbar_wait(g_full, tcount & 1u, abort_flag)) { alive = false; break; }
+                for (int slice = 0; slice < p.nslices && alive; ++slice, ++sc) {
+                    const uint32_t a = sc & 1u;
+                    if (!mbar_wait(&acc_empty[a], ((sc >> 1) & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + a * NCOLS;
+                    for (int ks = 0; ks < KST; ++ks) {
+                        if (!mbar_wait(&w_full[s], ph, abort_flag)) { alive = false; break; }
+                        tc_fence_after();
+                        const uint32_t g_hi = smem_u32(gtile + (size_t)ks * G_KTILE_BYTES);
+                        const uint32_t w_hi = smem_u32(wst + (size_t)s * wstage_bytes);
+                        const uint64_t dg_hi = smem_desc_kmajor(g_hi, 64, SWZ_64B);
+                        const uint64_t dw_hi = smem_desc_kmajor(w_hi, 64, SWZ_64B);
+#pragma unroll
+                        for (int k2 = 0; k2 < 2; ++k2) {
+                            const uint64_t adv = (uint64_t)(k2 * 2);
+                            const uint32_t first = (ks | k2) != 0;
+                            if (NSPLIT == 1) {
+                                mma_tf32(d_tmem, dg_hi + adv, dw_hi + adv, idesc, first);
+                            } else {
+                                const uint64_t dg_lo =
+                                    smem_desc_kmajor(g_hi + (uint32_t)(KST * G_KTILE_BYTES), 64, SWZ_64B);
+                                const uint64_t dw_lo = smem_desc_kmajor(w_hi + W_STAGE_BYTES, 64, SWZ_64B);
+                                mma_tf32(d_tmem, dg_lo + adv, dw_hi + adv, idesc, first);
+                                mma_tf32(d_tmem, dg_hi + adv, dw_lo + adv, idesc, 1u);
+                                mma_tf32(d_tmem, dg_hi + adv, dw_hi + adv, idesc, 1u);
+                            }
+                        }
+                        tc_commit(&w_empty[s]);
+                        if (++s == S) { s = 0; ph ^= 1u; }
+                    }
+                    if (alive) tc_commit(&acc_full[a]);
+                }
+                if (alive) tc_commit(g_empty);
+            }
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == EWARPS) tmem_dealloc(tmem_base, 512);
+    if (tid == 0 && *abort_flag && p.async_err) {
+        *p.async_err = 2;
+        __threadfence_system();
+    }
+}
+
+// ---------------------------------------------------------------------------- host side
+struct Plan { int nsplit, nq, nslices, kst, nmma, nstages, bary_rows, bpitch; size_t smem, wimg_bytes; };
+
+static bool f_templated(int F) { return F == 4 || F == 9 || F == 16 || F == 25 || F == 36; }
+
+bool supported(int Cin, int Cout, int F) {
+    return f_templated(F) && Cout % 4 == 0 && Cout >= 4 && Cout <= 256 && Cin >= 1;
+}
+
+Plan plan(int Cin, int Cout, int F, int precision) {
+    Plan pl;
+    pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
+    pl.nq = NCOLS / F;
+    if (pl.nq > Cin) pl.nq = Cin;
+    pl.nslices = (Cin + pl.nq - 1) / pl.nq;
+    pl.kst = (Cout + KS - 1) / KS;
+    pl.nmma = (pl.nq * F + 15) / 16 * 16;
+    pl.bpitch = ((F + 3) / 4 * 4) | 4;
+    const size_t budget = 222 * 1024;
+    size_t gt = (size_t)pl.nsplit * pl.kst * G_KTILE_BYTES;
+    size_t ws = (size_t)pl.nsplit * W_STAGE_BYTES;
+    size_t fixed = gt + 1024 + 256;
+    int stages = 4;
+    while (stages > 2 && fixed + stages * ws > budget) --stages;
+    pl.nstages = stages;
+    size_t left = budget > fixed + stages * ws ? budget - fixed - stages * ws : 0;
+    int rows = (int)(left / ((size_t)pl.bpitch * 4));
+    if (rows > 4 * TILE_M) rows = 4 * TILE_M;
+    if (rows < TILE_M) rows = 0;                    // too few to matter: read bary from global
+    pl.bary_rows = rows;
+    pl.smem = fixed + stages * ws + (size_t)rows * pl.bpitch * 4;
+    pl.wimg_bytes = (size_t)pl.nslices * pl.kst * ws;
+    return pl;
+}
+
+bool fits(int Cin, int Cout, int F, int precision) {
+    Plan pl = plan(Cin, Cout, F, precision);
+    return pl.smem <= 227 * 1024 && pl.nstages >= 2;
+}
+
+size_t workspace_bytes(int Cin, int Cout, int F, int precision) {
+    return align_up(plan(Cin, Cout, F, precision).wimg_bytes, 256);
+}
+
+template <int NSPLIT, int F>
+static int launch(const Params& p, int grid, size_t smem, cudaStream_t stream) {
+    PB_CUDA(cudaFuncSetAttribute(f2f_bwd_gin_tc_kernel<NSPLIT, F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    PB_LAUNCH("f2f_bwd_gin_tc", (f2f_bwd_gin_tc_kernel<NSPLIT, F>), grid, NTHREADS, smem, stream, p);
+    return PB200_OK;
+}
+
+template <int NSPLIT>
+static int launch_f(int F, const Params& p, int grid, size_t smem, cudaStream_t stream) {
+    switch (F) {
+        case 4: return launch<NSPLIT, 4>(p, grid, smem, stream);
+        case 9: return launch<NSPLIT, 9>(p, grid, smem, stream);
+        case 16: return launch<NSPLIT, 16>(p, grid, smem, stream);
+        case 25: return launch<NSPLIT, 25>(p, grid, smem, stream);
+        default: return launch<NSPLIT, 36>(p, grid, smem, stream);
+    }
+}
+
+int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* filter, const float* bary,
+                   const int32_t* cum, float* gin, int precision, void* ws, cudaStream_t stream) {
+    int rc = check_async_error("facet2facet_backward");
+    if (rc) return rc;
+    Plan pl = plan(Cin, Cout, F, precision);
+    uint8_t* wimg = (uint8_t*)ws;
+    int64_t items = (int64_t)pl.nslices * pl.kst * NCOLS * 4;
+    PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_kernel, persistent_blocks(items, 256, 8), 256, 0,
+              stream, F, Cin, Cout, pl.nq, pl.nslices, pl.kst, pl.nsplit, filter, wimg);
+    Params p;
+    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout;
+    p.nq = pl.nq; p.nslices = pl.nslices; p.kst = pl.kst; p.nmma = pl.nmma;
+    p.nstages = pl.nstages; p.bary_rows = pl.bary_rows; p.bpitch = pl.bpitch;
+    p.gout = gout; p.bary = bary; p.cum = cum; p.wimg = wimg; p.gin = gin;
+    p.async_err = async_error_word();
+    int64_t ntiles = ceil_div(Nf, TILE_M);
+    int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
+    return pl.nsplit == 2 ? launch_f<2>(F, p, grid, pl.smem, stream) : launch_f<1>(F, p, grid, pl.smem, stream);
+}
+
+}  // namespace gin
+}  // namespace tc
+}  // namespace pb

@@ -76,3 +76,52 @@ def test_forward_many_tiles_vs_ffma_path(mods):
         out = conv3d.facet2facet_forward(tex, W, bary, cum)
         torch.cuda.synchronize()
         assert rel_err(out, want) <= GATE[mode], (mode, rel_err(out, want))
+
+
+BWD_SHAPES = SHAPES + [
+    ("grid17x2", 7, 36, 12, 4),        # odd channel count, F = 36 (7 channels per slice), Cout = 12
+    ("grid17x2", 40, 25, 200, 4),      # Cout above 128: forward falls back, input gradient still tensor-core
+    ("ico2x3", 3, 16, 32, 4),          # the reference networks' texture entry: RGB in, 32 out
+]
+
+
+@pytest.mark.parametrize("mode", ["fp32", "tf32"])
+@pytest.mark.parametrize("kind,C,K,cout,tmax", BWD_SHAPES)
+def test_backward_matches_oracle(mods, kind, C, K, cout, tmax, mode):
+    conv3d, mo = mods
+    d = conv_inputs(kind, C, 1, K, cout, seed=43, max_per_face=tmax)
+    c = _dev(d)
+    wgin, wgf = mo.facet2facet_backward(d["g_f2f"].double(), d["tex"].double(), d["filt_f2f"].double(),
+                                        d["bary"].double(), d["cum"])
+    conv3d.set_f2f_precision(mode)
+    gin, gf = conv3d.facet2facet_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+    torch.cuda.synchronize()
+    assert gin.shape == wgin.shape and gf.shape == wgf.shape
+    assert rel_err(gin, wgin) <= GATE[mode], (mode, "gin", rel_err(gin, wgin))
+    assert rel_err(gf, wgf) <= GATE[mode], (mode, "gf", rel_err(gf, wgf))
+    gin2, gf2 = conv3d.facet2facet_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+    assert torch.equal(gin, gin2) and torch.equal(gf, gf2)
+
+
+def test_backward_many_tiles_vs_ffma_path(mods):
+    conv3d, _ = mods
+    from picassoplus_b200 import synth
+    mb = synth.heightfield_batch(1, 200, seed=9)
+    nf = mb.num_faces
+    counts, _ = synth.texture_samples(nf, 3)
+    g = torch.Generator().manual_seed(5)
+    cum = torch.cumsum(torch.from_numpy(counts), 0, dtype=torch.int32).cuda()
+    nik = int(counts.sum())
+    C, F, cout = 128, 25, 128
+    tex = torch.randn(nik, C, generator=g).cuda()
+    bary = torch.randn(nik, F, generator=g).cuda()
+    W = (torch.randn(cout, C, F, generator=g) / (C * F) ** 0.5).cuda()
+    go = torch.randn(nf, cout, generator=g).cuda()
+    conv3d.set_f2f_precision("fp32_ffma")
+    wgin, wgf = conv3d.facet2facet_backward(go, tex, W, bary, cum)
+    for mode in ("fp32", "tf32"):
+        conv3d.set_f2f_precision(mode)
+        gin, gf = conv3d.facet2facet_backward(go, tex, W, bary, cum)
+        torch.cuda.synchronize()
+        assert rel_err(gin, wgin) <= GATE[mode], (mode, rel_err(gin, wgin))
+        assert rel_err(gf, wgf) <= GATE[mode], (mode, rel_err(gf, wgf))
