@@ -9,7 +9,7 @@ int f2f_simt_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const fl
                      const float* bary, const int32_t* cum, float* output, void* ws, cudaStream_t stream);
 int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
                       const float* filter, const float* bary, const int32_t* cum, float* gin, float* gfilter,
-                      void* ws, cudaStream_t stream, bool want_gin);
+                      void* ws, cudaStream_t stream, bool want_gin, bool want_gfilter);
 namespace tc {
 bool fwd_supported(int Cin, int Cout, int F);
 size_t fwd_workspace_bytes(int Cin, int Cout, int F, int precision);
@@ -23,6 +23,13 @@ size_t workspace_bytes(int Cin, int Cout, int F, int precision);
 int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* filter, const float* bary,
                    const int32_t* cum, float* gin, int precision, void* ws, cudaStream_t stream);
 }  // namespace gin
+namespace gfilter {
+bool supported(int Cin, int Cout, int F);
+bool fits(int64_t Nf, int Cin, int Cout, int F, int precision);
+size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision);
+int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* input, const float* bary,
+                    const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream);
+}  // namespace gfilter
 }  // namespace tc
 }  // namespace pb
 
@@ -31,6 +38,10 @@ using namespace pb;
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static bool use_tc_fwd(int Cin, int Cout, int F, int precision) {
     return precision != PB200_PREC_FP32_FFMA && tc::fwd_supported(Cin, Cout, F);
+}
+static bool use_tc_gf(int64_t Nf, int Cin, int Cout, int F, int precision) {
+    return precision != PB200_PREC_FP32_FFMA && tc::gfilter::supported(Cin, Cout, F) &&
+           tc::gfilter::fits(Nf, Cin, Cout, F, precision);
 }
 static bool use_tc_gin(int Cin, int Cout, int F, int precision) {
     return precision != PB200_PREC_FP32_FFMA && tc::gin::supported(Cin, Cout, F) && tc::gin::fits(Cin, Cout, F, precision);
@@ -72,8 +83,10 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
 
 size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
     if (!f2f_sizes_ok(Nf, NiK, Cin, Cout, F)) return 0;
-    size_t n = f2f_simt_bwd_ws(Nf, Cin, Cout, F);
-    if (use_tc_gin(Cin, Cout, F, precision)) n += tc::gin::workspace_bytes(Cin, Cout, F, precision);
+    const bool tg = use_tc_gin(Cin, Cout, F, precision), tf = use_tc_gf(Nf, Cin, Cout, F, precision);
+    size_t n = (tg && tf) ? 0 : f2f_simt_bwd_ws(Nf, Cin, Cout, F);
+    if (tg) n += tc::gin::workspace_bytes(Cin, Cout, F, precision);
+    if (tf) n += tc::gfilter::workspace_bytes(Nf, Cin, Cout, F, precision);
     return n;
 }
 
@@ -95,15 +108,29 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
                "facet2facet_backward: null pointer");
     PB_REQUIRE(workspace && workspace_bytes >= pb200_facet2facet_backward_workspace_bytes(Nf, NiK, Cin, Cout, F, precision),
                PB200_EWORKSPACE, "facet2facet_backward: workspace too small");
-    const bool tc_gin = use_tc_gin(Cin, Cout, F, precision) && aligned16(gradOutput) && aligned16(workspace);
-    if (tc_gin && NiK > 0) {
-        void* wimg = (char*)workspace + f2f_simt_bwd_ws(Nf, Cin, Cout, F);
-        int rc = tc::gin::backward_input(Nf, Cin, Cout, F, gradOutput, filter, bary, numInterior, gradInput,
-                                         precision, wimg, stream);
+    const bool tg = use_tc_gin(Cin, Cout, F, precision), tf = use_tc_gf(Nf, Cin, Cout, F, precision);
+    if (tg || tf)
+        PB_REQUIRE(aligned16(gradOutput) && aligned16(workspace) && (NiK == 0 || aligned16(input)), PB200_EINVAL,
+                   "facet2facet_backward: gradOutput, input and workspace must be 16-byte aligned");
+    char* w = (char*)workspace;
+    void* simt_ws = w;
+    if (!(tg && tf)) w += f2f_simt_bwd_ws(Nf, Cin, Cout, F);
+    if (tg) {
+        if (NiK > 0) {
+            int rc = tc::gin::backward_input(Nf, Cin, Cout, F, gradOutput, filter, bary, numInterior, gradInput,
+                                             precision, w, stream);
+            if (rc) return rc;
+        }
+        w += tc::gin::workspace_bytes(Cin, Cout, F, precision);
+    }
+    if (tf) {
+        int rc = tc::gfilter::backward_filter(Nf, Cin, Cout, F, gradOutput, input, bary, numInterior, gradFilter,
+                                              precision, w, stream);
         if (rc) return rc;
     }
+    if (tg && tf) return PB200_OK;
     return f2f_simt_backward(Nf, NiK, Cin, Cout, F, gradOutput, input, filter, bary, numInterior, gradInput,
-                             gradFilter, workspace, stream, !tc_gin);
+                             gradFilter, simt_ws, stream, !tg, !tf);
 }
 
 }  // extern "C"

@@ -191,10 +191,10 @@ __global__ void f2f_gin_all_kernel(int64_t f0, int64_t nfaces, int64_t Nf, int F
     }
 }
 
-// want_gin = false skips the input-gradient half (the caller computes it elsewhere)
+// want_gin / want_gfilter = false skip that half (the caller computes it elsewhere)
 int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
                       const float* filter, const float* bary, const int32_t* cum, float* gin, float* gfilter,
-                      void* ws, cudaStream_t stream, bool want_gin) {
+                      void* ws, cudaStream_t stream, bool want_gin, bool want_gfilter) {
     const int Q = F * Cin;
     char* w = (char*)ws;
     float* Wt = (float*)w;  w += align_up(sizeof(float) * (size_t)Q * Cout, 256);
@@ -207,11 +207,14 @@ int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const f
     PB_CUDA(cudaMemsetAsync(gWt, 0, sizeof(float) * (size_t)Q * Cout, stream));
     for (int64_t f0 = 0; f0 < Nf; f0 += FC) {
         int64_t nf = Nf - f0 < FC ? Nf - f0 : FC;
-        PB_LAUNCH("f2f_build_A", f2f_build_A_kernel, persistent_blocks(nf * Q, 256, 16), 256, 0, stream, f0, nf, F, Cin,
-                  cum, bary, input, A);
-        // gWt[Q x Cout] += A^T[Q x nf] @ gout[nf x Cout]
-        int rc = sgemm(stream, "f2f_gfilter_sgemm", Q, Cout, nf, A, 1, Q, gout + f0 * Cout, Cout, 1, gWt, Cout, 1);
-        if (rc) return rc;
+        int rc = PB200_OK;
+        if (want_gfilter) {
+            PB_LAUNCH("f2f_build_A", f2f_build_A_kernel, persistent_blocks(nf * Q, 256, 16), 256, 0, stream, f0, nf, F,
+                      Cin, cum, bary, input, A);
+            // gWt[Q x Cout] += A^T[Q x nf] @ gout[nf x Cout]
+            rc = sgemm(stream, "f2f_gfilter_sgemm", Q, Cout, nf, A, 1, Q, gout + f0 * Cout, Cout, 1, gWt, Cout, 1);
+            if (rc) return rc;
+        }
         if (!want_gin) continue;
         // gA[nf x Q] = gout[nf x Cout] @ Wt^T[Cout x Q]
         rc = sgemm(stream, "f2f_gA_sgemm", nf, Q, Cout, gout + f0 * Cout, Cout, 1, Wt, 1, Cout, gA, Q, 0);
@@ -220,8 +223,9 @@ int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const f
             PB_LAUNCH("f2f_gin_from_gA", f2f_gin_all_kernel, persistent_blocks(nf * 3 * Cin, 256, 16), 256, 0, stream,
                       f0, nf, Nf, F, Cin, cum, bary, (const float*)gA, gin);
     }
-    PB_LAUNCH("f2f_untranspose_grad", f2f_untranspose_grad_kernel, persistent_blocks((int64_t)Q * Cout, 256, 8), 256, 0,
-              stream, F, Cin, Cout, (const float*)gWt, gfilter);
+    if (want_gfilter)
+        PB_LAUNCH("f2f_untranspose_grad", f2f_untranspose_grad_kernel, persistent_blocks((int64_t)Q * Cout, 256, 8), 256,
+                  0, stream, F, Cin, Cout, (const float*)gWt, gfilter);
     return PB200_OK;
 }
 
