@@ -165,30 +165,24 @@ __global__ void triangle_geometry_kernel(int64_t Nf, int64_t Nv, int vstride, co
 
 // ------------------------------------------------------------------------ row expansion
 // The samples of face f are rows cum[f-1] .. cum[f]-1 (cum = inclusive running count).
-__device__ __forceinline__ int64_t face_of_sample(const int32_t* __restrict__ cum, int64_t Nf, int64_t k) {
-    int64_t lo = 0, hi = Nf;            // first f with cum[f] > k
-    while (lo < hi) {
-        int64_t mid = (lo + hi) >> 1;
-        if (cum[mid] > k) hi = mid; else lo = mid + 1;
-    }
-    return lo;
-}
-
+// forward: one item per (face, channel group); the face's row is read once and written to
+// each of its samples (rows k0..k1-1, contiguous in the output)
 template <int VEC>
 __global__ void expand_rows_fwd_kernel(int64_t Nf, int64_t NiK, int CVn, const float* __restrict__ in,
                                        const int32_t* __restrict__ cum, float* __restrict__ out) {
-    int64_t total = NiK * CVn;
+    int64_t total = Nf * CVn;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
-        int64_t k = i / CVn;
-        int c = (int)(i - k * CVn);
-        int64_t f = face_of_sample(cum, Nf, k);
-        if (f >= Nf) continue;
+        int64_t f = i / CVn;
+        int c = (int)(i - f * CVn);
+        int k0 = f > 0 ? __ldg(cum + f - 1) : 0, k1 = __ldg(cum + f);
+        if (k1 > NiK) k1 = (int)NiK;
         if (VEC == 4) {
-            float4 v = __ldg(reinterpret_cast<const float4*>(in) + f * CVn + c);
-            __stcs(reinterpret_cast<float4*>(out) + i, v);
+            float4 v = __ldg(reinterpret_cast<const float4*>(in) + i);
+            for (int k = k0; k < k1; ++k) __stcs(reinterpret_cast<float4*>(out) + (int64_t)k * CVn + c, v);
         } else {
-            out[i] = in[f * CVn + c];
+            float v = in[i];
+            for (int k = k0; k < k1; ++k) out[(int64_t)k * CVn + c] = v;
         }
     }
 }
@@ -304,7 +298,7 @@ int pb200_expand_rows_forward(int64_t Nf, int64_t NiK, int C, const float* in, c
     PB_REQUIRE(in && cum && out, PB200_EINVAL, "expand_rows_forward: null pointer");
     bool vec = (C % 4 == 0) && aligned16(in) && aligned16(out);
     int CVn = vec ? C / 4 : C;
-    int grid = persistent_blocks(NiK * CVn, 256, 16);
+    int grid = persistent_blocks(Nf * CVn, 256, 16);
     if (vec) PB_LAUNCH("expand_rows_fwd", expand_rows_fwd_kernel<4>, grid, 256, 0, stream, Nf, NiK, CVn, in, cum, out);
     else     PB_LAUNCH("expand_rows_fwd", expand_rows_fwd_kernel<1>, grid, 256, 0, stream, Nf, NiK, CVn, in, cum, out);
     return PB200_OK;

@@ -6,9 +6,12 @@
 // D[co, (d,kk)] += g^T[co, f] * A^T[(d,kk), f].  A CTA owns one group of 16 input channels
 // (its F*16 <= 512 accumulator columns live in TMEM for the whole kernel) and one contiguous
 // chunk of faces; per stage of 16 faces
-//   * 8 producer warps build both operands in shared memory as K-major (face-contiguous)
-//     64-byte swizzled rows: the transposed gradOutput block (128 rows) and the A^T block
-//     (F*16 rows) -- thread = (face, 8 channels), a warp walks its share of the F bases;
+//   * 8 producer warps first copy the stage's raw rows (gradOutput rows, bary rows, the
+//     CTA's 16 input channels of every sample, sample ranges) from global memory with
+//     coalesced loads into a double-buffered raw area (one stage ahead of the math), then
+//     build both operands in shared memory as K-major (face-contiguous) 64-byte swizzled
+//     rows: the transposed gradOutput block (128 rows) and the A^T block (F*16 rows) --
+//     thread = (face, 8 channels), a warp walks its share of the F bases;
 //   * one thread issues tcgen05.mma (M = 128 output channels, N = F*16 in chunks of <= 256,
 //     K = 8 faces per instruction) and commits the stage back.
 // At the end the accumulator is drained once into partial[chunk] (final gradFilter layout);
@@ -34,6 +37,39 @@ constexpr int PWARPS = 8;
 constexpr int NTHREADS = (PWARPS + 1) * 32;   // + MMA warp
 constexpr int G_TILE_BYTES = UM * 64;
 constexpr int TREG = 4;
+// raw staging area of one stage (double-buffered)
+constexpr int RAW_SAMPLES = 64;               // samples of a stage that are staged (16 faces x 4)
+constexpr int RAW_G_PITCH = UM + 4;           // floats per gradOutput row (pitch = 4 mod 32: conflict-free 16-byte reads)
+constexpr int RAW_X_PITCH = 20;               // floats per sample row (16 channels + pad)
+constexpr int RAW_G_BYTES = KF * RAW_G_PITCH * 4;
+constexpr int RAW_X_BYTES = (RAW_SAMPLES + TREG) * RAW_X_PITCH * 4;   // + pad rows read (and masked) by short faces
+constexpr int RAW_B_BYTES = (RAW_SAMPLES + TREG) * 32 * 4;   // F <= 32
+constexpr int RAW_B_ITERS = RAW_SAMPLES * 32 / 256;       // 8 floats per thread at most
+constexpr int RAW_X_OFF = RAW_G_BYTES;
+constexpr int RAW_B_OFF = RAW_X_OFF + RAW_X_BYTES;
+constexpr int RAW_C_OFF = RAW_B_OFF + RAW_B_BYTES;
+constexpr int RAW_BYTES = (RAW_C_OFF + 128 + 127) / 128 * 128;
+
+// shared-window (32-bit address) accessors: one instruction each, immediate offsets fold in
+__device__ __forceinline__ float lds_f32(uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; }
+__device__ __forceinline__ int lds_i32(uint32_t a) { int v; asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+__device__ __forceinline__ float4 lds_f4(uint32_t a) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+// one operand element: tf32-rounded (1 split) or hi + lo (2 splits, lo block `lo_off` bytes further)
+template <int NSPLIT>
+__device__ __forceinline__ void put32(uint32_t a, uint32_t lo_off, float v) {
+    if (NSPLIT == 1) {
+        sts_f32(a, to_tf32_rna(v));
+    } else {
+        const float hv = tf32_hi(v);
+        sts_f32(a, hv);
+        sts_f32(a + lo_off, v - hv);
+    }
+}
 
 struct Params {
     int64_t Nf;
@@ -60,16 +96,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     const size_t at_bytes = (size_t)NR * 64;
     const size_t stage_bytes = (size_t)NSPLIT * (G_TILE_BYTES + at_bytes);   // [g hi][g lo?][A^T hi][A^T lo?]
     uint8_t* stages = smem;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)S * stage_bytes);
+    uint8_t* raw = smem + (size_t)S * stage_bytes;            // [2][RAW_BYTES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * RAW_BYTES);
     uint64_t* full = bars;                // [S] 8 producer warps
     uint64_t* empty = bars + S;           // [S] MMA done with the stage
     uint64_t* acc_done = bars + 2 * S;    // all MMAs of the CTA complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 1);
+    uint64_t* raw_ready = bars + 2 * S + 1;   // raw rows of a stage staged by all 8 warps
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(&full[s], PWARPS); mbar_init(&empty[s], 1); }
         mbar_init(acc_done, 1);
+        mbar_init(raw_ready, PWARPS);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -89,106 +128,226 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 
     if (warp < PWARPS) {
         // ==================================== producers ====================================
-        const int fl = lane >> 1, half = lane & 1;            // face of the stage, 8-channel half
+        const int half = lane >> 4, fl = lane & 15;           // 8-channel half, face of the stage
         const uint32_t fchunk = (uint32_t)(fl >> 2), fsub = (uint32_t)(fl & 3) * 4u;
+        constexpr int DMAX = 4;                               // bases per warp: ceil(32 / PWARPS)
+        // byte offsets, inside a 16-row group of a K-major 64B-swizzled block, of this thread's
+        // 8 rows (row = half*8 + jj) at face column fl.  The two halves of a warp must hit rows
+        // of different parity (distinct banks), so half 1 walks its rows rotated by one.
+        uint32_t row_off[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t jj = half ? (uint32_t)((j + 1) & 7) : (uint32_t)j;
+            const uint32_t row = (uint32_t)half * 8u + jj;
+            row_off[j] = row * 64u + ((fchunk ^ ((row >> 1) & 3u)) << 4) + fsub;
+        }
+        const int ptid = tid;
+        const uint32_t raw32 = smem_u32(raw), stages32 = smem_u32(stages);
+        // the pad rows behind the staged windows are read (their products are masked) but never
+        // written by raw_store: clear both buffers once so they hold finite values
+        for (int i = tid; i < 2 * RAW_BYTES / 4; i += PWARPS * 32) reinterpret_cast<float*>(raw)[i] = 0.f;
+        asm volatile("bar.sync 1, %0;" ::"n"(PWARPS * 32) : "memory");                                 // 0..255 over the producer warps
+        // ---- raw staging: what stage `st` needs, copied with coalesced loads
+        struct RawRegs { float4 g[2]; float4 x; float b[RAW_B_ITERS]; int cumv; int ks0, ns; };
+        auto raw_issue = [&](int64_t st) -> RawRegs {
+            RawRegs R;
+            R.g[0] = R.g[1] = zero4(); R.x = zero4(); R.cumv = 0; R.ks0 = 0; R.ns = 0;
+#pragma unroll
+            for (int i = 0; i < RAW_B_ITERS; ++i) R.b[i] = 0.f;
+            if (st >= nst) return R;
+            const int64_t f0 = (st0 + st) * KF;
+            const int64_t fe = f0 + KF < p.Nf ? f0 + KF : p.Nf;         // one past the stage's last face
+            const int ks0 = f0 > 0 ? __ldg(p.cum + f0 - 1) : 0;
+            const int ks1 = __ldg(p.cum + fe - 1);
+            int ns = ks1 - ks0;
+            if (ns > RAW_SAMPLES) ns = RAW_SAMPLES;
+            R.ks0 = ks0; R.ns = ns;
+            // gradOutput rows: 16 faces x Cout floats, contiguous in global memory
+            const int c4n = Cout >> 2;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int idx = ptid + i * 256;
+                const int fr = idx / 32, c4 = idx - fr * 32;             // up to 128 channels = 32 float4 per row
+                if (f0 + fr < fe && c4 < c4n)
+                    R.g[i] = ldg4(reinterpret_cast<const float4*>(p.gout + (f0 + fr) * Cout) + c4);
+            }
+            // this CTA's 16 input channels of every sample: thread = (sample, 16-byte quarter)
+            {
+                const int sr = ptid >> 2, qd = ptid & 3;
+                if (sr < ns) R.x = ldg4(reinterpret_cast<const float4*>(p.in + (int64_t)(ks0 + sr) * Cin + cgp * CG) + qd);
+            }
+            // bary rows of the stage's samples: one contiguous block of ns*F floats
+            {
+                const float* src = p.bary + (int64_t)ks0 * F;
+                const int nb = ns * F;
+#pragma unroll
+                for (int i = 0; i < RAW_B_ITERS; ++i) {
+                    const int idx = ptid + i * 256;
+                    if (idx < nb) R.b[i] = __ldg(src + idx);
+                }
+            }
+            if (ptid <= KF) {                                            // cum[f0-1 .. f0+15]
+                const int64_t fi = f0 - 1 + ptid;
+                R.cumv = fi < 0 ? 0 : (fi < p.Nf ? __ldg(p.cum + fi) : __ldg(p.cum + p.Nf - 1));
+            }
+            return R;
+        };
+        // Odd 8-channel groups of the gradOutput rows and of the sample rows are stored rotated
+        // left by one (slot j holds channel (j+1)&7 of the group): the half-1 lanes, which must
+        // walk their operand rows rotated, then read plain slots.
+        auto raw_store = [&](const RawRegs& R, int buf) {
+            uint8_t* rb = raw + (size_t)buf * RAW_BYTES;
+            float* g_raw = reinterpret_cast<float*>(rb);
+            float* x_raw = reinterpret_cast<float*>(rb + RAW_X_OFF);
+            float* b_raw = reinterpret_cast<float*>(rb + RAW_B_OFF);
+            int* c_raw = reinterpret_cast<int*>(rb + RAW_C_OFF);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int idx = ptid + i * 256;
+                const int fr = idx / 32, c4 = idx - fr * 32;
+                float* dst = g_raw + fr * RAW_G_PITCH + (c4 >> 1) * 8;
+                if (((c4 >> 1) & 1) == 0) {
+                    *reinterpret_cast<float4*>(dst + (c4 & 1) * 4) = R.g[i];
+                } else {
+                    const int e0 = (c4 & 1) * 4;                 // channels e0..e0+3 of the group
+                    dst[(e0 + 7) & 7] = R.g[i].x; dst[e0] = R.g[i].y; dst[e0 + 1] = R.g[i].z; dst[e0 + 2] = R.g[i].w;
+                }
+            }
+            {
+                const int sr = ptid >> 2, qd = ptid & 3;
+                float* dst = x_raw + sr * RAW_X_PITCH;
+                if (qd < 2) {
+                    *reinterpret_cast<float4*>(dst + qd * 4) = R.x;
+                } else {
+                    const int e0 = (qd & 1) * 4;
+                    float* d8 = dst + 8;
+                    d8[(e0 + 7) & 7] = R.x.x; d8[e0] = R.x.y; d8[e0 + 1] = R.x.z; d8[e0 + 2] = R.x.w;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < RAW_B_ITERS; ++i) b_raw[ptid + i * 256] = R.b[i];
+            if (ptid <= KF) c_raw[ptid] = R.cumv;
+            if (ptid == KF + 1) c_raw[KF + 1] = R.ks0;
+            if (ptid == KF + 2) c_raw[KF + 2] = R.ns;
+        };
+        auto raw_publish = [&]() {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(raw_ready);
+        };
+
         int si = 0;
         uint32_t sph = 0;
         bool alive = true;
+        {
+            RawRegs R0 = raw_issue(0);
+            raw_store(R0, 0);
+            raw_publish();
+        }
         for (int64_t st = 0; st < nst && alive; ++st) {
+            // loads of the next stage are in flight while this stage is computed
+            const RawRegs Rn = raw_issue(st + 1);
+            {
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(raw_ready, (uint32_t)(st & 1), abort_flag) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { alive = false; break; }
+            }
+            const uint32_t rb32 = raw32 + (uint32_t)(st & 1) * RAW_BYTES;
             const int64_t f = (st0 + st) * KF + fl;
             const bool valid = f < p.Nf;
-            int k0 = 0, k1 = 0;
-            if (valid) { k0 = f > 0 ? __ldg(p.cum + f - 1) : 0; k1 = __ldg(p.cum + f); }
-            const int T = k1 - k0;
+            const int k0 = valid ? lds_i32(rb32 + RAW_C_OFF + fl * 4) : 0;
+            const int T = valid ? lds_i32(rb32 + RAW_C_OFF + (fl + 1) * 4) - k0 : 0;
+            const int ks0 = lds_i32(rb32 + RAW_C_OFF + (KF + 1) * 4), ns = lds_i32(rb32 + RAW_C_OFF + (KF + 2) * 4);
+            const int kloc = valid ? k0 - ks0 : 0;             // lanes past the last face read row 0 (masked)
             const float invT = T > 0 ? 1.f / (float)T : 0.f;
-            // this thread's 8 input channels of up to TREG samples, pre-scaled by 1/T
-            float x[TREG][8];
-#pragma unroll
-            for (int t = 0; t < TREG; ++t) {
-                if (t < T) {
-                    const float4* src = reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8);
-                    float4 u = ldg4(src), w = ldg4(src + 1);
-                    x[t][0] = u.x * invT; x[t][1] = u.y * invT; x[t][2] = u.z * invT; x[t][3] = u.w * invT;
-                    x[t][4] = w.x * invT; x[t][5] = w.y * invT; x[t][6] = w.z * invT; x[t][7] = w.w * invT;
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) x[t][j] = 0.f;
-                }
-            }
-            // transposed gradOutput block: warp w copies output channels [16w, 16w+16)
-            float4 gv[2];
-            {
-                const int co0 = warp * 16 + half * 8;
-#pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    int co = co0 + i * 4;
-                    gv[i] = (valid && co < Cout) ? ldg4(reinterpret_cast<const float4*>(p.gout + f * Cout + co)) : zero4();
-                }
-            }
-            // wait for the stage to be free
+            // lean path: every face of the stage has at most TREG samples, all of them staged
+            const bool slow = __any_sync(0xffffffffu, (T > TREG) || (kloc + T > ns));
+            // wait for the operand stage to be free
             if (!mbar_try_wait(&empty[si], sph ^ 1u)) {
                 int ok = 1;
                 if (lane == 0) ok = mbar_wait(&empty[si], sph ^ 1u, abort_flag) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { alive = false; break; }
             }
-            uint8_t* sbase = stages + (size_t)si * stage_bytes;
-            uint8_t* g_hi = sbase;
-            uint8_t* at_hi = sbase + (size_t)NSPLIT * G_TILE_BYTES;
-            // element (row, face fl) of a K-major 64B-swizzled block
-            auto elem = [&](uint8_t* base, int row) -> float* {
-                return reinterpret_cast<float*>(base + (size_t)row * 64 + ((fchunk ^ (((uint32_t)row >> 1) & 3u)) << 4) + fsub);
-            };
-            auto put = [&](uint8_t* hi_base, size_t lo_off, int row, float v) {
-                if (NSPLIT == 1) {
-                    *elem(hi_base, row) = to_tf32_rna(v);
-                } else {
-                    float hv = tf32_hi(v);
-                    *elem(hi_base, row) = hv;
-                    *elem(hi_base + lo_off, row) = v - hv;
-                }
-            };
-            {
-                const int co0 = warp * 16 + half * 8;
-                const float g8[8] = {gv[0].x, gv[0].y, gv[0].z, gv[0].w, gv[1].x, gv[1].y, gv[1].z, gv[1].w};
+            // shared-window addresses of this thread's 8 rows inside its warp's 16-row group;
+            // the gradOutput block starts at +0, the A^T block at +NSPLIT*8 KB, basis d = warp + 8 i
+            // sits i*8 KB further on
+            const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes + (uint32_t)warp * 1024u;
+            uint32_t ra[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    // the two halves of a warp must hit rows of different parity (distinct banks):
-                    // half 1 walks its 8 rows rotated by one
-                    const int jr = (j + 1) & 7;
-                    put(g_hi, G_TILE_BYTES, co0 + (half ? jr : j), half ? g8[jr] : g8[j]);
-                }
-            }
-            for (int d = warp; d < F; d += PWARPS) {
-                float a[8];
+            for (int j = 0; j < 8; ++j) ra[j] = sb32 + row_off[j];
+            if (!slow) {
+                float x[TREG][8];
+                {
+                    const uint32_t xa = rb32 + RAW_X_OFF + (uint32_t)kloc * (RAW_X_PITCH * 4) + (uint32_t)half * 32u;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) a[j] = 0.f;
-#pragma unroll
-                for (int t = 0; t < TREG; ++t) {
-                    if (t < T) {
-                        const float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d);
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) a[j] = fmaf(b, x[t][j], a[j]);
+                    for (int t = 0; t < TREG; ++t) {
+                        const float4 u = lds_f4(xa + t * (RAW_X_PITCH * 4)), w = lds_f4(xa + t * (RAW_X_PITCH * 4) + 16);
+                        x[t][0] = u.x; x[t][1] = u.y; x[t][2] = u.z; x[t][3] = u.w;
+                        x[t][4] = w.x; x[t][5] = w.y; x[t][6] = w.z; x[t][7] = w.w;
                     }
                 }
-                for (int t = TREG; t < T; ++t) {               // faces with many samples
-                    const float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
-                    const float4* src = reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8);
-                    float4 u = ldg4(src), w = ldg4(src + 1);
-                    a[0] = fmaf(b, u.x, a[0]); a[1] = fmaf(b, u.y, a[1]); a[2] = fmaf(b, u.z, a[2]); a[3] = fmaf(b, u.w, a[3]);
-                    a[4] = fmaf(b, w.x, a[4]); a[5] = fmaf(b, w.y, a[5]); a[6] = fmaf(b, w.z, a[6]); a[7] = fmaf(b, w.w, a[7]);
+                {
+                    const uint32_t ga = rb32 + (uint32_t)fl * (RAW_G_PITCH * 4) + (uint32_t)(warp * 16 + half * 8) * 4u;
+                    const float4 u = lds_f4(ga), w = lds_f4(ga + 16);
+                    const float g8[8] = {u.x, u.y, u.z, u.w, w.x, w.y, w.z, w.w};
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) put32<NSPLIT>(ra[j], G_TILE_BYTES, g8[j]);
                 }
-                const int row0 = d * CG + half * 8;
+                const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(kloc * F) * 4u;
+#pragma unroll
+                for (int i = 0; i < DMAX; ++i) {
+                    const int d = warp + i * PWARPS;
+                    if (d < F) {
+                        float a[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) a[j] = 0.f;
+#pragma unroll
+                        for (int t = 0; t < TREG; ++t) {
+                            float b = lds_f32(ba + (uint32_t)(t * F + d) * 4u);
+                            b = t < T ? b * invT : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) a[j] = fmaf(b, x[t][j], a[j]);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            put32<NSPLIT>(ra[j] + (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)i * (PWARPS * 1024u),
+                                          (uint32_t)at_bytes, a[j]);
+                    }
+                }
+            } else {
+                // generic path, straight from global memory (position j of half 1 is channel (j+1)&7)
+                float g8[8];
+                const int co0 = warp * 16 + half * 8;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const int jr = (j + 1) & 7;
-                    put(at_hi, at_bytes, row0 + (half ? jr : j), half ? a[jr] : a[j]);
+                    const int co = co0 + (half ? ((j + 1) & 7) : j);
+                    g8[j] = (valid && co < Cout) ? __ldg(p.gout + f * Cout + co) : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) put32<NSPLIT>(ra[j], G_TILE_BYTES, g8[j]);
+                for (int d = warp; d < F; d += PWARPS) {
+                    float a[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) a[j] = 0.f;
+                    for (int t = 0; t < T; ++t) {
+                        const float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
+                        const float* xr = p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) a[j] = fmaf(b, __ldg(xr + (half ? ((j + 1) & 7) : j)), a[j]);
+                    }
+                    const uint32_t off = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(d - warp) * 1024u;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) put32<NSPLIT>(ra[j] + off, (uint32_t)at_bytes, a[j]);
                 }
             }
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&full[si]);
             if (++si == S) { si = 0; sph ^= 1u; }
+            // every warp has passed raw_ready(st), so nobody reads the other raw buffer any more
+            raw_store(Rn, (int)((st + 1) & 1));
+            raw_publish();
         }
         // ==================================== drain ====================================
         if (alive) {
@@ -275,7 +434,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 struct Plan { int nsplit, ncg, nchunks, nstages; int64_t stages_per_chunk; size_t smem, partial_bytes; };
 
 bool supported(int Cin, int Cout, int F) {
-    return Cin % CG == 0 && Cout % 4 == 0 && Cout >= 4 && Cout <= UM && F >= 1 && F * CG <= 512;
+    return Cin % CG == 0 && Cout % 4 == 0 && Cout >= 4 && Cout <= UM && F >= 1 && F <= 32;   // F*16 <= 512 columns
 }
 
 Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
@@ -290,9 +449,10 @@ Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     pl.nchunks = (int)ceil_div(total_stages, pl.stages_per_chunk);
     size_t stage = (size_t)pl.nsplit * (G_TILE_BYTES + (size_t)F * CG * 64);
     int S = 4;
-    while (S > 2 && (size_t)S * stage + 1024 + 256 > 224 * 1024) --S;
+    const size_t extra = 2 * (size_t)RAW_BYTES + 1024 + 256;
+    while (S > 2 && (size_t)S * stage + extra > 224 * 1024) --S;
     pl.nstages = S;
-    pl.smem = (size_t)S * stage + 1024 + 256;
+    pl.smem = (size_t)S * stage + extra;
     pl.partial_bytes = (size_t)pl.nchunks * Cout * Cin * F * sizeof(float);
     return pl;
 }

@@ -41,10 +41,13 @@ constexpr long long WAIT_CLOCK_BUDGET = 2000000000LL;
 
 // Bounded wait on one phase of an mbarrier.  Returns false (and raises *abort_flag) on
 // time-out, or as soon as another thread of the block has raised the flag.
+// A failed probe backs off with a short sleep so that a waiting role (the MMA issuer, the
+// bulk-copy thread) does not take issue slots from the warps it is waiting for.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
+        __nanosleep(i < 8 ? 20 : 100);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 63u) {
             if (*abort_flag) return false;
