@@ -162,7 +162,9 @@ def kernel_models(d):
         "v2f_bwd": dict(bytes=4 * Ci * Nf + 8 * Ci * Nv + 12 * Nf + 4 * Nv),
         "expand_rows_fwd": dict(bytes=4 * Ci * Nf + 4 * Nf + 4 * Ci * NiK),
         "expand_rows_bwd": dict(bytes=4 * Ci * Nf + 4 * Nf + 4 * Ci * NiK),
-        "f2v_fwd": dict(bytes=4 * Co * Nf + 4 * K * Nf + 12 * Nf + 8 * Nv + 4 * Co * Nv),
+        # facet2vertex forward = per-face products (wx) + CSR gather
+        "f2v_fwd_face": dict(bytes=8 * Co * Nf + 4 * K * Nf),
+        "f2v_fwd_gather": dict(bytes=4 * Co * Nf + 12 * Nf + 8 * Nv + 4 * Co * Nv),
         "f2v_bwd": dict(bytes=4 * Co * Nv + 8 * Co * Nf + 4 * K * Nf + 12 * Nf + 4 * Nv),
         # fp32 FFMA path of facet2facet (chunked through workspace)
         "f2f_build_A": dict(bytes=4 * Ci * NiK + 4 * K * NiK + 4 * Nf + 4 * Q * Nf),

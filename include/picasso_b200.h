@@ -126,10 +126,13 @@ int pb200_vertex2facet_backward_static(int64_t Nf, int64_t Nv, int C, int r, con
  * Replaces facet2vertexConv3dLauncher (mesh_conv3d_gpu.cu:299-329,428-433; binding
  * mesh_conv3d.cpp:33-74).  input (Nf,C), filter (K,C,r), coeff (Nf,K), nfCount (NvOut),
  * output (NvOut,C*r); rowptr/entries: CSR built with the same face/vtMap.  The kernels
- * never read vtMap or face here (the CSR carries them). */
+ * never read vtMap or face here (the CSR carries them).  Workspace: one (Nf, C) fp32 array
+ * for the per-face products w*input (0 bytes for shapes that take the scalar path). */
+size_t pb200_facet2vertex_forward_workspace_bytes(int64_t Nf, int C, int r, int K);
 int pb200_facet2vertex_forward(int64_t Nf, int64_t NvOut, int C, int r, int K, const float* input,
                                const float* filter, const float* coeff, const int32_t* nfCount,
-                               const int32_t* rowptr, const int32_t* entries, float* output, void* stream);
+                               const int32_t* rowptr, const int32_t* entries, float* output,
+                               void* workspace, size_t workspace_bytes, void* stream);
 
 /* gt[f,co] = sum_{j<3, vo_j>=0} gradOutput[vo_j,co] / nfCount[vo_j];
  * gradInput[f,c] = sum_m gt[f,co]*w[f,co];  gradFilter[k,c,m] = sum_f coeff[f,k]*input[f,c]*gt[f,co]

@@ -46,7 +46,8 @@ SIGNATURES = {
     "pb200_vertex2facet_backward": (i32, [i64, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_vertex2facet_backward_static_max_bytes": (sz, []),
     "pb200_vertex2facet_backward_static": (i32, [i64, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
-    "pb200_facet2vertex_forward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp]),
+    "pb200_facet2vertex_forward_workspace_bytes": (sz, [i64, i32, i32, i32]),
+    "pb200_facet2vertex_forward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_facet2vertex_backward_workspace_bytes": (sz, [i64, i32, i32, i32]),
     "pb200_facet2vertex_backward": (i32, [i64, i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                           vp, sz, vp]),

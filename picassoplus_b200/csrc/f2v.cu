@@ -6,55 +6,83 @@
 namespace pb {
 
 // -------------------------------------------------------------------- forward, vectorised
-// r == 1, C % 4 == 0.  Team per output vertex, thread per float4 of channels.  KT > 0: the
-// filter column of the thread's channels lives in registers (K == KT); KT == 0: it is
-// read from shared memory (any K).
-template <int TL, int KT>
+// r == 1, C % 4 == 0, K <= 64.  Two kernels:
+//   f2v_fwd_face    item = (face, float4 channel group): wx[f] = (sum_k coeff[f,k]*filter[k]) * input[f],
+//                   once per face (a vertex-centred pull would evaluate the K-term sum three
+//                   times per face), filter and the tile's coeff rows in shared memory;
+//   f2v_fwd_gather  team per output vertex: sum of the wx rows of its CSR entries in ascending
+//                   order, times 1/nfCount.  No atomics: deterministic.
+constexpr int F2VF_TF = 64;
+
 __global__ void __launch_bounds__(256)
-f2v_fwd_vec_kernel(int64_t NvOut, int CV, int K, const int32_t* __restrict__ rowptr,
-                   const int32_t* __restrict__ entries, const int32_t* __restrict__ nfCount,
-                   const float* __restrict__ coeff, const float4* __restrict__ in,
-                   const float4* __restrict__ filt, float4* __restrict__ out) {
-    extern __shared__ float4 sfilt[];          // [K][32] when KT == 0
+f2v_fwd_face_kernel(int64_t Nf, int CV, int K, const float* __restrict__ coeff, const float4* __restrict__ in,
+                    const float4* __restrict__ filt, float4* __restrict__ wx) {
+    extern __shared__ float4 smem[];
+    const int KP = (K + 3) / 4 * 4 + 4;
+    float4* sfilt = smem;                                          // [K][32]
+    float* scoef = reinterpret_cast<float*>(smem + K * 32);       // [TF][KP]
+    const int cg0 = blockIdx.y * 32;
+    const int CVc = CV - cg0 < 32 ? CV - cg0 : 32;
+    for (int i = threadIdx.x; i < K * 32; i += blockDim.x) {
+        int k = i >> 5, l = i & 31;
+        sfilt[i] = l < CVc ? filt[k * CV + cg0 + l] : zero4();
+    }
+    const int64_t ntiles = (Nf + F2VF_TF - 1) / F2VF_TF;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t f0 = tile * F2VF_TF;
+        const int nf_tile = Nf - f0 < F2VF_TF ? (int)(Nf - f0) : F2VF_TF;
+        __syncthreads();
+        for (int i = threadIdx.x; i < nf_tile * K; i += blockDim.x) {
+            int fl = i / K;
+            scoef[fl * KP + (i - fl * K)] = __ldg(coeff + f0 * K + i);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < nf_tile * CVc; i += blockDim.x) {
+            const int fl = i / CVc, c = i - fl * CVc;
+            const int64_t f = f0 + fl;
+            const float4 x = ldg4(in + f * CV + cg0 + c);
+            const float* cf = scoef + fl * KP;
+            float4 w = zero4();
+            int k = 0;
+            for (; k + 4 <= K; k += 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(cf + k);
+                fma4s(w, c4.x, sfilt[k * 32 + c]);
+                fma4s(w, c4.y, sfilt[(k + 1) * 32 + c]);
+                fma4s(w, c4.z, sfilt[(k + 2) * 32 + c]);
+                fma4s(w, c4.w, sfilt[(k + 3) * 32 + c]);
+            }
+            for (; k < K; ++k) fma4s(w, cf[k], sfilt[k * 32 + c]);
+            wx[f * CV + cg0 + c] = mul4(w, x);
+        }
+    }
+}
+
+template <int TL>
+__global__ void __launch_bounds__(256)
+f2v_fwd_gather_kernel(int64_t NvOut, int CV, const int32_t* __restrict__ rowptr, const int32_t* __restrict__ entries,
+                      const int32_t* __restrict__ nfCount, const float4* __restrict__ wx, float4* __restrict__ out) {
     const int lane = threadIdx.x % TL;
     const int team = threadIdx.x / TL;
     const int teams = blockDim.x / TL;
     const int cg = blockIdx.y * 32 + lane;
     const bool active = cg < CV;
-    float4 rf[KT > 0 ? KT : 1];
-    if (KT > 0) {
-#pragma unroll
-        for (int k = 0; k < KT; ++k) rf[k] = active ? filt[k * CV + cg] : zero4();
-    } else {
-        for (int i = threadIdx.x; i < K * 32; i += blockDim.x) {
-            int k = i >> 5, l = i & 31;
-            int g = blockIdx.y * 32 + l;
-            sfilt[i] = g < CV ? filt[k * CV + g] : zero4();
-        }
-        __syncthreads();
-    }
-    if (!active) return;
+    // inactive lanes stay in the loop: the team shares its CSR entries through shuffles
+    const unsigned tmask = TL == 32 ? 0xffffffffu : (((1u << TL) - 1u) << ((threadIdx.x & 31) / TL * TL));
     for (int64_t v = (int64_t)blockIdx.x * teams + team; v < NvOut; v += (int64_t)gridDim.x * teams) {
-        int beg = __ldg(rowptr + v), end = __ldg(rowptr + v + 1);
+        const int beg = __ldg(rowptr + v), end = __ldg(rowptr + v + 1);
         float4 acc = zero4();
-        for (int e = beg; e < end; ++e) {
-            int64_t f = __ldg(entries + e) >> 2;
-            float4 x = ldg4(in + f * CV + cg);
-            const float* cf = coeff + f * K;
-            float4 w = zero4();
-            if (KT > 0) {
-#pragma unroll
-                for (int k = 0; k < KT; ++k) fma4s(w, __ldg(cf + k), rf[k]);
-            } else {
-                for (int k = 0; k < K; ++k) fma4s(w, __ldg(cf + k), sfilt[k * 32 + lane]);
+        for (int base = beg; base < end; base += TL) {
+            const int mine = base + lane < end ? __ldg(entries + base + lane) : 0;
+            const int cnt = end - base < TL ? end - base : TL;
+            for (int i = 0; i < cnt; ++i) {
+                const int64_t f = __shfl_sync(tmask, mine, i, TL) >> 2;
+                if (active) add4(acc, ldg4(wx + f * CV + cg));
             }
-            fma4(acc, w, x);
         }
-        if (end > beg) {
-            float nf = (float)__ldg(nfCount + v);
-            acc = make_float4(acc.x / nf, acc.y / nf, acc.z / nf, acc.w / nf);
+        if (active) {
+            if (end > beg) acc = scale4(acc, 1.f / (float)__ldg(nfCount + v));
+            __stcs(out + v * CV + cg, acc);
         }
-        __stcs(out + v * CV + cg, acc);
     }
 }
 
@@ -83,70 +111,100 @@ __global__ void f2v_fwd_generic_kernel(int64_t NvOut, int C, int r, int K, const
 }
 
 // ------------------------------------------------------------------- backward, vectorised
-// Team per face f.  gt = sum over the three corners of gradOutput[vo]/nfCount[vo];
-// w = sum_k coeff[f,k]*filter[k];  gradInput[f] = gt*w;  gradFilter[k] += coeff[f,k]*x*gt.
-// The filter is read from shared memory, the K filter-gradient accumulators are registers.
-template <int TL, int KT>
+// r == 1, C % 4 == 0, any K <= 64.  A block walks tiles of 32 faces; per tile
+//   phase 1  item = (face, float4 channel group): gt = sum over the three corners of
+//            gradOutput[vo] * (1/nfCount[vo]);  w = sum_k coeff[f,k]*filter[k];
+//            gradInput[f] = gt*w;  t[f] = input[f]*gt is parked in shared memory;
+//   phase 2  item = (k, channel group), up to NACC per thread, kept in registers for the whole
+//            kernel: gradFilter[k] += coeff[f,k] * t[f] over the tile's faces in face order.
+// Phase 1 needs few registers (full occupancy hides the gather latency), phase 2 has no
+// global traffic.  Per-block accumulators go to partial[block][K][C]; a second kernel adds
+// the blocks in order, so the result is deterministic.
+constexpr int F2VB_TF = 32;
+
+template <int NACC>
 __global__ void __launch_bounds__(256)
-f2v_bwd_vec_kernel(int64_t Nf, int CV, const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap,
-                   const int32_t* __restrict__ nfCount, const float* __restrict__ coeff,
-                   const float4* __restrict__ in, const float4* __restrict__ filt, const float4* __restrict__ gout,
-                   float4* __restrict__ gin, float4* __restrict__ partial) {
-    extern __shared__ float4 smem[];           // [KT][32] filter, then [256] reduction slots
-    float4* sfilt = smem;
-    float4* red = smem + KT * 32;
-    const int lane = threadIdx.x % TL;
-    const int team = threadIdx.x / TL;
-    const int teams = blockDim.x / TL;
-    const int cg = blockIdx.y * 32 + lane;
-    const bool active = cg < CV;
-    for (int i = threadIdx.x; i < KT * 32; i += blockDim.x) {
+f2v_bwd_tile_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap,
+                    const int32_t* __restrict__ nfCount, const float* __restrict__ coeff,
+                    const float4* __restrict__ in, const float4* __restrict__ filt, const float4* __restrict__ gout,
+                    float4* __restrict__ gin, float4* __restrict__ partial) {
+    extern __shared__ float4 smem[];
+    const int KP = (K + 3) / 4 * 4 + 4;                       // coeff row pitch (floats): 16-byte rows, spread banks
+    float4* sfilt = smem;                                      // [K][32]
+    float4* st = smem + K * 32;                                // [TF][32]   t = input * gt
+    float* scoef = reinterpret_cast<float*>(st + F2VB_TF * 32);    // [TF][KP]
+    const int cg0 = blockIdx.y * 32;
+    const int CVc = CV - cg0 < 32 ? CV - cg0 : 32;             // channel groups of this chunk
+    for (int i = threadIdx.x; i < K * 32; i += blockDim.x) {
         int k = i >> 5, l = i & 31;
-        int g = blockIdx.y * 32 + l;
-        sfilt[i] = g < CV ? filt[k * CV + g] : zero4();
+        sfilt[i] = l < CVc ? filt[k * CV + cg0 + l] : zero4();
     }
-    __syncthreads();
-    float4 gf[KT];
+    // this thread's accumulator items (k, c): j = tid + 256 n
+    float4 acc[NACC];
+    int ak[NACC], ac[NACC];
 #pragma unroll
-    for (int k = 0; k < KT; ++k) gf[k] = zero4();
-    if (active) {
-        for (int64_t f = (int64_t)blockIdx.x * teams + team; f < Nf; f += (int64_t)gridDim.x * teams) {
+    for (int n = 0; n < NACC; ++n) {
+        int j = threadIdx.x + 256 * n;
+        ak[n] = j / CVc; ac[n] = j - ak[n] * CVc;
+        if (ak[n] >= K) { ak[n] = -1; ac[n] = 0; }
+        acc[n] = zero4();
+    }
+    const int64_t ntiles = (Nf + F2VB_TF - 1) / F2VB_TF;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t f0 = tile * F2VB_TF;
+        const int nf_tile = Nf - f0 < F2VB_TF ? (int)(Nf - f0) : F2VB_TF;
+        __syncthreads();                                       // previous tile fully consumed
+        for (int i = threadIdx.x; i < nf_tile * K; i += blockDim.x) {
+            int fl = i / K;
+            scoef[fl * KP + (i - fl * K)] = __ldg(coeff + f0 * K + i);
+        }
+        __syncthreads();
+        // ---- phase 1
+        for (int i = threadIdx.x; i < nf_tile * CVc; i += blockDim.x) {
+            const int fl = i / CVc, c = i - fl * CVc;
+            const int64_t f = f0 + fl;
+            const int cg = cg0 + c;
             float4 gt = zero4();
 #pragma unroll
             for (int j = 0; j < 3; ++j) {
                 int vi = __ldg(face + 3 * f + j);
                 int vo = vtMap ? __ldg(vtMap + vi) : vi;
                 if (vo >= 0) {
-                    float nf = (float)__ldg(nfCount + vo);
-                    float4 g = ldg4(gout + (int64_t)vo * CV + cg);
-                    gt.x += g.x / nf; gt.y += g.y / nf; gt.z += g.z / nf; gt.w += g.w / nf;
+                    float rn = __frcp_rn((float)__ldg(nfCount + vo));
+                    fma4s(gt, rn, ldg4(gout + (int64_t)vo * CV + cg));
                 }
             }
-            float4 x = ldg4(in + f * CV + cg);
-            float4 t = mul4(x, gt);
-            const float* cf = coeff + f * KT;
+            const float4 x = ldg4(in + f * CV + cg);
+            const float* cf = scoef + fl * KP;
             float4 w = zero4();
-#pragma unroll
-            for (int k = 0; k < KT; ++k) {
-                float ck = __ldg(cf + k);
-                fma4s(w, ck, sfilt[k * 32 + lane]);
-                fma4s(gf[k], ck, t);
+            int k = 0;
+            for (; k + 4 <= K; k += 4) {
+                const float4 c4 = *reinterpret_cast<const float4*>(cf + k);
+                fma4s(w, c4.x, sfilt[k * 32 + c]);
+                fma4s(w, c4.y, sfilt[(k + 1) * 32 + c]);
+                fma4s(w, c4.z, sfilt[(k + 2) * 32 + c]);
+                fma4s(w, c4.w, sfilt[(k + 3) * 32 + c]);
             }
+            for (; k < K; ++k) fma4s(w, cf[k], sfilt[k * 32 + c]);
             __stcs(gin + f * CV + cg, mul4(gt, w));
+            st[fl * 32 + c] = mul4(x, gt);
         }
-    }
-    // block reduction in team order, one k at a time
+        __syncthreads();
+        // ---- phase 2
 #pragma unroll
-    for (int k = 0; k < KT; ++k) {
-        red[threadIdx.x] = gf[k];
-        __syncthreads();
-        if (team == 0 && active) {
-            float4 s = zero4();
-            for (int t = 0; t < teams; ++t) add4(s, red[t * TL + lane]);
-            partial[((int64_t)blockIdx.x * KT + k) * CV + cg] = s;
+        for (int n = 0; n < NACC; ++n) {
+            if (ak[n] >= 0) {
+                const float* cf = scoef + ak[n];
+                const float4* tp = st + ac[n];
+                float4 a = acc[n];
+                for (int fl = 0; fl < nf_tile; ++fl) fma4s(a, cf[fl * KP], tp[fl * 32]);
+                acc[n] = a;
+            }
         }
-        __syncthreads();
     }
+#pragma unroll
+    for (int n = 0; n < NACC; ++n)
+        if (ak[n] >= 0) partial[((int64_t)blockIdx.x * K + ak[n]) * CV + cg0 + ac[n]] = acc[n];
 }
 
 // ---------------------------------------------------------------------- backward, generic
@@ -206,7 +264,7 @@ __global__ void f2v_bwd_filter_generic_kernel(int64_t Nf, int C, int r, int K, i
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static bool vec_ok(int C, int r) { return r == 1 && C % 4 == 0; }
-static bool kt_ok(int K) { return K == 4 || K == 9 || K == 16 || K == 25 || K == 36; }
+static bool kt_ok(int K) { return K >= 1 && K <= 64; }
 
 struct F2VBwdPlan { bool vec; int grid_x; int64_t faces_per_chunk; };
 static F2VBwdPlan f2v_bwd_plan(int64_t Nf, int C, int r, int K) {
@@ -214,8 +272,7 @@ static F2VBwdPlan f2v_bwd_plan(int64_t Nf, int C, int r, int K) {
     p.vec = vec_ok(C, r) && kt_ok(K);
     int64_t n = Nf > 0 ? Nf : 1;
     if (p.vec) {
-        TeamGeom g = team_geom(C / 4);
-        p.grid_x = persistent_blocks(n, g.teams, 4);
+        p.grid_x = persistent_blocks(n, F2VB_TF, 4);
         p.faces_per_chunk = 0;
     } else {
         int64_t chunks = ceil_div(n, 64);
@@ -227,47 +284,48 @@ static F2VBwdPlan f2v_bwd_plan(int64_t Nf, int C, int r, int K) {
     return p;
 }
 
-#define PB_DISPATCH_KT(Kv, ...)                                      \
-    switch (Kv) {                                                    \
-        case 4:  { constexpr int KT = 4;  __VA_ARGS__; } break;      \
-        case 9:  { constexpr int KT = 9;  __VA_ARGS__; } break;      \
-        case 16: { constexpr int KT = 16; __VA_ARGS__; } break;      \
-        case 25: { constexpr int KT = 25; __VA_ARGS__; } break;      \
-        default: { constexpr int KT = 36; __VA_ARGS__; } break;      \
-    }
-
 }  // namespace pb
 
 using namespace pb;
 
 extern "C" {
 
+size_t pb200_facet2vertex_forward_workspace_bytes(int64_t Nf, int C, int r, int K) {
+    if (Nf < 0 || C <= 0 || r <= 0 || K <= 0) return 0;
+    if (vec_ok(C, r) && kt_ok(K)) return align_up(sizeof(float) * (size_t)(Nf > 0 ? Nf : 1) * C, 256);
+    return 0;
+}
+
 int pb200_facet2vertex_forward(int64_t Nf, int64_t NvOut, int C, int r, int K, const float* input,
                                const float* filter, const float* coeff, const int32_t* nfCount,
-                               const int32_t* rowptr, const int32_t* entries, float* output, void* stream_) {
+                               const int32_t* rowptr, const int32_t* entries, float* output,
+                               void* workspace, size_t workspace_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     PB_REQUIRE(Nf >= 0 && NvOut >= 0 && C > 0 && r > 0 && K > 0, PB200_EINVAL, "facet2vertex_forward: bad sizes");
     if (NvOut == 0) return PB200_OK;
     PB_REQUIRE(output && rowptr && nfCount, PB200_EINVAL, "facet2vertex_forward: null pointer");
     PB_REQUIRE(Nf == 0 || (input && filter && coeff && entries), PB200_EINVAL, "facet2vertex_forward: null pointer");
-    if (vec_ok(C, r) && aligned16(input) && aligned16(filter) && aligned16(output)) {
+    const bool vec = vec_ok(C, r) && kt_ok(K) && aligned16(input) && aligned16(filter) && aligned16(output) &&
+                     workspace && aligned16(workspace) &&
+                     workspace_bytes >= pb200_facet2vertex_forward_workspace_bytes(Nf, C, r, K);
+    if (vec_ok(C, r) && kt_ok(K) && aligned16(input) && aligned16(filter) && aligned16(output))
+        PB_REQUIRE(vec, PB200_EWORKSPACE, "facet2vertex_forward: workspace missing, misaligned or too small");
+    if (vec) {
         int CV = C / 4;
+        float4* wx = (float4*)workspace;
+        if (Nf > 0) {
+            const int KP = (K + 3) / 4 * 4 + 4;
+            size_t smem = sizeof(float4) * 32 * (size_t)K + sizeof(float) * F2VF_TF * KP;
+            dim3 gridf(persistent_blocks(Nf, F2VF_TF, 6), (unsigned)ceil_div(CV, 32));
+            if (smem > 48 * 1024)
+                PB_CUDA(cudaFuncSetAttribute(f2v_fwd_face_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            PB_LAUNCH("f2v_fwd_face", f2v_fwd_face_kernel, gridf, 256, smem, stream, Nf, CV, K, coeff,
+                      (const float4*)input, (const float4*)filter, wx);
+        }
         TeamGeom g = team_geom(CV);
         dim3 grid(persistent_blocks(NvOut, g.teams, 8), g.chunks);
-        const float4 *in4 = (const float4*)input, *f4 = (const float4*)filter;
-        float4* o4 = (float4*)output;
-        if (K == 16) {
-            PB_DISPATCH_TL(g.TL, PB_LAUNCH("f2v_fwd", (f2v_fwd_vec_kernel<TL, 16>), grid, 256, 0, stream, NvOut, CV, K,
-                                           rowptr, entries, nfCount, coeff, in4, f4, o4));
-        } else if (K == 25) {
-            PB_DISPATCH_TL(g.TL, PB_LAUNCH("f2v_fwd", (f2v_fwd_vec_kernel<TL, 25>), grid, 256, 0, stream, NvOut, CV, K,
-                                           rowptr, entries, nfCount, coeff, in4, f4, o4));
-        } else {
-            size_t smem = sizeof(float4) * 32 * (size_t)K;
-            PB_REQUIRE(smem <= 48 * 1024, PB200_EINVAL, "facet2vertex_forward: K too large (%d)", K);
-            PB_DISPATCH_TL(g.TL, PB_LAUNCH("f2v_fwd", (f2v_fwd_vec_kernel<TL, 0>), grid, 256, smem, stream, NvOut, CV,
-                                           K, rowptr, entries, nfCount, coeff, in4, f4, o4));
-        }
+        PB_DISPATCH_TL(g.TL, PB_LAUNCH("f2v_fwd_gather", f2v_fwd_gather_kernel<TL>, grid, 256, 0, stream, NvOut, CV,
+                                       rowptr, entries, nfCount, (const float4*)wx, (float4*)output));
     } else {
         int grid = persistent_blocks(NvOut * C * r, 256, 16);
         PB_LAUNCH("f2v_fwd_generic", f2v_fwd_generic_kernel, grid, 256, 0, stream, NvOut, C, r, K, rowptr, entries,
@@ -305,14 +363,23 @@ int pb200_facet2vertex_backward(int64_t Nf, int64_t NvIn, int64_t NvOut, int C, 
     bool vec = p.vec && aligned16(gradOutput) && aligned16(input) && aligned16(filter) && aligned16(gradInput);
     if (vec) {
         int CV = C / 4;
-        TeamGeom g = team_geom(CV);
-        dim3 grid(p.grid_x, g.chunks);
-        size_t smem = sizeof(float4) * (32 * (size_t)K + 256);
-        PB_DISPATCH_KT(K, PB_DISPATCH_TL(g.TL, PB_LAUNCH("f2v_bwd", (f2v_bwd_vec_kernel<TL, KT>), grid, 256, smem,
-                                                         stream, Nf, CV, face, vtMap, nfCount, coeff,
-                                                         (const float4*)input, (const float4*)filter,
-                                                         (const float4*)gradOutput, (float4*)gradInput,
-                                                         (float4*)partial)));
+        dim3 grid(p.grid_x, (unsigned)ceil_div(CV, 32));
+        const int KP = (K + 3) / 4 * 4 + 4;
+        size_t smem = sizeof(float4) * (32 * (size_t)K + F2VB_TF * 32) + sizeof(float) * F2VB_TF * KP;
+        const int cvc = CV < 32 ? CV : 32;
+        const int nacc = (int)ceil_div((int64_t)K * cvc, 256);
+#define PB_F2VB_LAUNCH(N)                                                                                        \
+        PB_LAUNCH("f2v_bwd", f2v_bwd_tile_kernel<N>, grid, 256, smem, stream, Nf, CV, K, face, vtMap, nfCount,   \
+                  coeff, (const float4*)input, (const float4*)filter, (const float4*)gradOutput,                \
+                  (float4*)gradInput, (float4*)partial)
+        if (smem > 48 * 1024) {
+            PB_CUDA(cudaFuncSetAttribute(f2v_bwd_tile_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            PB_F2VB_LAUNCH(8);
+        } else if (nacc <= 1) { PB_F2VB_LAUNCH(1); }
+        else if (nacc <= 2) { PB_F2VB_LAUNCH(2); }
+        else if (nacc <= 4) { PB_F2VB_LAUNCH(4); }
+        else { PB_F2VB_LAUNCH(8); }
+#undef PB_F2VB_LAUNCH
         return reduce_partials(partial, p.grid_x, (int64_t)K * Cr, gradFilter, stream);
     }
     F2VBwdPlan q = p;

@@ -166,8 +166,10 @@ def facet2vertex_forward(input, filter, coeff, face, nfCount, vtMap, csr=None):
         if csr is None:
             csr = vertex_csr(face, vtMap, NvIn, NvOut)
         out = torch.empty(NvOut, Cc * r, dtype=input.dtype, device=dev)
+        nb = _lib.query("pb200_facet2vertex_forward_workspace_bytes", Nf, Cc, r, K)
+        ws = _ws(nb, dev)
         _lib.call("pb200_facet2vertex_forward", Nf, NvOut, Cc, r, K, ptr(input), ptr(filter), ptr(coeff),
-                  ptr(nfCount), ptr(csr.rowptr), ptr(csr.entries), ptr(out), stream_ptr(dev))
+                  ptr(nfCount), ptr(csr.rowptr), ptr(csr.entries), ptr(out), ptr(ws), nb, stream_ptr(dev))
     return out
 
 
