@@ -241,12 +241,74 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             }
             const int kloc = k0 - kt0;
             const bool staged = valid && (kloc + T <= nrows);
+            // bary rows of the face's first four samples, packed (even d, odd d), zero beyond T / F
+            constexpr int FH = (F + 1) / 2;
+            const bool lean = !__any_sync(0xffffffffu, valid && T > 4);
+            float2 breg[4][FH];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float* src = p.bary + (int64_t)(k0 + (t < T ? t : 0)) * F;
+#pragma unroll
+                for (int d = 0; d < FH; ++d) {
+                    float lo_ = 0.f, hi_ = 0.f;
+                    if (lean && t < T) {
+                        lo_ = __ldg(src + 2 * d);
+                        if (2 * d + 1 < F) hi_ = __ldg(src + 2 * d + 1);
+                    }
+                    breg[t][d] = make_float2(lo_, hi_);
+                }
+            }
             // ---- 3. per slice: drain the accumulator, contract with bary, store gradInput
             for (int slice = 0; slice < p.nslices && alive; ++slice, ++sc) {
                 const uint32_t a = sc & 1u;
                 if (!warp_wait(&acc_full[a], (sc >> 1) & 1u)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + a * NCOLS;
+                // lean path: every face of the warp has at most 4 samples; their bary rows were loaded
+                // into registers once per tile (packed as (even d, odd d) pairs).  The sum over the F
+                // bases runs with fma.f32x2 on those pairs, four samples and two channels at a time:
+                // 8 independent chains per thread, no shared-memory traffic at all.
+                if (lean) {
+                    for (int pr = pair_lo; pr < pair_hi; ++pr) {
+                        const int cil = 2 * pr;
+                        const int ci = slice * p.nq + cil;
+                        const bool has_b = (cil + 1 < p.nq) && (ci + 1 < Cin);
+                        float2 va[FH], vb[FH];
+                        va[FH - 1] = make_float2(0.f, 0.f);
+                        vb[FH - 1] = make_float2(0.f, 0.f);
+                        tmem_ld_row<F>(tbase + (uint32_t)(cil * F), reinterpret_cast<float*>(va));
+                        if (cil + 1 < p.nq) tmem_ld_row<F>(tbase + (uint32_t)((cil + 1) * F), reinterpret_cast<float*>(vb));
+                        else {
+#pragma unroll
+                            for (int d = 0; d < FH; ++d) vb[d] = make_float2(0.f, 0.f);
+                        }
+                        tmem_ld_wait();
+                        if (F & 1) { va[FH - 1].y = 0.f; vb[FH - 1].y = 0.f; }
+                        float2 sa[4], sb[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) { sa[t] = make_float2(0.f, 0.f); sb[t] = make_float2(0.f, 0.f); }
+#pragma unroll
+                        for (int d = 0; d < FH; ++d) {
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                sa[t] = __ffma2_rn(breg[t][d], va[d], sa[t]);
+                                sb[t] = __ffma2_rn(breg[t][d], vb[d], sb[t]);
+                            }
+                        }
+                        if (ci < Cin) {
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                if (t < T) {
+                                    const float ga = (sa[t].x + sa[t].y) * invT, gb = (sb[t].x + sb[t].y) * invT;
+                                    const int64_t idx = (int64_t)(k0 + t) * Cin + ci;
+                                    float* dst = p.gin + idx;
+                                    if (has_b && ((idx & 1) == 0)) *reinterpret_cast<float2*>(dst) = make_float2(ga, gb);
+                                    else { dst[0] = ga; if (has_b) dst[1] = gb; }
+                                }
+                            }
+                        }
+                    }
+                } else {
                 for (int pr = pair_lo; pr < pair_hi; ++pr) {
                     const int cil = 2 * pr;
                     const int ci = slice * p.nq + cil;
@@ -291,6 +353,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                             else { dst[0] = ga * invT; if (has_b) dst[1] = gb * invT; }
                         }
                     }
+                }
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -393,17 +456,16 @@ Plan plan(int Cin, int Cout, int F, int precision) {
     pl.kst = (Cout + KS - 1) / KS;
     pl.nmma = (pl.nq * F + 15) / 16 * 16;
     pl.bpitch = ((F + 3) / 4 * 4) | 4;
-    const size_t budget = 222 * 1024;
+    const size_t budget = 226 * 1024;
     size_t gt = (size_t)pl.nsplit * pl.kst * G_KTILE_BYTES;
     size_t ws = (size_t)pl.nsplit * W_STAGE_BYTES;
     size_t fixed = gt + 1024 + 256;
-    int stages = 4;
+    int stages = 6;
     while (stages > 2 && fixed + stages * ws > budget) --stages;
     pl.nstages = stages;
-    size_t left = budget > fixed + stages * ws ? budget - fixed - stages * ws : 0;
-    int rows = (int)(left / ((size_t)pl.bpitch * 4));
-    if (rows > 4 * TILE_M) rows = 4 * TILE_M;
-    if (rows < TILE_M) rows = 0;                    // too few to matter: read bary from global
+    // bary rows live in registers (faces with up to four samples) or are read from global
+    // memory (faces with more): nothing is staged in shared memory
+    int rows = 0;
     pl.bary_rows = rows;
     pl.smem = fixed + stages * ws + (size_t)rows * pl.bpitch * 4;
     pl.wimg_bytes = (size_t)pl.nslices * pl.kst * ws;
