@@ -52,6 +52,7 @@ def parse_args():
     ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-variants", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
     return ap.parse_args()
 
@@ -183,6 +184,14 @@ def kernel_models(d):
     return m
 
 
+# DRAM bytes per face of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu
+# capture on a 2-mesh case of the same shapes, divided by its face count; traffic grows in
+# proportion to the faces).  Source: the summaries under profiles/.
+MEASURED_DRAM_BYTES_PER_FACE = {
+    ("c5", "f2f_bwd_gfilter_tc"): 2077.0,
+}
+
+
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -226,6 +235,10 @@ def roofline_from_profile(records, steps, dims):
                         frac=top["hbm_frac"], traffic=None)
         roof.update(kernel=top["kernel"], peak_source=peaks["source"], ms_per_launch_set=top["ms_per_step"],
                     share_of_step=top["share"])
+        per_face = MEASURED_DRAM_BYTES_PER_FACE.get((dims.get("config"), top["kernel"]))
+        if per_face is not None:
+            roof["traffic"] = per_face * dims["Nf"]
+            roof["traffic_note"] = "ncu dram bytes of a 2-mesh capture scaled by faces (profiles/)"
     return roof, table
 
 
@@ -345,8 +358,21 @@ def run_ours(args):
     _lib.prof_enable(False)
     records = _lib.prof_read(64)
     _lib.prof_reset()
-    dims = dict(Nv=h["Nv"], Nf=h["Nf"], NiK=h["NiK"], cin=cfg["cin"], cout=cfg["cout"], K=K)
+    dims = dict(Nv=h["Nv"], Nf=h["Nf"], NiK=h["NiK"], cin=cfg["cin"], cout=cfg["cout"], K=K, config=args.config)
     roof, table = roofline_from_profile(records, prof_steps, dims)
+
+    # the tf32-operand variant of the facet2facet contraction (gate 2e-3), same step, same inputs
+    variants = None
+    if args.precision == "fp32" and not args.no_variants:
+        conv3d.set_f2f_precision("tf32")
+        for _ in range(2):
+            step_resident()
+        vms, _ = timed(step_resident, max(2, min(args.steps, 5)))
+        vsteps = max(2, min(args.steps, 5))
+        variants = {"tf32": dict(value=faces_total / (vms / vsteps / 1e3), unit=UNIT, ms_per_step=vms / vsteps,
+                                 note="facet2facet operands rounded to tf32 (1 MMA per product), fp32 accumulation; "
+                                      "relative error gate 2e-3")}
+        conv3d.set_f2f_precision(args.precision)
 
     e2e = None
     if not args.no_e2e:
@@ -377,7 +403,7 @@ def run_ours(args):
                        "l2_policy": "inputs larger than L2 (no flush)" if h["Nf"] * cfg["cin"] * 4 > 256e6
                        else "inputs smaller than L2, no flush"},
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-            "clocks": clocks, "kernels": table[:12],
+            "clocks": clocks, "variants": variants, "kernels": table[:12],
             "allreduce_bytes": allreduce.nbytes if world > 1 else 0,
         }
         print(json.dumps(line))

@@ -154,6 +154,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
         for (int i = lane; i < p.smaxw * FP; i += 32) wb[i] = 0.f;
         const uint32_t off0 = swz64_offset((uint32_t)m, (uint32_t)(2 * h));
         const uint32_t off1 = swz64_offset((uint32_t)m, (uint32_t)(2 * h + 1));
+        const uint32_t stages32 = smem_u32(stages), wb32 = smem_u32(wb);
         int st_i = 0;                                         // running stage index and phase
         uint32_t st_ph = 0;
         uint32_t tcount = 0;
@@ -167,21 +168,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) return false;
             }
-            uint8_t* st = stages + (size_t)st_i * stage_bytes;
+            const uint32_t st = stages32 + (uint32_t)st_i * (uint32_t)stage_bytes;
             if (NSPLIT == 1) {
-                *reinterpret_cast<float4*>(st + off0) =
-                    make_float4(to_tf32_rna(a0.x), to_tf32_rna(a0.y), to_tf32_rna(a0.z), to_tf32_rna(a0.w));
-                *reinterpret_cast<float4*>(st + off1) =
-                    make_float4(to_tf32_rna(a1.x), to_tf32_rna(a1.y), to_tf32_rna(a1.z), to_tf32_rna(a1.w));
+                sts_f4(st + off0, make_float4(to_tf32_rna(a0.x), to_tf32_rna(a0.y), to_tf32_rna(a0.z), to_tf32_rna(a0.w)));
+                sts_f4(st + off1, make_float4(to_tf32_rna(a1.x), to_tf32_rna(a1.y), to_tf32_rna(a1.z), to_tf32_rna(a1.w)));
             } else {
-                float4 h0 = make_float4(tf32_hi(a0.x), tf32_hi(a0.y), tf32_hi(a0.z), tf32_hi(a0.w));
-                float4 h1 = make_float4(tf32_hi(a1.x), tf32_hi(a1.y), tf32_hi(a1.z), tf32_hi(a1.w));
-                *reinterpret_cast<float4*>(st + off0) = h0;
-                *reinterpret_cast<float4*>(st + off1) = h1;
-                *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off0) =
-                    make_float4(a0.x - h0.x, a0.y - h0.y, a0.z - h0.z, a0.w - h0.w);
-                *reinterpret_cast<float4*>(st + FACE_TILE_BYTES + off1) =
-                    make_float4(a1.x - h1.x, a1.y - h1.y, a1.z - h1.z, a1.w - h1.w);
+                const float4 h0 = make_float4(tf32_hi(a0.x), tf32_hi(a0.y), tf32_hi(a0.z), tf32_hi(a0.w));
+                const float4 h1 = make_float4(tf32_hi(a1.x), tf32_hi(a1.y), tf32_hi(a1.z), tf32_hi(a1.w));
+                sts_f4(st + off0, h0);
+                sts_f4(st + off1, h1);
+                sts_f4(st + FACE_TILE_BYTES + off0, make_float4(a0.x - h0.x, a0.y - h0.y, a0.z - h0.z, a0.w - h0.w));
+                sts_f4(st + FACE_TILE_BYTES + off1, make_float4(a1.x - h1.x, a1.y - h1.y, a1.z - h1.z, a1.w - h1.w));
             }
             fence_proxy_async();
             __syncwarp();
@@ -222,12 +219,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
             const int kloc = valid ? k0 - kw0 : 0;            // row of the face's first sample in wb
             if (!slow) {
                 // rows of the face's samples; unused slots point at a valid row and meet x == 0
-                const float* bp[TREG];
+                uint32_t bp[TREG];
 #pragma unroll
                 for (int t = 0; t < TREG; ++t) {
                     int row = kloc + (t < T ? t : (T > 0 ? T - 1 : 0));
                     if (row >= p.smaxw) row = 0;
-                    bp[t] = wb + row * FP;
+                    bp[t] = wb32 + (uint32_t)(row * FP) * 4u;
                 }
                 for (int c16 = 0; c16 < Cin / KS && alive; ++c16) {
                     float4 x[TREG][2];
@@ -245,7 +242,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                     for (int d4 = 0; d4 < F && alive; d4 += 4) {
                         float4 b[TREG];
 #pragma unroll
-                        for (int t = 0; t < TREG; ++t) b[t] = *reinterpret_cast<const float4*>(bp[t] + d4);
+                        for (int t = 0; t < TREG; ++t) b[t] = lds_f4(bp[t] + (uint32_t)d4 * 4u);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             if (d4 + j < F) {

@@ -50,15 +50,6 @@ constexpr int RAW_B_OFF = RAW_X_OFF + RAW_X_BYTES;
 constexpr int RAW_C_OFF = RAW_B_OFF + RAW_B_BYTES;
 constexpr int RAW_BYTES = (RAW_C_OFF + 128 + 127) / 128 * 128;
 
-// shared-window (32-bit address) accessors: one instruction each, immediate offsets fold in
-__device__ __forceinline__ float lds_f32(uint32_t a) { float v; asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a)); return v; }
-__device__ __forceinline__ int lds_i32(uint32_t a) { int v; asm volatile("ld.shared.s32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
-__device__ __forceinline__ float4 lds_f4(uint32_t a) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
-    return v;
-}
-__device__ __forceinline__ void sts_f32(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
 // one operand element: tf32-rounded (1 split) or hi + lo (2 splits, lo block `lo_off` bytes further)
 template <int NSPLIT>
 __device__ __forceinline__ void put32(uint32_t a, uint32_t lo_off, float v) {
