@@ -324,6 +324,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
         // ================================ MMA issuer =========================================
         if (lane == 0) {
             constexpr uint32_t idesc = instr_desc(FMT_TF32, UM, TILE_F);
+            const uint64_t dbase = smem_desc_kmajor(smem_u32(stages), 64, SWZ_64B);
             int s = 0;
             uint32_t ph = 0;
             bool alive = true;
@@ -331,9 +332,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(&full[s], ph, abort_flag)) { alive = false; break; }
                     tc_fence_after();
-                    const uint32_t st = smem_u32(stages + (size_t)s * stage_bytes);
-                    const uint64_t face_hi = smem_desc_kmajor(st, 64, SWZ_64B);
-                    const uint64_t filt_hi = smem_desc_kmajor(st + NSPLIT * FACE_TILE_BYTES, 64, SWZ_64B);
+                    // descriptors differ only in the 16-byte-unit start address: add offsets to one base
+                    const uint64_t face_hi = dbase + (uint64_t)(((uint32_t)s * (uint32_t)stage_bytes) >> 4);
+                    const uint64_t filt_hi = face_hi + (uint64_t)((NSPLIT * FACE_TILE_BYTES) >> 4);
 #pragma unroll
                     for (int ks = 0; ks < 2; ++ks) {          // 2 x (K = 8 tf32 = 32 bytes)
                         const uint64_t adv = (uint64_t)(ks * 2);
@@ -341,9 +342,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                         if (NSPLIT == 1) {
                             mma_tf32(tmem_base, filt_hi + adv, face_hi + adv, idesc, first);
                         } else {
-                            const uint64_t face_lo = smem_desc_kmajor(st + FACE_TILE_BYTES, 64, SWZ_64B);
-                            const uint64_t filt_lo =
-                                smem_desc_kmajor(st + NSPLIT * FACE_TILE_BYTES + FILT_TILE_BYTES, 64, SWZ_64B);
+                            const uint64_t face_lo = face_hi + (uint64_t)(FACE_TILE_BYTES >> 4);
+                            const uint64_t filt_lo = filt_hi + (uint64_t)(FILT_TILE_BYTES >> 4);
                             mma_tf32(tmem_base, filt_lo + adv, face_hi + adv, idesc, first);
                             mma_tf32(tmem_base, filt_hi + adv, face_lo + adv, idesc, 1u);
                             mma_tf32(tmem_base, filt_hi + adv, face_hi + adv, idesc, 1u);

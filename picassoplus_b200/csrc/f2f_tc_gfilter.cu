@@ -375,14 +375,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             const int n1 = NR < 256 ? NR : 256, n2 = NR - n1;
             const uint32_t idesc1 = instr_desc(FMT_TF32, UM, (uint32_t)n1);
             const uint32_t idesc2 = instr_desc(FMT_TF32, UM, (uint32_t)(n2 > 0 ? n2 : 16));
+            const uint64_t dbase = smem_desc_kmajor(smem_u32(stages), 64, SWZ_64B);
             int si = 0;
             uint32_t sph = 0;
             bool alive = true;
             for (int64_t st = 0; st < nst; ++st) {
                 if (!mbar_wait(&full[si], sph, abort_flag)) { alive = false; break; }
                 tc_fence_after();
-                const uint32_t sb = smem_u32(stages + (size_t)si * stage_bytes);
-                const uint32_t g_hi = sb, at_hi = sb + NSPLIT * G_TILE_BYTES;
+                const uint64_t dg_hi0 = dbase + (uint64_t)(((uint32_t)si * (uint32_t)stage_bytes) >> 4);
+                const uint64_t da_hi0 = dg_hi0 + (uint64_t)((NSPLIT * G_TILE_BYTES) >> 4);
 #pragma unroll
                 for (int k2 = 0; k2 < 2; ++k2) {
                     const uint64_t adv = (uint64_t)(k2 * 2);
@@ -390,14 +391,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                     for (int c = 0; c < (n2 > 0 ? 2 : 1); ++c) {
                         const uint32_t d_tmem = tmem_base + (uint32_t)(c * 256);
                         const uint32_t idesc = c == 0 ? idesc1 : idesc2;
-                        const uint32_t at_c = at_hi + (uint32_t)(c * 256 * 64);
-                        const uint64_t dg_hi = smem_desc_kmajor(g_hi, 64, SWZ_64B) + adv;
-                        const uint64_t da_hi = smem_desc_kmajor(at_c, 64, SWZ_64B) + adv;
+                        const uint64_t dg_hi = dg_hi0 + adv;
+                        const uint64_t da_hi = da_hi0 + (uint64_t)((c * 256 * 64) >> 4) + adv;
                         if (NSPLIT == 1) {
                             mma_tf32(d_tmem, dg_hi, da_hi, idesc, first);
                         } else {
-                            const uint64_t dg_lo = smem_desc_kmajor(g_hi + G_TILE_BYTES, 64, SWZ_64B) + adv;
-                            const uint64_t da_lo = smem_desc_kmajor(at_c + (uint32_t)at_bytes, 64, SWZ_64B) + adv;
+                            const uint64_t dg_lo = dg_hi + (uint64_t)(G_TILE_BYTES >> 4);
+                            const uint64_t da_lo = da_hi + (uint64_t)(at_bytes >> 4);
                             mma_tf32(d_tmem, dg_lo, da_hi, idesc, first);
                             mma_tf32(d_tmem, dg_hi, da_lo, idesc, 1u);
                             mma_tf32(d_tmem, dg_hi, da_hi, idesc, 1u);

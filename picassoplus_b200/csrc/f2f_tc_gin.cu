@@ -386,6 +386,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
         // ===================== MMA issuer =====================
         if (lane == 0) {
             const uint32_t idesc = instr_desc(FMT_TF32, TILE_M, (uint32_t)p.nmma);
+            const uint64_t dg_base = smem_desc_kmajor(smem_u32(gtile), 64, SWZ_64B);
+            const uint64_t dw_base = smem_desc_kmajor(smem_u32(wst), 64, SWZ_64B);
             int s = 0;
             uint32_t ph = 0, tcount = 0, sc = 0;
             bool alive = true;
@@ -399,10 +401,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                     for (int ks = 0; ks < KST; ++ks) {
                         if (!mbar_wait(&w_full[s], ph, abort_flag)) { alive = false; break; }
                         tc_fence_after();
-                        const uint32_t g_hi = smem_u32(gtile + (size_t)ks * G_KTILE_BYTES);
-                        const uint32_t w_hi = smem_u32(wst + (size_t)s * wstage_bytes);
-                        const uint64_t dg_hi = smem_desc_kmajor(g_hi, 64, SWZ_64B);
-                        const uint64_t dw_hi = smem_desc_kmajor(w_hi, 64, SWZ_64B);
+                        // descriptors differ only in the 16-byte-unit start address: add offsets to a base
+                        const uint64_t dg_hi = dg_base + (uint64_t)(((uint32_t)ks * G_KTILE_BYTES) >> 4);
+                        const uint64_t dw_hi = dw_base + (uint64_t)(((uint32_t)s * (uint32_t)wstage_bytes) >> 4);
 #pragma unroll
                         for (int k2 = 0; k2 < 2; ++k2) {
                             const uint64_t adv = (uint64_t)(k2 * 2);
@@ -410,9 +411,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                             if (NSPLIT == 1) {
                                 mma_tf32(d_tmem, dg_hi + adv, dw_hi + adv, idesc, first);
                             } else {
-                                const uint64_t dg_lo =
-                                    smem_desc_kmajor(g_hi + (uint32_t)(KST * G_KTILE_BYTES), 64, SWZ_64B);
-                                const uint64_t dw_lo = smem_desc_kmajor(w_hi + W_STAGE_BYTES, 64, SWZ_64B);
+                                const uint64_t dg_lo = dg_hi + (uint64_t)(((uint32_t)KST * G_KTILE_BYTES) >> 4);
+                                const uint64_t dw_lo = dw_hi + (uint64_t)(W_STAGE_BYTES >> 4);
                                 mma_tf32(d_tmem, dg_lo + adv, dw_hi + adv, idesc, first);
                                 mma_tf32(d_tmem, dg_hi + adv, dw_lo + adv, idesc, 1u);
                                 mma_tf32(d_tmem, dg_hi + adv, dw_hi + adv, idesc, 1u);
