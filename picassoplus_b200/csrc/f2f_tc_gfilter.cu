@@ -8,10 +8,12 @@
 // chunk of faces; per stage of 16 faces
 //   * 8 producer warps first copy the stage's raw rows (gradOutput rows, bary rows, the
 //     CTA's 16 input channels of every sample, sample ranges) from global memory with
-//     coalesced loads into a double-buffered raw area (one stage ahead of the math), then
-//     build both operands in shared memory as K-major (face-contiguous) 64-byte swizzled
-//     rows: the transposed gradOutput block (128 rows) and the A^T block (F*16 rows) --
-//     thread = (face, 8 channels), a warp walks its share of the F bases;
+//     coalesced loads into a double-buffered raw area (two stages ahead of the math), then
+//     build both operands in shared memory MN-major (128-byte swizzle, 32-byte base): a face
+//     is a K-row whose 128-byte pieces hold 32 consecutive output channels (gradOutput block)
+//     or 32 consecutive (basis, channel) columns (A block), so that neither operand is
+//     transposed and every thread stores 16-byte vectors -- thread = (face, 8 channels), a
+//     warp walks its share of the F bases;
 //   * one thread issues tcgen05.mma (M = 128 output channels, N = F*16 in chunks of <= 256,
 //     K = 8 faces per instruction) and commits the stage back.
 // At the end the accumulator is drained once into partial[chunk] (final gradFilter layout);
@@ -32,14 +34,17 @@ using namespace ptx;
 
 constexpr int UM = 128;                       // output channels (UMMA M), Cout zero-padded
 constexpr int CG = 16;                        // input channels per CTA
-constexpr int KF = 16;                        // faces per stage (64-byte K-major rows)
+constexpr int KF = 16;                        // faces per stage (four groups of 4 K-rows, two per instruction)
 constexpr int PWARPS = 8;
 constexpr int NTHREADS = (PWARPS + 1) * 32;   // + MMA warp
-constexpr int G_TILE_BYTES = UM * 64;
+constexpr int ATOM_BYTES = 512;               // 4 K-rows x 128 bytes (32 M/N elements)
+constexpr int G_SBO = (UM / 32) * ATOM_BYTES; // gradOutput block: [4-face group][32-channel block][atom]
+constexpr int G_TILE_BYTES = (KF / 4) * G_SBO;
 constexpr int TREG = 4;
 // raw staging area of one stage (double-buffered)
 constexpr int RAW_SAMPLES = 64;               // samples of a stage that are staged (16 faces x 4)
 constexpr int RAW_G_PITCH = UM + 4;           // floats per gradOutput row (pitch = 4 mod 32: conflict-free 16-byte reads)
+__host__ __device__ constexpr int at_blocks(int F) { return (F * CG + 31) / 32; }   // 32-column blocks of the A operand
 constexpr int RAW_X_PITCH = 20;               // floats per sample row (16 channels + pad)
 constexpr int RAW_G_BYTES = KF * RAW_G_PITCH * 4;
 constexpr int RAW_X_BYTES = (RAW_SAMPLES + TREG) * RAW_X_PITCH * 4;   // + pad rows read (and masked) by short faces
@@ -52,13 +57,13 @@ constexpr int RAW_BYTES = (RAW_C_OFF + 128 + 127) / 128 * 128;
 
 // one operand element: tf32-rounded (1 split) or hi + lo (2 splits, lo block `lo_off` bytes further)
 template <int NSPLIT>
-__device__ __forceinline__ void put32(uint32_t a, uint32_t lo_off, float v) {
+__device__ __forceinline__ void put4(uint32_t a, uint32_t lo_off, const float4& v) {
     if (NSPLIT == 1) {
-        sts_f32(a, to_tf32_rna(v));
+        sts_f4(a, make_float4(to_tf32_rna(v.x), to_tf32_rna(v.y), to_tf32_rna(v.z), to_tf32_rna(v.w)));
     } else {
-        const float hv = tf32_hi(v);
-        sts_f32(a, hv);
-        sts_f32(a + lo_off, v - hv);
+        const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+        sts_f4(a, h);
+        sts_f4(a + lo_off, make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w));
     }
 }
 
@@ -84,8 +89,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = p.nstages, F = p.F, Cin = p.Cin, Cout = p.Cout;
     const int NR = F * CG;                                   // accumulator columns / A^T rows
-    const size_t at_bytes = (size_t)NR * 64;
-    const size_t stage_bytes = (size_t)NSPLIT * (G_TILE_BYTES + at_bytes);   // [g hi][g lo?][A^T hi][A^T lo?]
+    const uint32_t at_sbo = (uint32_t)at_blocks(F) * ATOM_BYTES;             // A block: [4-face group][32-column block][atom]
+    const size_t at_bytes = (KF / 4) * (size_t)at_sbo;
+    const size_t stage_bytes = (size_t)NSPLIT * (G_TILE_BYTES + at_bytes);   // [g hi][g lo?][A hi][A lo?]
     uint8_t* stages = smem;
     uint8_t* raw = smem + (size_t)S * stage_bytes;            // [2][RAW_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * RAW_BYTES);
@@ -120,18 +126,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     if (warp < PWARPS) {
         // ==================================== producers ====================================
         const int half = lane >> 4, fl = lane & 15;           // 8-channel half, face of the stage
-        const uint32_t fchunk = (uint32_t)(fl >> 2), fsub = (uint32_t)(fl & 3) * 4u;
         constexpr int DMAX = 4;                               // bases per warp: ceil(32 / PWARPS)
-        // byte offsets, inside a 16-row group of a K-major 64B-swizzled block, of this thread's
-        // 8 rows (row = half*8 + jj) at face column fl.  The two halves of a warp must hit rows
-        // of different parity (distinct banks), so half 1 walks its rows rotated by one.
-        uint32_t row_off[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t jj = half ? (uint32_t)((j + 1) & 7) : (uint32_t)j;
-            const uint32_t row = (uint32_t)half * 8u + jj;
-            row_off[j] = row * 64u + ((fchunk ^ ((row >> 1) & 3u)) << 4) + fsub;
-        }
+        // This thread's 8 consecutive columns 16*g + 8*half (g = warp for the gradOutput block,
+        // g = basis d = warp + 8 i for the A block) of K-row fl are 32-byte chunk j of 32-column
+        // block g>>1; chunk j of K-row k is stored at chunk j ^ (k & 3).  A quarter warp (faces
+        // 0..7 or 8..15, same j) covers two 4-face groups whose lanes would meet in the same
+        // 16-byte bank group: the lanes with fl & 4 keep their two 4-channel halves swapped in
+        // registers (`sw`), so the first store of a pair lands in the other half of the chunk.
+        const uint32_t j32 = 2u * (uint32_t)(warp & 1) + (uint32_t)half;
+        const uint32_t sw = (fl & 4) ? 16u : 0u;
+        const uint32_t toff = (uint32_t)(warp >> 1) * ATOM_BYTES + (uint32_t)(fl & 3) * 128u + ((j32 ^ (uint32_t)(fl & 3)) << 5) + sw;
+        const uint32_t g_off = (uint32_t)(fl >> 2) * G_SBO + toff;
+        const uint32_t a_off = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(fl >> 2) * at_sbo + toff;
         const int ptid = tid;
         const uint32_t raw32 = smem_u32(raw), stages32 = smem_u32(stages);
         // the pad rows behind the staged windows are read (their products are masked) but never
@@ -140,7 +146,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         asm volatile("bar.sync 1, %0;" ::"n"(PWARPS * 32) : "memory");                                 // 0..255 over the producer warps
         // ---- raw staging: what stage `st` needs, copied with coalesced loads
         struct RawRegs { float4 g[2]; float4 x; float b[RAW_B_ITERS]; int cumv; int ks0, ns; };
-        auto raw_issue = [&](int64_t st) -> RawRegs {
+        // sample range [ks0, ks1) of stage `st`: loaded one stage before the loads that depend on
+        // it are issued, so that no warp ever waits on this (dependent) load
+        auto ks_pair = [&](int64_t st) -> int2 {
+            if (st >= nst) return make_int2(0, 0);
+            const int64_t f0 = (st0 + st) * KF;
+            const int64_t fe = f0 + KF < p.Nf ? f0 + KF : p.Nf;
+            return make_int2(f0 > 0 ? __ldg(p.cum + f0 - 1) : 0, __ldg(p.cum + fe - 1));
+        };
+        auto raw_issue = [&](int64_t st, int2 ks) -> RawRegs {
             RawRegs R;
             R.g[0] = R.g[1] = zero4(); R.x = zero4(); R.cumv = 0; R.ks0 = 0; R.ns = 0;
 #pragma unroll
@@ -148,8 +162,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             if (st >= nst) return R;
             const int64_t f0 = (st0 + st) * KF;
             const int64_t fe = f0 + KF < p.Nf ? f0 + KF : p.Nf;         // one past the stage's last face
-            const int ks0 = f0 > 0 ? __ldg(p.cum + f0 - 1) : 0;
-            const int ks1 = __ldg(p.cum + fe - 1);
+            const int ks0 = ks.x, ks1 = ks.y;
             int ns = ks1 - ks0;
             if (ns > RAW_SAMPLES) ns = RAW_SAMPLES;
             R.ks0 = ks0; R.ns = ns;
@@ -183,9 +196,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             }
             return R;
         };
-        // Odd 8-channel groups of the gradOutput rows and of the sample rows are stored rotated
-        // left by one (slot j holds channel (j+1)&7 of the group): the half-1 lanes, which must
-        // walk their operand rows rotated, then read plain slots.
         auto raw_store = [&](const RawRegs& R, int buf) {
             uint8_t* rb = raw + (size_t)buf * RAW_BYTES;
             float* g_raw = reinterpret_cast<float*>(rb);
@@ -196,24 +206,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             for (int i = 0; i < 2; ++i) {
                 const int idx = ptid + i * 256;
                 const int fr = idx / 32, c4 = idx - fr * 32;
-                float* dst = g_raw + fr * RAW_G_PITCH + (c4 >> 1) * 8;
-                if (((c4 >> 1) & 1) == 0) {
-                    *reinterpret_cast<float4*>(dst + (c4 & 1) * 4) = R.g[i];
-                } else {
-                    const int e0 = (c4 & 1) * 4;                 // channels e0..e0+3 of the group
-                    dst[(e0 + 7) & 7] = R.g[i].x; dst[e0] = R.g[i].y; dst[e0 + 1] = R.g[i].z; dst[e0 + 2] = R.g[i].w;
-                }
+                *reinterpret_cast<float4*>(g_raw + fr * RAW_G_PITCH + c4 * 4) = R.g[i];
             }
             {
                 const int sr = ptid >> 2, qd = ptid & 3;
-                float* dst = x_raw + sr * RAW_X_PITCH;
-                if (qd < 2) {
-                    *reinterpret_cast<float4*>(dst + qd * 4) = R.x;
-                } else {
-                    const int e0 = (qd & 1) * 4;
-                    float* d8 = dst + 8;
-                    d8[(e0 + 7) & 7] = R.x.x; d8[e0] = R.x.y; d8[e0 + 1] = R.x.z; d8[e0 + 2] = R.x.w;
-                }
+                *reinterpret_cast<float4*>(x_raw + sr * RAW_X_PITCH + qd * 4) = R.x;
             }
 #pragma unroll
             for (int i = 0; i < RAW_B_ITERS; ++i) b_raw[ptid + i * 256] = R.b[i];
@@ -229,14 +226,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         int si = 0;
         uint32_t sph = 0;
         bool alive = true;
+        // Global loads run two stages ahead of the stage being computed (their registers are
+        // parked for one stage), the sample-range loads three stages ahead.
         {
-            RawRegs R0 = raw_issue(0);
+            RawRegs R0 = raw_issue(0, ks_pair(0));
             raw_store(R0, 0);
             raw_publish();
         }
+        RawRegs Rn = raw_issue(1, ks_pair(1));
+        int2 ksn = ks_pair(2);
         for (int64_t st = 0; st < nst && alive; ++st) {
-            // loads of the next stage are in flight while this stage is computed
-            const RawRegs Rn = raw_issue(st + 1);
+            const RawRegs Rn2 = raw_issue(st + 2, ksn);
+            ksn = ks_pair(st + 3);
             {
                 int ok = 1;
                 if (lane == 0) ok = mbar_wait(raw_ready, (uint32_t)(st & 1), abort_flag) ? 1 : 0;
@@ -260,30 +261,28 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { alive = false; break; }
             }
-            // shared-window addresses of this thread's 8 rows inside its warp's 16-row group;
-            // the gradOutput block starts at +0, the A^T block at +NSPLIT*8 KB, basis d = warp + 8 i
-            // sits i*8 KB further on
-            const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes + (uint32_t)warp * 1024u;
-            uint32_t ra[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) ra[j] = sb32 + row_off[j];
+            // shared-window addresses of this thread's first 16-byte store in the gradOutput block
+            // and in the A block (basis d = warp + 8 i sits 4 column blocks = 2 KB further on per i);
+            // the second store is the other half of the same 32-byte chunk
+            const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes;
+            const uint32_t ga32 = sb32 + g_off, aa32 = sb32 + a_off;
             if (!slow) {
                 float x[TREG][8];
                 {
                     const uint32_t xa = rb32 + RAW_X_OFF + (uint32_t)kloc * (RAW_X_PITCH * 4) + (uint32_t)half * 32u;
+                    const uint32_t xu = xa + sw, xw = xa + (16u - sw);
 #pragma unroll
                     for (int t = 0; t < TREG; ++t) {
-                        const float4 u = lds_f4(xa + t * (RAW_X_PITCH * 4)), w = lds_f4(xa + t * (RAW_X_PITCH * 4) + 16);
+                        const float4 u = lds_f4(xu + t * (RAW_X_PITCH * 4)), w = lds_f4(xw + t * (RAW_X_PITCH * 4));
                         x[t][0] = u.x; x[t][1] = u.y; x[t][2] = u.z; x[t][3] = u.w;
                         x[t][4] = w.x; x[t][5] = w.y; x[t][6] = w.z; x[t][7] = w.w;
                     }
                 }
                 {
                     const uint32_t ga = rb32 + (uint32_t)fl * (RAW_G_PITCH * 4) + (uint32_t)(warp * 16 + half * 8) * 4u;
-                    const float4 u = lds_f4(ga), w = lds_f4(ga + 16);
-                    const float g8[8] = {u.x, u.y, u.z, u.w, w.x, w.y, w.z, w.w};
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) put32<NSPLIT>(ra[j], G_TILE_BYTES, g8[j]);
+                    const float4 u = lds_f4(ga + sw), w = lds_f4(ga + (16u - sw));
+                    put4<NSPLIT>(ga32, G_TILE_BYTES, u);
+                    put4<NSPLIT>(ga32 ^ 16u, G_TILE_BYTES, w);
                 }
                 const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(kloc * F) * 4u;
 #pragma unroll
@@ -300,23 +299,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 #pragma unroll
                             for (int j = 0; j < 8; ++j) a[j] = fmaf(b, x[t][j], a[j]);
                         }
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            put32<NSPLIT>(ra[j] + (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)i * (PWARPS * 1024u),
-                                          (uint32_t)at_bytes, a[j]);
+                        const uint32_t da32 = aa32 + (uint32_t)i * (4u * ATOM_BYTES);
+                        put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
+                        put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[4], a[5], a[6], a[7]));
                     }
                 }
             } else {
-                // generic path, straight from global memory (position j of half 1 is channel (j+1)&7)
+                // generic path, straight from global memory
                 float g8[8];
                 const int co0 = warp * 16 + half * 8;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const int co = co0 + (half ? ((j + 1) & 7) : j);
+                    const int co = co0 + (j ^ (int)(sw >> 2));                 // halves swapped where sw is set
                     g8[j] = (valid && co < Cout) ? __ldg(p.gout + f * Cout + co) : 0.f;
                 }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) put32<NSPLIT>(ra[j], G_TILE_BYTES, g8[j]);
+                put4<NSPLIT>(ga32, G_TILE_BYTES, make_float4(g8[0], g8[1], g8[2], g8[3]));
+                put4<NSPLIT>(ga32 ^ 16u, G_TILE_BYTES, make_float4(g8[4], g8[5], g8[6], g8[7]));
                 for (int d = warp; d < F; d += PWARPS) {
                     float a[8];
 #pragma unroll
@@ -325,11 +323,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                         const float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
                         const float* xr = p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) a[j] = fmaf(b, __ldg(xr + (half ? ((j + 1) & 7) : j)), a[j]);
+                        for (int j = 0; j < 8; ++j) a[j] = fmaf(b, __ldg(xr + (j ^ (int)(sw >> 2))), a[j]);
                     }
-                    const uint32_t off = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(d - warp) * 1024u;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) put32<NSPLIT>(ra[j] + off, (uint32_t)at_bytes, a[j]);
+                    const uint32_t da32 = aa32 + (uint32_t)((d - warp) >> 3) * (4u * ATOM_BYTES);
+                    put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
+                    put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[4], a[5], a[6], a[7]));
                 }
             }
             fence_proxy_async();
@@ -339,6 +337,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             // every warp has passed raw_ready(st), so nobody reads the other raw buffer any more
             raw_store(Rn, (int)((st + 1) & 1));
             raw_publish();
+            Rn = Rn2;
         }
         // ==================================== drain ====================================
         if (alive) {
@@ -373,26 +372,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // ==================================== MMA issuer ====================================
         if (lane == 0) {
             const int n1 = NR < 256 ? NR : 256, n2 = NR - n1;
-            const uint32_t idesc1 = instr_desc(FMT_TF32, UM, (uint32_t)n1);
-            const uint32_t idesc2 = instr_desc(FMT_TF32, UM, (uint32_t)(n2 > 0 ? n2 : 16));
-            const uint64_t dbase = smem_desc_kmajor(smem_u32(stages), 64, SWZ_64B);
+            const uint32_t idesc1 = instr_desc_mnmajor(FMT_TF32, UM, (uint32_t)n1);
+            const uint32_t idesc2 = instr_desc_mnmajor(FMT_TF32, UM, (uint32_t)(n2 > 0 ? n2 : 16));
+            const uint64_t dbase_g = smem_desc_mnmajor_b32(smem_u32(stages), ATOM_BYTES, G_SBO);
+            const uint64_t dbase_a = smem_desc_mnmajor_b32(smem_u32(stages) + NSPLIT * G_TILE_BYTES, ATOM_BYTES, at_sbo);
             int si = 0;
             uint32_t sph = 0;
             bool alive = true;
             for (int64_t st = 0; st < nst; ++st) {
                 if (!mbar_wait(&full[si], sph, abort_flag)) { alive = false; break; }
                 tc_fence_after();
-                const uint64_t dg_hi0 = dbase + (uint64_t)(((uint32_t)si * (uint32_t)stage_bytes) >> 4);
-                const uint64_t da_hi0 = dg_hi0 + (uint64_t)((NSPLIT * G_TILE_BYTES) >> 4);
+                const uint64_t soff = (uint64_t)(((uint32_t)si * (uint32_t)stage_bytes) >> 4);
+                const uint64_t dg_hi0 = dbase_g + soff, da_hi0 = dbase_a + soff;
 #pragma unroll
-                for (int k2 = 0; k2 < 2; ++k2) {
-                    const uint64_t adv = (uint64_t)(k2 * 2);
+                for (int k2 = 0; k2 < 2; ++k2) {                        // one instruction = 8 faces = two 4-face groups
                     const uint32_t first = (st != 0 || k2 != 0) ? 1u : 0u;
                     for (int c = 0; c < (n2 > 0 ? 2 : 1); ++c) {
                         const uint32_t d_tmem = tmem_base + (uint32_t)(c * 256);
                         const uint32_t idesc = c == 0 ? idesc1 : idesc2;
-                        const uint64_t dg_hi = dg_hi0 + adv;
-                        const uint64_t da_hi = da_hi0 + (uint64_t)((c * 256 * 64) >> 4) + adv;
+                        const uint64_t dg_hi = dg_hi0 + (uint64_t)((k2 * 2 * G_SBO) >> 4);
+                        const uint64_t da_hi = da_hi0 + (uint64_t)(((uint32_t)k2 * 2u * at_sbo + (uint32_t)c * (8u * ATOM_BYTES)) >> 4);
                         if (NSPLIT == 1) {
                             mma_tf32(d_tmem, dg_hi, da_hi, idesc, first);
                         } else {
@@ -438,7 +437,7 @@ Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     if (nch > total_stages) nch = (int)total_stages;
     pl.stages_per_chunk = ceil_div(total_stages, nch);
     pl.nchunks = (int)ceil_div(total_stages, pl.stages_per_chunk);
-    size_t stage = (size_t)pl.nsplit * (G_TILE_BYTES + (size_t)F * CG * 64);
+    size_t stage = (size_t)pl.nsplit * (G_TILE_BYTES + (KF / 4) * (size_t)at_blocks(F) * ATOM_BYTES);
     int S = 4;
     const size_t extra = 2 * (size_t)RAW_BYTES + 1024 + 256;
     while (S > 2 && (size_t)S * stage + extra > 224 * 1024) --S;

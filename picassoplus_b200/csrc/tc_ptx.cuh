@@ -144,10 +144,31 @@ __device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t smem_addr, uint32_
     return d;
 }
 
+// Shared-memory matrix descriptor of an MN-major operand tile of 32-bit elements (the one
+// layout tf32 accepts MN-major: 128-byte swizzle with a 32-byte base).  A 512-byte atom holds
+// 4 K-rows of 128 bytes (32 consecutive M/N elements); `lbo_bytes` steps to the next 32 M/N
+// elements, `sbo_bytes` to the next 4 K-rows.  32-byte chunk j of K-row k sits at chunk
+// j ^ (k & 3) of the row (address bits [5,7) ^= bits [7,9)); atoms are 512-byte aligned.
+constexpr uint64_t SWZ_128B_BASE32B = 1;
+__device__ __forceinline__ uint64_t smem_desc_mnmajor_b32(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= SWZ_128B_BASE32B << 61;
+    return d;
+}
+
 // Instruction descriptor: fp32 accumulate, both operands K-major, M x N tile.
 constexpr uint32_t FMT_F16 = 0, FMT_BF16 = 1, FMT_TF32 = 2;
 __host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt_ab, uint32_t M, uint32_t N) {
     return (1u << 4) | (fmt_ab << 7) | (fmt_ab << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+// the same with both operands MN-major (bits 15 and 16)
+__host__ __device__ constexpr uint32_t instr_desc_mnmajor(uint32_t fmt_ab, uint32_t M, uint32_t N) {
+    return instr_desc(fmt_ab, M, N) | (1u << 15) | (1u << 16);
 }
 
 // byte offset of 16-byte chunk `c` of row `r` inside a K-major tile with 64-byte rows and
