@@ -27,8 +27,8 @@ namespace gfilter {
 bool supported(int Cin, int Cout, int F);
 bool fits(int64_t Nf, int Cin, int Cout, int F, int precision);
 size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision);
-int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* input, const float* bary,
-                    const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream);
+int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
+                    const float* bary, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream);
 }  // namespace gfilter
 }  // namespace tc
 }  // namespace pb
@@ -110,8 +110,8 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
                PB200_EWORKSPACE, "facet2facet_backward: workspace too small");
     const bool tg = use_tc_gin(Cin, Cout, F, precision), tf = use_tc_gf(Nf, Cin, Cout, F, precision);
     if (tg || tf)
-        PB_REQUIRE(aligned16(gradOutput) && aligned16(workspace) && (NiK == 0 || aligned16(input)), PB200_EINVAL,
-                   "facet2facet_backward: gradOutput, input and workspace must be 16-byte aligned");
+        PB_REQUIRE(aligned16(gradOutput) && aligned16(workspace) && (NiK == 0 || (aligned16(input) && aligned16(bary))),
+                   PB200_EINVAL, "facet2facet_backward: gradOutput, input, bary and workspace must be 16-byte aligned");
     char* w = (char*)workspace;
     void* simt_ws = w;
     if (!(tg && tf)) w += f2f_simt_bwd_ws(Nf, Cin, Cout, F);
@@ -124,7 +124,7 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
         w += tc::gin::workspace_bytes(Cin, Cout, F, precision);
     }
     if (tf) {
-        int rc = tc::gfilter::backward_filter(Nf, Cin, Cout, F, gradOutput, input, bary, numInterior, gradFilter,
+        int rc = tc::gfilter::backward_filter(Nf, NiK, Cin, Cout, F, gradOutput, input, bary, numInterior, gradFilter,
                                               precision, w, stream);
         if (rc) return rc;
     }

@@ -5,15 +5,18 @@
 // The reduction runs over FACES, so faces are the K dimension of the tensor-core product
 // D[co, (d,kk)] += g^T[co, f] * A^T[(d,kk), f].  A CTA owns one group of 16 input channels
 // (its F*16 <= 512 accumulator columns live in TMEM for the whole kernel) and one contiguous
-// chunk of faces; per stage of 16 faces
-//   * 8 producer warps first copy the stage's raw rows (gradOutput rows, bary rows, the
-//     CTA's 16 input channels of every sample, sample ranges) from global memory with
-//     coalesced loads into a double-buffered raw area (two stages ahead of the math), then
-//     build both operands in shared memory MN-major (128-byte swizzle, 32-byte base): a face
-//     is a K-row whose 128-byte pieces hold 32 consecutive output channels (gradOutput block)
-//     or 32 consecutive (basis, channel) columns (A block), so that neither operand is
-//     transposed and every thread stores 16-byte vectors -- thread = (face, 8 channels), a
-//     warp walks its share of the F bases;
+// chunk of faces.  Per stage of 16 faces three roles cooperate through mbarriers:
+//   * two loader warps fill a ring of raw buffers: one writes a record per face (first
+//     sample, sample count, 1/T) and fetches the stage's bary block with one bulk copy, the
+//     other fetches the CTA's 16 input channels of every sample with 16-byte asynchronous
+//     copies into per-face slots; the sample ranges they need are loaded three stages ahead;
+//   * the compute warps turn a raw buffer into both operands in shared memory, MN-major
+//     (128-byte swizzle, 32-byte base): a face is a K-row whose 128-byte pieces hold 32
+//     consecutive output channels (gradOutput block) or 32 consecutive (basis, channel)
+//     columns (A block), so neither operand is transposed and every store is a 16-byte
+//     vector.  Work unit = 16 columns x 16 faces (thread = face x 8 columns): 8 units of
+//     the gradOutput block (read straight from global memory into registers, two stages
+//     ahead) and F units (one per basis) of the A block, dealt round-robin;
 //   * one thread issues tcgen05.mma (M = 128 output channels, N = F*16 in chunks of <= 256,
 //     K = 8 faces per instruction) and commits the stage back.
 // At the end the accumulator is drained once into partial[chunk] (final gradFilter layout);
@@ -35,27 +38,52 @@ using namespace ptx;
 constexpr int UM = 128;                       // output channels (UMMA M), Cout zero-padded
 constexpr int CG = 16;                        // input channels per CTA
 constexpr int KF = 16;                        // faces per stage (four groups of 4 K-rows, two per instruction)
-constexpr int PWARPS = 8;
-constexpr int NTHREADS = (PWARPS + 1) * 32;   // + MMA warp
+constexpr int CWARPS = 12;                    // compute warps 0..CWARPS-1 (a multiple of 4, at least 8)
+constexpr int REC_WARP = CWARPS;              // loader: face records + bary block
+constexpr int X_WARP = CWARPS + 1;            // loader: sample rows
+constexpr int MMA_WARP = CWARPS + 2;
+constexpr int NTHREADS = (CWARPS + 3) * 32;
+constexpr int GUNITS = UM / 16;               // work units of the gradOutput block
+constexpr int UMAX = (GUNITS + 32 + CWARPS - 1) / CWARPS;   // units per warp at most (F <= 32)
 constexpr int ATOM_BYTES = 512;               // 4 K-rows x 128 bytes (32 M/N elements)
 constexpr int G_SBO = (UM / 32) * ATOM_BYTES; // gradOutput block: [4-face group][32-channel block][atom]
 constexpr int G_TILE_BYTES = (KF / 4) * G_SBO;
-constexpr int TREG = 4;
-// raw staging area of one stage (double-buffered)
-constexpr int RAW_SAMPLES = 64;               // samples of a stage that are staged (16 faces x 4)
-constexpr int RAW_G_PITCH = UM + 4;           // floats per gradOutput row (pitch = 4 mod 32: conflict-free 16-byte reads)
+constexpr int TREG = 4;                       // samples per face on the fast path
 __host__ __device__ constexpr int at_blocks(int F) { return (F * CG + 31) / 32; }   // 32-column blocks of the A operand
-constexpr int RAW_X_PITCH = 20;               // floats per sample row (16 channels + pad)
-constexpr int RAW_G_BYTES = KF * RAW_G_PITCH * 4;
-constexpr int RAW_X_BYTES = (RAW_SAMPLES + TREG) * RAW_X_PITCH * 4;   // + pad rows read (and masked) by short faces
-constexpr int RAW_B_BYTES = (RAW_SAMPLES + TREG) * 32 * 4;   // F <= 32
-constexpr int RAW_B_ITERS = RAW_SAMPLES * 32 / 256;       // 8 floats per thread at most
-constexpr int RAW_X_OFF = RAW_G_BYTES;
-constexpr int RAW_B_OFF = RAW_X_OFF + RAW_X_BYTES;
-constexpr int RAW_C_OFF = RAW_B_OFF + RAW_B_BYTES;
-constexpr int RAW_BYTES = (RAW_C_OFF + 128 + 127) / 128 * 128;
 
-// one operand element: tf32-rounded (1 split) or hi + lo (2 splits, lo block `lo_off` bytes further)
+// one raw buffer: what a stage needs from global memory, as it lies there
+constexpr int RAW_SAMPLES = 64;               // samples of a stage that are staged (16 faces x 4)
+// Sample rows are staged per face: slot fl*4 + t (128 bytes) holds the CTA's 16 channels of
+// sample t of face fl as four 16-byte pieces, piece q at chunk q ^ (fl & 7) -- the 8 lanes of
+// a quarter warp (8 faces) then read 8 distinct bank groups.
+constexpr int RAW_X_SLOT = 128;
+constexpr int RAW_X_BYTES = KF * TREG * RAW_X_SLOT;
+constexpr int RAW_B_BYTES = ((RAW_SAMPLES + TREG) * 32 + 4) * 4;      // F <= 32; + the shift of a 16-byte aligned start
+constexpr int RAW_REC_BYTES = KF * 16 + 32;   // per face {first sample - ks0, T, 1/T, first sample}; then {slow, shift, ks0, ns}
+constexpr int RAW_X_OFF = 0;
+constexpr int RAW_B_OFF = RAW_X_OFF + RAW_X_BYTES;
+constexpr int RAW_REC_OFF = RAW_B_OFF + RAW_B_BYTES;
+constexpr int RAW_BYTES = (RAW_REC_OFF + RAW_REC_BYTES + 127) / 128 * 128;
+static_assert(RAW_X_OFF % 16 == 0 && RAW_B_OFF % 16 == 0 && RAW_REC_OFF % 16 == 0, "copy destinations are 16-byte aligned");
+
+// 16-byte asynchronous copy global -> shared (no register staging), and the arrival of all
+// such copies of the calling thread on an mbarrier (counted in the barrier's expected arrivals)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void sts_i4(uint32_t a, int x, int y, int z, int w) {
+    asm volatile("st.shared.v4.s32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ int4 lds_i4(uint32_t a) {
+    int4 v;
+    asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+
+// four operand elements: tf32-rounded (1 split) or hi + lo (2 splits, lo block `lo_off` bytes further)
 template <int NSPLIT>
 __device__ __forceinline__ void put4(uint32_t a, uint32_t lo_off, const float4& v) {
     if (NSPLIT == 1) {
@@ -67,13 +95,25 @@ __device__ __forceinline__ void put4(uint32_t a, uint32_t lo_off, const float4& 
     }
 }
 
+// one whole warp waits on an mbarrier phase: every lane probes once, then lane 0 waits (bounded)
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity) ? 1 : 0)) return true;
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) (void)mbar_try_wait(bar, parity);   // every lane observes the completed phase itself
+    return ok != 0;
+}
+
 struct Params {
     int64_t Nf;
+    int64_t nbary;            // floats in the bary array (samples * F)
     int Cin, Cout, F;
     int ncg;                  // channel groups = Cin / 16
     int nchunks;              // face chunks
     int64_t stages_per_chunk; // 16-face stages per chunk
-    int nstages;              // ring depth
+    int nstages;              // operand ring depth
+    int nraw;                 // raw ring depth
     const float* gout;
     const float* in;
     const float* bary;
@@ -87,29 +127,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int S = p.nstages, F = p.F, Cin = p.Cin, Cout = p.Cout;
-    const int NR = F * CG;                                   // accumulator columns / A^T rows
+    const int S = p.nstages, NRAW = p.nraw, F = p.F, Cin = p.Cin, Cout = p.Cout;
+    const int NR = F * CG;                                   // accumulator columns / A columns
     const uint32_t at_sbo = (uint32_t)at_blocks(F) * ATOM_BYTES;             // A block: [4-face group][32-column block][atom]
     const size_t at_bytes = (KF / 4) * (size_t)at_sbo;
     const size_t stage_bytes = (size_t)NSPLIT * (G_TILE_BYTES + at_bytes);   // [g hi][g lo?][A hi][A lo?]
     uint8_t* stages = smem;
-    uint8_t* raw = smem + (size_t)S * stage_bytes;            // [2][RAW_BYTES]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + 2 * RAW_BYTES);
-    uint64_t* full = bars;                // [S] 8 producer warps
-    uint64_t* empty = bars + S;           // [S] MMA done with the stage
-    uint64_t* acc_done = bars + 2 * S;    // all MMAs of the CTA complete
-    uint64_t* raw_ready = bars + 2 * S + 1;   // raw rows of a stage staged by all 8 warps
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2);
+    uint8_t* raw = smem + (size_t)S * stage_bytes;            // [NRAW][RAW_BYTES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(raw + (size_t)NRAW * RAW_BYTES);
+    uint64_t* full = bars;                        // [S]    operands of a stage written by all compute warps
+    uint64_t* empty = bars + S;                   // [S]    MMA done with the stage
+    uint64_t* raw_ready = bars + 2 * S;           // [NRAW] copies of a raw buffer landed, records written
+    uint64_t* raw_free = bars + 2 * S + NRAW;     // [NRAW] all compute warps done with a raw buffer
+    uint64_t* acc_done = bars + 2 * S + 2 * NRAW; // all MMAs of the CTA complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&full[s], PWARPS); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], CWARPS); mbar_init(&empty[s], 1); }
+        // the sample-row warp's 32 asynchronous-copy arrivals + the record warp's arrival that
+        // announces the bulk-copy bytes
+        for (int r = 0; r < NRAW; ++r) { mbar_init(&raw_ready[r], 33); mbar_init(&raw_free[r], CWARPS); }
         mbar_init(acc_done, 1);
-        mbar_init(raw_ready, PWARPS);
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == PWARPS) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    // Pad rows and pad columns of the raw buffers are read (their products are masked) but never
+    // written by a copy: clear the buffers once so that they hold finite values.  The copies that
+    // overwrite them later go through the asynchronous proxy.
+    for (int i = tid; i < NRAW * RAW_BYTES / 4; i += NTHREADS) reinterpret_cast<float*>(raw)[i] = 0.f;
+    fence_proxy_async();
+    if (warp == MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -122,251 +170,217 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     int64_t st1 = st0 + p.stages_per_chunk;
     if (st1 > total_stages) st1 = total_stages;
     const int64_t nst = st1 > st0 ? st1 - st0 : 0;
+    const uint32_t raw32 = smem_u32(raw), stages32 = smem_u32(stages);
 
-    if (warp < PWARPS) {
-        // ==================================== producers ====================================
-        const int half = lane >> 4, fl = lane & 15;           // 8-channel half, face of the stage
-        constexpr int DMAX = 4;                               // bases per warp: ceil(32 / PWARPS)
-        // This thread's 8 consecutive columns 16*g + 8*half (g = warp for the gradOutput block,
-        // g = basis d = warp + 8 i for the A block) of K-row fl are 32-byte chunk j of 32-column
-        // block g>>1; chunk j of K-row k is stored at chunk j ^ (k & 3).  A quarter warp (faces
-        // 0..7 or 8..15, same j) covers two 4-face groups whose lanes would meet in the same
-        // 16-byte bank group: the lanes with fl & 4 keep their two 4-channel halves swapped in
-        // registers (`sw`), so the first store of a pair lands in the other half of the chunk.
-        const uint32_t j32 = 2u * (uint32_t)(warp & 1) + (uint32_t)half;
-        const uint32_t sw = (fl & 4) ? 16u : 0u;
-        const uint32_t toff = (uint32_t)(warp >> 1) * ATOM_BYTES + (uint32_t)(fl & 3) * 128u + ((j32 ^ (uint32_t)(fl & 3)) << 5) + sw;
-        const uint32_t g_off = (uint32_t)(fl >> 2) * G_SBO + toff;
-        const uint32_t a_off = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(fl >> 2) * at_sbo + toff;
-        const int ptid = tid;
-        const uint32_t raw32 = smem_u32(raw), stages32 = smem_u32(stages);
-        // the pad rows behind the staged windows are read (their products are masked) but never
-        // written by raw_store: clear both buffers once so they hold finite values
-        for (int i = tid; i < 2 * RAW_BYTES / 4; i += PWARPS * 32) reinterpret_cast<float*>(raw)[i] = 0.f;
-        asm volatile("bar.sync 1, %0;" ::"n"(PWARPS * 32) : "memory");                                 // 0..255 over the producer warps
-        // ---- raw staging: what stage `st` needs, copied with coalesced loads
-        struct RawRegs { float4 g[2]; float4 x; float b[RAW_B_ITERS]; int cumv; int ks0, ns; };
-        // sample range [ks0, ks1) of stage `st`: loaded one stage before the loads that depend on
-        // it are issued, so that no warp ever waits on this (dependent) load
-        auto ks_pair = [&](int64_t st) -> int2 {
-            if (st >= nst) return make_int2(0, 0);
-            const int64_t f0 = (st0 + st) * KF;
-            const int64_t fe = f0 + KF < p.Nf ? f0 + KF : p.Nf;
-            return make_int2(f0 > 0 ? __ldg(p.cum + f0 - 1) : 0, __ldg(p.cum + fe - 1));
+    if (warp == REC_WARP || warp == X_WARP) {
+        // ===================================== loaders =====================================
+        // lane l holds cum[f0 - 1 + l] of a stage (l = 0..16): the sample ranges of its 16 faces.
+        // Both loader warps keep the values of the next three stages in registers.
+        auto load_cum = [&](int64_t st) -> int {
+            if (st >= nst || lane > KF) return 0;
+            int64_t fi = (st0 + st) * KF - 1 + lane;
+            if (fi < 0) return 0;
+            if (fi > p.Nf - 1) fi = p.Nf - 1;
+            return __ldg(p.cum + fi);
         };
-        auto raw_issue = [&](int64_t st, int2 ks) -> RawRegs {
-            RawRegs R;
-            R.g[0] = R.g[1] = zero4(); R.x = zero4(); R.cumv = 0; R.ks0 = 0; R.ns = 0;
-#pragma unroll
-            for (int i = 0; i < RAW_B_ITERS; ++i) R.b[i] = 0.f;
-            if (st >= nst) return R;
+        int cv = load_cum(0), cv1 = load_cum(1), cv2 = load_cum(2);
+        int rbuf = 0;
+        uint32_t rph = 0;
+        for (int64_t st = 0; st < nst; ++st) {
+            const int cv3 = load_cum(st + 3);                // in flight for three stages
+            if (!warp_wait(&raw_free[rbuf], rph ^ 1u, abort_flag, lane)) break;
+            const uint32_t rb32 = raw32 + (uint32_t)rbuf * RAW_BYTES;
+            uint64_t* bar = &raw_ready[rbuf];
             const int64_t f0 = (st0 + st) * KF;
-            const int64_t fe = f0 + KF < p.Nf ? f0 + KF : p.Nf;         // one past the stage's last face
-            const int ks0 = ks.x, ks1 = ks.y;
+            const int nvf = p.Nf - f0 < KF ? (int)(p.Nf - f0) : KF;          // faces of the stage
+            const int ks0 = __shfl_sync(0xffffffffu, cv, 0), ks1 = __shfl_sync(0xffffffffu, cv, nvf);
+            const int k1 = __shfl_down_sync(0xffffffffu, cv, 1);
+            const bool face = lane < nvf;
+            const int T = face ? k1 - cv : 0, kloc = face ? cv - ks0 : 0;
             int ns = ks1 - ks0;
             if (ns > RAW_SAMPLES) ns = RAW_SAMPLES;
-            R.ks0 = ks0; R.ns = ns;
-            // gradOutput rows: 16 faces x Cout floats, contiguous in global memory
-            const int c4n = Cout >> 2;
-#pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int idx = ptid + i * 256;
-                const int fr = idx / 32, c4 = idx - fr * 32;             // up to 128 channels = 32 float4 per row
-                if (f0 + fr < fe && c4 < c4n)
-                    R.g[i] = ldg4(reinterpret_cast<const float4*>(p.gout + (f0 + fr) * Cout) + c4);
-            }
-            // this CTA's 16 input channels of every sample: thread = (sample, 16-byte quarter)
-            {
-                const int sr = ptid >> 2, qd = ptid & 3;
-                if (sr < ns) R.x = ldg4(reinterpret_cast<const float4*>(p.in + (int64_t)(ks0 + sr) * Cin + cgp * CG) + qd);
-            }
-            // bary rows of the stage's samples: one contiguous block of ns*F floats
-            {
-                const float* src = p.bary + (int64_t)ks0 * F;
-                const int nb = ns * F;
-#pragma unroll
-                for (int i = 0; i < RAW_B_ITERS; ++i) {
-                    const int idx = ptid + i * 256;
-                    if (idx < nb) R.b[i] = __ldg(src + idx);
+            const int slow = __any_sync(0xffffffffu, (T > TREG) || (kloc + T > ns)) ? 1 : 0;
+            const int64_t bfirst = (int64_t)ks0 * F;                          // first bary float of the stage
+            const int64_t a0 = bfirst & ~(int64_t)3;                          // 16-byte aligned start
+            const int bshift = (int)(bfirst - a0);
+            int nb4 = (ns * F + bshift + 3) >> 2;                             // 16-byte pieces wanted
+            const int64_t avail4 = (p.nbary - a0) >> 2;                       // whole pieces the array still holds
+            int tail = 0;                                                     // floats behind the last whole piece
+            if (nb4 > avail4) { tail = (int)(p.nbary - a0 - avail4 * 4); nb4 = (int)avail4; }
+            if (warp == REC_WARP) {
+                if (lane < KF) sts_i4(rb32 + RAW_REC_OFF + lane * 16, kloc, T, __float_as_int(T > 0 ? 1.f / (float)T : 0.f), cv);
+                if (lane == KF) sts_i4(rb32 + RAW_REC_OFF + KF * 16, slow, bshift, ks0, ns);
+                if (lane < tail) sts_f32(rb32 + RAW_B_OFF + (uint32_t)(nb4 * 4 + lane) * 4u, __ldg(p.bary + a0 + nb4 * 4 + lane));
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar, (uint32_t)(nb4 * 16));
+                    if (nb4 > 0) bulk_g2s(raw + (size_t)rbuf * RAW_BYTES + RAW_B_OFF, p.bary + a0, (uint32_t)(nb4 * 16), bar);
                 }
-            }
-            if (ptid <= KF) {                                            // cum[f0-1 .. f0+15]
-                const int64_t fi = f0 - 1 + ptid;
-                R.cumv = fi < 0 ? 0 : (fi < p.Nf ? __ldg(p.cum + fi) : __ldg(p.cum + p.Nf - 1));
-            }
-            return R;
-        };
-        auto raw_store = [&](const RawRegs& R, int buf) {
-            uint8_t* rb = raw + (size_t)buf * RAW_BYTES;
-            float* g_raw = reinterpret_cast<float*>(rb);
-            float* x_raw = reinterpret_cast<float*>(rb + RAW_X_OFF);
-            float* b_raw = reinterpret_cast<float*>(rb + RAW_B_OFF);
-            int* c_raw = reinterpret_cast<int*>(rb + RAW_C_OFF);
+            } else {
+                // this CTA's 16 input channels of the first TREG samples of every face:
+                // (face, sample, 16-byte quarter) per lane
+                const float* xsrc = p.in + cgp * CG;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int idx = ptid + i * 256;
-                const int fr = idx / 32, c4 = idx - fr * 32;
-                *reinterpret_cast<float4*>(g_raw + fr * RAW_G_PITCH + c4 * 4) = R.g[i];
+                for (int i = 0; i < KF * TREG * 4 / 32; ++i) {
+                    const int idx = lane + i * 32, qd = idx & 3, t = (idx >> 2) & 3, xf = idx >> 4;
+                    const int Tf = __shfl_sync(0xffffffffu, T, xf), kf = __shfl_sync(0xffffffffu, cv, xf);
+                    if (t < Tf && !slow)
+                        cp_async16(rb32 + RAW_X_OFF + (uint32_t)((xf * TREG + t) * RAW_X_SLOT + ((qd ^ (xf & 7)) << 4)),
+                                   xsrc + (int64_t)(kf + t) * Cin + qd * 4);
+                }
+                cp_async_arrive(bar);
             }
-            {
-                const int sr = ptid >> 2, qd = ptid & 3;
-                *reinterpret_cast<float4*>(x_raw + sr * RAW_X_PITCH + qd * 4) = R.x;
-            }
-#pragma unroll
-            for (int i = 0; i < RAW_B_ITERS; ++i) b_raw[ptid + i * 256] = R.b[i];
-            if (ptid <= KF) c_raw[ptid] = R.cumv;
-            if (ptid == KF + 1) c_raw[KF + 1] = R.ks0;
-            if (ptid == KF + 2) c_raw[KF + 2] = R.ns;
-        };
-        auto raw_publish = [&]() {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(raw_ready);
-        };
-
-        int si = 0;
-        uint32_t sph = 0;
-        bool alive = true;
-        // Global loads run two stages ahead of the stage being computed (their registers are
-        // parked for one stage), the sample-range loads three stages ahead.
-        {
-            RawRegs R0 = raw_issue(0, ks_pair(0));
-            raw_store(R0, 0);
-            raw_publish();
+            cv = cv1; cv1 = cv2; cv2 = cv3;
+            if (++rbuf == NRAW) { rbuf = 0; rph ^= 1u; }
         }
-        RawRegs Rn = raw_issue(1, ks_pair(1));
-        int2 ksn = ks_pair(2);
-        for (int64_t st = 0; st < nst && alive; ++st) {
-            const RawRegs Rn2 = raw_issue(st + 2, ksn);
-            ksn = ks_pair(st + 3);
-            {
-                int ok = 1;
-                if (lane == 0) ok = mbar_wait(raw_ready, (uint32_t)(st & 1), abort_flag) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) { alive = false; break; }
-            }
-            const uint32_t rb32 = raw32 + (uint32_t)(st & 1) * RAW_BYTES;
+    } else if (warp < CWARPS) {
+        // ================================== compute warps ==================================
+        const int half = lane >> 4, fl = lane & 15;           // 8-column half of a unit, face of the stage
+        // This thread's 8 consecutive columns 16*g + 8*half of K-row fl (g = unit of the
+        // gradOutput block, or basis d of the A block) are 32-byte chunk j of 32-column block
+        // g>>1; chunk j of K-row k is stored at chunk j ^ (k & 3).  All units of a warp have the
+        // parity of the warp index, so j is fixed per thread.  A quarter warp (faces 0..7 or
+        // 8..15, same j) covers two 4-face groups whose lanes would meet in the same 16-byte
+        // bank group: the lanes with fl & 4 keep their two 4-column halves swapped in registers
+        // (`sw`), so the first store of a pair lands in the other half of the chunk.
+        const uint32_t j32 = 2u * (uint32_t)(warp & 1) + (uint32_t)half;
+        const uint32_t sw = (fl & 4) ? 16u : 0u;
+        const uint32_t tcol = (uint32_t)(fl & 3) * 128u + ((j32 ^ (uint32_t)(fl & 3)) << 5) + sw;
+        const uint32_t g_off = (uint32_t)(fl >> 2) * G_SBO + (uint32_t)(warp >> 1) * ATOM_BYTES + tcol;
+        // unit u = warp + CWARPS i is basis d = u - 8: column block (d >> 1) = (warp >> 1) - 4 + (CWARPS / 2) i
+        const uint32_t a_off = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(fl >> 2) * at_sbo + tcol
+                               + (uint32_t)(warp >> 1) * ATOM_BYTES - 4u * ATOM_BYTES;
+        bool has_basis = false;
+#pragma unroll
+        for (int i = 0; i < UMAX; ++i) {
+            const int d = warp - GUNITS + i * CWARPS;
+            has_basis = has_basis || (d >= 0 && d < F);
+        }
+        // gradOutput rows of a unit: 32 bytes per thread straight from global memory
+        const bool g_warp = warp < GUNITS;
+        const int gco = warp * 16 + half * 8;                 // first channel of this thread
+        auto load_g = [&](int64_t st, float4& u, float4& w) {
+            u = zero4(); w = zero4();
             const int64_t f = (st0 + st) * KF + fl;
-            const bool valid = f < p.Nf;
-            const int k0 = valid ? lds_i32(rb32 + RAW_C_OFF + fl * 4) : 0;
-            const int T = valid ? lds_i32(rb32 + RAW_C_OFF + (fl + 1) * 4) - k0 : 0;
-            const int ks0 = lds_i32(rb32 + RAW_C_OFF + (KF + 1) * 4), ns = lds_i32(rb32 + RAW_C_OFF + (KF + 2) * 4);
-            const int kloc = valid ? k0 - ks0 : 0;             // lanes past the last face read row 0 (masked)
-            const float invT = T > 0 ? 1.f / (float)T : 0.f;
-            // lean path: every face of the stage has at most TREG samples, all of them staged
-            const bool slow = __any_sync(0xffffffffu, (T > TREG) || (kloc + T > ns));
-            // wait for the operand stage to be free
-            if (!mbar_try_wait(&empty[si], sph ^ 1u)) {
-                int ok = 1;
-                if (lane == 0) ok = mbar_wait(&empty[si], sph ^ 1u, abort_flag) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) { alive = false; break; }
-            }
-            // shared-window addresses of this thread's first 16-byte store in the gradOutput block
-            // and in the A block (basis d = warp + 8 i sits 4 column blocks = 2 KB further on per i);
-            // the second store is the other half of the same 32-byte chunk
+            if (!g_warp || st >= nst || f >= p.Nf) return;
+            const float* src = p.gout + f * Cout + gco;
+            const int cu = (int)(sw >> 2), cw = 4 - cu;       // the two 4-channel halves (swapped where sw is set)
+            if (gco + cu < Cout) u = ldg4(reinterpret_cast<const float4*>(src + cu));
+            if (gco + cw < Cout) w = ldg4(reinterpret_cast<const float4*>(src + cw));
+        };
+        float4 gu0, gw0, gu1, gw1;                            // stages st and st + 1
+        load_g(0, gu0, gw0);
+        load_g(1, gu1, gw1);
+        int si = 0, rbuf = 0;
+        uint32_t sph = 0, rph = 0;
+        bool alive = true;
+        for (int64_t st = 0; st < nst; ++st) {
+            float4 gu2, gw2;
+            load_g(st + 2, gu2, gw2);
+            if (!warp_wait(&raw_ready[rbuf], rph, abort_flag, lane)) { alive = false; break; }
+            const uint32_t rb32 = raw32 + (uint32_t)rbuf * RAW_BYTES;
+            const int4 rec = lds_i4(rb32 + RAW_REC_OFF + fl * 16);           // {kloc, T, 1/T, first sample}
+            const int4 info = lds_i4(rb32 + RAW_REC_OFF + KF * 16);          // {slow, shift, ks0, ns}
+            const int kloc = rec.x, T = rec.y;
+            const float invT = __int_as_float(rec.z);
+            if (!warp_wait(&empty[si], sph ^ 1u, abort_flag, lane)) { alive = false; break; }
             const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes;
-            const uint32_t ga32 = sb32 + g_off, aa32 = sb32 + a_off;
-            if (!slow) {
-                float x[TREG][8];
-                {
-                    const uint32_t xa = rb32 + RAW_X_OFF + (uint32_t)kloc * (RAW_X_PITCH * 4) + (uint32_t)half * 32u;
-                    const uint32_t xu = xa + sw, xw = xa + (16u - sw);
+            if (g_warp) {
+                // a unit of the gradOutput block: a plain (split) copy of 16 channels x 16 faces
+                put4<NSPLIT>(sb32 + g_off, G_TILE_BYTES, gu0);
+                put4<NSPLIT>((sb32 + g_off) ^ 16u, G_TILE_BYTES, gw0);
+            }
+            gu0 = gu1; gw0 = gw1; gu1 = gu2; gw1 = gw2;
+            if (has_basis) {
+                const uint32_t aa32 = sb32 + a_off;
+                if (!info.x) {
+                    // fast path: every face of the stage has at most TREG samples, all of them staged
+                    // (rows behind a face's last sample belong to other faces or are stale: their
+                    // weight is zero, so they only matter if the input holds non-finite values)
+                    float2 x[TREG][4];
+                    float wt[TREG];
+                    {
+                        const uint32_t xa = rb32 + RAW_X_OFF + (uint32_t)fl * (TREG * RAW_X_SLOT);
+                        const uint32_t qu = 2u * (uint32_t)half + (sw >> 4);            // 16-byte quarter held first
+                        const uint32_t xu = xa + ((qu ^ (uint32_t)(fl & 7)) << 4), xw = xa + (((qu ^ 1u) ^ (uint32_t)(fl & 7)) << 4);
 #pragma unroll
-                    for (int t = 0; t < TREG; ++t) {
-                        const float4 u = lds_f4(xu + t * (RAW_X_PITCH * 4)), w = lds_f4(xw + t * (RAW_X_PITCH * 4));
-                        x[t][0] = u.x; x[t][1] = u.y; x[t][2] = u.z; x[t][3] = u.w;
-                        x[t][4] = w.x; x[t][5] = w.y; x[t][6] = w.z; x[t][7] = w.w;
+                        for (int t = 0; t < TREG; ++t) {
+                            const float4 u = lds_f4(xu + t * RAW_X_SLOT), w = lds_f4(xw + t * RAW_X_SLOT);
+                            x[t][0] = make_float2(u.x, u.y); x[t][1] = make_float2(u.z, u.w);
+                            x[t][2] = make_float2(w.x, w.y); x[t][3] = make_float2(w.z, w.w);
+                            wt[t] = t < T ? invT : 0.f;
+                        }
                     }
-                }
-                {
-                    const uint32_t ga = rb32 + (uint32_t)fl * (RAW_G_PITCH * 4) + (uint32_t)(warp * 16 + half * 8) * 4u;
-                    const float4 u = lds_f4(ga + sw), w = lds_f4(ga + (16u - sw));
-                    put4<NSPLIT>(ga32, G_TILE_BYTES, u);
-                    put4<NSPLIT>(ga32 ^ 16u, G_TILE_BYTES, w);
-                }
-                const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(kloc * F) * 4u;
+                    const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(info.y + kloc * F) * 4u;
 #pragma unroll
-                for (int i = 0; i < DMAX; ++i) {
-                    const int d = warp + i * PWARPS;
-                    if (d < F) {
+                    for (int i = 0; i < UMAX; ++i) {
+                        const int d = warp - GUNITS + i * CWARPS;
+                        if (d >= 0 && d < F) {
+                            float2 a[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) a[j] = make_float2(0.f, 0.f);
+#pragma unroll
+                            for (int t = 0; t < TREG; ++t) {
+                                const float b = lds_f32(ba + (uint32_t)(t * F + d) * 4u) * wt[t];
+                                const float2 b2 = make_float2(b, b);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) a[j] = __ffma2_rn(b2, x[t][j], a[j]);
+                            }
+                            const uint32_t da32 = aa32 + (uint32_t)i * ((CWARPS / 2) * ATOM_BYTES);
+                            put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0].x, a[0].y, a[1].x, a[1].y));
+                            put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[2].x, a[2].y, a[3].x, a[3].y));
+                        }
+                    }
+                } else {
+                    // generic path, straight from global memory (halves swapped where sw is set)
+                    const int k0 = rec.w, jsw = (int)(sw >> 2);
+                    for (int i = 0; i < UMAX; ++i) {
+                        const int d = warp - GUNITS + i * CWARPS;
+                        if (d < 0 || d >= F) continue;
                         float a[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) a[j] = 0.f;
+                        for (int t = 0; t < T; ++t) {
+                            const float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
+                            const float* xr = p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8;
 #pragma unroll
-                        for (int t = 0; t < TREG; ++t) {
-                            float b = lds_f32(ba + (uint32_t)(t * F + d) * 4u);
-                            b = t < T ? b * invT : 0.f;
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) a[j] = fmaf(b, x[t][j], a[j]);
+                            for (int j = 0; j < 8; ++j) a[j] = fmaf(b, __ldg(xr + (j ^ jsw)), a[j]);
                         }
-                        const uint32_t da32 = aa32 + (uint32_t)i * (4u * ATOM_BYTES);
+                        const uint32_t da32 = aa32 + (uint32_t)i * ((CWARPS / 2) * ATOM_BYTES);
                         put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
                         put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[4], a[5], a[6], a[7]));
                     }
                 }
-            } else {
-                // generic path, straight from global memory
-                float g8[8];
-                const int co0 = warp * 16 + half * 8;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int co = co0 + (j ^ (int)(sw >> 2));                 // halves swapped where sw is set
-                    g8[j] = (valid && co < Cout) ? __ldg(p.gout + f * Cout + co) : 0.f;
-                }
-                put4<NSPLIT>(ga32, G_TILE_BYTES, make_float4(g8[0], g8[1], g8[2], g8[3]));
-                put4<NSPLIT>(ga32 ^ 16u, G_TILE_BYTES, make_float4(g8[4], g8[5], g8[6], g8[7]));
-                for (int d = warp; d < F; d += PWARPS) {
-                    float a[8];
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) a[j] = 0.f;
-                    for (int t = 0; t < T; ++t) {
-                        const float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
-                        const float* xr = p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) a[j] = fmaf(b, __ldg(xr + (j ^ (int)(sw >> 2))), a[j]);
-                    }
-                    const uint32_t da32 = aa32 + (uint32_t)((d - warp) >> 3) * (4u * ATOM_BYTES);
-                    put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
-                    put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[4], a[5], a[6], a[7]));
-                }
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&full[si]);
+            if (lane == 0) { mbar_arrive(&full[si]); mbar_arrive(&raw_free[rbuf]); }
             if (++si == S) { si = 0; sph ^= 1u; }
-            // every warp has passed raw_ready(st), so nobody reads the other raw buffer any more
-            raw_store(Rn, (int)((st + 1) & 1));
-            raw_publish();
-            Rn = Rn2;
+            if (++rbuf == NRAW) { rbuf = 0; rph ^= 1u; }
         }
         // ==================================== drain ====================================
-        if (alive) {
-            int ok = 1;
-            if (lane == 0) ok = mbar_wait(acc_done, 0u, abort_flag) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (ok) {
-                tc_fence_after();
-                const int q = warp & 3, hcol = warp >> 2;       // TMEM lane quadrant, half of the 32-column groups
-                const int co = q * 32 + lane;
-                float* out = p.partial + (int64_t)chunk * Cout * Cin * F;
-                const int ngroups = (NR + 31) / 32;
-                for (int gi = hcol; gi < ngroups; gi += 2) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 32), r);
-                    tmem_ld_wait();
-                    if (co < Cout) {
+        if (alive && warp_wait(acc_done, 0u, abort_flag, lane)) {
+            tc_fence_after();
+            const int q = warp & 3, hcol = warp >> 2;       // TMEM lane quadrant, third of the 32-column groups
+            const int co = q * 32 + lane;
+            float* out = p.partial + (int64_t)chunk * Cout * Cin * F;
+            const int ngroups = (NR + 31) / 32;
+            for (int gi = hcol; gi < ngroups; gi += CWARPS / 4) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 32), r);
+                tmem_ld_wait();
+                if (co < Cout) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            int col = gi * 32 + j;
-                            if (col < NR) {
-                                int d = col / CG, kk = col - d * CG;
-                                out[((int64_t)co * Cin + cgp * CG + kk) * F + d] = nst > 0 ? __uint_as_float(r[j]) : 0.f;
-                            }
+                    for (int j = 0; j < 32; ++j) {
+                        int col = gi * 32 + j;
+                        if (col < NR) {
+                            int d = col / CG, kk = col - d * CG;
+                            out[((int64_t)co * Cin + cgp * CG + kk) * F + d] = nst > 0 ? __uint_as_float(r[j]) : 0.f;
                         }
                     }
                 }
-                tc_fence_before();
             }
+            tc_fence_before();
         }
     } else {
         // ==================================== MMA issuer ====================================
@@ -374,8 +388,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             const int n1 = NR < 256 ? NR : 256, n2 = NR - n1;
             const uint32_t idesc1 = instr_desc_mnmajor(FMT_TF32, UM, (uint32_t)n1);
             const uint32_t idesc2 = instr_desc_mnmajor(FMT_TF32, UM, (uint32_t)(n2 > 0 ? n2 : 16));
-            const uint64_t dbase_g = smem_desc_mnmajor_b32(smem_u32(stages), ATOM_BYTES, G_SBO);
-            const uint64_t dbase_a = smem_desc_mnmajor_b32(smem_u32(stages) + NSPLIT * G_TILE_BYTES, ATOM_BYTES, at_sbo);
+            const uint64_t dbase_g = smem_desc_mnmajor_b32(stages32, ATOM_BYTES, G_SBO);
+            const uint64_t dbase_a = smem_desc_mnmajor_b32(stages32 + NSPLIT * G_TILE_BYTES, ATOM_BYTES, at_sbo);
             int si = 0;
             uint32_t sph = 0;
             bool alive = true;
@@ -413,7 +427,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == PWARPS) tmem_dealloc(tmem_base, 512);
+    if (warp == MMA_WARP) tmem_dealloc(tmem_base, 512);
     if (tid == 0 && *abort_flag && p.async_err) {
         *p.async_err = 3;
         __threadfence_system();
@@ -421,7 +435,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 }
 
 // ---------------------------------------------------------------------------- host side
-struct Plan { int nsplit, ncg, nchunks, nstages; int64_t stages_per_chunk; size_t smem, partial_bytes; };
+struct Plan { int nsplit, ncg, nchunks, nstages, nraw; int64_t stages_per_chunk; size_t smem, partial_bytes; };
 
 bool supported(int Cin, int Cout, int F) {
     return Cin % CG == 0 && Cout % 4 == 0 && Cout >= 4 && Cout <= UM && F >= 1 && F <= 32;   // F*16 <= 512 columns
@@ -437,12 +451,15 @@ Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     if (nch > total_stages) nch = (int)total_stages;
     pl.stages_per_chunk = ceil_div(total_stages, nch);
     pl.nchunks = (int)ceil_div(total_stages, pl.stages_per_chunk);
-    size_t stage = (size_t)pl.nsplit * (G_TILE_BYTES + (KF / 4) * (size_t)at_blocks(F) * ATOM_BYTES);
-    int S = 4;
-    const size_t extra = 2 * (size_t)RAW_BYTES + 1024 + 256;
-    while (S > 2 && (size_t)S * stage + extra > 224 * 1024) --S;
+    const size_t stage = (size_t)pl.nsplit * (G_TILE_BYTES + (KF / 4) * (size_t)at_blocks(F) * ATOM_BYTES);
+    const size_t budget = 224 * 1024, fixed = 1024 + 256;
+    // operand ring as deep as fits beside a raw ring of 2 (at most 4), then the raw ring as deep as fits
+    int S = 4, R = 4;
+    while (S > 2 && (size_t)S * stage + 2 * (size_t)RAW_BYTES + fixed > budget) --S;
+    while (R > 2 && (size_t)S * stage + (size_t)R * RAW_BYTES + fixed > budget) --R;
     pl.nstages = S;
-    pl.smem = (size_t)S * stage + extra;
+    pl.nraw = R;
+    pl.smem = (size_t)S * stage + (size_t)R * RAW_BYTES + fixed;
     pl.partial_bytes = (size_t)pl.nchunks * Cout * Cin * F * sizeof(float);
     return pl;
 }
@@ -455,14 +472,15 @@ size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision) {
     return align_up(plan(Nf, Cin, Cout, F, precision).partial_bytes, 256);
 }
 
-int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* input, const float* bary,
-                    const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream) {
+int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
+                    const float* bary, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream) {
     int rc = check_async_error("facet2facet_backward");
     if (rc) return rc;
     Plan pl = plan(Nf, Cin, Cout, F, precision);
     Params p;
-    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F;
-    p.ncg = pl.ncg; p.nchunks = pl.nchunks; p.stages_per_chunk = pl.stages_per_chunk; p.nstages = pl.nstages;
+    p.Nf = Nf; p.nbary = NiK * F; p.Cin = Cin; p.Cout = Cout; p.F = F;
+    p.ncg = pl.ncg; p.nchunks = pl.nchunks; p.stages_per_chunk = pl.stages_per_chunk;
+    p.nstages = pl.nstages; p.nraw = pl.nraw;
     p.gout = gout; p.in = input; p.bary = bary; p.cum = cum; p.partial = (float*)ws;
     p.async_err = async_error_word();
     int grid = pl.ncg * pl.nchunks;

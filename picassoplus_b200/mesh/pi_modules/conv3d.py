@@ -38,6 +38,12 @@ def _check(t, name, dims, dtype):
         raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
 
 
+def _aligned16(t):
+    """The tensor-core kernels copy rows with 16-byte vector and bulk copies; a contiguous view
+    that starts off a 16-byte boundary (a slice of a larger tensor) is moved to fresh storage."""
+    return t if t.data_ptr() % 16 == 0 else t.clone()
+
+
 def _ws(nbytes, dev):
     return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=dev)
 
@@ -59,6 +65,7 @@ def facet2facet_forward(textureIn, filter, baryCoeff, numTexture):
         raise RuntimeError("Dimension of bary_coeff mismatches number of filters.")
     if baryCoeff.shape[0] != NiK:
         raise RuntimeError("The shape of bary_coeff should be (NiK, Dim)).")
+    textureIn = _aligned16(textureIn)
     dev = textureIn.device
     with torch.cuda.device(dev):
         out = torch.empty(Nf, Cout, dtype=textureIn.dtype, device=dev)
@@ -86,6 +93,7 @@ def facet2facet_backward(grad_output, textureIn, filter, baryCoeff, numTexture):
         raise RuntimeError("The shape of bary_coeff should be (NiK, Dim)).")
     if tuple(grad_output.shape) != (Nf, Cout):
         raise RuntimeError("grad_output must have shape (NfIn, out_channels)")
+    grad_output, textureIn, baryCoeff = _aligned16(grad_output), _aligned16(textureIn), _aligned16(baryCoeff)
     dev = textureIn.device
     with torch.cuda.device(dev):
         gin = torch.empty(NiK, Cin, dtype=textureIn.dtype, device=dev)
