@@ -26,7 +26,7 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
 namespace gfilter {
 bool supported(int Cin, int Cout, int F);
 bool fits(int64_t Nf, int Cin, int Cout, int F, int precision);
-size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision);
+size_t workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision);
 int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
                     const float* bary, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream);
 }  // namespace gfilter
@@ -86,7 +86,7 @@ size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int C
     const bool tg = use_tc_gin(Cin, Cout, F, precision), tf = use_tc_gf(Nf, Cin, Cout, F, precision);
     size_t n = (tg && tf) ? 0 : f2f_simt_bwd_ws(Nf, Cin, Cout, F);
     if (tg) n += tc::gin::workspace_bytes(Cin, Cout, F, precision);
-    if (tf) n += tc::gfilter::workspace_bytes(Nf, Cin, Cout, F, precision);
+    if (tf) n += tc::gfilter::workspace_bytes(Nf, NiK, Cin, Cout, F, precision);
     return n;
 }
 

@@ -38,13 +38,12 @@ using namespace ptx;
 constexpr int UM = 128;                       // output channels (UMMA M), Cout zero-padded
 constexpr int CG = 16;                        // input channels per CTA
 constexpr int KF = 16;                        // faces per stage (four groups of 4 K-rows, two per instruction)
-constexpr int CWARPS = 12;                    // compute warps 0..CWARPS-1 (a multiple of 4, at least 8)
+constexpr int CWARPS = 8;                     // compute warps 0..7: two faces x 16 channels each
 constexpr int REC_WARP = CWARPS;              // loader: face records + bary block
 constexpr int X_WARP = CWARPS + 1;            // loader: sample rows
 constexpr int MMA_WARP = CWARPS + 2;
 constexpr int NTHREADS = (CWARPS + 3) * 32;
-constexpr int GUNITS = UM / 16;               // work units of the gradOutput block
-constexpr int UMAX = (GUNITS + 32 + CWARPS - 1) / CWARPS;   // units per warp at most (F <= 32)
+static_assert(CWARPS * 16 == UM && CWARPS * 2 == KF, "one 16-channel gradOutput unit and two faces per compute warp");
 constexpr int ATOM_BYTES = 512;               // 4 K-rows x 128 bytes (32 M/N elements)
 constexpr int G_SBO = (UM / 32) * ATOM_BYTES; // gradOutput block: [4-face group][32-channel block][atom]
 constexpr int G_TILE_BYTES = (KF / 4) * G_SBO;
@@ -54,12 +53,12 @@ __host__ __device__ constexpr int at_blocks(int F) { return (F * CG + 31) / 32; 
 // one raw buffer: what a stage needs from global memory, as it lies there
 constexpr int RAW_SAMPLES = 64;               // samples of a stage that are staged (16 faces x 4)
 // Sample rows are staged per face: slot fl*4 + t (128 bytes) holds the CTA's 16 channels of
-// sample t of face fl as four 16-byte pieces, piece q at chunk q ^ (fl & 7) -- the 8 lanes of
-// a quarter warp (8 faces) then read 8 distinct bank groups.
+// sample t of face fl in its first (even fl) or second (odd fl) 64 bytes, so that the two
+// faces of a compute warp read different banks.
 constexpr int RAW_X_SLOT = 128;
 constexpr int RAW_X_BYTES = KF * TREG * RAW_X_SLOT;
-constexpr int RAW_B_BYTES = ((RAW_SAMPLES + TREG) * 32 + 4) * 4;      // F <= 32; + the shift of a 16-byte aligned start
-constexpr int RAW_REC_BYTES = KF * 16 + 32;   // per face {first sample - ks0, T, 1/T, first sample}; then {slow, shift, ks0, ns}
+constexpr int RAW_B_BYTES = (RAW_SAMPLES + TREG) * 32 * 4;            // bary rows padded to Fp <= 32 floats; + rows read (weight 0) by short faces
+constexpr int RAW_REC_BYTES = KF * 16 + 32;   // per face {first sample - ks0, T, 1/T, first sample}; then {slow, 0, ks0, ns}
 constexpr int RAW_X_OFF = 0;
 constexpr int RAW_B_OFF = RAW_X_OFF + RAW_X_BYTES;
 constexpr int RAW_REC_OFF = RAW_B_OFF + RAW_B_BYTES;
@@ -95,6 +94,21 @@ __device__ __forceinline__ void put4(uint32_t a, uint32_t lo_off, const float4& 
     }
 }
 
+template <int NSPLIT>
+__device__ __forceinline__ void put1(uint32_t a, uint32_t lo_off, float v) {
+    if (NSPLIT == 1) {
+        sts_f32(a, to_tf32_rna(v));
+    } else {
+        const float h = tf32_hi(v);
+        sts_f32(a, h);
+        sts_f32(a + lo_off, v - h);
+    }
+}
+// byte offset of column n inside the K-row k of an MN-major block (without the row's own offset)
+__device__ __forceinline__ uint32_t col_off(uint32_t n, uint32_t k) {
+    return (n >> 5) * ATOM_BYTES + ((((n & 31u) >> 3) ^ (k & 3u)) << 5) + (n & 7u) * 4u;
+}
+
 // one whole warp waits on an mbarrier phase: every lane probes once, then lane 0 waits (bounded)
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
     if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity) ? 1 : 0)) return true;
@@ -107,8 +121,8 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 
 struct Params {
     int64_t Nf;
-    int64_t nbary;            // floats in the bary array (samples * F)
     int Cin, Cout, F;
+    int Fp;                   // floats per row of the padded bary copy (F rounded up to 4)
     int ncg;                  // channel groups = Cin / 16
     int nchunks;              // face chunks
     int64_t stages_per_chunk; // 16-face stages per chunk
@@ -116,7 +130,7 @@ struct Params {
     int nraw;                 // raw ring depth
     const float* gout;
     const float* in;
-    const float* bary;
+    const float* bary;        // padded copy: [samples][Fp], pad columns zero
     const int32_t* cum;
     float* partial;           // [nchunks][Cout*Cin*F]
     int* async_err;
@@ -200,21 +214,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             int ns = ks1 - ks0;
             if (ns > RAW_SAMPLES) ns = RAW_SAMPLES;
             const int slow = __any_sync(0xffffffffu, (T > TREG) || (kloc + T > ns)) ? 1 : 0;
-            const int64_t bfirst = (int64_t)ks0 * F;                          // first bary float of the stage
-            const int64_t a0 = bfirst & ~(int64_t)3;                          // 16-byte aligned start
-            const int bshift = (int)(bfirst - a0);
-            int nb4 = (ns * F + bshift + 3) >> 2;                             // 16-byte pieces wanted
-            const int64_t avail4 = (p.nbary - a0) >> 2;                       // whole pieces the array still holds
-            int tail = 0;                                                     // floats behind the last whole piece
-            if (nb4 > avail4) { tail = (int)(p.nbary - a0 - avail4 * 4); nb4 = (int)avail4; }
             if (warp == REC_WARP) {
                 if (lane < KF) sts_i4(rb32 + RAW_REC_OFF + lane * 16, kloc, T, __float_as_int(T > 0 ? 1.f / (float)T : 0.f), cv);
-                if (lane == KF) sts_i4(rb32 + RAW_REC_OFF + KF * 16, slow, bshift, ks0, ns);
-                if (lane < tail) sts_f32(rb32 + RAW_B_OFF + (uint32_t)(nb4 * 4 + lane) * 4u, __ldg(p.bary + a0 + nb4 * 4 + lane));
+                if (lane == KF) sts_i4(rb32 + RAW_REC_OFF + KF * 16, slow, 0, ks0, ns);
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive_expect_tx(bar, (uint32_t)(nb4 * 16));
-                    if (nb4 > 0) bulk_g2s(raw + (size_t)rbuf * RAW_BYTES + RAW_B_OFF, p.bary + a0, (uint32_t)(nb4 * 16), bar);
+                    // the stage's bary rows: one bulk copy (rows are 16-byte multiples)
+                    const uint32_t bbytes = (uint32_t)(ns * p.Fp * 4);
+                    mbar_arrive_expect_tx(bar, bbytes);
+                    if (bbytes > 0) bulk_g2s(raw + (size_t)rbuf * RAW_BYTES + RAW_B_OFF, p.bary + (int64_t)ks0 * p.Fp, bbytes, bar);
                 }
             } else {
                 // this CTA's 16 input channels of the first TREG samples of every face:
@@ -225,7 +233,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                     const int idx = lane + i * 32, qd = idx & 3, t = (idx >> 2) & 3, xf = idx >> 4;
                     const int Tf = __shfl_sync(0xffffffffu, T, xf), kf = __shfl_sync(0xffffffffu, cv, xf);
                     if (t < Tf && !slow)
-                        cp_async16(rb32 + RAW_X_OFF + (uint32_t)((xf * TREG + t) * RAW_X_SLOT + ((qd ^ (xf & 7)) << 4)),
+                        cp_async16(rb32 + RAW_X_OFF + (uint32_t)((xf * TREG + t) * RAW_X_SLOT + (xf & 1) * 64 + qd * 16),
                                    xsrc + (int64_t)(kf + t) * Cin + qd * 4);
                 }
                 cp_async_arrive(bar);
@@ -235,38 +243,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         }
     } else if (warp < CWARPS) {
         // ================================== compute warps ==================================
-        const int half = lane >> 4, fl = lane & 15;           // 8-column half of a unit, face of the stage
-        // This thread's 8 consecutive columns 16*g + 8*half of K-row fl (g = unit of the
-        // gradOutput block, or basis d of the A block) are 32-byte chunk j of 32-column block
-        // g>>1; chunk j of K-row k is stored at chunk j ^ (k & 3).  All units of a warp have the
-        // parity of the warp index, so j is fixed per thread.  A quarter warp (faces 0..7 or
-        // 8..15, same j) covers two 4-face groups whose lanes would meet in the same 16-byte
-        // bank group: the lanes with fl & 4 keep their two 4-column halves swapped in registers
-        // (`sw`), so the first store of a pair lands in the other half of the chunk.
-        const uint32_t j32 = 2u * (uint32_t)(warp & 1) + (uint32_t)half;
-        const uint32_t sw = (fl & 4) ? 16u : 0u;
-        const uint32_t tcol = (uint32_t)(fl & 3) * 128u + ((j32 ^ (uint32_t)(fl & 3)) << 5) + sw;
-        const uint32_t g_off = (uint32_t)(fl >> 2) * G_SBO + (uint32_t)(warp >> 1) * ATOM_BYTES + tcol;
-        // unit u = warp + CWARPS i is basis d = u - 8: column block (d >> 1) = (warp >> 1) - 4 + (CWARPS / 2) i
-        const uint32_t a_off = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(fl >> 2) * at_sbo + tcol
-                               + (uint32_t)(warp >> 1) * ATOM_BYTES - 4u * ATOM_BYTES;
-        bool has_basis = false;
-#pragma unroll
-        for (int i = 0; i < UMAX; ++i) {
-            const int d = warp - GUNITS + i * CWARPS;
-            has_basis = has_basis || (d >= 0 && d < F);
-        }
-        // gradOutput rows of a unit: 32 bytes per thread straight from global memory
-        const bool g_warp = warp < GUNITS;
-        const int gco = warp * 16 + half * 8;                 // first channel of this thread
+        // --- A block: thread = (face k of the stage, channel ch of the CTA's 16), all bases.
+        // Columns are ordered [group q of 4 bases][channel][basis in group], then the F % 4 left-over
+        // bases as [channel][basis]: a thread's 4 bases of a group are one 16-byte store and the 8
+        // lanes of a quarter warp (8 channels of one face) store 128 consecutive bytes.
+        const int ka = 2 * warp + (lane >> 4), ch = lane & 15;
+        const int FQ = F >> 2, FR = F & 3;                     // whole groups, left-over bases
+        // column n of K-row k lives at 32-column block n>>5, 32-byte chunk ((n&31)>>3) ^ (k&3)
+        const uint32_t a_row = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(ka >> 2) * at_sbo + (uint32_t)(ka & 3) * 128u;
+        const uint32_t a_off = a_row + (uint32_t)(ch >> 3) * ATOM_BYTES + (((uint32_t)((ch & 7) >> 1) ^ (uint32_t)(ka & 3)) << 5)
+                               + (uint32_t)(ch & 1) * 16u;    // + q * 1024 for group q
+        // --- gradOutput block: warp w copies the rows of faces 2w and 2w+1 straight from global
+        // memory (registers, two stages ahead): lane l holds channels 4l..4l+3 of both, so a warp
+        // load reads one whole row and the 8 lanes of a quarter warp store 128 consecutive bytes
+        // of the face's K-row (16-byte piece l&7 of 32-channel block l>>3).
+        auto g_row_off = [&](int k) -> uint32_t {
+            return (uint32_t)(k >> 2) * G_SBO + (uint32_t)(k & 3) * 128u + (uint32_t)(lane >> 3) * ATOM_BYTES
+                   + ((((uint32_t)(lane & 7) >> 1) ^ (uint32_t)(k & 3)) << 5) + (uint32_t)(lane & 1) * 16u;
+        };
+        const uint32_t g_off0 = g_row_off(2 * warp), g_off1 = g_row_off(2 * warp + 1);
         auto load_g = [&](int64_t st, float4& u, float4& w) {
             u = zero4(); w = zero4();
-            const int64_t f = (st0 + st) * KF + fl;
-            if (!g_warp || st >= nst || f >= p.Nf) return;
-            const float* src = p.gout + f * Cout + gco;
-            const int cu = (int)(sw >> 2), cw = 4 - cu;       // the two 4-channel halves (swapped where sw is set)
-            if (gco + cu < Cout) u = ldg4(reinterpret_cast<const float4*>(src + cu));
-            if (gco + cw < Cout) w = ldg4(reinterpret_cast<const float4*>(src + cw));
+            const int64_t f = (st0 + st) * KF + 2 * warp;
+            if (st >= nst || 4 * lane >= Cout) return;
+            if (f < p.Nf) u = ldg4(reinterpret_cast<const float4*>(p.gout + f * Cout) + lane);
+            if (f + 1 < p.Nf) w = ldg4(reinterpret_cast<const float4*>(p.gout + (f + 1) * Cout) + lane);
         };
         float4 gu0, gw0, gu1, gw1;                            // stages st and st + 1
         load_g(0, gu0, gw0);
@@ -279,76 +280,72 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             load_g(st + 2, gu2, gw2);
             if (!warp_wait(&raw_ready[rbuf], rph, abort_flag, lane)) { alive = false; break; }
             const uint32_t rb32 = raw32 + (uint32_t)rbuf * RAW_BYTES;
-            const int4 rec = lds_i4(rb32 + RAW_REC_OFF + fl * 16);           // {kloc, T, 1/T, first sample}
-            const int4 info = lds_i4(rb32 + RAW_REC_OFF + KF * 16);          // {slow, shift, ks0, ns}
+            const int4 rec = lds_i4(rb32 + RAW_REC_OFF + ka * 16);           // {kloc, T, 1/T, first sample}
+            const int slow = lds_i32(rb32 + RAW_REC_OFF + KF * 16);
             const int kloc = rec.x, T = rec.y;
             const float invT = __int_as_float(rec.z);
             if (!warp_wait(&empty[si], sph ^ 1u, abort_flag, lane)) { alive = false; break; }
             const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes;
-            if (g_warp) {
-                // a unit of the gradOutput block: a plain (split) copy of 16 channels x 16 faces
-                put4<NSPLIT>(sb32 + g_off, G_TILE_BYTES, gu0);
-                put4<NSPLIT>((sb32 + g_off) ^ 16u, G_TILE_BYTES, gw0);
-            }
+            put4<NSPLIT>(sb32 + g_off0, G_TILE_BYTES, gu0);
+            put4<NSPLIT>(sb32 + g_off1, G_TILE_BYTES, gw0);
             gu0 = gu1; gw0 = gw1; gu1 = gu2; gw1 = gw2;
-            if (has_basis) {
-                const uint32_t aa32 = sb32 + a_off;
-                if (!info.x) {
-                    // fast path: every face of the stage has at most TREG samples, all of them staged
-                    // (rows behind a face's last sample belong to other faces or are stale: their
-                    // weight is zero, so they only matter if the input holds non-finite values)
-                    float2 x[TREG][4];
-                    float wt[TREG];
-                    {
-                        const uint32_t xa = rb32 + RAW_X_OFF + (uint32_t)fl * (TREG * RAW_X_SLOT);
-                        const uint32_t qu = 2u * (uint32_t)half + (sw >> 4);            // 16-byte quarter held first
-                        const uint32_t xu = xa + ((qu ^ (uint32_t)(fl & 7)) << 4), xw = xa + (((qu ^ 1u) ^ (uint32_t)(fl & 7)) << 4);
+            const uint32_t aa32 = sb32 + a_off;
+            if (!slow) {
+                // fast path: every face of the stage has at most TREG samples, all of them staged.
+                // (Rows behind a face's last sample belong to other faces or are stale: their weight
+                // is zero, so they only matter if the input holds non-finite values.)
+                float2 x2[TREG];
 #pragma unroll
-                        for (int t = 0; t < TREG; ++t) {
-                            const float4 u = lds_f4(xu + t * RAW_X_SLOT), w = lds_f4(xw + t * RAW_X_SLOT);
-                            x[t][0] = make_float2(u.x, u.y); x[t][1] = make_float2(u.z, u.w);
-                            x[t][2] = make_float2(w.x, w.y); x[t][3] = make_float2(w.z, w.w);
-                            wt[t] = t < T ? invT : 0.f;
-                        }
+                for (int t = 0; t < TREG; ++t) {
+                    const float xv = lds_f32(rb32 + RAW_X_OFF + (uint32_t)((ka * TREG + t) * RAW_X_SLOT + (ka & 1) * 64 + ch * 4))
+                                     * (t < T ? invT : 0.f);
+                    x2[t] = make_float2(xv, xv);
+                }
+                const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(kloc * p.Fp) * 4u;
+                const uint32_t bpitch = (uint32_t)p.Fp * 4u;
+#pragma unroll 2
+                for (int q = 0; q < FQ; ++q) {
+                    float2 a01 = make_float2(0.f, 0.f), a23 = a01;
+#pragma unroll
+                    for (int t = 0; t < TREG; ++t) {
+                        const float4 b = lds_f4(ba + (uint32_t)t * bpitch + (uint32_t)q * 16u);
+                        a01 = __ffma2_rn(x2[t], make_float2(b.x, b.y), a01);
+                        a23 = __ffma2_rn(x2[t], make_float2(b.z, b.w), a23);
                     }
-                    const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(info.y + kloc * F) * 4u;
+                    put4<NSPLIT>(aa32 + (uint32_t)q * (2u * ATOM_BYTES), (uint32_t)at_bytes, make_float4(a01.x, a01.y, a23.x, a23.y));
+                }
+                if (FR) {
+                    float2 a01 = make_float2(0.f, 0.f), a23 = a01;
 #pragma unroll
-                    for (int i = 0; i < UMAX; ++i) {
-                        const int d = warp - GUNITS + i * CWARPS;
-                        if (d >= 0 && d < F) {
-                            float2 a[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) a[j] = make_float2(0.f, 0.f);
-#pragma unroll
-                            for (int t = 0; t < TREG; ++t) {
-                                const float b = lds_f32(ba + (uint32_t)(t * F + d) * 4u) * wt[t];
-                                const float2 b2 = make_float2(b, b);
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) a[j] = __ffma2_rn(b2, x[t][j], a[j]);
-                            }
-                            const uint32_t da32 = aa32 + (uint32_t)i * ((CWARPS / 2) * ATOM_BYTES);
-                            put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0].x, a[0].y, a[1].x, a[1].y));
-                            put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[2].x, a[2].y, a[3].x, a[3].y));
-                        }
+                    for (int t = 0; t < TREG; ++t) {
+                        const float4 b = lds_f4(ba + (uint32_t)t * bpitch + (uint32_t)FQ * 16u);   // pad columns of the row are zero
+                        a01 = __ffma2_rn(x2[t], make_float2(b.x, b.y), a01);
+                        a23 = __ffma2_rn(x2[t], make_float2(b.z, b.w), a23);
                     }
-                } else {
-                    // generic path, straight from global memory (halves swapped where sw is set)
-                    const int k0 = rec.w, jsw = (int)(sw >> 2);
-                    for (int i = 0; i < UMAX; ++i) {
-                        const int d = warp - GUNITS + i * CWARPS;
-                        if (d < 0 || d >= F) continue;
-                        float a[8];
+                    const float av[3] = {a01.x, a01.y, a23.x};
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) a[j] = 0.f;
-                        for (int t = 0; t < T; ++t) {
-                            const float b = __ldg(p.bary + (int64_t)(k0 + t) * F + d) * invT;
-                            const float* xr = p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8;
+                    for (int r = 0; r < 3; ++r)
+                        if (r < FR)
+                            put1<NSPLIT>(sb32 + a_row + col_off((uint32_t)(FQ * 64 + ch * FR + r), (uint32_t)ka), (uint32_t)at_bytes, av[r]);
+                }
+            } else {
+                // generic path, straight from global memory: any number of samples per face
+                const int k0 = rec.w;
+                for (int q = 0; q <= FQ; ++q) {
+                    if (q == FQ && FR == 0) break;
+                    float a[4] = {0.f, 0.f, 0.f, 0.f};
+                    for (int t = 0; t < T; ++t) {
+                        const float xv = __ldg(p.in + (int64_t)(k0 + t) * Cin + cgp * CG + ch) * invT;
+                        const float4 b = ldg4(reinterpret_cast<const float4*>(p.bary + (int64_t)(k0 + t) * p.Fp) + q);
+                        a[0] = fmaf(xv, b.x, a[0]); a[1] = fmaf(xv, b.y, a[1]); a[2] = fmaf(xv, b.z, a[2]); a[3] = fmaf(xv, b.w, a[3]);
+                    }
+                    if (q < FQ) {
+                        put4<NSPLIT>(aa32 + (uint32_t)q * (2u * ATOM_BYTES), (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
+                    } else {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) a[j] = fmaf(b, __ldg(xr + (j ^ jsw)), a[j]);
-                        }
-                        const uint32_t da32 = aa32 + (uint32_t)i * ((CWARPS / 2) * ATOM_BYTES);
-                        put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
-                        put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[4], a[5], a[6], a[7]));
+                        for (int r = 0; r < 3; ++r)
+                            if (r < FR)
+                                put1<NSPLIT>(sb32 + a_row + col_off((uint32_t)(FQ * 64 + ch * FR + r), (uint32_t)ka), (uint32_t)at_bytes, a[r]);
                     }
                 }
             }
@@ -361,7 +358,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // ==================================== drain ====================================
         if (alive && warp_wait(acc_done, 0u, abort_flag, lane)) {
             tc_fence_after();
-            const int q = warp & 3, hcol = warp >> 2;       // TMEM lane quadrant, third of the 32-column groups
+            const int q = warp & 3, hcol = warp >> 2;       // TMEM lane quadrant, half of the 32-column groups
+            const int FQ = F >> 2, FR = F & 3;
             const int co = q * 32 + lane;
             float* out = p.partial + (int64_t)chunk * Cout * Cin * F;
             const int ngroups = (NR + 31) / 32;
@@ -374,7 +372,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                     for (int j = 0; j < 32; ++j) {
                         int col = gi * 32 + j;
                         if (col < NR) {
-                            int d = col / CG, kk = col - d * CG;
+                            int d, kk;                       // column order: see the compute warps
+                            if (col < FQ * 64) { d = (col >> 6) * 4 + (col & 3); kk = (col & 63) >> 2; }
+                            else { const int c2 = col - FQ * 64; kk = c2 / FR; d = FQ * 4 + (c2 - kk * FR); }
                             out[((int64_t)co * Cin + cgp * CG + kk) * F + d] = nst > 0 ? __uint_as_float(r[j]) : 0.f;
                         }
                     }
@@ -434,6 +434,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     }
 }
 
+// bary rows padded to Fp = F rounded up to 4 floats (pad columns zero): rows start on 16-byte
+// boundaries, so a stage's block is one bulk copy and a thread reads 4 bases per 16-byte load
+__global__ void pad_bary_kernel(int64_t n, int F, int Fp, const float* __restrict__ src, float* __restrict__ dst) {
+    const int64_t total = n * Fp;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t s = i / Fp;
+        const int d = (int)(i - s * Fp);
+        dst[i] = d < F ? __ldg(src + s * F + d) : 0.f;
+    }
+}
+
 // ---------------------------------------------------------------------------- host side
 struct Plan { int nsplit, ncg, nchunks, nstages, nraw; int64_t stages_per_chunk; size_t smem, partial_bytes; };
 
@@ -468,8 +479,13 @@ bool fits(int64_t Nf, int Cin, int Cout, int F, int precision) {
     return plan(Nf, Cin, Cout, F, precision).smem <= 227 * 1024;
 }
 
-size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision) {
-    return align_up(plan(Nf, Cin, Cout, F, precision).partial_bytes, 256);
+static int padded_F(int F) { return (F + 3) / 4 * 4; }
+static size_t padded_bary_bytes(int64_t NiK, int F) {
+    return F % 4 == 0 ? 0 : align_up((size_t)NiK * padded_F(F) * sizeof(float), 256);
+}
+
+size_t workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
+    return align_up(plan(Nf, Cin, Cout, F, precision).partial_bytes, 256) + padded_bary_bytes(NiK, F);
 }
 
 int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
@@ -478,10 +494,16 @@ int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const flo
     if (rc) return rc;
     Plan pl = plan(Nf, Cin, Cout, F, precision);
     Params p;
-    p.Nf = Nf; p.nbary = NiK * F; p.Cin = Cin; p.Cout = Cout; p.F = F;
+    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F; p.Fp = padded_F(F);
     p.ncg = pl.ncg; p.nchunks = pl.nchunks; p.stages_per_chunk = pl.stages_per_chunk;
     p.nstages = pl.nstages; p.nraw = pl.nraw;
-    p.gout = gout; p.in = input; p.bary = bary; p.cum = cum; p.partial = (float*)ws;
+    p.gout = gout; p.in = input; p.cum = cum; p.partial = (float*)ws;
+    p.bary = bary;
+    if (F % 4 != 0 && NiK > 0) {
+        float* padded = reinterpret_cast<float*>((char*)ws + align_up(pl.partial_bytes, 256));
+        PB_LAUNCH("f2f_pad_bary", pad_bary_kernel, persistent_blocks(NiK * p.Fp, 256, 8), 256, 0, stream, NiK, F, p.Fp, bary, padded);
+        p.bary = padded;
+    }
     p.async_err = async_error_word();
     int grid = pl.ncg * pl.nchunks;
     if (pl.nsplit == 2) {
