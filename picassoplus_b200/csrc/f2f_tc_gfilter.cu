@@ -7,18 +7,23 @@
 // (its F*16 <= 512 accumulator columns live in TMEM for the whole kernel) and one contiguous
 // chunk of faces.  Per stage of 16 faces three roles cooperate through mbarriers:
 //   * two loader warps fill a ring of raw buffers: one writes a record per face (first
-//     sample, sample count, 1/T) and fetches the stage's bary block with one bulk copy, the
-//     other fetches the CTA's 16 input channels of every sample with 16-byte asynchronous
-//     copies into per-face slots; the sample ranges they need are loaded three stages ahead;
-//   * the compute warps turn a raw buffer into both operands in shared memory, MN-major
-//     (128-byte swizzle, 32-byte base): a face is a K-row whose 128-byte pieces hold 32
-//     consecutive output channels (gradOutput block) or 32 consecutive (basis, channel)
-//     columns (A block), so neither operand is transposed and every store is a 16-byte
-//     vector.  Work unit = 16 columns x 16 faces (thread = face x 8 columns): 8 units of
-//     the gradOutput block (read straight from global memory into registers, two stages
-//     ahead) and F units (one per basis) of the A block, dealt round-robin;
+//     sample, sample count, 1/T) and fetches the stage's bary rows with one bulk copy (from a
+//     copy of bary whose rows are padded to a multiple of 4 floats), the other fetches the
+//     CTA's 16 input channels of every sample with 16-byte asynchronous copies into per-face
+//     slots; the sample ranges they need are loaded three stages ahead;
+//   * 8 compute warps build both operands in shared memory, MN-major (128-byte swizzle,
+//     32-byte base): a face is a K-row whose 128-byte pieces hold 32 consecutive output
+//     channels (gradOutput block) or 32 consecutive (basis, channel) columns (A block), so
+//     neither operand is transposed and every store is a 16-byte vector.  Warp w copies the
+//     gradOutput rows of faces 2w, 2w+1 (straight from global memory into registers, two
+//     stages ahead) and builds the A columns of bases 4w..4w+3 (thread = face x 8 channels,
+//     one 16-byte bary load per sample);
 //   * one thread issues tcgen05.mma (M = 128 output channels, N = F*16 in chunks of <= 256,
 //     K = 8 faces per instruction) and commits the stage back.
+// What bounds it: every 16-byte shared-memory access of a warp costs at least 4 passes of the
+// load/store pipe, so the layout of every access is chosen to touch 512 distinct bytes; in
+// the hi+lo mode the three MMAs per product read their operands from shared memory three
+// times, and that traffic (about 123 KB per stage) is the floor.
 // At the end the accumulator is drained once into partial[chunk] (final gradFilter layout);
 // a second kernel adds the chunks in order, so the result is deterministic.
 // Modes: 1 split (tf32 operands) or 2 splits (tf32 hi+lo, three MMAs per k-step).
@@ -53,8 +58,8 @@ __host__ __device__ constexpr int at_blocks(int F) { return (F * CG + 31) / 32; 
 // one raw buffer: what a stage needs from global memory, as it lies there
 constexpr int RAW_SAMPLES = 64;               // samples of a stage that are staged (16 faces x 4)
 // Sample rows are staged per face: slot fl*4 + t (128 bytes) holds the CTA's 16 channels of
-// sample t of face fl in its first (even fl) or second (odd fl) 64 bytes, so that the two
-// faces of a compute warp read different banks.
+// sample t of face fl as four 16-byte pieces, piece q at chunk q ^ (fl & 7) -- the 8 lanes of
+// a quarter warp (8 faces) then read 8 distinct bank groups.
 constexpr int RAW_X_SLOT = 128;
 constexpr int RAW_X_BYTES = KF * TREG * RAW_X_SLOT;
 constexpr int RAW_B_BYTES = (RAW_SAMPLES + TREG) * 32 * 4;            // bary rows padded to Fp <= 32 floats; + rows read (weight 0) by short faces
@@ -92,21 +97,6 @@ __device__ __forceinline__ void put4(uint32_t a, uint32_t lo_off, const float4& 
         sts_f4(a, h);
         sts_f4(a + lo_off, make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w));
     }
-}
-
-template <int NSPLIT>
-__device__ __forceinline__ void put1(uint32_t a, uint32_t lo_off, float v) {
-    if (NSPLIT == 1) {
-        sts_f32(a, to_tf32_rna(v));
-    } else {
-        const float h = tf32_hi(v);
-        sts_f32(a, h);
-        sts_f32(a + lo_off, v - h);
-    }
-}
-// byte offset of column n inside the K-row k of an MN-major block (without the row's own offset)
-__device__ __forceinline__ uint32_t col_off(uint32_t n, uint32_t k) {
-    return (n >> 5) * ATOM_BYTES + ((((n & 31u) >> 3) ^ (k & 3u)) << 5) + (n & 7u) * 4u;
 }
 
 // one whole warp waits on an mbarrier phase: every lane probes once, then lane 0 waits (bounded)
@@ -233,7 +223,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                     const int idx = lane + i * 32, qd = idx & 3, t = (idx >> 2) & 3, xf = idx >> 4;
                     const int Tf = __shfl_sync(0xffffffffu, T, xf), kf = __shfl_sync(0xffffffffu, cv, xf);
                     if (t < Tf && !slow)
-                        cp_async16(rb32 + RAW_X_OFF + (uint32_t)((xf * TREG + t) * RAW_X_SLOT + (xf & 1) * 64 + qd * 16),
+                        cp_async16(rb32 + RAW_X_OFF + (uint32_t)((xf * TREG + t) * RAW_X_SLOT + ((qd ^ (xf & 7)) << 4)),
                                    xsrc + (int64_t)(kf + t) * Cin + qd * 4);
                 }
                 cp_async_arrive(bar);
@@ -243,16 +233,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         }
     } else if (warp < CWARPS) {
         // ================================== compute warps ==================================
-        // --- A block: thread = (face k of the stage, channel ch of the CTA's 16), all bases.
-        // Columns are ordered [group q of 4 bases][channel][basis in group], then the F % 4 left-over
-        // bases as [channel][basis]: a thread's 4 bases of a group are one 16-byte store and the 8
-        // lanes of a quarter warp (8 channels of one face) store 128 consecutive bytes.
-        const int ka = 2 * warp + (lane >> 4), ch = lane & 15;
-        const int FQ = F >> 2, FR = F & 3;                     // whole groups, left-over bases
-        // column n of K-row k lives at 32-column block n>>5, 32-byte chunk ((n&31)>>3) ^ (k&3)
-        const uint32_t a_row = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(ka >> 2) * at_sbo + (uint32_t)(ka & 3) * 128u;
-        const uint32_t a_off = a_row + (uint32_t)(ch >> 3) * ATOM_BYTES + (((uint32_t)((ch & 7) >> 1) ^ (uint32_t)(ka & 3)) << 5)
-                               + (uint32_t)(ch & 1) * 16u;    // + q * 1024 for group q
+        // --- A block: warp q builds the columns of bases 4q..4q+3; thread = (face fl, 8 channels).
+        // Column n = d*16 + channel; the thread's 8 columns of basis d are 32-byte chunk
+        // 2*(d&1) + half of 32-column block d>>1, and chunk j of K-row k is stored at j ^ (k&3).
+        // A quarter warp (faces 0..7 or 8..15) covers two 4-face groups whose lanes would meet in
+        // the same 16-byte bank group: the lanes with fl & 4 keep their two 4-channel halves
+        // swapped in registers (`sw`), so the first store of a pair lands in the other half.
+        const int half = lane >> 4, fl = lane & 15;
+        const uint32_t sw = (fl & 4) ? 16u : 0u;
+        const uint32_t a_row = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(fl >> 2) * at_sbo + (uint32_t)(fl & 3) * 128u
+                               + (uint32_t)(2 * warp) * ATOM_BYTES + sw;
+        const uint32_t a_off0 = a_row + (((uint32_t)half ^ (uint32_t)(fl & 3)) << 5);          // even bases
+        const uint32_t a_off1 = a_row + (((2u + (uint32_t)half) ^ (uint32_t)(fl & 3)) << 5);   // odd bases
+        const bool has_unit = 4 * warp < F;
         // --- gradOutput block: warp w copies the rows of faces 2w and 2w+1 straight from global
         // memory (registers, two stages ahead): lane l holds channels 4l..4l+3 of both, so a warp
         // load reads one whole row and the 8 lanes of a quarter warp store 128 consecutive bytes
@@ -280,7 +273,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             load_g(st + 2, gu2, gw2);
             if (!warp_wait(&raw_ready[rbuf], rph, abort_flag, lane)) { alive = false; break; }
             const uint32_t rb32 = raw32 + (uint32_t)rbuf * RAW_BYTES;
-            const int4 rec = lds_i4(rb32 + RAW_REC_OFF + ka * 16);           // {kloc, T, 1/T, first sample}
+            const int4 rec = lds_i4(rb32 + RAW_REC_OFF + fl * 16);           // {kloc, T, 1/T, first sample}
             const int slow = lds_i32(rb32 + RAW_REC_OFF + KF * 16);
             const int kloc = rec.x, T = rec.y;
             const float invT = __int_as_float(rec.z);
@@ -289,64 +282,62 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             put4<NSPLIT>(sb32 + g_off0, G_TILE_BYTES, gu0);
             put4<NSPLIT>(sb32 + g_off1, G_TILE_BYTES, gw0);
             gu0 = gu1; gw0 = gw1; gu1 = gu2; gw1 = gw2;
-            const uint32_t aa32 = sb32 + a_off;
-            if (!slow) {
+            if (has_unit && !slow) {
                 // fast path: every face of the stage has at most TREG samples, all of them staged.
                 // (Rows behind a face's last sample belong to other faces or are stale: their weight
                 // is zero, so they only matter if the input holds non-finite values.)
-                float2 x2[TREG];
-#pragma unroll
-                for (int t = 0; t < TREG; ++t) {
-                    const float xv = lds_f32(rb32 + RAW_X_OFF + (uint32_t)((ka * TREG + t) * RAW_X_SLOT + (ka & 1) * 64 + ch * 4))
-                                     * (t < T ? invT : 0.f);
-                    x2[t] = make_float2(xv, xv);
-                }
-                const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(kloc * p.Fp) * 4u;
-                const uint32_t bpitch = (uint32_t)p.Fp * 4u;
-#pragma unroll 2
-                for (int q = 0; q < FQ; ++q) {
-                    float2 a01 = make_float2(0.f, 0.f), a23 = a01;
+                float2 x[TREG][4];
+                float4 b[TREG];
+                {
+                    const uint32_t xa = rb32 + RAW_X_OFF + (uint32_t)fl * (TREG * RAW_X_SLOT);
+                    const uint32_t qu = 2u * (uint32_t)half + (sw >> 4);            // 16-byte quarter held first
+                    const uint32_t xu = xa + ((qu ^ (uint32_t)(fl & 7)) << 4), xw = xa + (((qu ^ 1u) ^ (uint32_t)(fl & 7)) << 4);
+                    const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(kloc * p.Fp + 4 * warp) * 4u;
 #pragma unroll
                     for (int t = 0; t < TREG; ++t) {
-                        const float4 b = lds_f4(ba + (uint32_t)t * bpitch + (uint32_t)q * 16u);
-                        a01 = __ffma2_rn(x2[t], make_float2(b.x, b.y), a01);
-                        a23 = __ffma2_rn(x2[t], make_float2(b.z, b.w), a23);
+                        const float4 u = lds_f4(xu + t * RAW_X_SLOT), w = lds_f4(xw + t * RAW_X_SLOT);
+                        b[t] = lds_f4(ba + (uint32_t)(t * p.Fp) * 4u);
+                        const float wt = t < T ? invT : 0.f;
+                        x[t][0] = make_float2(u.x * wt, u.y * wt); x[t][1] = make_float2(u.z * wt, u.w * wt);
+                        x[t][2] = make_float2(w.x * wt, w.y * wt); x[t][3] = make_float2(w.z * wt, w.w * wt);
                     }
-                    put4<NSPLIT>(aa32 + (uint32_t)q * (2u * ATOM_BYTES), (uint32_t)at_bytes, make_float4(a01.x, a01.y, a23.x, a23.y));
                 }
-                if (FR) {
-                    float2 a01 = make_float2(0.f, 0.f), a23 = a01;
 #pragma unroll
-                    for (int t = 0; t < TREG; ++t) {
-                        const float4 b = lds_f4(ba + (uint32_t)t * bpitch + (uint32_t)FQ * 16u);   // pad columns of the row are zero
-                        a01 = __ffma2_rn(x2[t], make_float2(b.x, b.y), a01);
-                        a23 = __ffma2_rn(x2[t], make_float2(b.z, b.w), a23);
+                for (int dd = 0; dd < 4; ++dd) {
+                    if (4 * warp + dd < F) {
+                        float2 a[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) a[j] = make_float2(0.f, 0.f);
+#pragma unroll
+                        for (int t = 0; t < TREG; ++t) {
+                            const float bv = dd == 0 ? b[t].x : dd == 1 ? b[t].y : dd == 2 ? b[t].z : b[t].w;
+                            const float2 b2 = make_float2(bv, bv);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) a[j] = __ffma2_rn(b2, x[t][j], a[j]);
+                        }
+                        const uint32_t da32 = sb32 + ((dd & 1) ? a_off1 : a_off0) + (uint32_t)(dd >> 1) * ATOM_BYTES;
+                        put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0].x, a[0].y, a[1].x, a[1].y));
+                        put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[2].x, a[2].y, a[3].x, a[3].y));
                     }
-                    const float av[3] = {a01.x, a01.y, a23.x};
-#pragma unroll
-                    for (int r = 0; r < 3; ++r)
-                        if (r < FR)
-                            put1<NSPLIT>(sb32 + a_row + col_off((uint32_t)(FQ * 64 + ch * FR + r), (uint32_t)ka), (uint32_t)at_bytes, av[r]);
                 }
-            } else {
-                // generic path, straight from global memory: any number of samples per face
-                const int k0 = rec.w;
-                for (int q = 0; q <= FQ; ++q) {
-                    if (q == FQ && FR == 0) break;
-                    float a[4] = {0.f, 0.f, 0.f, 0.f};
+            } else if (has_unit) {
+                // generic path, straight from global memory (halves swapped where sw is set)
+                const int k0 = rec.w, jsw = (int)(sw >> 2);
+                for (int dd = 0; dd < 4; ++dd) {
+                    const int d = 4 * warp + dd;
+                    if (d >= F) break;
+                    float a[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) a[j] = 0.f;
                     for (int t = 0; t < T; ++t) {
-                        const float xv = __ldg(p.in + (int64_t)(k0 + t) * Cin + cgp * CG + ch) * invT;
-                        const float4 b = ldg4(reinterpret_cast<const float4*>(p.bary + (int64_t)(k0 + t) * p.Fp) + q);
-                        a[0] = fmaf(xv, b.x, a[0]); a[1] = fmaf(xv, b.y, a[1]); a[2] = fmaf(xv, b.z, a[2]); a[3] = fmaf(xv, b.w, a[3]);
-                    }
-                    if (q < FQ) {
-                        put4<NSPLIT>(aa32 + (uint32_t)q * (2u * ATOM_BYTES), (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
-                    } else {
+                        const float bv = __ldg(p.bary + (int64_t)(k0 + t) * p.Fp + d) * invT;
+                        const float* xr = p.in + (int64_t)(k0 + t) * Cin + cgp * CG + half * 8;
 #pragma unroll
-                        for (int r = 0; r < 3; ++r)
-                            if (r < FR)
-                                put1<NSPLIT>(sb32 + a_row + col_off((uint32_t)(FQ * 64 + ch * FR + r), (uint32_t)ka), (uint32_t)at_bytes, a[r]);
+                        for (int j = 0; j < 8; ++j) a[j] = fmaf(bv, __ldg(xr + (j ^ jsw)), a[j]);
                     }
+                    const uint32_t da32 = sb32 + ((dd & 1) ? a_off1 : a_off0) + (uint32_t)(dd >> 1) * ATOM_BYTES;
+                    put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
+                    put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[4], a[5], a[6], a[7]));
                 }
             }
             fence_proxy_async();
@@ -359,7 +350,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         if (alive && warp_wait(acc_done, 0u, abort_flag, lane)) {
             tc_fence_after();
             const int q = warp & 3, hcol = warp >> 2;       // TMEM lane quadrant, half of the 32-column groups
-            const int FQ = F >> 2, FR = F & 3;
             const int co = q * 32 + lane;
             float* out = p.partial + (int64_t)chunk * Cout * Cin * F;
             const int ngroups = (NR + 31) / 32;
@@ -372,9 +362,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                     for (int j = 0; j < 32; ++j) {
                         int col = gi * 32 + j;
                         if (col < NR) {
-                            int d, kk;                       // column order: see the compute warps
-                            if (col < FQ * 64) { d = (col >> 6) * 4 + (col & 3); kk = (col & 63) >> 2; }
-                            else { const int c2 = col - FQ * 64; kk = c2 / FR; d = FQ * 4 + (c2 - kk * FR); }
+                            const int d = col / CG, kk = col - d * CG;
                             out[((int64_t)co * Cin + cgp * CG + kk) * F + d] = nst > 0 ? __uint_as_float(r[j]) : 0.f;
                         }
                     }
