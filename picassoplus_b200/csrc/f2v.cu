@@ -57,6 +57,62 @@ f2v_fwd_face_kernel(int64_t Nf, int CV, int K, const float* __restrict__ coeff, 
     }
 }
 
+// The same for whole 128-channel chunks (lane = float4 channel group) and K <= 32, register-
+// blocked so that the shared-memory pipe is not the limit: warp w owns faces w, w+8, ..., w+56
+// of the tile, and a filter row read from shared memory (512 distinct bytes per warp) is used
+// for all eight; the coefficient loads are one broadcast address per warp.
+__global__ void __launch_bounds__(256)
+f2v_fwd_face_blocked_kernel(int64_t Nf, int CV, int K, const float* __restrict__ coeff, const float4* __restrict__ in,
+                            const float4* __restrict__ filt, float4* __restrict__ wx) {
+    extern __shared__ float4 smem[];
+    constexpr int FB = F2VF_TF / 8;                            // faces per warp
+    const int KP = (K + 3) / 4 * 4, KG = KP / 4;               // coeff row pitch, pad columns zero
+    float4* sfilt = smem;                                      // [KP][32], rows K..KP-1 zero
+    float4* scoef = smem + KP * 32;                            // [TF][KG]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cg = blockIdx.y * 32 + lane;
+    for (int i = threadIdx.x; i < KP * 32; i += blockDim.x) {
+        const int k = i >> 5;
+        sfilt[i] = k < K ? filt[k * CV + blockIdx.y * 32 + (i & 31)] : zero4();
+    }
+    for (int i = threadIdx.x; i < F2VF_TF * KG; i += blockDim.x) scoef[i] = zero4();
+    const int64_t ntiles = (Nf + F2VF_TF - 1) / F2VF_TF;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        const int64_t f0 = tile * F2VF_TF;
+        const int nf_tile = Nf - f0 < F2VF_TF ? (int)(Nf - f0) : F2VF_TF;
+        __syncthreads();
+        {
+            float* sc = reinterpret_cast<float*>(scoef);
+            for (int i = threadIdx.x; i < nf_tile * K; i += blockDim.x) {
+                const int fl = i / K;
+                sc[fl * KP + (i - fl * K)] = __ldg(coeff + f0 * K + i);
+            }
+        }
+        __syncthreads();
+        float4 x[FB], w[FB];
+#pragma unroll
+        for (int i = 0; i < FB; ++i) {
+            const int fl = warp + 8 * i;
+            w[i] = zero4();
+            x[i] = fl < nf_tile ? ldg4(in + (f0 + fl) * CV + cg) : zero4();
+        }
+        for (int g = 0; g < KG; ++g) {
+            const float4 f0v = sfilt[(4 * g) * 32 + lane], f1v = sfilt[(4 * g + 1) * 32 + lane];
+            const float4 f2v = sfilt[(4 * g + 2) * 32 + lane], f3v = sfilt[(4 * g + 3) * 32 + lane];
+#pragma unroll
+            for (int i = 0; i < FB; ++i) {
+                const float4 cf = scoef[(warp + 8 * i) * KG + g];        // rows past the tile are stale or zero: unused
+                fma4s(w[i], cf.x, f0v); fma4s(w[i], cf.y, f1v); fma4s(w[i], cf.z, f2v); fma4s(w[i], cf.w, f3v);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < FB; ++i) {
+            const int fl = warp + 8 * i;
+            if (fl < nf_tile) wx[(f0 + fl) * CV + cg] = mul4(w[i], x[i]);
+        }
+    }
+}
+
 template <int TL>
 __global__ void __launch_bounds__(256)
 f2v_fwd_gather_kernel(int64_t NvOut, int CV, const int32_t* __restrict__ rowptr, const int32_t* __restrict__ entries,
@@ -207,6 +263,133 @@ f2v_bwd_tile_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ face,
         if (ak[n] >= 0) partial[((int64_t)blockIdx.x * K + ak[n]) * CV + cg0 + ac[n]] = acc[n];
 }
 
+// The same two phases, register-blocked for whole 128-channel chunks (lane = float4 channel
+// group) and K <= 32, so that the shared-memory pipe is not the limit: every 16-byte shared
+// load of a warp is either 512 distinct bytes or one broadcast address.
+//   phase 1  warp w owns faces w, w+8, w+16, w+24 of the tile: a filter row read from shared
+//            memory is used for all four faces;
+//   phase 2  warp g owns the coefficients 4g..4g+3: a row of t read from shared memory feeds
+//            four accumulators.
+// The index chain of the gather (face -> vtMap -> nfCount) is resolved by 96 threads one hop
+// per tile for the block's next three tiles, so that phase 1 finds output vertex and 1/nfCount
+// of every corner in shared memory and issues its twelve gradOutput row loads at once.
+__global__ void __launch_bounds__(256)
+f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap,
+                       const int32_t* __restrict__ nfCount, const float* __restrict__ coeff,
+                       const float4* __restrict__ in, const float4* __restrict__ filt, const float4* __restrict__ gout,
+                       float4* __restrict__ gin, float4* __restrict__ partial) {
+    extern __shared__ float4 smem[];
+    const int KP = (K + 3) / 4 * 4;                            // coeff row pitch (floats), pad columns zero
+    const int KG = KP / 4;                                     // groups of 4 coefficients (<= 8)
+    float4* sfilt = smem;                                      // [KP][32], rows K..KP-1 zero
+    float4* st = smem + KP * 32;                               // [TF][32]   t = input * gt
+    float4* scoef = st + F2VB_TF * 32;                         // [TF][KG]
+    int* svo = reinterpret_cast<int*>(scoef + F2VB_TF * KG);   // [2][96] output vertex of (face, corner), -1 = none
+    float* srn = reinterpret_cast<float*>(svo + 2 * 96);       // [2][96] 1 / nfCount of that vertex
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cg = blockIdx.y * 32 + lane;                     // this lane's channel group
+    for (int i = threadIdx.x; i < KP * 32; i += blockDim.x) {
+        const int k = i >> 5;
+        sfilt[i] = k < K ? filt[k * CV + blockIdx.y * 32 + (i & 31)] : zero4();
+    }
+    for (int i = threadIdx.x; i < F2VB_TF * KG; i += blockDim.x) scoef[i] = zero4();
+    float4 acc[4] = {zero4(), zero4(), zero4(), zero4()};     // coefficients 4*warp .. 4*warp+3
+    const int64_t ntiles = (Nf + F2VB_TF - 1) / F2VB_TF;
+    // index pipeline of thread e < 96 (entry e = 3*face + corner of a tile): vertex id of the
+    // tile three steps ahead, output vertex two steps ahead, 1/nfCount one step ahead
+    const bool ix = threadIdx.x < 96;
+    auto hop_face = [&](int64_t tile) -> int {
+        const int64_t e = tile * (F2VB_TF * 3) + threadIdx.x;
+        return (ix && tile < ntiles && e < Nf * 3) ? __ldg(face + e) : -1;
+    };
+    auto hop_vo = [&](int vi) -> int { return vi < 0 ? -1 : (vtMap ? __ldg(vtMap + vi) : vi); };
+    auto hop_rn = [&](int vo) -> float { return vo < 0 ? 0.f : __frcp_rn((float)__ldg(nfCount + vo)); };
+    const int64_t tstep = gridDim.x;
+    int vo1 = hop_vo(hop_face(blockIdx.x));                                   // first tile: resolved up front
+    float rn1 = hop_rn(vo1);
+    if (ix) { svo[threadIdx.x] = vo1; srn[threadIdx.x] = rn1; }
+    vo1 = hop_vo(hop_face(blockIdx.x + tstep));                               // second tile
+    int vi2 = hop_face(blockIdx.x + 2 * tstep);                               // third tile
+    int buf = 0;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += tstep, buf ^= 1) {
+        const int64_t f0 = tile * F2VB_TF;
+        const int nf_tile = Nf - f0 < F2VB_TF ? (int)(Nf - f0) : F2VB_TF;
+        // one hop for each of the next three tiles (results are used in the next iteration)
+        const float rn_next = hop_rn(vo1);
+        const int vo_next = hop_vo(vi2);
+        const int vi_next = hop_face(tile + 3 * tstep);
+        __syncthreads();                                       // previous tile fully consumed
+        {
+            float* sc = reinterpret_cast<float*>(scoef);
+            for (int i = threadIdx.x; i < nf_tile * K; i += blockDim.x) {
+                const int fl = i / K;
+                sc[fl * KP + (i - fl * K)] = __ldg(coeff + f0 * K + i);
+            }
+        }
+        __syncthreads();
+        // ---- phase 1: faces warp, warp+8, warp+16, warp+24
+        float4 gt[4], x[4], w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int fl = warp + 8 * i;
+            gt[i] = zero4(); x[i] = zero4(); w[i] = zero4();
+            if (fl < nf_tile) {
+                const int64_t f = f0 + fl;
+                float4 gr[3];
+                float rn[3];
+#pragma unroll
+                for (int j = 0; j < 3; ++j) {
+                    const int vo = svo[buf * 96 + fl * 3 + j];
+                    rn[j] = srn[buf * 96 + fl * 3 + j];
+                    gr[j] = vo >= 0 ? ldg4(gout + (int64_t)vo * CV + cg) : zero4();
+                }
+                x[i] = ldg4(in + f * CV + cg);
+#pragma unroll
+                for (int j = 0; j < 3; ++j) fma4s(gt[i], rn[j], gr[j]);
+            }
+        }
+        for (int g = 0; g < KG; ++g) {
+            float4 cf[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cf[i] = scoef[(warp + 8 * i) * KG + g];   // rows past the tile are stale or zero: unused
+            const float4 f0v = sfilt[(4 * g) * 32 + lane], f1v = sfilt[(4 * g + 1) * 32 + lane];
+            const float4 f2v = sfilt[(4 * g + 2) * 32 + lane], f3v = sfilt[(4 * g + 3) * 32 + lane];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                fma4s(w[i], cf[i].x, f0v); fma4s(w[i], cf[i].y, f1v); fma4s(w[i], cf[i].z, f2v); fma4s(w[i], cf[i].w, f3v);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int fl = warp + 8 * i;
+            if (fl < nf_tile) {
+                __stcs(gin + (f0 + fl) * CV + cg, mul4(gt[i], w[i]));
+                st[fl * 32 + lane] = mul4(x[i], gt[i]);
+            }
+        }
+        __syncthreads();
+        // the next tile's corners go to the other index buffer (its readers are behind the barrier above)
+        if (ix) { svo[(buf ^ 1) * 96 + threadIdx.x] = vo1; srn[(buf ^ 1) * 96 + threadIdx.x] = rn_next; }
+        vo1 = vo_next; vi2 = vi_next;
+        // ---- phase 2: coefficients 4*warp .. 4*warp+3, faces in order
+        if (warp < KG) {
+#pragma unroll 4
+            for (int fl = 0; fl < nf_tile; ++fl) {
+                const float4 c = scoef[fl * KG + warp];
+                const float4 t = st[fl * 32 + lane];
+                fma4s(acc[0], c.x, t); fma4s(acc[1], c.y, t); fma4s(acc[2], c.z, t); fma4s(acc[3], c.w, t);
+            }
+        }
+    }
+    if (warp < KG) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = 4 * warp + j;
+            if (k < K) partial[((int64_t)blockIdx.x * K + k) * CV + cg] = acc[j];
+        }
+    }
+}
+
 // ---------------------------------------------------------------------- backward, generic
 __device__ __forceinline__ float f2v_gt(const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap,
                                         const int32_t* __restrict__ nfCount, const float* __restrict__ gout,
@@ -313,7 +496,13 @@ int pb200_facet2vertex_forward(int64_t Nf, int64_t NvOut, int C, int r, int K, c
     if (vec) {
         int CV = C / 4;
         float4* wx = (float4*)workspace;
-        if (Nf > 0) {
+        if (Nf > 0 && CV % 32 == 0 && K <= 32) {
+            const int KPb = (K + 3) / 4 * 4;
+            const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + F2VF_TF * (KPb / 4));
+            dim3 gridf(persistent_blocks(Nf, F2VF_TF, 4), (unsigned)(CV / 32));
+            PB_LAUNCH("f2v_fwd_face", f2v_fwd_face_blocked_kernel, gridf, 256, smemb, stream, Nf, CV, K, coeff,
+                      (const float4*)input, (const float4*)filter, wx);
+        } else if (Nf > 0) {
             const int KP = (K + 3) / 4 * 4 + 4;
             size_t smem = sizeof(float4) * 32 * (size_t)K + sizeof(float) * F2VF_TF * KP;
             dim3 gridf(persistent_blocks(Nf, F2VF_TF, 6), (unsigned)ceil_div(CV, 32));
@@ -366,6 +555,14 @@ int pb200_facet2vertex_backward(int64_t Nf, int64_t NvIn, int64_t NvOut, int C, 
         dim3 grid(p.grid_x, (unsigned)ceil_div(CV, 32));
         const int KP = (K + 3) / 4 * 4 + 4;
         size_t smem = sizeof(float4) * (32 * (size_t)K + F2VB_TF * 32) + sizeof(float) * F2VB_TF * KP;
+        if (CV % 32 == 0 && K <= 32) {
+            const int KPb = (K + 3) / 4 * 4;
+            const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + F2VB_TF * 32 + F2VB_TF * (KPb / 4)) + 2 * 96 * 8;
+            PB_LAUNCH("f2v_bwd", f2v_bwd_blocked_kernel, grid, 256, smemb, stream, Nf, CV, K, face, vtMap, nfCount, coeff,
+                      (const float4*)input, (const float4*)filter, (const float4*)gradOutput, (float4*)gradInput,
+                      (float4*)partial);
+            return reduce_partials(partial, p.grid_x, (int64_t)K * Cr, gradFilter, stream);
+        }
         const int cvc = CV < 32 ? CV : 32;
         const int nacc = (int)ceil_div((int64_t)K * cvc, 256);
 #define PB_F2VB_LAUNCH(N)                                                                                        \

@@ -24,6 +24,7 @@ CASES = [
     ("grid9x1", 12, 1, 36, 5),
     ("grid9x1", 8, 1, 7, 5),        # K without a register-resident variant
     ("grid9x1", 160, 1, 16, 4),     # more than one 128-channel chunk
+    ("grid17x2+drop", 256, 1, 9, 8),   # two whole 128-channel chunks: register-blocked facet2vertex kernels
     ("tri", 4, 1, 4, 2),
     ("tet+iso", 3, 1, 1, 2),
 ]
