@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-groups", type=int, default=8,
+                    help="mesh groups of the end-to-end step (host-to-device copy of one overlaps compute of another)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
@@ -250,7 +252,7 @@ def run_ours(args):
     from picassoplus_b200.math_utils import sph_harm_coeff
     from picassoplus_b200.mesh import utils as mesh_utils
     from picassoplus_b200.mesh.pi_modules import conv3d
-    from picassoplus_b200.parallel import FilterGradAllReduce, partition_meshes
+    from picassoplus_b200.parallel import FilterGradAllReduce, HostBatchFeed, partition_meshes
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -299,21 +301,38 @@ def run_ours(args):
         o.backward(G)
         allreduce()
 
-    h2d_bytes = sum(pin[k].numel() * pin[k].element_size() for k in pin)
+    # End to end: the rank's meshes are fed from pinned host memory in groups; the copy of
+    # group g+1 overlaps the fwd+bwd of group g (filter gradients accumulate over the groups).
+    ngroups = max(1, min(args.e2e_groups, count))
+    feed = None
+    if not args.no_e2e:
+        pinned_groups, group_G = [], []
+        for gfirst, gcount in [(first + a, b) for a, b in partition_meshes([1] * count, ngroups) if b > 0]:
+            hg = h if ngroups == 1 else host_inputs(cfg, gfirst, gcount)
+            pinned_groups.append({k: hg[k].pin_memory() for k in ("vertex", "face", "x", "cum", "bary_xyz")})
+            gg = torch.Generator(device=dev).manual_seed(cfg["seed"] * 31 + gfirst)
+            group_G.append(torch.randn(hg["Nv"], cfg["cout"], generator=gg, device=dev))
+        feed = HostBatchFeed(pinned_groups, dev, depth=2)
+    h2d_bytes = feed.bytes_per_pass if feed is not None else 0
 
     def step_e2e():
         for p in params:
             p.grad = None
-        with torch.no_grad():
-            for k in pin:
-                d[k].copy_(pin[k], non_blocking=True)      # bumps the version: topology is rebuilt
-        xe = d["x"].detach().requires_grad_()
-        nfc_, coeff_, bary_ = prepare()
-        o = conv_block(xe, params[0], params[1], params[2], d["face"], d["cum"], bary_, coeff_, nfc_, vt_map, sh_eye)
-        loss = (o * G).sum()
-        loss.backward()
+        total = torch.zeros((), device=dev)
+        for gi, b in enumerate(feed):                      # fresh copies: topology is rebuilt per group
+            nv = b["vertex"].shape[0]
+            vt = vt_map[:nv]
+            nfc_ = mesh_utils.count_vertex_adjface(b["face"], vt, b["vertex"])
+            geo = mesh_utils.compute_triangle_geometry(b["vertex"], b["face"])
+            coeff_ = sph_harm_coeff(L, geo[:, :3].contiguous())
+            bary_ = sph_harm_coeff(L, b["bary_xyz"])
+            xe = b["x"].detach().requires_grad_()
+            o = conv_block(xe, params[0], params[1], params[2], b["face"], b["cum"], bary_, coeff_, nfc_, vt, sh_eye)
+            loss = (o * group_G[gi]).sum()
+            loss.backward()
+            total = total + loss.detach()
         allreduce()
-        return float(loss.item())
+        return float(total.item())
 
     def barrier():
         if world > 1:
@@ -382,8 +401,10 @@ def run_ours(args):
         ems, _ = timed(step_e2e, e_steps)
         e2e = dict(value=faces_total / (ems / e_steps / 1e3), unit=UNIT, ms_per_step=ems / e_steps,
                    h2d_bytes_per_step=int(h2d_bytes), d2h_bytes_per_step=4, steps=e_steps,
-                   includes="H2D of vertices/faces/features/texture samples, nfCount + normals + SH + CSR "
-                            "rebuild, fwd+bwd, loss D2H")
+                   mesh_groups=len(feed.batches),
+                   includes="H2D of vertices/faces/features/texture samples (per mesh group, double-buffered: "
+                            "the copy of one group overlaps the compute of the previous one), nfCount + normals "
+                            "+ SH + CSR rebuild, fwd+bwd, loss D2H")
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

@@ -85,3 +85,57 @@ class FilterGradAllReduce:
                 p.grad = v.clone()
             else:
                 p.grad.copy_(v)
+
+
+class HostBatchFeed:
+    """Double-buffered host-to-device feed for a sequence of mesh batches that live in pinned
+    host memory: while the caller's stream computes batch g, batch g+1 is copied on a side
+    stream into the other device buffer.  Iterating yields, per batch, a dict of device
+    tensors (views of the buffers, valid until the next batch is requested).
+
+    The batches of one step are independent under the mesh convolutions (filter gradients
+    accumulate over them), so a step over all of them equals a step over their concatenation.
+    """
+
+    def __init__(self, pinned_batches: Sequence[dict], device: torch.device, depth: int = 2):
+        assert depth >= 1 and len(pinned_batches) > 0
+        self.batches = list(pinned_batches)
+        self.device = device
+        self.depth = depth
+        self.copy_stream = torch.cuda.Stream(device=device)
+        keys = list(self.batches[0].keys())
+        self.bufs = []
+        for _ in range(min(depth, len(self.batches))):
+            buf = {}
+            for k in keys:
+                rows = max(b[k].shape[0] for b in self.batches)
+                t0 = self.batches[0][k]
+                buf[k] = torch.empty((rows,) + tuple(t0.shape[1:]), dtype=t0.dtype, device=device)
+            self.bufs.append(buf)
+        self.free = [None] * len(self.bufs)
+        self.bytes_per_pass = sum(t.numel() * t.element_size() for b in self.batches for t in b.values())
+
+    def _issue(self, g: int) -> torch.cuda.Event:
+        slot = g % len(self.bufs)
+        with torch.cuda.stream(self.copy_stream):
+            if self.free[slot] is not None:
+                self.copy_stream.wait_event(self.free[slot])
+            for k, t in self.batches[g].items():
+                self.bufs[slot][k][: t.shape[0]].copy_(t, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+        return ev
+
+    def __iter__(self):
+        n, nb = len(self.batches), len(self.bufs)
+        cur = torch.cuda.current_stream(self.device)
+        copied = {g: self._issue(g) for g in range(min(nb, n))}
+        for g in range(n):
+            cur.wait_event(copied.pop(g))
+            slot = g % nb
+            yield {k: self.bufs[slot][k][: t.shape[0]] for k, t in self.batches[g].items()}
+            done = torch.cuda.Event()
+            done.record(cur)
+            self.free[slot] = done
+            if g + nb < n:
+                copied[g + nb] = self._issue(g + nb)
