@@ -190,7 +190,9 @@ def kernel_models(d):
 # capture on a 2-mesh case of the same shapes, divided by its face count; traffic grows in
 # proportion to the faces).  Source: the summaries under profiles/.
 MEASURED_DRAM_BYTES_PER_FACE = {
-    ("c5", "f2f_bwd_gfilter_tc"): 2077.0,
+    ("c5", "f2f_fwd_tc"): 2032.0,
+    ("c5", "f2f_bwd_gin_tc"): 2105.0,
+    ("c5", "f2f_bwd_gfilter_tc"): 2157.0,
 }
 
 
