@@ -21,15 +21,19 @@ bool supported(int Cin, int Cout, int F);
 bool fits(int Cin, int Cout, int F, int precision);
 size_t workspace_bytes(int Cin, int Cout, int F, int precision);
 int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* filter, const float* bary,
-                   const int32_t* cum, float* gin, int precision, void* ws, cudaStream_t stream);
+                   const float* bary_p, int Fp, const int32_t* cum, float* gin, int precision, void* ws,
+                   cudaStream_t stream);
 }  // namespace gin
 namespace gfilter {
 bool supported(int Cin, int Cout, int F);
 bool fits(int64_t Nf, int Cin, int Cout, int F, int precision);
-size_t workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision);
-int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
-                    const float* bary, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream);
+size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision);
+int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* input, const float* bary_p,
+                    int Fp, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream);
 }  // namespace gfilter
+int padded_F(int F);
+size_t padded_bary_bytes(int64_t NiK, int F);
+int pad_bary(int64_t NiK, int F, const float* bary, float* dst, cudaStream_t stream);
 }  // namespace tc
 }  // namespace pb
 
@@ -86,7 +90,8 @@ size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int C
     const bool tg = use_tc_gin(Cin, Cout, F, precision), tf = use_tc_gf(Nf, Cin, Cout, F, precision);
     size_t n = (tg && tf) ? 0 : f2f_simt_bwd_ws(Nf, Cin, Cout, F);
     if (tg) n += tc::gin::workspace_bytes(Cin, Cout, F, precision);
-    if (tf) n += tc::gfilter::workspace_bytes(Nf, NiK, Cin, Cout, F, precision);
+    if (tf) n += tc::gfilter::workspace_bytes(Nf, Cin, Cout, F, precision);
+    if (tg || tf) n += tc::padded_bary_bytes(NiK, F);
     return n;
 }
 
@@ -115,16 +120,26 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
     char* w = (char*)workspace;
     void* simt_ws = w;
     if (!(tg && tf)) w += f2f_simt_bwd_ws(Nf, Cin, Cout, F);
+    // both tensor-core kernels read bary rows with 16-byte loads: rows padded to 4 floats
+    const float* bary_p = bary;
+    const int Fp = tc::padded_F(F);
+    if ((tg || tf) && F % 4 != 0 && NiK > 0) {
+        char* wp = w + (tg ? tc::gin::workspace_bytes(Cin, Cout, F, precision) : 0) +
+                   (tf ? tc::gfilter::workspace_bytes(Nf, Cin, Cout, F, precision) : 0);
+        int rc = tc::pad_bary(NiK, F, bary, (float*)wp, stream);
+        if (rc) return rc;
+        bary_p = (const float*)wp;
+    }
     if (tg) {
         if (NiK > 0) {
-            int rc = tc::gin::backward_input(Nf, Cin, Cout, F, gradOutput, filter, bary, numInterior, gradInput,
-                                             precision, w, stream);
+            int rc = tc::gin::backward_input(Nf, Cin, Cout, F, gradOutput, filter, bary, bary_p, Fp, numInterior,
+                                             gradInput, precision, w, stream);
             if (rc) return rc;
         }
         w += tc::gin::workspace_bytes(Cin, Cout, F, precision);
     }
     if (tf) {
-        int rc = tc::gfilter::backward_filter(Nf, NiK, Cin, Cout, F, gradOutput, input, bary, numInterior, gradFilter,
+        int rc = tc::gfilter::backward_filter(Nf, Cin, Cout, F, gradOutput, input, bary_p, Fp, numInterior, gradFilter,
                                               precision, w, stream);
         if (rc) return rc;
     }

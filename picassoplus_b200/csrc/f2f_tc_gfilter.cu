@@ -467,31 +467,22 @@ bool fits(int64_t Nf, int Cin, int Cout, int F, int precision) {
     return plan(Nf, Cin, Cout, F, precision).smem <= 227 * 1024;
 }
 
-static int padded_F(int F) { return (F + 3) / 4 * 4; }
-static size_t padded_bary_bytes(int64_t NiK, int F) {
-    return F % 4 == 0 ? 0 : align_up((size_t)NiK * padded_F(F) * sizeof(float), 256);
+size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision) {
+    return align_up(plan(Nf, Cin, Cout, F, precision).partial_bytes, 256);
 }
 
-size_t workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
-    return align_up(plan(Nf, Cin, Cout, F, precision).partial_bytes, 256) + padded_bary_bytes(NiK, F);
-}
-
-int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gout, const float* input,
-                    const float* bary, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream) {
+// `bary_p`: bary with rows of `Fp` floats (F rounded up to 4, pad columns zero; see tc::pad_bary)
+int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* input, const float* bary_p,
+                    int Fp, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream) {
     int rc = check_async_error("facet2facet_backward");
     if (rc) return rc;
     Plan pl = plan(Nf, Cin, Cout, F, precision);
     Params p;
-    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F; p.Fp = padded_F(F);
+    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F; p.Fp = Fp;
     p.ncg = pl.ncg; p.nchunks = pl.nchunks; p.stages_per_chunk = pl.stages_per_chunk;
     p.nstages = pl.nstages; p.nraw = pl.nraw;
     p.gout = gout; p.in = input; p.cum = cum; p.partial = (float*)ws;
-    p.bary = bary;
-    if (F % 4 != 0 && NiK > 0) {
-        float* padded = reinterpret_cast<float*>((char*)ws + align_up(pl.partial_bytes, 256));
-        PB_LAUNCH("f2f_pad_bary", pad_bary_kernel, persistent_blocks(NiK * p.Fp, 256, 8), 256, 0, stream, NiK, F, p.Fp, bary, padded);
-        p.bary = padded;
-    }
+    p.bary = bary_p;
     p.async_err = async_error_word();
     int grid = pl.ncg * pl.nchunks;
     if (pl.nsplit == 2) {
@@ -505,5 +496,18 @@ int backward_filter(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const flo
 }
 
 }  // namespace gfilter
+
+// bary rows padded to a multiple of 4 floats, shared by the two backward kernels
+int padded_F(int F) { return (F + 3) / 4 * 4; }
+size_t padded_bary_bytes(int64_t NiK, int F) {
+    return F % 4 == 0 ? 0 : align_up((size_t)(NiK > 0 ? NiK : 1) * padded_F(F) * sizeof(float), 256);
+}
+int pad_bary(int64_t NiK, int F, const float* bary, float* dst, cudaStream_t stream) {
+    if (NiK <= 0) return PB200_OK;
+    const int Fp = padded_F(F);
+    PB_LAUNCH("f2f_pad_bary", gfilter::pad_bary_kernel, persistent_blocks(NiK * Fp, 256, 8), 256, 0, stream, NiK, F, Fp,
+              bary, dst);
+    return PB200_OK;
+}
 }  // namespace tc
 }  // namespace pb

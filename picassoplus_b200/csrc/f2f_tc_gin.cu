@@ -125,6 +125,8 @@ struct Params {
     int bary_rows, bpitch;           // staged bary rows per tile (0 = read from global), row pitch in floats
     const float* gout;
     const float* bary;
+    const float* bary_p;             // bary with rows padded to Fp floats (pad columns zero)
+    int Fp;
     const int32_t* cum;
     const uint8_t* wimg;
     float* gin;
@@ -247,15 +249,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             float2 breg[4][FH];
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
-                const float* src = p.bary + (int64_t)(k0 + (t < T ? t : 0)) * F;
+                // 16-byte loads from the padded rows (pad columns are zero)
+                const float4* src = reinterpret_cast<const float4*>(p.bary_p + (int64_t)(k0 + (t < T ? t : 0)) * p.Fp);
 #pragma unroll
-                for (int d = 0; d < FH; ++d) {
-                    float lo_ = 0.f, hi_ = 0.f;
-                    if (lean && t < T) {
-                        lo_ = __ldg(src + 2 * d);
-                        if (2 * d + 1 < F) hi_ = __ldg(src + 2 * d + 1);
-                    }
-                    breg[t][d] = make_float2(lo_, hi_);
+                for (int q4 = 0; q4 < (F + 3) / 4; ++q4) {
+                    const float4 v = (lean && t < T) ? ldg4(src + q4) : zero4();
+                    breg[t][2 * q4] = make_float2(v.x, v.y);
+                    if (2 * q4 + 1 < FH) breg[t][2 * q4 + 1] = make_float2(v.z, v.w);
                 }
             }
             // ---- 3. per slice: drain the accumulator, contract with bary, store gradInput
@@ -501,7 +501,8 @@ static int launch_f(int F, const Params& p, int grid, size_t smem, cudaStream_t 
 }
 
 int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* filter, const float* bary,
-                   const int32_t* cum, float* gin, int precision, void* ws, cudaStream_t stream) {
+                   const float* bary_p, int Fp, const int32_t* cum, float* gin, int precision, void* ws,
+                   cudaStream_t stream) {
     int rc = check_async_error("facet2facet_backward");
     if (rc) return rc;
     Plan pl = plan(Cin, Cout, F, precision);
@@ -513,7 +514,7 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
     p.Nf = Nf; p.Cin = Cin; p.Cout = Cout;
     p.nq = pl.nq; p.nslices = pl.nslices; p.kst = pl.kst; p.nmma = pl.nmma;
     p.nstages = pl.nstages; p.bary_rows = pl.bary_rows; p.bpitch = pl.bpitch;
-    p.gout = gout; p.bary = bary; p.cum = cum; p.wimg = wimg; p.gin = gin;
+    p.gout = gout; p.bary = bary; p.bary_p = bary_p; p.Fp = Fp; p.cum = cum; p.wimg = wimg; p.gin = gin;
     p.async_err = async_error_word();
     int64_t ntiles = ceil_div(Nf, TILE_M);
     int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
