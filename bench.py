@@ -51,8 +51,9 @@ def parse_args():
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--e2e-groups", type=int, default=8,
-                    help="mesh groups of the end-to-end step (host-to-device copy of one overlaps compute of another)")
+    ap.add_argument("--e2e-groups", type=int, default=0,
+                    help="mesh groups of the end-to-end step (host-to-device copy of one overlaps compute of another); "
+                         "0 = one group per 128 MB of host input, at most 8")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
@@ -305,7 +306,9 @@ def run_ours(args):
 
     # End to end: the rank's meshes are fed from pinned host memory in groups; the copy of
     # group g+1 overlaps the fwd+bwd of group g (filter gradients accumulate over the groups).
-    ngroups = max(1, min(args.e2e_groups, count))
+    host_bytes = sum(h[k].numel() * h[k].element_size() for k in ("vertex", "face", "x", "cum", "bary_xyz"))
+    want_groups = args.e2e_groups if args.e2e_groups > 0 else min(8, host_bytes // (128 << 20))
+    ngroups = max(1, min(want_groups, count))
     feed = None
     if not args.no_e2e:
         pinned_groups, group_G = [], []
