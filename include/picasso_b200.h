@@ -161,7 +161,10 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
 /* gradInput[k,ci] = (1/T_f) sum_d bary[k,d] * sum_co gradOutput[f,co]*filter[co,ci,d];
  * gradFilter[co,ci,d] = sum_f gradOutput[f,co]*A[f,d,ci]
  * Replaces facet2facetConv3dGradLauncher (mesh_conv3d_gpu.cu:45-135,144-168; binding
- * mesh_conv3d.cpp:229-269). */
+ * mesh_conv3d.cpp:229-269).  The tensor-core modes need gradOutput, input, bary and the
+ * workspace on 16-byte boundaries (PB200_EINVAL otherwise); the workspace holds the filter
+ * image of the input-gradient kernel, the per-chunk filter-gradient partials and, when F is
+ * not a multiple of 4, a copy of bary with rows padded to 4 floats. */
 size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision);
 int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
                                const float* input, const float* filter, const float* bary,
