@@ -13,9 +13,14 @@
 //     instruction, tf32 operands, fp32 accumulation in TMEM) and commits stages back;
 //   * the producer warps drain the 128 x 256 accumulator with tcgen05.ld and store
 //     out[f, co] coalesced along co.
-// Precision modes: 1 split  = operands rounded to tf32;
-//                  2 splits = every operand as tf32 hi + tf32 lo, three MMAs per k-step
-//                             (hi*hi + hi*lo + lo*hi): fp32-faithful products.
+// Operand formats (template BF): tf32 -- a 64-byte operand row holds 16 values = one k-block
+// (16 channels x 1 basis) -- or bf16 -- a row holds 32 values = two bases of the 16 channels,
+// so a stage carries twice the work in the same bytes and its MMAs (kind::f16, K = 16) run at
+// twice the tf32 rate.
+// Precision modes: 1 split  = operands rounded to the format;
+//                  2 splits = every operand as hi + lo of the format, three MMAs per k-step
+//                             (hi*hi + hi*lo + lo*hi).  bf16 hi+lo keeps 16 mantissa bits per
+//                             operand (products good to about 2^-16), tf32 hi+lo about 21.
 // All waits are bounded (tc_ptx.cuh); on a time-out the block unwinds, frees its TMEM and
 // raises the library's asynchronous error word.
 #include "common.cuh"
@@ -66,6 +71,51 @@ int check_async_error(const char* where) {
     return PB200_OK;
 }
 
+// two floats -> packed bf16x2 (round to nearest even), first value in the low half
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// hi = bf16(v), lo = bf16(v - hi) for two values at once
+__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
+    hi = pack_bf16x2(a, b);
+    const float ah = __uint_as_float(hi << 16), bh = __uint_as_float(hi & 0xFFFF0000u);
+    lo = pack_bf16x2(a - ah, b - bh);
+}
+
+// ---- bf16 filter image: Wimg[kb][split][co 0..127][32 bf16, 64B-swizzled], kb = c16*ceil(F/2) + dp,
+//      element (co, j*16 + kk) = filter[co][c16*16 + kk][2*dp + j]  (0 for a basis >= F)
+__global__ void f2f_tc_prep_filter_bf16_kernel(int F, int Cin, int Cout, int nsplit, const float* __restrict__ filter,
+                                               uint8_t* __restrict__ wimg) {
+    const int nd2 = (F + 1) / 2;
+    const int nkb = (Cin / 16) * nd2;
+    int64_t total = (int64_t)nkb * 128 * 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i & 3);                   // 16-byte chunk: basis j = c >> 1, channels 8*(c&1)..+7
+        const int co = (int)((i >> 2) % 128);
+        const int kb = (int)(i / (4 * 128));
+        const int c16 = kb / nd2, d = 2 * (kb - c16 * nd2) + (c >> 1);
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int ci = c16 * 16 + (c & 1) * 8 + 2 * j + e;
+                v[e] = (co < Cout && d < F) ? __ldg(filter + ((int64_t)co * Cin + ci) * F + d) : 0.f;
+            }
+            if (nsplit == 1) { hi[j] = pack_bf16x2(v[0], v[1]); lo[j] = 0u; }
+            else split_bf16x2(v[0], v[1], hi[j], lo[j]);
+        }
+        uint8_t* base = wimg + (int64_t)kb * nsplit * (128 * 64);
+        const uint32_t off = swz64_offset((uint32_t)co, (uint32_t)c);
+        *reinterpret_cast<uint4*>(base + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        if (nsplit == 2) *reinterpret_cast<uint4*>(base + 128 * 64 + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
 // ---- filter image: Wimg[kb][split][co 0..127][16 floats, 64B-swizzled], kb = c16*F + d,
 //      element (co, kk) = filter[co][c16*16 + kk][d]
 __global__ void f2f_tc_prep_filter_kernel(int F, int Cin, int Cout, int nsplit, const float* __restrict__ filter,
@@ -111,7 +161,7 @@ __host__ __device__ inline size_t fwd_stage_bytes(int nsplit) {
     return (size_t)nsplit * (FACE_TILE_BYTES + FILT_TILE_BYTES);
 }
 
-template <int NSPLIT>
+template <int NSPLIT, bool BF>
 __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -144,7 +194,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
     const uint32_t tmem_base = *tmem_slot;
 
     const int64_t ntiles = (p.Nf + TILE_F - 1) / TILE_F;
-    const int nkb = (Cin / KS) * F;
+    const int nkb = (Cin / KS) * (BF ? (F + 1) / 2 : F);     // stages per tile
 
     if (warp < PWARPS) {
         // ================================ producers + epilogue ================================
@@ -154,22 +204,45 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
         for (int i = lane; i < p.smaxw * FP; i += 32) wb[i] = 0.f;
         const uint32_t off0 = swz64_offset((uint32_t)m, (uint32_t)(2 * h));
         const uint32_t off1 = swz64_offset((uint32_t)m, (uint32_t)(2 * h + 1));
+        // bf16 rows: chunk 2*j + h holds the thread's 8 channels of basis j of the stage's pair
+        const uint32_t offb0 = swz64_offset((uint32_t)m, (uint32_t)h), offb1 = swz64_offset((uint32_t)m, (uint32_t)(2 + h));
         const uint32_t stages32 = smem_u32(stages), wb32 = smem_u32(wb);
         int st_i = 0;                                         // running stage index and phase
         uint32_t st_ph = 0;
         uint32_t tcount = 0;
         bool alive = true;
 
-        // publish one operand row segment (a0, a1 = 8 channels of A[f, d, :]) into the current stage
-        auto publish = [&](const float4& a0, const float4& a1) -> bool {
-            if (!mbar_try_wait(&empty[st_i], st_ph ^ 1u)) {
-                int ok = 1;
-                if (lane == 0) ok = mbar_wait(&empty[st_i], st_ph ^ 1u, abort_flag) ? 1 : 0;
-                ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) return false;
+        // publish one operand row segment (a0, a1 = 8 channels of A[f, d, :]) into the current stage;
+        // a bf16 stage takes two bases (d even, then d odd; an odd F ends with a zero partner)
+        auto publish = [&](const float4& a0, const float4& a1, int d) -> bool {
+            if (!BF || (d & 1) == 0) {
+                if (!mbar_try_wait(&empty[st_i], st_ph ^ 1u)) {
+                    int ok = 1;
+                    if (lane == 0) ok = mbar_wait(&empty[st_i], st_ph ^ 1u, abort_flag) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, ok, 0);
+                    if (!ok) return false;
+                }
             }
             const uint32_t st = stages32 + (uint32_t)st_i * (uint32_t)stage_bytes;
-            if (NSPLIT == 1) {
+            if (BF) {
+                uint32_t hi[4], lo[4];
+                if (NSPLIT == 1) {
+                    hi[0] = pack_bf16x2(a0.x, a0.y); hi[1] = pack_bf16x2(a0.z, a0.w);
+                    hi[2] = pack_bf16x2(a1.x, a1.y); hi[3] = pack_bf16x2(a1.z, a1.w);
+                } else {
+                    split_bf16x2(a0.x, a0.y, hi[0], lo[0]); split_bf16x2(a0.z, a0.w, hi[1], lo[1]);
+                    split_bf16x2(a1.x, a1.y, hi[2], lo[2]); split_bf16x2(a1.z, a1.w, hi[3], lo[3]);
+                }
+                const uint32_t ob = (d & 1) ? offb1 : offb0;
+                sts_f4(st + ob, make_float4(__uint_as_float(hi[0]), __uint_as_float(hi[1]), __uint_as_float(hi[2]), __uint_as_float(hi[3])));
+                if (NSPLIT == 2)
+                    sts_f4(st + FACE_TILE_BYTES + ob, make_float4(__uint_as_float(lo[0]), __uint_as_float(lo[1]), __uint_as_float(lo[2]), __uint_as_float(lo[3])));
+                if ((d & 1) == 0) {
+                    if (d + 1 < F) return true;                // the stage is complete with the next basis
+                    sts_f4(st + offb1, zero4());
+                    if (NSPLIT == 2) sts_f4(st + FACE_TILE_BYTES + offb1, zero4());
+                }
+            } else if (NSPLIT == 1) {
                 sts_f4(st + off0, make_float4(to_tf32_rna(a0.x), to_tf32_rna(a0.y), to_tf32_rna(a0.z), to_tf32_rna(a0.w)));
                 sts_f4(st + off1, make_float4(to_tf32_rna(a1.x), to_tf32_rna(a1.y), to_tf32_rna(a1.z), to_tf32_rna(a1.w)));
             } else {
@@ -253,7 +326,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                                     fma4s(a0, bj, x[t][0]);
                                     fma4s(a1, bj, x[t][1]);
                                 }
-                                if (!publish(a0, a1)) { alive = false; break; }
+                                if (!publish(a0, a1, d4 + j)) { alive = false; break; }
                             }
                         }
                     }
@@ -270,7 +343,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                             fma4s(a0, b, ldg4(src));
                             fma4s(a1, b, ldg4(src + 1));
                         }
-                        if (!publish(a0, a1)) { alive = false; break; }
+                        if (!publish(a0, a1, d)) { alive = false; break; }
                     }
                 }
             }
@@ -323,7 +396,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
     } else {
         // ================================ MMA issuer =========================================
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(FMT_TF32, UM, TILE_F);
+            constexpr uint32_t idesc = instr_desc(BF ? FMT_BF16 : FMT_TF32, UM, TILE_F);
             const uint64_t dbase = smem_desc_kmajor(smem_u32(stages), 64, SWZ_64B);
             int s = 0;
             uint32_t ph = 0;
@@ -336,17 +409,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                     const uint64_t face_hi = dbase + (uint64_t)(((uint32_t)s * (uint32_t)stage_bytes) >> 4);
                     const uint64_t filt_hi = face_hi + (uint64_t)((NSPLIT * FACE_TILE_BYTES) >> 4);
 #pragma unroll
-                    for (int ks = 0; ks < 2; ++ks) {          // 2 x (K = 8 tf32 = 32 bytes)
+                    for (int ks = 0; ks < 2; ++ks) {          // 2 x 32 bytes of K (8 tf32 or 16 bf16)
                         const uint64_t adv = (uint64_t)(ks * 2);
                         const uint32_t first = (kb | ks) != 0;
+                        auto mma = [&](uint64_t a, uint64_t b, uint32_t acc) {
+                            if (BF) mma_f16(tmem_base, a, b, idesc, acc); else mma_tf32(tmem_base, a, b, idesc, acc);
+                        };
                         if (NSPLIT == 1) {
-                            mma_tf32(tmem_base, filt_hi + adv, face_hi + adv, idesc, first);
+                            mma(filt_hi + adv, face_hi + adv, first);
                         } else {
                             const uint64_t face_lo = face_hi + (uint64_t)(FACE_TILE_BYTES >> 4);
                             const uint64_t filt_lo = filt_hi + (uint64_t)(FILT_TILE_BYTES >> 4);
-                            mma_tf32(tmem_base, filt_lo + adv, face_hi + adv, idesc, first);
-                            mma_tf32(tmem_base, filt_hi + adv, face_lo + adv, idesc, 1u);
-                            mma_tf32(tmem_base, filt_hi + adv, face_hi + adv, idesc, 1u);
+                            mma(filt_lo + adv, face_hi + adv, first);
+                            mma(filt_hi + adv, face_lo + adv, 1u);
+                            mma(filt_hi + adv, face_hi + adv, 1u);
                         }
                     }
                     tc_commit(&empty[s]);
@@ -368,13 +444,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
 }
 
 // ---------------------------------------------------------------------------- host side
-struct FwdPlan { int nsplit, nstages, smaxw, bpitch; size_t smem; size_t wimg_bytes; };
+struct FwdPlan { int nsplit, bf, nkb, nstages, smaxw, bpitch; size_t smem; size_t wimg_bytes; };
 
 bool fwd_supported(int Cin, int Cout, int F) { return Cin % KS == 0 && Cout >= 1 && Cout <= UM && F >= 1 && F <= 50; }
 
 FwdPlan fwd_plan(int Cin, int Cout, int F, int precision) {
     FwdPlan pl;
+    // fp32: bf16 hi+lo operands (three MMAs); tf32: tf32 operands; bf16: bf16 operands
+    static const bool fp32_as_tf32 = getenv("PB200_FP32_TF32_SPLIT") != nullptr;   // the tf32 hi+lo variant of fp32
     pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
+    pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
+    pl.nkb = (Cin / KS) * (pl.bf ? (F + 1) / 2 : F);
     pl.nstages = pl.nsplit == 2 ? 2 : 4;
     const int FP = ((F + 3) / 4 * 4) | 4;
     pl.bpitch = FP;
@@ -385,7 +465,7 @@ FwdPlan fwd_plan(int Cin, int Cout, int F, int precision) {
     if (smaxw < 0) smaxw = 0;
     pl.smaxw = smaxw;
     pl.smem = fixed + (size_t)PWARPS * smaxw * FP * 4;
-    pl.wimg_bytes = (size_t)(Cin / KS) * F * pl.nsplit * FILT_TILE_BYTES;
+    pl.wimg_bytes = (size_t)pl.nkb * pl.nsplit * FILT_TILE_BYTES;
     return pl;
 }
 
@@ -400,9 +480,14 @@ int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* inpu
     if (rc) return rc;
     FwdPlan pl = fwd_plan(Cin, Cout, F, precision);
     uint8_t* wimg = (uint8_t*)ws;
-    int64_t prep_items = (int64_t)(Cin / KS) * F * UM * 4;
-    PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_kernel, persistent_blocks(prep_items, 256, 8), 256, 0, stream,
-              F, Cin, Cout, pl.nsplit, filter, wimg);
+    int64_t prep_items = (int64_t)pl.nkb * UM * 4;
+    if (pl.bf) {
+        PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_bf16_kernel, persistent_blocks(prep_items, 256, 8), 256, 0,
+                  stream, F, Cin, Cout, pl.nsplit, filter, wimg);
+    } else {
+        PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_kernel, persistent_blocks(prep_items, 256, 8), 256, 0, stream,
+                  F, Cin, Cout, pl.nsplit, filter, wimg);
+    }
     FwdParams p;
     p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F;
     p.nstages = pl.nstages; p.smaxw = pl.smaxw; p.bpitch = pl.bpitch;
@@ -410,13 +495,17 @@ int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* inpu
     p.async_err = async_error_word();
     int64_t ntiles = ceil_div(Nf, TILE_F);
     int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
-    if (pl.nsplit == 2) {
-        PB_CUDA(cudaFuncSetAttribute(f2f_fwd_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-        PB_LAUNCH("f2f_fwd_tc", f2f_fwd_tc_kernel<2>, grid, NTHREADS, pl.smem, stream, p);
-    } else {
-        PB_CUDA(cudaFuncSetAttribute(f2f_fwd_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-        PB_LAUNCH("f2f_fwd_tc", f2f_fwd_tc_kernel<1>, grid, NTHREADS, pl.smem, stream, p);
-    }
+#define PB_FWD_LAUNCH(NS, BFV)                                                                                      \
+    do {                                                                                                              \
+        PB_CUDA(cudaFuncSetAttribute(f2f_fwd_tc_kernel<NS, BFV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                     (int)pl.smem));                                                                  \
+        PB_LAUNCH("f2f_fwd_tc", (f2f_fwd_tc_kernel<NS, BFV>), grid, NTHREADS, pl.smem, stream, p);                    \
+    } while (0)
+    if (pl.nsplit == 2 && pl.bf) PB_FWD_LAUNCH(2, true);
+    else if (pl.nsplit == 2) PB_FWD_LAUNCH(2, false);
+    else if (pl.bf) PB_FWD_LAUNCH(1, true);
+    else PB_FWD_LAUNCH(1, false);
+#undef PB_FWD_LAUNCH
     return PB200_OK;
 }
 
