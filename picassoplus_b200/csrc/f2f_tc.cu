@@ -71,19 +71,6 @@ int check_async_error(const char* where) {
     return PB200_OK;
 }
 
-// two floats -> packed bf16x2 (round to nearest even), first value in the low half
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-// hi = bf16(v), lo = bf16(v - hi) for two values at once
-__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
-    hi = pack_bf16x2(a, b);
-    const float ah = __uint_as_float(hi << 16), bh = __uint_as_float(hi & 0xFFFF0000u);
-    lo = pack_bf16x2(a - ah, b - bh);
-}
-
 // ---- bf16 filter image: Wimg[kb][split][co 0..127][32 bf16, 64B-swizzled], kb = c16*ceil(F/2) + dp,
 //      element (co, j*16 + kk) = filter[co][c16*16 + kk][2*dp + j]  (0 for a basis >= F)
 __global__ void f2f_tc_prep_filter_bf16_kernel(int F, int Cin, int Cout, int nsplit, const float* __restrict__ filter,

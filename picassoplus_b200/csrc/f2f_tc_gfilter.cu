@@ -99,6 +99,46 @@ __device__ __forceinline__ void put4(uint32_t a, uint32_t lo_off, const float4& 
     }
 }
 
+// bf16 operands (MN-major, 128-byte swizzle): a K-row piece of 128 bytes holds 64 columns, an
+// atom 8 K-rows; blocks of 64 columns are 1 KB apart, the two 8-face groups of a stage
+// `blocks` KB apart.
+constexpr int BATOM_BYTES = 1024;
+constexpr int BG_SBO = (UM / 64) * BATOM_BYTES;
+constexpr int BG_TILE_BYTES = (KF / 8) * BG_SBO;
+__host__ __device__ constexpr int at_blocks_b16(int F) { return (F * CG + 63) / 64; }
+__device__ __forceinline__ void sts_u2(uint32_t a, uint32_t x, uint32_t y) {
+    asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(a), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void sts_u4(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// eight operand elements as bf16 (1 split) or bf16 hi + bf16 lo (2 splits): one 16-byte store each
+template <int NSPLIT>
+__device__ __forceinline__ void put8_b16(uint32_t a, uint32_t lo_off, const float4& u, const float4& w) {
+    uint32_t hi[4], lo[4];
+    if (NSPLIT == 1) {
+        hi[0] = pack_bf16x2(u.x, u.y); hi[1] = pack_bf16x2(u.z, u.w); hi[2] = pack_bf16x2(w.x, w.y); hi[3] = pack_bf16x2(w.z, w.w);
+        sts_u4(a, hi[0], hi[1], hi[2], hi[3]);
+    } else {
+        split_bf16x2(u.x, u.y, hi[0], lo[0]); split_bf16x2(u.z, u.w, hi[1], lo[1]);
+        split_bf16x2(w.x, w.y, hi[2], lo[2]); split_bf16x2(w.z, w.w, hi[3], lo[3]);
+        sts_u4(a, hi[0], hi[1], hi[2], hi[3]);
+        sts_u4(a + lo_off, lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+// four elements: one 8-byte store each
+template <int NSPLIT>
+__device__ __forceinline__ void put4_b16(uint32_t a, uint32_t lo_off, const float4& v) {
+    uint32_t hi[2], lo[2];
+    if (NSPLIT == 1) {
+        sts_u2(a, pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+    } else {
+        split_bf16x2(v.x, v.y, hi[0], lo[0]); split_bf16x2(v.z, v.w, hi[1], lo[1]);
+        sts_u2(a, hi[0], hi[1]);
+        sts_u2(a + lo_off, lo[0], lo[1]);
+    }
+}
+
 // one whole warp waits on an mbarrier phase: every lane probes once, then lane 0 waits (bounded)
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
     if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity) ? 1 : 0)) return true;
@@ -126,16 +166,19 @@ struct Params {
     int* async_err;
 };
 
-template <int NSPLIT>
+template <int NSPLIT, bool BF>
 __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int S = p.nstages, NRAW = p.nraw, F = p.F, Cin = p.Cin, Cout = p.Cout;
     const int NR = F * CG;                                   // accumulator columns / A columns
-    const uint32_t at_sbo = (uint32_t)at_blocks(F) * ATOM_BYTES;             // A block: [4-face group][32-column block][atom]
-    const size_t at_bytes = (KF / 4) * (size_t)at_sbo;
-    const size_t stage_bytes = (size_t)NSPLIT * (G_TILE_BYTES + at_bytes);   // [g hi][g lo?][A hi][A lo?]
+    // A block: [face group][column block][atom]; tf32: groups of 4 faces, blocks of 32 columns, 512-byte
+    // atoms; bf16: groups of 8 faces, blocks of 64 columns, 1 KB atoms
+    const uint32_t at_sbo = BF ? (uint32_t)at_blocks_b16(F) * BATOM_BYTES : (uint32_t)at_blocks(F) * ATOM_BYTES;
+    const size_t at_bytes = (BF ? KF / 8 : KF / 4) * (size_t)at_sbo;
+    constexpr uint32_t GT = BF ? BG_TILE_BYTES : G_TILE_BYTES;              // gradOutput block of one split
+    const size_t stage_bytes = (size_t)NSPLIT * (GT + at_bytes);             // [g hi][g lo?][A hi][A lo?]
     uint8_t* stages = smem;
     uint8_t* raw = smem + (size_t)S * stage_bytes;            // [NRAW][RAW_BYTES]
     uint64_t* bars = reinterpret_cast<uint64_t*>(raw + (size_t)NRAW * RAW_BYTES);
@@ -240,17 +283,37 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // the same 16-byte bank group: the lanes with fl & 4 keep their two 4-channel halves
         // swapped in registers (`sw`), so the first store of a pair lands in the other half.
         const int half = lane >> 4, fl = lane & 15;
-        const uint32_t sw = (fl & 4) ? 16u : 0u;
-        const uint32_t a_row = (uint32_t)(NSPLIT * G_TILE_BYTES) + (uint32_t)(fl >> 2) * at_sbo + (uint32_t)(fl & 3) * 128u
-                               + (uint32_t)(2 * warp) * ATOM_BYTES + sw;
-        const uint32_t a_off0 = a_row + (((uint32_t)half ^ (uint32_t)(fl & 3)) << 5);          // even bases
-        const uint32_t a_off1 = a_row + (((2u + (uint32_t)half) ^ (uint32_t)(fl & 3)) << 5);   // odd bases
+        // bf16: the thread's 8 columns of basis 4q + dd are 16-byte chunk 2*dd + half of 64-column
+        // block q, chunk c of K-row k is stored at c ^ (k & 7): the 8 lanes of a quarter warp hit 8
+        // distinct bank groups without any swap.
+        const uint32_t sw = BF ? 0u : ((fl & 4) ? 16u : 0u);
+        const uint32_t a_row = BF ? (uint32_t)(NSPLIT * GT) + (uint32_t)(fl >> 3) * at_sbo + (uint32_t)(fl & 7) * 128u
+                                        + (uint32_t)warp * BATOM_BYTES
+                                  : (uint32_t)(NSPLIT * GT) + (uint32_t)(fl >> 2) * at_sbo + (uint32_t)(fl & 3) * 128u
+                                        + (uint32_t)(2 * warp) * ATOM_BYTES + sw;
+        const uint32_t a_off0 = a_row + (((uint32_t)half ^ (uint32_t)(fl & 3)) << 5);          // tf32, even bases
+        const uint32_t a_off1 = a_row + (((2u + (uint32_t)half) ^ (uint32_t)(fl & 3)) << 5);   // tf32, odd bases
+        // byte address (inside a stage) of the thread's 8 columns of basis 4q + dd
+        auto a_addr = [&](int dd) -> uint32_t {
+            if (BF) return a_row + (((uint32_t)(2 * dd + half) ^ (uint32_t)(fl & 7)) << 4);
+            return ((dd & 1) ? a_off1 : a_off0) + (uint32_t)(dd >> 1) * ATOM_BYTES;
+        };
+        // the thread's 8 values of a basis (first four, last four) into the A block
+        auto put_a = [&](uint32_t sb32, int dd, const float4& u, const float4& w) {
+            const uint32_t da32 = sb32 + a_addr(dd);
+            if (BF) put8_b16<NSPLIT>(da32, (uint32_t)at_bytes, u, w);
+            else { put4<NSPLIT>(da32, (uint32_t)at_bytes, u); put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, w); }
+        };
         const bool has_unit = 4 * warp < F;
         // --- gradOutput block: warp w copies the rows of faces 2w and 2w+1 straight from global
         // memory (registers, two stages ahead): lane l holds channels 4l..4l+3 of both, so a warp
         // load reads one whole row and the 8 lanes of a quarter warp store 128 consecutive bytes
         // of the face's K-row (16-byte piece l&7 of 32-channel block l>>3).
+        // (bf16: 8-byte piece l&15 of 64-channel block l>>4)
         auto g_row_off = [&](int k) -> uint32_t {
+            if (BF)
+                return (uint32_t)(k >> 3) * BG_SBO + (uint32_t)(k & 7) * 128u + (uint32_t)(lane >> 4) * BATOM_BYTES
+                       + ((((uint32_t)(lane & 15) >> 1) ^ (uint32_t)(k & 7)) << 4) + (uint32_t)(lane & 1) * 8u;
             return (uint32_t)(k >> 2) * G_SBO + (uint32_t)(k & 3) * 128u + (uint32_t)(lane >> 3) * ATOM_BYTES
                    + ((((uint32_t)(lane & 7) >> 1) ^ (uint32_t)(k & 3)) << 5) + (uint32_t)(lane & 1) * 16u;
         };
@@ -279,8 +342,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             const float invT = __int_as_float(rec.z);
             if (!warp_wait(&empty[si], sph ^ 1u, abort_flag, lane)) { alive = false; break; }
             const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes;
-            put4<NSPLIT>(sb32 + g_off0, G_TILE_BYTES, gu0);
-            put4<NSPLIT>(sb32 + g_off1, G_TILE_BYTES, gw0);
+            if (BF) { put4_b16<NSPLIT>(sb32 + g_off0, GT, gu0); put4_b16<NSPLIT>(sb32 + g_off1, GT, gw0); }
+            else { put4<NSPLIT>(sb32 + g_off0, GT, gu0); put4<NSPLIT>(sb32 + g_off1, GT, gw0); }
             gu0 = gu1; gw0 = gw1; gu1 = gu2; gw1 = gw2;
             if (has_unit && !slow) {
                 // fast path: every face of the stage has at most TREG samples, all of them staged.
@@ -315,9 +378,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 #pragma unroll
                             for (int j = 0; j < 4; ++j) a[j] = __ffma2_rn(b2, x[t][j], a[j]);
                         }
-                        const uint32_t da32 = sb32 + ((dd & 1) ? a_off1 : a_off0) + (uint32_t)(dd >> 1) * ATOM_BYTES;
-                        put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0].x, a[0].y, a[1].x, a[1].y));
-                        put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[2].x, a[2].y, a[3].x, a[3].y));
+                        put_a(sb32, dd, make_float4(a[0].x, a[0].y, a[1].x, a[1].y), make_float4(a[2].x, a[2].y, a[3].x, a[3].y));
                     }
                 }
             } else if (has_unit) {
@@ -335,9 +396,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 #pragma unroll
                         for (int j = 0; j < 8; ++j) a[j] = fmaf(bv, __ldg(xr + (j ^ jsw)), a[j]);
                     }
-                    const uint32_t da32 = sb32 + ((dd & 1) ? a_off1 : a_off0) + (uint32_t)(dd >> 1) * ATOM_BYTES;
-                    put4<NSPLIT>(da32, (uint32_t)at_bytes, make_float4(a[0], a[1], a[2], a[3]));
-                    put4<NSPLIT>(da32 ^ 16u, (uint32_t)at_bytes, make_float4(a[4], a[5], a[6], a[7]));
+                    put_a(sb32, dd, make_float4(a[0], a[1], a[2], a[3]), make_float4(a[4], a[5], a[6], a[7]));
                 }
             }
             fence_proxy_async();
@@ -374,10 +433,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // ==================================== MMA issuer ====================================
         if (lane == 0) {
             const int n1 = NR < 256 ? NR : 256, n2 = NR - n1;
-            const uint32_t idesc1 = instr_desc_mnmajor(FMT_TF32, UM, (uint32_t)n1);
-            const uint32_t idesc2 = instr_desc_mnmajor(FMT_TF32, UM, (uint32_t)(n2 > 0 ? n2 : 16));
-            const uint64_t dbase_g = smem_desc_mnmajor_b32(stages32, ATOM_BYTES, G_SBO);
-            const uint64_t dbase_a = smem_desc_mnmajor_b32(stages32 + NSPLIT * G_TILE_BYTES, ATOM_BYTES, at_sbo);
+            const uint32_t idesc1 = instr_desc_mnmajor(BF ? FMT_BF16 : FMT_TF32, UM, (uint32_t)n1);
+            const uint32_t idesc2 = instr_desc_mnmajor(BF ? FMT_BF16 : FMT_TF32, UM, (uint32_t)(n2 > 0 ? n2 : 16));
+            const uint64_t dbase_g = BF ? smem_desc_mnmajor_b16(stages32, BATOM_BYTES, BG_SBO)
+                                        : smem_desc_mnmajor_b32(stages32, ATOM_BYTES, G_SBO);
+            const uint64_t dbase_a = BF ? smem_desc_mnmajor_b16(stages32 + NSPLIT * GT, BATOM_BYTES, at_sbo)
+                                        : smem_desc_mnmajor_b32(stages32 + NSPLIT * GT, ATOM_BYTES, at_sbo);
+            // tf32: one instruction = 8 faces = two 4-face groups, two per stage; bf16: one
+            // instruction = 16 faces = two 8-face groups, one per stage
+            constexpr int KSTEPS = BF ? 1 : 2;
+            const uint32_t g_kstep = 2 * G_SBO, a_kstep = 2 * at_sbo;
+            const uint32_t n_chunk = BF ? 4u * BATOM_BYTES : 8u * ATOM_BYTES;      // 256 columns further on
             int si = 0;
             uint32_t sph = 0;
             bool alive = true;
@@ -387,21 +453,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                 const uint64_t soff = (uint64_t)(((uint32_t)si * (uint32_t)stage_bytes) >> 4);
                 const uint64_t dg_hi0 = dbase_g + soff, da_hi0 = dbase_a + soff;
 #pragma unroll
-                for (int k2 = 0; k2 < 2; ++k2) {                        // one instruction = 8 faces = two 4-face groups
+                for (int k2 = 0; k2 < KSTEPS; ++k2) {
                     const uint32_t first = (st != 0 || k2 != 0) ? 1u : 0u;
                     for (int c = 0; c < (n2 > 0 ? 2 : 1); ++c) {
                         const uint32_t d_tmem = tmem_base + (uint32_t)(c * 256);
                         const uint32_t idesc = c == 0 ? idesc1 : idesc2;
-                        const uint64_t dg_hi = dg_hi0 + (uint64_t)((k2 * 2 * G_SBO) >> 4);
-                        const uint64_t da_hi = da_hi0 + (uint64_t)(((uint32_t)k2 * 2u * at_sbo + (uint32_t)c * (8u * ATOM_BYTES)) >> 4);
+                        const uint64_t dg_hi = dg_hi0 + (uint64_t)(((uint32_t)k2 * g_kstep) >> 4);
+                        const uint64_t da_hi = da_hi0 + (uint64_t)(((uint32_t)k2 * a_kstep + (uint32_t)c * n_chunk) >> 4);
+                        auto mma = [&](uint64_t a, uint64_t b, uint32_t acc) {
+                            if (BF) mma_f16(d_tmem, a, b, idesc, acc); else mma_tf32(d_tmem, a, b, idesc, acc);
+                        };
                         if (NSPLIT == 1) {
-                            mma_tf32(d_tmem, dg_hi, da_hi, idesc, first);
+                            mma(dg_hi, da_hi, first);
                         } else {
-                            const uint64_t dg_lo = dg_hi + (uint64_t)(G_TILE_BYTES >> 4);
+                            const uint64_t dg_lo = dg_hi + (uint64_t)(GT >> 4);
                             const uint64_t da_lo = da_hi + (uint64_t)(at_bytes >> 4);
-                            mma_tf32(d_tmem, dg_lo, da_hi, idesc, first);
-                            mma_tf32(d_tmem, dg_hi, da_lo, idesc, 1u);
-                            mma_tf32(d_tmem, dg_hi, da_hi, idesc, 1u);
+                            mma(dg_lo, da_hi, first);
+                            mma(dg_hi, da_lo, 1u);
+                            mma(dg_hi, da_hi, 1u);
                         }
                     }
                 }
@@ -434,7 +503,7 @@ __global__ void pad_bary_kernel(int64_t n, int F, int Fp, const float* __restric
 }
 
 // ---------------------------------------------------------------------------- host side
-struct Plan { int nsplit, ncg, nchunks, nstages, nraw; int64_t stages_per_chunk; size_t smem, partial_bytes; };
+struct Plan { int nsplit, bf, ncg, nchunks, nstages, nraw; int64_t stages_per_chunk; size_t smem, partial_bytes; };
 
 bool supported(int Cin, int Cout, int F) {
     return Cin % CG == 0 && Cout % 4 == 0 && Cout >= 4 && Cout <= UM && F >= 1 && F <= 32;   // F*16 <= 512 columns
@@ -442,7 +511,10 @@ bool supported(int Cin, int Cout, int F) {
 
 Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     Plan pl;
+    // fp32: bf16 hi+lo operands (three MMAs); tf32: tf32 operands; bf16: bf16 operands
+    static const bool fp32_as_tf32 = getenv("PB200_FP32_TF32_SPLIT") != nullptr;   // the tf32 hi+lo variant of fp32
     pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
+    pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
     pl.ncg = Cin / CG;
     int64_t total_stages = ceil_div(Nf > 0 ? Nf : 1, KF);
     int nch = sm_count() / pl.ncg;
@@ -450,7 +522,8 @@ Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     if (nch > total_stages) nch = (int)total_stages;
     pl.stages_per_chunk = ceil_div(total_stages, nch);
     pl.nchunks = (int)ceil_div(total_stages, pl.stages_per_chunk);
-    const size_t stage = (size_t)pl.nsplit * (G_TILE_BYTES + (KF / 4) * (size_t)at_blocks(F) * ATOM_BYTES);
+    const size_t stage = pl.bf ? (size_t)pl.nsplit * (BG_TILE_BYTES + (KF / 8) * (size_t)at_blocks_b16(F) * BATOM_BYTES)
+                               : (size_t)pl.nsplit * (G_TILE_BYTES + (KF / 4) * (size_t)at_blocks(F) * ATOM_BYTES);
     const size_t budget = 224 * 1024, fixed = 1024 + 256;
     // operand ring as deep as fits beside a raw ring of 2 (at most 4), then the raw ring as deep as fits
     int S = 4, R = 4;
@@ -485,13 +558,17 @@ int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, con
     p.bary = bary_p;
     p.async_err = async_error_word();
     int grid = pl.ncg * pl.nchunks;
-    if (pl.nsplit == 2) {
-        PB_CUDA(cudaFuncSetAttribute(f2f_bwd_gfilter_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-        PB_LAUNCH("f2f_bwd_gfilter_tc", f2f_bwd_gfilter_tc_kernel<2>, grid, NTHREADS, pl.smem, stream, p);
-    } else {
-        PB_CUDA(cudaFuncSetAttribute(f2f_bwd_gfilter_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
-        PB_LAUNCH("f2f_bwd_gfilter_tc", f2f_bwd_gfilter_tc_kernel<1>, grid, NTHREADS, pl.smem, stream, p);
-    }
+#define PB_GF_LAUNCH(NS, BFV)                                                                                       \
+    do {                                                                                                              \
+        PB_CUDA(cudaFuncSetAttribute(f2f_bwd_gfilter_tc_kernel<NS, BFV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                     (int)pl.smem));                                                                  \
+        PB_LAUNCH("f2f_bwd_gfilter_tc", (f2f_bwd_gfilter_tc_kernel<NS, BFV>), grid, NTHREADS, pl.smem, stream, p);    \
+    } while (0)
+    if (pl.nsplit == 2 && pl.bf) PB_GF_LAUNCH(2, true);
+    else if (pl.nsplit == 2) PB_GF_LAUNCH(2, false);
+    else if (pl.bf) PB_GF_LAUNCH(1, true);
+    else PB_GF_LAUNCH(1, false);
+#undef PB_GF_LAUNCH
     return reduce_partials((const float*)ws, pl.nchunks, (int64_t)Cout * Cin * F, gfilter, stream);
 }
 

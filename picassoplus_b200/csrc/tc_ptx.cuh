@@ -207,5 +207,32 @@ __device__ __forceinline__ float to_tf32_rna(float x) {
 }
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
+// two floats -> packed bf16x2 (round to nearest even), first value in the low half
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// hi = bf16(v), lo = bf16(v - hi) for two values at once
+__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
+    hi = pack_bf16x2(a, b);
+    const float ah = __uint_as_float(hi << 16), bh = __uint_as_float(hi & 0xFFFF0000u);
+    lo = pack_bf16x2(a - ah, b - bh);
+}
+
+// Shared-memory matrix descriptor of an MN-major operand tile of 16-bit elements with the
+// 128-byte swizzle: a 1 KB atom holds 8 K-rows of 128 bytes (64 consecutive M/N elements);
+// `lbo_bytes` steps to the next 64 M/N elements, `sbo_bytes` to the next 8 K-rows.  16-byte
+// chunk c of K-row k sits at chunk c ^ (k & 7) of the row; atoms are 1 KB aligned.
+__device__ __forceinline__ uint64_t smem_desc_mnmajor_b16(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(lbo_bytes >> 4) << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= SWZ_128B << 61;
+    return d;
+}
+
 }  // namespace ptx
 }  // namespace pb
