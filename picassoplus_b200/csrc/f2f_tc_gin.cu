@@ -117,6 +117,39 @@ __global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int Cout, int nq, 
     }
 }
 
+// ---- bf16 filter image: Wimg[slice][kst][split][row 0..255][32 bf16, 64B-swizzled];
+//      row = cil*F + d, element (row, kk) = filter[co = kst*32 + kk][ci = slice*NQ + cil][d]
+__global__ void f2f_tc_gin_prep_filter_bf16_kernel(int F, int Cin, int Cout, int nq, int nslices, int kst, int nsplit,
+                                                   const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
+    int64_t total = (int64_t)nslices * kst * NCOLS * 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int c = (int)(i & 3);
+        int row = (int)((i >> 2) % NCOLS);
+        int64_t blk = i / (4 * NCOLS);
+        int ks = (int)(blk % kst);
+        int slice = (int)(blk / kst);
+        int cil = row / F, d = row - cil * F;
+        int ci = slice * nq + cil;
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                int co = ks * 32 + c * 8 + 2 * j + e;
+                v[e] = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)co * Cin + ci) * F + d) : 0.f;
+            }
+            if (nsplit == 1) { hi[j] = pack_bf16x2(v[0], v[1]); lo[j] = 0u; }
+            else split_bf16x2(v[0], v[1], hi[j], lo[j]);
+        }
+        uint8_t* base = wimg + blk * (int64_t)nsplit * W_STAGE_BYTES;
+        uint32_t off = swz64_offset((uint32_t)row, (uint32_t)c);
+        *reinterpret_cast<uint4*>(base + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        if (nsplit == 2) *reinterpret_cast<uint4*>(base + W_STAGE_BYTES + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+}
+
 struct Params {
     int64_t Nf;
     int Cin, Cout;
@@ -133,7 +166,9 @@ struct Params {
     int* async_err;
 };
 
-template <int NSPLIT, int F>
+// BF: operands as bf16 (a 64-byte operand row holds 32 output channels, MMAs of kind::f16 at
+// twice the tf32 rate) instead of tf32 (16 output channels per row)
+template <int NSPLIT, int F, bool BF>
 __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -203,6 +238,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                 const int rr = tid & 127, cg = tid >> 7;         // 256 threads: row, chunk parity
                 const int64_t fr = f0 + rr;
                 const float4* src = reinterpret_cast<const float4*>(p.gout + fr * Cout);
+                if (BF) {
+                    for (int c = cg; c < KST * 4; c += 2) {      // 16-byte chunk = 8 output channels
+                        float4 u = zero4(), w = zero4();
+                        if (fr < p.Nf && c * 8 < Cout) u = ldg4(src + 2 * c);
+                        if (fr < p.Nf && c * 8 + 4 < Cout) w = ldg4(src + 2 * c + 1);
+                        uint8_t* dst = gtile + (size_t)(c >> 2) * G_KTILE_BYTES + swz64_offset((uint32_t)rr, (uint32_t)(c & 3));
+                        uint32_t hi[4], lo[4];
+                        if (NSPLIT == 1) {
+                            hi[0] = pack_bf16x2(u.x, u.y); hi[1] = pack_bf16x2(u.z, u.w);
+                            hi[2] = pack_bf16x2(w.x, w.y); hi[3] = pack_bf16x2(w.z, w.w);
+                        } else {
+                            split_bf16x2(u.x, u.y, hi[0], lo[0]); split_bf16x2(u.z, u.w, hi[1], lo[1]);
+                            split_bf16x2(w.x, w.y, hi[2], lo[2]); split_bf16x2(w.z, w.w, hi[3], lo[3]);
+                            *reinterpret_cast<uint4*>(dst + (size_t)KST * G_KTILE_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        }
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    }
+                } else
                 for (int c = cg; c < KST * 4; c += 2) {
                     float4 v = zero4();
                     if (fr < p.Nf && c * 4 < Cout) v = ldg4(src + c);
@@ -385,7 +438,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
     } else {
         // ===================== MMA issuer =====================
         if (lane == 0) {
-            const uint32_t idesc = instr_desc(FMT_TF32, TILE_M, (uint32_t)p.nmma);
+            const uint32_t idesc = instr_desc(BF ? FMT_BF16 : FMT_TF32, TILE_M, (uint32_t)p.nmma);
             const uint64_t dg_base = smem_desc_kmajor(smem_u32(gtile), 64, SWZ_64B);
             const uint64_t dw_base = smem_desc_kmajor(smem_u32(wst), 64, SWZ_64B);
             int s = 0;
@@ -408,14 +461,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                         for (int k2 = 0; k2 < 2; ++k2) {
                             const uint64_t adv = (uint64_t)(k2 * 2);
                             const uint32_t first = (ks | k2) != 0;
+                            auto mma = [&](uint64_t a_, uint64_t b_, uint32_t acc) {
+                                if (BF) mma_f16(d_tmem, a_, b_, idesc, acc); else mma_tf32(d_tmem, a_, b_, idesc, acc);
+                            };
                             if (NSPLIT == 1) {
-                                mma_tf32(d_tmem, dg_hi + adv, dw_hi + adv, idesc, first);
+                                mma(dg_hi + adv, dw_hi + adv, first);
                             } else {
                                 const uint64_t dg_lo = dg_hi + (uint64_t)(((uint32_t)KST * G_KTILE_BYTES) >> 4);
                                 const uint64_t dw_lo = dw_hi + (uint64_t)(W_STAGE_BYTES >> 4);
-                                mma_tf32(d_tmem, dg_lo + adv, dw_hi + adv, idesc, first);
-                                mma_tf32(d_tmem, dg_hi + adv, dw_lo + adv, idesc, 1u);
-                                mma_tf32(d_tmem, dg_hi + adv, dw_hi + adv, idesc, 1u);
+                                mma(dg_lo + adv, dw_hi + adv, first);
+                                mma(dg_hi + adv, dw_lo + adv, 1u);
+                                mma(dg_hi + adv, dw_hi + adv, 1u);
                             }
                         }
                         tc_commit(&w_empty[s]);
@@ -439,7 +495,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
 }
 
 // ---------------------------------------------------------------------------- host side
-struct Plan { int nsplit, nq, nslices, kst, nmma, nstages, bary_rows, bpitch; size_t smem, wimg_bytes; };
+struct Plan { int nsplit, bf, nq, nslices, kst, nmma, nstages, bary_rows, bpitch; size_t smem, wimg_bytes; };
 
 static bool f_templated(int F) { return F == 4 || F == 9 || F == 16 || F == 25 || F == 36; }
 
@@ -449,11 +505,14 @@ bool supported(int Cin, int Cout, int F) {
 
 Plan plan(int Cin, int Cout, int F, int precision) {
     Plan pl;
+    // fp32: bf16 hi+lo operands (three MMAs); tf32: tf32 operands; bf16: bf16 operands
+    static const bool fp32_as_tf32 = getenv("PB200_FP32_TF32_SPLIT") != nullptr;   // the tf32 hi+lo variant of fp32
     pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
+    pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
     pl.nq = NCOLS / F;
     if (pl.nq > Cin) pl.nq = Cin;
     pl.nslices = (Cin + pl.nq - 1) / pl.nq;
-    pl.kst = (Cout + KS - 1) / KS;
+    pl.kst = pl.bf ? (Cout + 31) / 32 : (Cout + KS - 1) / KS;    // K blocks of one 64-byte operand row
     pl.nmma = (pl.nq * F + 15) / 16 * 16;
     pl.bpitch = ((F + 3) / 4 * 4) | 4;
     const size_t budget = 226 * 1024;
@@ -481,22 +540,22 @@ size_t workspace_bytes(int Cin, int Cout, int F, int precision) {
     return align_up(plan(Cin, Cout, F, precision).wimg_bytes, 256);
 }
 
-template <int NSPLIT, int F>
+template <int NSPLIT, int F, bool BF>
 static int launch(const Params& p, int grid, size_t smem, cudaStream_t stream) {
-    PB_CUDA(cudaFuncSetAttribute(f2f_bwd_gin_tc_kernel<NSPLIT, F>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    PB_CUDA(cudaFuncSetAttribute(f2f_bwd_gin_tc_kernel<NSPLIT, F, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
-    PB_LAUNCH("f2f_bwd_gin_tc", (f2f_bwd_gin_tc_kernel<NSPLIT, F>), grid, NTHREADS, smem, stream, p);
+    PB_LAUNCH("f2f_bwd_gin_tc", (f2f_bwd_gin_tc_kernel<NSPLIT, F, BF>), grid, NTHREADS, smem, stream, p);
     return PB200_OK;
 }
 
-template <int NSPLIT>
+template <int NSPLIT, bool BF>
 static int launch_f(int F, const Params& p, int grid, size_t smem, cudaStream_t stream) {
     switch (F) {
-        case 4: return launch<NSPLIT, 4>(p, grid, smem, stream);
-        case 9: return launch<NSPLIT, 9>(p, grid, smem, stream);
-        case 16: return launch<NSPLIT, 16>(p, grid, smem, stream);
-        case 25: return launch<NSPLIT, 25>(p, grid, smem, stream);
-        default: return launch<NSPLIT, 36>(p, grid, smem, stream);
+        case 4: return launch<NSPLIT, 4, BF>(p, grid, smem, stream);
+        case 9: return launch<NSPLIT, 9, BF>(p, grid, smem, stream);
+        case 16: return launch<NSPLIT, 16, BF>(p, grid, smem, stream);
+        case 25: return launch<NSPLIT, 25, BF>(p, grid, smem, stream);
+        default: return launch<NSPLIT, 36, BF>(p, grid, smem, stream);
     }
 }
 
@@ -508,8 +567,13 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
     Plan pl = plan(Cin, Cout, F, precision);
     uint8_t* wimg = (uint8_t*)ws;
     int64_t items = (int64_t)pl.nslices * pl.kst * NCOLS * 4;
-    PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_kernel, persistent_blocks(items, 256, 8), 256, 0,
-              stream, F, Cin, Cout, pl.nq, pl.nslices, pl.kst, pl.nsplit, filter, wimg);
+    if (pl.bf) {
+        PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_bf16_kernel, persistent_blocks(items, 256, 8), 256, 0,
+                  stream, F, Cin, Cout, pl.nq, pl.nslices, pl.kst, pl.nsplit, filter, wimg);
+    } else {
+        PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_kernel, persistent_blocks(items, 256, 8), 256, 0,
+                  stream, F, Cin, Cout, pl.nq, pl.nslices, pl.kst, pl.nsplit, filter, wimg);
+    }
     Params p;
     p.Nf = Nf; p.Cin = Cin; p.Cout = Cout;
     p.nq = pl.nq; p.nslices = pl.nslices; p.kst = pl.kst; p.nmma = pl.nmma;
@@ -518,7 +582,8 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
     p.async_err = async_error_word();
     int64_t ntiles = ceil_div(Nf, TILE_M);
     int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
-    return pl.nsplit == 2 ? launch_f<2>(F, p, grid, pl.smem, stream) : launch_f<1>(F, p, grid, pl.smem, stream);
+    if (pl.bf) return pl.nsplit == 2 ? launch_f<2, true>(F, p, grid, pl.smem, stream) : launch_f<1, true>(F, p, grid, pl.smem, stream);
+    return pl.nsplit == 2 ? launch_f<2, false>(F, p, grid, pl.smem, stream) : launch_f<1, false>(F, p, grid, pl.smem, stream);
 }
 
 }  // namespace gin
