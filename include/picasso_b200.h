@@ -35,8 +35,11 @@ extern "C" {
 #define PB200_EINDEX       -4   /* an index array holds an out-of-range value              */
 
 /* contraction precision for facet2facet (fp32 accumulation in every mode) */
-#define PB200_PREC_FP32     0   /* fp32-faithful (tf32 hi+lo split on the tensor cores where the
-                                   shape allows, FFMA otherwise): meets the 1e-4 relative gate */
+#define PB200_PREC_FP32     0   /* every operand as bf16 hi + bf16 lo, three tensor-core products
+                                   per term (FFMA where the shape has no tensor-core kernel):
+                                   about 1e-5 relative error, meets the 1e-4 gate.  With the
+                                   environment variable PB200_FP32_TF32_SPLIT set the split is
+                                   tf32 hi + lo instead (about 2e-6, a quarter slower).        */
 #define PB200_PREC_TF32     1   /* tf32 operands on the tensor cores                       */
 #define PB200_PREC_BF16     2   /* bf16 operands on the tensor cores (2e-2 relative gate)  */
 #define PB200_PREC_FP32_FFMA 3  /* fp32 FFMA path (no tensor cores), every shape            */
