@@ -60,7 +60,16 @@ f2v_fwd_face_kernel(int64_t Nf, int CV, int K, const float* __restrict__ coeff, 
 // The same for whole 128-channel chunks (lane = float4 channel group) and K <= 32, register-
 // blocked so that the shared-memory pipe is not the limit: warp w owns faces w, w+8, ..., w+56
 // of the tile, and a filter row read from shared memory (512 distinct bytes per warp) is used
-// for all eight; the coefficient loads are one broadcast address per warp.
+// for all eight; the coefficient loads are one broadcast address per warp.  The coefficient
+// rows of the next tile arrive by 4-byte asynchronous copies while this tile is computed.
+__device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __global__ void __launch_bounds__(256)
 f2v_fwd_face_blocked_kernel(int64_t Nf, int CV, int K, const float* __restrict__ coeff, const float4* __restrict__ in,
                             const float4* __restrict__ filt, float4* __restrict__ wx) {
@@ -68,27 +77,37 @@ f2v_fwd_face_blocked_kernel(int64_t Nf, int CV, int K, const float* __restrict__
     constexpr int FB = F2VF_TF / 8;                            // faces per warp
     const int KP = (K + 3) / 4 * 4, KG = KP / 4;               // coeff row pitch, pad columns zero
     float4* sfilt = smem;                                      // [KP][32], rows K..KP-1 zero
-    float4* scoef = smem + KP * 32;                            // [TF][KG]
+    float4* scoef0 = smem + KP * 32;                           // [2][TF][KG], double-buffered
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cg = blockIdx.y * 32 + lane;
     for (int i = threadIdx.x; i < KP * 32; i += blockDim.x) {
         const int k = i >> 5;
         sfilt[i] = k < K ? filt[k * CV + blockIdx.y * 32 + (i & 31)] : zero4();
     }
-    for (int i = threadIdx.x; i < F2VF_TF * KG; i += blockDim.x) scoef[i] = zero4();
+    for (int i = threadIdx.x; i < 2 * F2VF_TF * KG; i += blockDim.x) scoef0[i] = zero4();
+    __syncthreads();
     const int64_t ntiles = (Nf + F2VF_TF - 1) / F2VF_TF;
-    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int64_t f0 = tile * F2VF_TF;
-        const int nf_tile = Nf - f0 < F2VF_TF ? (int)(Nf - f0) : F2VF_TF;
-        __syncthreads();
-        {
-            float* sc = reinterpret_cast<float*>(scoef);
+    auto fetch_coef = [&](int64_t tile, int buf) {             // the pad columns stay zero
+        if (tile < ntiles) {
+            const int64_t f0 = tile * F2VF_TF;
+            const int nf_tile = Nf - f0 < F2VF_TF ? (int)(Nf - f0) : F2VF_TF;
+            float* sc = reinterpret_cast<float*>(scoef0 + buf * F2VF_TF * KG);
             for (int i = threadIdx.x; i < nf_tile * K; i += blockDim.x) {
                 const int fl = i / K;
-                sc[fl * KP + (i - fl * K)] = __ldg(coeff + f0 * K + i);
+                cp_async4(sc + fl * KP + (i - fl * K), coeff + f0 * K + i);
             }
         }
-        __syncthreads();
+        cp_async_commit();
+    };
+    fetch_coef(blockIdx.x, 0);
+    int buf = 0;
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, buf ^= 1) {
+        const int64_t f0 = tile * F2VF_TF;
+        const int nf_tile = Nf - f0 < F2VF_TF ? (int)(Nf - f0) : F2VF_TF;
+        fetch_coef(tile + gridDim.x, buf ^ 1);                 // its readers finished behind the barrier below
+        cp_async_wait<1>();                                    // this tile's rows have landed (own copies) ...
+        __syncthreads();                                       // ... and everybody else's
+        const float4* scoef = scoef0 + buf * F2VF_TF * KG;
         float4 x[FB], w[FB];
 #pragma unroll
         for (int i = 0; i < FB; ++i) {
@@ -110,7 +129,9 @@ f2v_fwd_face_blocked_kernel(int64_t Nf, int CV, int K, const float* __restrict__
             const int fl = warp + 8 * i;
             if (fl < nf_tile) wx[(f0 + fl) * CV + cg] = mul4(w[i], x[i]);
         }
+        __syncthreads();                                       // this tile's buffer may be refilled now
     }
+    cp_async_wait<0>();
 }
 
 template <int TL>
@@ -283,8 +304,8 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
     const int KG = KP / 4;                                     // groups of 4 coefficients (<= 8)
     float4* sfilt = smem;                                      // [KP][32], rows K..KP-1 zero
     float4* st = smem + KP * 32;                               // [TF][32]   t = input * gt
-    float4* scoef = st + F2VB_TF * 32;                         // [TF][KG]
-    int* svo = reinterpret_cast<int*>(scoef + F2VB_TF * KG);   // [2][96] output vertex of (face, corner), -1 = none
+    float4* scoef0 = st + F2VB_TF * 32;                        // [2][TF][KG], double-buffered (asynchronous copies)
+    int* svo = reinterpret_cast<int*>(scoef0 + 2 * F2VB_TF * KG);   // [2][96] output vertex of (face, corner), -1 = none
     float* srn = reinterpret_cast<float*>(svo + 2 * 96);       // [2][96] 1 / nfCount of that vertex
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int cg = blockIdx.y * 32 + lane;                     // this lane's channel group
@@ -292,7 +313,7 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
         const int k = i >> 5;
         sfilt[i] = k < K ? filt[k * CV + blockIdx.y * 32 + (i & 31)] : zero4();
     }
-    for (int i = threadIdx.x; i < F2VB_TF * KG; i += blockDim.x) scoef[i] = zero4();
+    for (int i = threadIdx.x; i < 2 * F2VB_TF * KG; i += blockDim.x) scoef0[i] = zero4();
     float4 acc[4] = {zero4(), zero4(), zero4(), zero4()};     // coefficients 4*warp .. 4*warp+3
     const int64_t ntiles = (Nf + F2VB_TF - 1) / F2VB_TF;
     // index pipeline of thread e < 96 (entry e = 3*face + corner of a tile): vertex id of the
@@ -310,6 +331,20 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
     if (ix) { svo[threadIdx.x] = vo1; srn[threadIdx.x] = rn1; }
     vo1 = hop_vo(hop_face(blockIdx.x + tstep));                               // second tile
     int vi2 = hop_face(blockIdx.x + 2 * tstep);                               // third tile
+    auto fetch_coef = [&](int64_t tile, int b) {               // the pad columns stay zero
+        if (tile < ntiles) {
+            const int64_t f0 = tile * F2VB_TF;
+            const int nf_tile = Nf - f0 < F2VB_TF ? (int)(Nf - f0) : F2VB_TF;
+            float* sc = reinterpret_cast<float*>(scoef0 + b * F2VB_TF * KG);
+            for (int i = threadIdx.x; i < nf_tile * K; i += blockDim.x) {
+                const int fl = i / K;
+                cp_async4(sc + fl * KP + (i - fl * K), coeff + f0 * K + i);
+            }
+        }
+        cp_async_commit();
+    };
+    __syncthreads();                                           // the zero fill above is complete
+    fetch_coef(blockIdx.x, 0);
     int buf = 0;
     for (int64_t tile = blockIdx.x; tile < ntiles; tile += tstep, buf ^= 1) {
         const int64_t f0 = tile * F2VB_TF;
@@ -319,14 +354,10 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
         const int vo_next = hop_vo(vi2);
         const int vi_next = hop_face(tile + 3 * tstep);
         __syncthreads();                                       // previous tile fully consumed
-        {
-            float* sc = reinterpret_cast<float*>(scoef);
-            for (int i = threadIdx.x; i < nf_tile * K; i += blockDim.x) {
-                const int fl = i / K;
-                sc[fl * KP + (i - fl * K)] = __ldg(coeff + f0 * K + i);
-            }
-        }
-        __syncthreads();
+        fetch_coef(tile + tstep, buf ^ 1);                     // the next tile's coefficient rows, asynchronously
+        cp_async_wait<1>();                                    // this tile's rows have landed (own copies) ...
+        __syncthreads();                                       // ... and everybody else's
+        const float4* scoef = scoef0 + buf * F2VB_TF * KG;
         // ---- phase 1: faces warp, warp+8, warp+16, warp+24
         float4 gt[4], x[4], w[4];
 #pragma unroll
@@ -381,6 +412,7 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
             }
         }
     }
+    cp_async_wait<0>();
     if (warp < KG) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -498,7 +530,7 @@ int pb200_facet2vertex_forward(int64_t Nf, int64_t NvOut, int C, int r, int K, c
         float4* wx = (float4*)workspace;
         if (Nf > 0 && CV % 32 == 0 && K <= 32) {
             const int KPb = (K + 3) / 4 * 4;
-            const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + F2VF_TF * (KPb / 4));
+            const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + 2 * F2VF_TF * (KPb / 4));
             dim3 gridf(persistent_blocks(Nf, F2VF_TF, 4), (unsigned)(CV / 32));
             PB_LAUNCH("f2v_fwd_face", f2v_fwd_face_blocked_kernel, gridf, 256, smemb, stream, Nf, CV, K, coeff,
                       (const float4*)input, (const float4*)filter, wx);
@@ -557,7 +589,7 @@ int pb200_facet2vertex_backward(int64_t Nf, int64_t NvIn, int64_t NvOut, int C, 
         size_t smem = sizeof(float4) * (32 * (size_t)K + F2VB_TF * 32) + sizeof(float) * F2VB_TF * KP;
         if (CV % 32 == 0 && K <= 32) {
             const int KPb = (K + 3) / 4 * 4;
-            const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + F2VB_TF * 32 + F2VB_TF * (KPb / 4)) + 2 * 96 * 8;
+            const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + F2VB_TF * 32 + 2 * F2VB_TF * (KPb / 4)) + 2 * 96 * 8;
             PB_LAUNCH("f2v_bwd", f2v_bwd_blocked_kernel, grid, 256, smemb, stream, Nf, CV, K, face, vtMap, nfCount, coeff,
                       (const float4*)input, (const float4*)filter, (const float4*)gradOutput, (float4*)gradInput,
                       (float4*)partial);
