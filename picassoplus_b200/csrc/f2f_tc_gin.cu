@@ -32,7 +32,8 @@ constexpr int TILE_M = 128;
 constexpr int NCOLS = 256;
 constexpr int KS = 16;
 constexpr int EWARPS = 8;
-constexpr int NTHREADS = (EWARPS + 2) * 32;
+constexpr int GWARPS = 2;                        // gradOutput tile loaders
+constexpr int NTHREADS = (EWARPS + 2 + GWARPS) * 32;
 constexpr int G_KTILE_BYTES = TILE_M * 64;      // one 16-channel block of the gradOutput tile
 constexpr int W_STAGE_BYTES = NCOLS * 64;       // one 16-channel block of a filter slice
 
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EWARPS); }
-        mbar_init(g_full, EWARPS);
+        mbar_init(g_full, GWARPS);
         mbar_init(g_empty, 1);
         mbar_init(b_ready, EWARPS);
         mbar_init(b_free, EWARPS);
@@ -224,56 +225,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
             return __shfl_sync(0xffffffffu, ok, 0) != 0;
         };
+        // sample range of the thread's face, fetched one tile ahead
+        int k0n = 0, k1n = 0;
+        {
+            const int64_t f = (int64_t)blockIdx.x * TILE_M + r;
+            if (f < p.Nf) { k0n = f > 0 ? __ldg(p.cum + f - 1) : 0; k1n = __ldg(p.cum + f); }
+        }
         for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t f0 = tile * TILE_M;
             const int64_t f = f0 + r;
             const bool valid = f < p.Nf;
-            int k0 = 0, k1 = 0;
-            if (valid) { k0 = f > 0 ? __ldg(p.cum + f - 1) : 0; k1 = __ldg(p.cum + f); }
+            const int k0 = k0n, k1 = k1n;
+            {
+                const int64_t fn = f + (int64_t)gridDim.x * TILE_M;
+                k0n = 0; k1n = 0;
+                if (fn < p.Nf) { k0n = __ldg(p.cum + fn - 1); k1n = __ldg(p.cum + fn); }
+            }
             const int T = k1 - k0;
             const float invT = T > 0 ? 1.f / (float)T : 0.f;
-            // ---- 1. the tile's gradOutput rows -> K-major swizzled operand blocks
-            if (!warp_wait(g_empty, (tcount & 1u) ^ 1u)) { alive = false; break; }
-            {
-                const int rr = tid & 127, cg = tid >> 7;         // 256 threads: row, chunk parity
-                const int64_t fr = f0 + rr;
-                const float4* src = reinterpret_cast<const float4*>(p.gout + fr * Cout);
-                if (BF) {
-                    for (int c = cg; c < KST * 4; c += 2) {      // 16-byte chunk = 8 output channels
-                        float4 u = zero4(), w = zero4();
-                        if (fr < p.Nf && c * 8 < Cout) u = ldg4(src + 2 * c);
-                        if (fr < p.Nf && c * 8 + 4 < Cout) w = ldg4(src + 2 * c + 1);
-                        uint8_t* dst = gtile + (size_t)(c >> 2) * G_KTILE_BYTES + swz64_offset((uint32_t)rr, (uint32_t)(c & 3));
-                        uint32_t hi[4], lo[4];
-                        if (NSPLIT == 1) {
-                            hi[0] = pack_bf16x2(u.x, u.y); hi[1] = pack_bf16x2(u.z, u.w);
-                            hi[2] = pack_bf16x2(w.x, w.y); hi[3] = pack_bf16x2(w.z, w.w);
-                        } else {
-                            split_bf16x2(u.x, u.y, hi[0], lo[0]); split_bf16x2(u.z, u.w, hi[1], lo[1]);
-                            split_bf16x2(w.x, w.y, hi[2], lo[2]); split_bf16x2(w.z, w.w, hi[3], lo[3]);
-                            *reinterpret_cast<uint4*>(dst + (size_t)KST * G_KTILE_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                        }
-                        *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                    }
-                } else
-                for (int c = cg; c < KST * 4; c += 2) {
-                    float4 v = zero4();
-                    if (fr < p.Nf && c * 4 < Cout) v = ldg4(src + c);
-                    uint8_t* dst = gtile + (size_t)(c >> 2) * G_KTILE_BYTES + swz64_offset((uint32_t)rr, (uint32_t)(c & 3));
-                    if (NSPLIT == 1) {
-                        *reinterpret_cast<float4*>(dst) =
-                            make_float4(to_tf32_rna(v.x), to_tf32_rna(v.y), to_tf32_rna(v.z), to_tf32_rna(v.w));
-                    } else {
-                        float4 hv = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
-                        *reinterpret_cast<float4*>(dst) = hv;
-                        *reinterpret_cast<float4*>(dst + (size_t)KST * G_KTILE_BYTES) =
-                            make_float4(v.x - hv.x, v.y - hv.y, v.z - hv.z, v.w - hv.w);
-                    }
-                }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(g_full);
             // ---- 2. stage the bary rows of the tile's samples (as many as fit)
             int kt0 = 0, kt1 = 0;
             {
@@ -299,65 +268,79 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             // bary rows of the face's first four samples, packed (even d, odd d), zero beyond T / F
             constexpr int FH = (F + 1) / 2;
             const bool lean = !__any_sync(0xffffffffu, valid && T > 4);
-            float2 breg[4][FH];
+            // lean path: the two warps of a TMEM quadrant share the samples of a face: warp `half` takes
+            // samples 2*half and 2*half + 1 for every channel of the slice
+            const int ts = 2 * half;
+            float2 breg[2][FH];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
+            for (int t = 0; t < 2; ++t) {
                 // 16-byte loads from the padded rows (pad columns are zero)
-                const float4* src = reinterpret_cast<const float4*>(p.bary_p + (int64_t)(k0 + (t < T ? t : 0)) * p.Fp);
+                const bool on = lean && ts + t < T;
+                const float4* src = reinterpret_cast<const float4*>(p.bary_p + (int64_t)(k0 + (on ? ts + t : 0)) * p.Fp);
 #pragma unroll
                 for (int q4 = 0; q4 < (F + 3) / 4; ++q4) {
-                    const float4 v = (lean && t < T) ? ldg4(src + q4) : zero4();
+                    const float4 v = on ? ldg4(src + q4) : zero4();
                     breg[t][2 * q4] = make_float2(v.x, v.y);
                     if (2 * q4 + 1 < FH) breg[t][2 * q4 + 1] = make_float2(v.z, v.w);
                 }
             }
+            float* const row0 = p.gin + (int64_t)(k0 + ts) * Cin;     // gradInput rows of the thread's two samples
+            const bool on0 = ts < T, on1 = ts + 1 < T;
             // ---- 3. per slice: drain the accumulator, contract with bary, store gradInput
             for (int slice = 0; slice < p.nslices && alive; ++slice, ++sc) {
                 const uint32_t a = sc & 1u;
                 if (!warp_wait(&acc_full[a], (sc >> 1) & 1u)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + a * NCOLS;
-                // lean path: every face of the warp has at most 4 samples; their bary rows were loaded
-                // into registers once per tile (packed as (even d, odd d) pairs).  The sum over the F
-                // bases runs with fma.f32x2 on those pairs, four samples and two channels at a time:
-                // 8 independent chains per thread, no shared-memory traffic at all.
+                // The bary rows of the thread's two samples were loaded into registers once per tile
+                // (packed as (even d, odd d) pairs).  The sum over the F bases runs with fma.f32x2 on
+                // those pairs, two samples and two channels at a time, no shared-memory traffic at all.
                 if (lean) {
-                    for (int pr = pair_lo; pr < pair_hi; ++pr) {
-                        const int cil = 2 * pr;
-                        const int ci = slice * p.nq + cil;
+                    const int ci0 = slice * p.nq;
+                    const bool vec = ((ci0 | Cin) & 1) == 0;           // float2 stores stay 8-byte aligned
+                    // accumulator columns of the first channel pair; later pairs are requested as soon as
+                    // the registers of the previous one are free, so the loads overlap the sums and stores
+                    float2 va[FH], vb[FH];
+#pragma unroll
+                    for (int d = 0; d < FH; ++d) { va[d] = make_float2(0.f, 0.f); vb[d] = make_float2(0.f, 0.f); }
+                    tmem_ld_row<F>(tbase, reinterpret_cast<float*>(va));
+                    if (1 < p.nq) tmem_ld_row<F>(tbase + (uint32_t)F, reinterpret_cast<float*>(vb));
+                    for (int cil = 0; cil < p.nq; cil += 2) {
+                        const int ci = ci0 + cil;
                         const bool has_b = (cil + 1 < p.nq) && (ci + 1 < Cin);
-                        float2 va[FH], vb[FH];
-                        va[FH - 1] = make_float2(0.f, 0.f);
-                        vb[FH - 1] = make_float2(0.f, 0.f);
-                        tmem_ld_row<F>(tbase + (uint32_t)(cil * F), reinterpret_cast<float*>(va));
-                        if (cil + 1 < p.nq) tmem_ld_row<F>(tbase + (uint32_t)((cil + 1) * F), reinterpret_cast<float*>(vb));
+                        const int nx = cil + 2;
+                        tmem_ld_wait();
+                        if (F & 1) { va[FH - 1].y = 0.f; vb[FH - 1].y = 0.f; }
+                        float2 sa[2], sb[2];
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) { sa[t] = make_float2(0.f, 0.f); sb[t] = make_float2(0.f, 0.f); }
+#pragma unroll
+                        for (int d = 0; d < FH; ++d) {
+#pragma unroll
+                            for (int t = 0; t < 2; ++t) sa[t] = __ffma2_rn(breg[t][d], va[d], sa[t]);
+                        }
+                        if (nx < p.nq) tmem_ld_row<F>(tbase + (uint32_t)(nx * F), reinterpret_cast<float*>(va));
+#pragma unroll
+                        for (int d = 0; d < FH; ++d) {
+#pragma unroll
+                            for (int t = 0; t < 2; ++t) sb[t] = __ffma2_rn(breg[t][d], vb[d], sb[t]);
+                        }
+                        if (nx + 1 < p.nq) tmem_ld_row<F>(tbase + (uint32_t)((nx + 1) * F), reinterpret_cast<float*>(vb));
                         else {
 #pragma unroll
                             for (int d = 0; d < FH; ++d) vb[d] = make_float2(0.f, 0.f);
                         }
-                        tmem_ld_wait();
-                        if (F & 1) { va[FH - 1].y = 0.f; vb[FH - 1].y = 0.f; }
-                        float2 sa[4], sb[4];
-#pragma unroll
-                        for (int t = 0; t < 4; ++t) { sa[t] = make_float2(0.f, 0.f); sb[t] = make_float2(0.f, 0.f); }
-#pragma unroll
-                        for (int d = 0; d < FH; ++d) {
-#pragma unroll
-                            for (int t = 0; t < 4; ++t) {
-                                sa[t] = __ffma2_rn(breg[t][d], va[d], sa[t]);
-                                sb[t] = __ffma2_rn(breg[t][d], vb[d], sb[t]);
-                            }
-                        }
                         if (ci < Cin) {
-#pragma unroll
-                            for (int t = 0; t < 4; ++t) {
-                                if (t < T) {
-                                    const float ga = (sa[t].x + sa[t].y) * invT, gb = (sb[t].x + sb[t].y) * invT;
-                                    const int64_t idx = (int64_t)(k0 + t) * Cin + ci;
-                                    float* dst = p.gin + idx;
-                                    if (has_b && ((idx & 1) == 0)) *reinterpret_cast<float2*>(dst) = make_float2(ga, gb);
-                                    else { dst[0] = ga; if (has_b) dst[1] = gb; }
-                                }
+                            const float2 g0 = make_float2((sa[0].x + sa[0].y) * invT, (sb[0].x + sb[0].y) * invT);
+                            const float2 g1 = make_float2((sa[1].x + sa[1].y) * invT, (sb[1].x + sb[1].y) * invT);
+                            float* d0 = row0 + ci;
+                            float* d1 = d0 + Cin;
+                            if (vec && has_b) {
+                                if (on0) *reinterpret_cast<float2*>(d0) = g0;
+                                if (on1) *reinterpret_cast<float2*>(d1) = g1;
+                            } else {
+                                if (on0) { d0[0] = g0.x; if (has_b) d0[1] = g0.y; }
+                                if (on1) { d1[0] = g1.x; if (has_b) d1[1] = g1.y; }
                             }
                         }
                     }
@@ -414,6 +397,74 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             }
             if (!alive) break;
             if (p.bary_rows > 0) { __syncwarp(); if (lane == 0) mbar_arrive(b_free); }
+        }
+    } else if (warp >= EWARPS + 2) {
+        // ===================== gradOutput tile loaders =====================
+        // The tile's rows become the K-major M-side operand (64-byte swizzled rows).  A task is one
+        // 16-byte operand chunk of one row (8 channels as bf16, 4 as tf32); consecutive lanes take
+        // consecutive chunks of a row, so a warp reads whole rows.  The copy of tile t+1 starts as
+        // soon as the last MMAs of tile t have read the operand, while the epilogue warps still
+        // drain the last accumulators of tile t.
+        const int gt = tid - (EWARPS + 2) * 32;                 // 0 .. GWARPS*32-1
+        const int cpr = KST * 4;                                // chunks per row
+        const int ntasks = TILE_M * cpr;
+        constexpr int U = BF ? 6 : 12;                          // tasks in flight per thread
+        uint32_t tcount = 0;
+        bool alive = true;
+        for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
+            const int64_t f0 = tile * TILE_M;
+            {
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(g_empty, (tcount & 1u) ^ 1u, abort_flag) ? 1 : 0;
+                if (!__shfl_sync(0xffffffffu, ok, 0)) { alive = false; break; }
+            }
+            for (int base = 0; base < ntasks; base += U * GWARPS * 32) {
+                float4 u[U], w[U];
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const int idx = base + j * GWARPS * 32 + gt;
+                    const int rr = idx / cpr, c = idx - rr * cpr;
+                    const int64_t fr = f0 + rr;
+                    const float4* src = reinterpret_cast<const float4*>(p.gout + fr * Cout);
+                    u[j] = zero4(); w[j] = zero4();
+                    if (BF) {
+                        if (idx < ntasks && fr < p.Nf && c * 8 < Cout) u[j] = ldg4(src + 2 * c);
+                        if (idx < ntasks && fr < p.Nf && c * 8 + 4 < Cout) w[j] = ldg4(src + 2 * c + 1);
+                    } else {
+                        if (idx < ntasks && fr < p.Nf && c * 4 < Cout) u[j] = ldg4(src + c);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const int idx = base + j * GWARPS * 32 + gt;
+                    if (idx >= ntasks) continue;
+                    const int rr = idx / cpr, c = idx - rr * cpr;
+                    uint8_t* dst = gtile + (size_t)(c >> 2) * G_KTILE_BYTES + swz64_offset((uint32_t)rr, (uint32_t)(c & 3));
+                    if (BF) {
+                        uint32_t hi[4], lo[4];
+                        if (NSPLIT == 1) {
+                            hi[0] = pack_bf16x2(u[j].x, u[j].y); hi[1] = pack_bf16x2(u[j].z, u[j].w);
+                            hi[2] = pack_bf16x2(w[j].x, w[j].y); hi[3] = pack_bf16x2(w[j].z, w[j].w);
+                        } else {
+                            split_bf16x2(u[j].x, u[j].y, hi[0], lo[0]); split_bf16x2(u[j].z, u[j].w, hi[1], lo[1]);
+                            split_bf16x2(w[j].x, w[j].y, hi[2], lo[2]); split_bf16x2(w[j].z, w[j].w, hi[3], lo[3]);
+                            *reinterpret_cast<uint4*>(dst + (size_t)KST * G_KTILE_BYTES) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        }
+                        *reinterpret_cast<uint4*>(dst) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    } else if (NSPLIT == 1) {
+                        *reinterpret_cast<float4*>(dst) =
+                            make_float4(to_tf32_rna(u[j].x), to_tf32_rna(u[j].y), to_tf32_rna(u[j].z), to_tf32_rna(u[j].w));
+                    } else {
+                        const float4 hv = make_float4(tf32_hi(u[j].x), tf32_hi(u[j].y), tf32_hi(u[j].z), tf32_hi(u[j].w));
+                        *reinterpret_cast<float4*>(dst) = hv;
+                        *reinterpret_cast<float4*>(dst + (size_t)KST * G_KTILE_BYTES) =
+                            make_float4(u[j].x - hv.x, u[j].y - hv.y, u[j].z - hv.z, u[j].w - hv.w);
+                    }
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(g_full);
         }
     } else if (warp == EWARPS) {
         // ===================== filter loader (TMA engine) =====================
@@ -511,6 +562,7 @@ Plan plan(int Cin, int Cout, int F, int precision) {
     pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
     pl.nq = NCOLS / F;
     if (pl.nq > Cin) pl.nq = Cin;
+    if (const char* e = getenv("PB200_GIN_NQ")) pl.nq = atoi(e);
     pl.nslices = (Cin + pl.nq - 1) / pl.nq;
     pl.kst = pl.bf ? (Cout + 31) / 32 : (Cout + KS - 1) / KS;    // K blocks of one 64-byte operand row
     pl.nmma = (pl.nq * F + 15) / 16 * 16;
