@@ -156,6 +156,7 @@ struct Params {
     int Cin, Cout;
     int nq, nslices, kst, nmma;      // channels per slice, slices, 16-channel K blocks, UMMA N
     int nstages;                     // filter ring depth
+    int gbufs;                       // gradOutput tile buffers (2 = the copy runs a tile ahead)
     int bary_rows, bpitch;           // staged bary rows per tile (0 = read from global), row pitch in floats
     const float* gout;
     const float* bary;
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
     const size_t gtile_bytes = (size_t)NSPLIT * KST * G_KTILE_BYTES;       // [split][kst][8 KB]
     const size_t wstage_bytes = (size_t)NSPLIT * W_STAGE_BYTES;           // [split][16 KB]
     uint8_t* gtile = smem;
-    uint8_t* wst = smem + gtile_bytes;
+    uint8_t* wst = smem + (size_t)p.gbufs * gtile_bytes;        // one or two gradOutput tile buffers
     float* bary_s = reinterpret_cast<float*>(wst + (size_t)S * wstage_bytes);
     uint8_t* tail = reinterpret_cast<uint8_t*>(bary_s + (size_t)p.bary_rows * p.bpitch);
     uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(tail) + 15) & ~(uintptr_t)15);
@@ -187,18 +188,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
     uint64_t* w_empty = bars + S;             // [S]
     uint64_t* acc_full = bars + 2 * S;        // [2]
     uint64_t* acc_empty = bars + 2 * S + 2;   // [2]
-    uint64_t* g_full = bars + 2 * S + 4;      // gradOutput tile written
-    uint64_t* g_empty = bars + 2 * S + 5;     // all MMAs of the tile done reading it
-    uint64_t* b_ready = bars + 2 * S + 6;     // bary rows of the tile staged
-    uint64_t* b_free = bars + 2 * S + 7;      // all warps done with the staged rows
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 8);
+    uint64_t* g_full = bars + 2 * S + 4;      // [2] gradOutput tile buffer written
+    uint64_t* g_empty = bars + 2 * S + 6;     // [2] all MMAs of the tile done reading the buffer
+    uint64_t* b_ready = bars + 2 * S + 8;     // bary rows of the tile staged
+    uint64_t* b_free = bars + 2 * S + 9;      // all warps done with the staged rows
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 10);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(&w_full[s], 1); mbar_init(&w_empty[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EWARPS); }
-        mbar_init(g_full, GWARPS);
-        mbar_init(g_empty, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&g_full[b], GWARPS); mbar_init(&g_empty[b], 1); }
         mbar_init(b_ready, EWARPS);
         mbar_init(b_free, EWARPS);
         *abort_flag = 0;
@@ -413,9 +413,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
         bool alive = true;
         for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t f0 = tile * TILE_M;
+            // with two buffers the copy runs a whole tile ahead of the MMAs
+            const uint32_t gb = p.gbufs == 2 ? (tcount & 1u) : 0u;
+            const uint32_t gph = p.gbufs == 2 ? ((tcount >> 1) & 1u) : (tcount & 1u);
+            uint8_t* const gdst = gtile + (size_t)gb * gtile_bytes;
             {
                 int ok = 1;
-                if (lane == 0) ok = mbar_wait(g_empty, (tcount & 1u) ^ 1u, abort_flag) ? 1 : 0;
+                if (lane == 0) ok = mbar_wait(&g_empty[gb], gph ^ 1u, abort_flag) ? 1 : 0;
                 if (!__shfl_sync(0xffffffffu, ok, 0)) { alive = false; break; }
             }
             for (int base = 0; base < ntasks; base += U * GWARPS * 32) {
@@ -439,7 +443,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                     const int idx = base + j * GWARPS * 32 + gt;
                     if (idx >= ntasks) continue;
                     const int rr = idx / cpr, c = idx - rr * cpr;
-                    uint8_t* dst = gtile + (size_t)(c >> 2) * G_KTILE_BYTES + swz64_offset((uint32_t)rr, (uint32_t)(c & 3));
+                    uint8_t* dst = gdst + (size_t)(c >> 2) * G_KTILE_BYTES + swz64_offset((uint32_t)rr, (uint32_t)(c & 3));
                     if (BF) {
                         uint32_t hi[4], lo[4];
                         if (NSPLIT == 1) {
@@ -464,7 +468,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(g_full);
+            if (lane == 0) mbar_arrive(&g_full[gb]);
         }
     } else if (warp == EWARPS) {
         // ===================== filter loader (TMA engine) =====================
@@ -496,7 +500,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             uint32_t ph = 0, tcount = 0, sc = 0;
             bool alive = true;
             for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
-                if (!mbar_wait(g_full, tcount & 1u, abort_flag)) { alive = false; break; }
+                const uint32_t gb = p.gbufs == 2 ? (tcount & 1u) : 0u;
+                const uint32_t gph = p.gbufs == 2 ? ((tcount >> 1) & 1u) : (tcount & 1u);
+                const uint64_t dg_tile = dg_base + (uint64_t)((gb * (uint32_t)gtile_bytes) >> 4);
+                if (!mbar_wait(&g_full[gb], gph, abort_flag)) { alive = false; break; }
                 for (int slice = 0; slice < p.nslices && alive; ++slice, ++sc) {
                     const uint32_t a = sc & 1u;
                     if (!mbar_wait(&acc_empty[a], ((sc >> 1) & 1u) ^ 1u, abort_flag)) { alive = false; break; }
@@ -506,7 +513,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                         if (!mbar_wait(&w_full[s], ph, abort_flag)) { alive = false; break; }
                         tc_fence_after();
                         // descriptors differ only in the 16-byte-unit start address: add offsets to a base
-                        const uint64_t dg_hi = dg_base + (uint64_t)(((uint32_t)ks * G_KTILE_BYTES) >> 4);
+                        const uint64_t dg_hi = dg_tile + (uint64_t)(((uint32_t)ks * G_KTILE_BYTES) >> 4);
                         const uint64_t dw_hi = dw_base + (uint64_t)(((uint32_t)s * (uint32_t)wstage_bytes) >> 4);
 #pragma unroll
                         for (int k2 = 0; k2 < 2; ++k2) {
@@ -530,7 +537,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                     }
                     if (alive) tc_commit(&acc_full[a]);
                 }
-                if (alive) tc_commit(g_empty);
+                if (alive) tc_commit(&g_empty[gb]);
             }
         }
     }
@@ -546,7 +553,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
 }
 
 // ---------------------------------------------------------------------------- host side
-struct Plan { int nsplit, bf, nq, nslices, kst, nmma, nstages, bary_rows, bpitch; size_t smem, wimg_bytes; };
+struct Plan { int nsplit, bf, nq, nslices, kst, nmma, nstages, gbufs, bary_rows, bpitch; size_t smem, wimg_bytes; };
 
 static bool f_templated(int F) { return F == 4 || F == 9 || F == 16 || F == 25 || F == 36; }
 
@@ -562,7 +569,6 @@ Plan plan(int Cin, int Cout, int F, int precision) {
     pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
     pl.nq = NCOLS / F;
     if (pl.nq > Cin) pl.nq = Cin;
-    if (const char* e = getenv("PB200_GIN_NQ")) pl.nq = atoi(e);
     pl.nslices = (Cin + pl.nq - 1) / pl.nq;
     pl.kst = pl.bf ? (Cout + 31) / 32 : (Cout + KS - 1) / KS;    // K blocks of one 64-byte operand row
     pl.nmma = (pl.nq * F + 15) / 16 * 16;
@@ -570,7 +576,10 @@ Plan plan(int Cin, int Cout, int F, int precision) {
     const size_t budget = 226 * 1024;
     size_t gt = (size_t)pl.nsplit * pl.kst * G_KTILE_BYTES;
     size_t ws = (size_t)pl.nsplit * W_STAGE_BYTES;
-    size_t fixed = gt + 1024 + 256;
+    // a second tile buffer takes the gradOutput copy off the critical path of every tile; it is
+    // used when at least three filter stages still fit beside it
+    pl.gbufs = (2 * gt + 1024 + 256 + 3 * ws <= budget) ? 2 : 1;
+    size_t fixed = pl.gbufs * gt + 1024 + 256;
     int stages = 6;
     while (stages > 2 && fixed + stages * ws > budget) --stages;
     pl.nstages = stages;
@@ -629,7 +638,7 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
     Params p;
     p.Nf = Nf; p.Cin = Cin; p.Cout = Cout;
     p.nq = pl.nq; p.nslices = pl.nslices; p.kst = pl.kst; p.nmma = pl.nmma;
-    p.nstages = pl.nstages; p.bary_rows = pl.bary_rows; p.bpitch = pl.bpitch;
+    p.nstages = pl.nstages; p.gbufs = pl.gbufs; p.bary_rows = pl.bary_rows; p.bpitch = pl.bpitch;
     p.gout = gout; p.bary = bary; p.bary_p = bary_p; p.Fp = Fp; p.cum = cum; p.wimg = wimg; p.gin = gin;
     p.async_err = async_error_word();
     int64_t ntiles = ceil_div(Nf, TILE_M);
