@@ -286,6 +286,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             }
             float* const row0 = p.gin + (int64_t)(k0 + ts) * Cin;     // gradInput rows of the thread's two samples
             const bool on0 = ts < T, on1 = ts + 1 < T;
+            // 16-byte stores: rows and channel quadruples aligned, every slice made of whole pairs
+            const bool vec4 = (Cin % 4 == 0) && (p.nq % 2 == 0) && ((reinterpret_cast<uintptr_t>(p.gin) & 15) == 0);
+            float2 h0 = make_float2(0.f, 0.f), h1 = h0;
             // ---- 3. per slice: drain the accumulator, contract with bary, store gradInput
             for (int slice = 0; slice < p.nslices && alive; ++slice, ++sc) {
                 const uint32_t a = sc & 1u;
@@ -311,19 +314,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                         const int nx = cil + 2;
                         tmem_ld_wait();
                         if (F & 1) { va[FH - 1].y = 0.f; vb[FH - 1].y = 0.f; }
-                        float2 sa[2], sb[2];
+                        // two partial sums per sample and channel: four independent chains per block
+                        float2 sa[2], sb[2], sa2[2], sb2[2];
 #pragma unroll
-                        for (int t = 0; t < 2; ++t) { sa[t] = make_float2(0.f, 0.f); sb[t] = make_float2(0.f, 0.f); }
+                        for (int t = 0; t < 2; ++t) {
+                            sa[t] = make_float2(0.f, 0.f); sb[t] = make_float2(0.f, 0.f);
+                            sa2[t] = make_float2(0.f, 0.f); sb2[t] = make_float2(0.f, 0.f);
+                        }
 #pragma unroll
                         for (int d = 0; d < FH; ++d) {
 #pragma unroll
-                            for (int t = 0; t < 2; ++t) sa[t] = __ffma2_rn(breg[t][d], va[d], sa[t]);
+                            for (int t = 0; t < 2; ++t) {
+                                if (d & 1) sa2[t] = __ffma2_rn(breg[t][d], va[d], sa2[t]);
+                                else sa[t] = __ffma2_rn(breg[t][d], va[d], sa[t]);
+                            }
                         }
                         if (nx < p.nq) tmem_ld_row<F>(tbase + (uint32_t)(nx * F), reinterpret_cast<float*>(va));
 #pragma unroll
                         for (int d = 0; d < FH; ++d) {
 #pragma unroll
-                            for (int t = 0; t < 2; ++t) sb[t] = __ffma2_rn(breg[t][d], vb[d], sb[t]);
+                            for (int t = 0; t < 2; ++t) {
+                                if (d & 1) sb2[t] = __ffma2_rn(breg[t][d], vb[d], sb2[t]);
+                                else sb[t] = __ffma2_rn(breg[t][d], vb[d], sb[t]);
+                            }
+                        }
+#pragma unroll
+                        for (int t = 0; t < 2; ++t) {
+                            sa[t].x += sa2[t].x; sa[t].y += sa2[t].y;
+                            sb[t].x += sb2[t].x; sb[t].y += sb2[t].y;
                         }
                         if (nx + 1 < p.nq) tmem_ld_row<F>(tbase + (uint32_t)((nx + 1) * F), reinterpret_cast<float*>(vb));
                         else {
@@ -335,7 +353,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                             const float2 g1 = make_float2((sa[1].x + sa[1].y) * invT, (sb[1].x + sb[1].y) * invT);
                             float* d0 = row0 + ci;
                             float* d1 = d0 + Cin;
-                            if (vec && has_b) {
+                            if (vec4) {
+                                // channels ci..ci+1 wait for ci+2..ci+3: one 16-byte store per sample and
+                                // four channels (a scattered store costs the same pass whatever its width)
+                                if ((ci & 2) == 0) { h0 = g0; h1 = g1; }
+                                else {
+                                    if (on0) *reinterpret_cast<float4*>(d0 - 2) = make_float4(h0.x, h0.y, g0.x, g0.y);
+                                    if (on1) *reinterpret_cast<float4*>(d1 - 2) = make_float4(h1.x, h1.y, g1.x, g1.y);
+                                }
+                            } else if (vec && has_b) {
                                 if (on0) *reinterpret_cast<float2*>(d0) = g0;
                                 if (on1) *reinterpret_cast<float2*>(d1) = g1;
                             } else {
