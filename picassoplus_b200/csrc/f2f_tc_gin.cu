@@ -5,15 +5,18 @@
 //
 // gA (F*Cin floats per face, 12.8 KB at 128 channels x 25 bases) never leaves the SM.
 // Per CTA (persistent) and per tile of 128 faces (UMMA M = TMEM lanes = faces):
-//   * the epilogue warps copy the tile's gradOutput rows into shared memory once, as the
-//     K-major M-side operand (64-byte swizzled rows, one 8 KB block per 16 output channels);
-//   * one thread streams pre-swizzled filter blocks W'[(ci,d) rows][16 co] (N-side operand,
+//   * two loader warps copy the tile's gradOutput rows into shared memory as the K-major M-side
+//     operand (64-byte swizzled rows; bf16 hi+lo, bf16 or tf32), into one of two tile buffers, so
+//     the copy of tile t+1 runs while tile t is multiplied and drained;
+//   * one thread streams pre-swizzled filter blocks W'[(ci,d) rows][K block] (N-side operand,
 //     N = up to 256 rows = NQ channels x F bases per slice) with 1-D bulk copies;
 //   * one thread issues tcgen05.mma into one of two 256-column accumulators;
-//   * 8 epilogue warps (thread = face) drain the other accumulator: for every channel pair
-//     they read the F columns of both channels, contract with the bary rows of the face's
-//     samples and store float2 results.
-// Modes: 1 split (tf32 operands) or 2 splits (tf32 hi+lo, three MMAs per k-step).
+//   * 8 epilogue warps (thread = face) drain the other accumulator.  The two warps of a TMEM
+//     quadrant split the samples of a face (samples 0,1 / 2,3), whose bary rows stay in
+//     registers for the whole tile; for every channel pair a thread reads the F columns of both
+//     channels (the next pair's columns are requested while the current sums run), contracts
+//     them with its two bary rows in packed f32x2 FMAs and writes 16-byte pieces of gradInput.
+// Modes: one operand (tf32 or bf16) or hi+lo operands (bf16 or tf32; three MMAs per k-step).
 // All waits are bounded; on a time-out the block unwinds and raises the async error word.
 #include "common.cuh"
 #include "tc_ptx.cuh"
