@@ -78,14 +78,25 @@ v2f_bwd_vec_kernel(int64_t Nv, int CV, const int32_t* __restrict__ rowptr, const
             float4 acc = zero4();
             if (end > beg) {
                 float4 x = ldg4(in + v * CV + cg);
-                for (int e = beg; e < end; ++e) {
-                    int ent = __ldg(entries + e);
-                    int k = ent & 3;
-                    float4 g = ldg4(gout + (int64_t)(ent >> 2) * CV + cg);
-                    float4 fk = (k == 0) ? f0 : ((k == 1) ? f1 : f2);
+                auto accumulate = [&](int ent, const float4& g) {
+                    const int k = ent & 3;
+                    const float4 fk = (k == 0) ? f0 : ((k == 1) ? f1 : f2);
                     fma4(acc, g, fk);
-                    float4 t = mul4(g, x);
+                    const float4 t = mul4(g, x);
                     if (k == 0) add4(gf0, t); else if (k == 1) add4(gf1, t); else add4(gf2, t);
+                };
+                // two gradOutput rows in flight at a time, added in entry order
+                int e = beg;
+                for (; e + 1 < end; e += 2) {
+                    const int ent0 = __ldg(entries + e), ent1 = __ldg(entries + e + 1);
+                    const float4 g0 = ldg4(gout + (int64_t)(ent0 >> 2) * CV + cg);
+                    const float4 g1 = ldg4(gout + (int64_t)(ent1 >> 2) * CV + cg);
+                    accumulate(ent0, g0);
+                    accumulate(ent1, g1);
+                }
+                if (e < end) {
+                    const int ent = __ldg(entries + e);
+                    accumulate(ent, ldg4(gout + (int64_t)(ent >> 2) * CV + cg));
                 }
             }
             gin[v * CV + cg] = acc;
