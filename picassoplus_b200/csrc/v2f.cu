@@ -60,7 +60,7 @@ __global__ void v2f_fwd_generic_kernel(int64_t Nf, int C, int r, const int32_t* 
 // The per-thread filter-gradient partials are summed over the teams of the block in team
 // order and written to partial[blockIdx.x][3][C]; a second kernel adds the blocks in order.
 template <int TL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 v2f_bwd_vec_kernel(int64_t Nv, int CV, const int32_t* __restrict__ rowptr, const int32_t* __restrict__ entries,
                    const float4* __restrict__ gout, const float4* __restrict__ in, const float4* __restrict__ filt,
                    float4* __restrict__ gin, float4* __restrict__ partial) {
@@ -85,8 +85,18 @@ v2f_bwd_vec_kernel(int64_t Nv, int CV, const int32_t* __restrict__ rowptr, const
                     const float4 t = mul4(g, x);
                     if (k == 0) add4(gf0, t); else if (k == 1) add4(gf1, t); else add4(gf2, t);
                 };
-                // two gradOutput rows in flight at a time, added in entry order
+                // four gradOutput rows in flight at a time, added in entry order
                 int e = beg;
+                for (; e + 3 < end; e += 4) {
+                    int ent[4];
+                    float4 g[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) ent[u] = __ldg(entries + e + u);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) g[u] = ldg4(gout + (int64_t)(ent[u] >> 2) * CV + cg);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) accumulate(ent[u], g[u]);
+                }
                 for (; e + 1 < end; e += 2) {
                     const int ent0 = __ldg(entries + e), ent1 = __ldg(entries + e + 1);
                     const float4 g0 = ldg4(gout + (int64_t)(ent0 >> 2) * CV + cg);
