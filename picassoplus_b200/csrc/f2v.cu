@@ -294,7 +294,7 @@ f2v_bwd_tile_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ face,
 // The index chain of the gather (face -> vtMap -> nfCount) is resolved by 96 threads one hop
 // per tile for the block's next three tiles, so that phase 1 finds output vertex and 1/nfCount
 // of every corner in shared memory and issues its twelve gradOutput row loads at once.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap,
                        const int32_t* __restrict__ nfCount, const float* __restrict__ coeff,
                        const float4* __restrict__ in, const float4* __restrict__ filt, const float4* __restrict__ gout,
@@ -359,24 +359,24 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
         __syncthreads();                                       // ... and everybody else's
         const float4* scoef = scoef0 + buf * F2VB_TF * KG;
         // ---- phase 1: faces warp, warp+8, warp+16, warp+24
-        float4 gt[4], x[4], w[4];
+        // all sixteen row loads of the warp's four faces are issued first; the filter sums below need
+        // only the coefficients and run while the rows are on their way
+        float4 gt[4], x[4], w[4], gr[4][3];
+        float rn[4][3];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int fl = warp + 8 * i;
-            gt[i] = zero4(); x[i] = zero4(); w[i] = zero4();
+            x[i] = zero4(); w[i] = zero4();
+#pragma unroll
+            for (int j = 0; j < 3; ++j) { gr[i][j] = zero4(); rn[i][j] = 0.f; }
             if (fl < nf_tile) {
-                const int64_t f = f0 + fl;
-                float4 gr[3];
-                float rn[3];
 #pragma unroll
                 for (int j = 0; j < 3; ++j) {
                     const int vo = svo[buf * 96 + fl * 3 + j];
-                    rn[j] = srn[buf * 96 + fl * 3 + j];
-                    gr[j] = vo >= 0 ? ldg4(gout + (int64_t)vo * CV + cg) : zero4();
+                    rn[i][j] = srn[buf * 96 + fl * 3 + j];
+                    if (vo >= 0) gr[i][j] = ldg4(gout + (int64_t)vo * CV + cg);
                 }
-                x[i] = ldg4(in + f * CV + cg);
-#pragma unroll
-                for (int j = 0; j < 3; ++j) fma4s(gt[i], rn[j], gr[j]);
+                x[i] = ldg4(in + (f0 + fl) * CV + cg);
             }
         }
         for (int g = 0; g < KG; ++g) {
@@ -389,6 +389,12 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
             for (int i = 0; i < 4; ++i) {
                 fma4s(w[i], cf[i].x, f0v); fma4s(w[i], cf[i].y, f1v); fma4s(w[i], cf[i].z, f2v); fma4s(w[i], cf[i].w, f3v);
             }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            gt[i] = zero4();
+#pragma unroll
+            for (int j = 0; j < 3; ++j) fma4s(gt[i], rn[i][j], gr[i][j]);
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
