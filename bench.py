@@ -193,9 +193,9 @@ def kernel_models(d):
 # capture on a 2-mesh case of the same shapes, divided by its face count; traffic grows in
 # proportion to the faces).  Source: the summaries under profiles/.
 MEASURED_DRAM_BYTES_PER_FACE = {
-    ("c5", "f2f_fwd_tc"): 2000.0,
-    ("c5", "f2f_bwd_gin_tc"): 2163.0,
-    ("c5", "f2f_bwd_gfilter_tc"): 2125.0,
+    ("c5", "f2f_fwd_tc"): 2001.0,
+    ("c5", "f2f_bwd_gin_tc"): 1998.0,
+    ("c5", "f2f_bwd_gfilter_tc"): 2150.0,
 }
 
 
