@@ -115,8 +115,9 @@ class HostBatchFeed:
         self.free = [None] * len(self.bufs)
         self.bytes_per_pass = sum(t.numel() * t.element_size() for b in self.batches for t in b.values())
 
-    def _issue(self, g: int) -> torch.cuda.Event:
-        slot = g % len(self.bufs)
+    def _issue(self, i: int) -> torch.cuda.Event:
+        """Copies batch i % len(batches) into buffer i % len(bufs) on the copy stream."""
+        g, slot = i % len(self.batches), i % len(self.bufs)
         with torch.cuda.stream(self.copy_stream):
             if self.free[slot] is not None:
                 self.copy_stream.wait_event(self.free[slot])
@@ -126,16 +127,31 @@ class HostBatchFeed:
             ev.record(self.copy_stream)
         return ev
 
-    def __iter__(self):
+    def _run(self, total):
+        """Yields batches with running index 0, 1, ... (batch = index modulo the number of batches);
+        `total` = how many to yield, None = without end."""
         n, nb = len(self.batches), len(self.bufs)
         cur = torch.cuda.current_stream(self.device)
-        copied = {g: self._issue(g) for g in range(min(nb, n))}
-        for g in range(n):
-            cur.wait_event(copied.pop(g))
-            slot = g % nb
+        ahead = nb if total is None else min(nb, total)
+        copied = {i: self._issue(i) for i in range(ahead)}
+        i = 0
+        while total is None or i < total:
+            cur.wait_event(copied.pop(i))
+            slot, g = i % nb, i % n
             yield {k: self.bufs[slot][k][: t.shape[0]] for k, t in self.batches[g].items()}
             done = torch.cuda.Event()
             done.record(cur)
             self.free[slot] = done
-            if g + nb < n:
-                copied[g + nb] = self._issue(g + nb)
+            if total is None or i + nb < total:
+                copied[i + nb] = self._issue(i + nb)
+            i += 1
+
+    def __iter__(self):
+        """One pass over the batches."""
+        return self._run(len(self.batches))
+
+    def cycle(self):
+        """Endless iterator over pass after pass (a training loop over the same pinned batches):
+        the copy of the first batch of the next pass overlaps the last batch of the current one,
+        so no pass starts with an exposed copy."""
+        return self._run(None)

@@ -27,3 +27,21 @@ def test_feed_order_and_contents():
         for i, (sa, sb, ca, cb) in enumerate(sums):
             assert torch.equal(ca.cpu(), batches[i]["a"]) and torch.equal(cb.cpu(), batches[i]["b"])
             assert float(sa) == float(batches[i]["a"].double().sum()) and int(sb) == int(batches[i]["b"].long().sum())
+
+
+def test_feed_cycle_crosses_pass_boundaries():
+    """cycle(): pass after pass as one stream (odd batch count, two buffers: the buffer of a batch
+    alternates between passes), contents and order stay exact."""
+    from picassoplus_b200.parallel import HostBatchFeed
+    g = torch.Generator().manual_seed(5)
+    batches = [dict(a=torch.randn(rows, 5, generator=g).pin_memory()) for rows in (513, 64, 2049)]
+    feed = HostBatchFeed(batches, torch.device("cuda", 0), depth=2)
+    it = feed.cycle()
+    kept = []
+    for i in range(10):
+        d = next(it)
+        assert d["a"].shape == batches[i % 3]["a"].shape
+        kept.append(d["a"].clone())
+    torch.cuda.synchronize()
+    for i, c in enumerate(kept):
+        assert torch.equal(c.cpu(), batches[i % 3]["a"])
