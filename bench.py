@@ -55,7 +55,7 @@ def parse_args():
                     "(done by default when a step takes less than 3 ms)")
     ap.add_argument("--e2e-groups", type=int, default=0,
                     help="mesh groups of the end-to-end step (host-to-device copy of one overlaps compute of another); "
-                         "0 = one group per 128 MB of host input, at most 8")
+                         "0 = one group per 256 MB of host input, at most 4")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
@@ -309,7 +309,7 @@ def run_ours(args):
     # End to end: the rank's meshes are fed from pinned host memory in groups; the copy of
     # group g+1 overlaps the fwd+bwd of group g (filter gradients accumulate over the groups).
     host_bytes = sum(h[k].numel() * h[k].element_size() for k in ("vertex", "face", "x", "cum", "bary_xyz"))
-    want_groups = args.e2e_groups if args.e2e_groups > 0 else min(8, host_bytes // (128 << 20))
+    want_groups = args.e2e_groups if args.e2e_groups > 0 else min(4, host_bytes // (256 << 20))
     ngroups = max(1, min(want_groups, count))
     feed = None
     if not args.no_e2e:

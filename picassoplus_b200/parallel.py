@@ -105,7 +105,7 @@ class HostBatchFeed:
         self.copy_stream = torch.cuda.Stream(device=device)
         keys = list(self.batches[0].keys())
         self.bufs = []
-        for _ in range(min(depth, len(self.batches))):
+        for _ in range(depth):                 # also for a single batch: cycle() copies pass p+1 during pass p
             buf = {}
             for k in keys:
                 rows = max(b[k].shape[0] for b in self.batches)
