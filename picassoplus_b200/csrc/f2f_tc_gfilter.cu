@@ -493,12 +493,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 
 // bary rows padded to Fp = F rounded up to 4 floats (pad columns zero): rows start on 16-byte
 // boundaries, so a stage's block is one bulk copy and a thread reads 4 bases per 16-byte load
+// (thread = one 16-byte piece of a padded row)
 __global__ void pad_bary_kernel(int64_t n, int F, int Fp, const float* __restrict__ src, float* __restrict__ dst) {
-    const int64_t total = n * Fp;
+    const int q = Fp / 4;                                    // pieces per row
+    const int64_t total = n * q;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t s = i / Fp;
-        const int d = (int)(i - s * Fp);
-        dst[i] = d < F ? __ldg(src + s * F + d) : 0.f;
+        int64_t s;
+        int d;
+        if (total < (int64_t)1 << 32) { const uint32_t u = (uint32_t)i; s = u / (uint32_t)q; d = 4 * (int)(u - (uint32_t)s * (uint32_t)q); }
+        else { s = i / q; d = 4 * (int)(i - s * q); }
+        const float* r = src + s * F + d;
+        float4 v;
+        v.x = __ldg(r);                                       // d < F always: Fp - F < 4
+        v.y = d + 1 < F ? __ldg(r + 1) : 0.f;
+        v.z = d + 2 < F ? __ldg(r + 2) : 0.f;
+        v.w = d + 3 < F ? __ldg(r + 3) : 0.f;
+        reinterpret_cast<float4*>(dst)[i] = v;
     }
 }
 
@@ -582,7 +592,7 @@ size_t padded_bary_bytes(int64_t NiK, int F) {
 int pad_bary(int64_t NiK, int F, const float* bary, float* dst, cudaStream_t stream) {
     if (NiK <= 0) return PB200_OK;
     const int Fp = padded_F(F);
-    PB_LAUNCH("f2f_pad_bary", gfilter::pad_bary_kernel, persistent_blocks(NiK * Fp, 256, 8), 256, 0, stream, NiK, F, Fp,
+    PB_LAUNCH("f2f_pad_bary", gfilter::pad_bary_kernel, persistent_blocks(NiK * (Fp / 4), 256, 8), 256, 0, stream, NiK, F, Fp,
               bary, dst);
     return PB200_OK;
 }
