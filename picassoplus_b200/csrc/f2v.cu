@@ -5,15 +5,6 @@
 
 namespace pb {
 
-// acc += s * b with two packed f32x2 FMAs (half the issue slots of four scalar ones)
-__device__ __forceinline__ void fma4p(float4& acc, float s, const float4& b) {
-    const float2 s2 = make_float2(s, s);
-    const float2 lo = __ffma2_rn(s2, make_float2(b.x, b.y), make_float2(acc.x, acc.y));
-    const float2 hi = __ffma2_rn(s2, make_float2(b.z, b.w), make_float2(acc.z, acc.w));
-    acc = make_float4(lo.x, lo.y, hi.x, hi.y);
-}
-
-
 // -------------------------------------------------------------------- forward, vectorised
 // r == 1, C % 4 == 0, K <= 64.  Two kernels:
 //   f2v_fwd_face    item = (face, float4 channel group): wx[f] = (sum_k coeff[f,k]*filter[k]) * input[f],
@@ -130,7 +121,7 @@ f2v_fwd_face_blocked_kernel(int64_t Nf, int CV, int K, const float* __restrict__
 #pragma unroll
             for (int i = 0; i < FB; ++i) {
                 const float4 cf = scoef[(warp + 8 * i) * KG + g];        // rows past the tile are stale or zero: unused
-                fma4p(w[i], cf.x, f0v); fma4p(w[i], cf.y, f1v); fma4p(w[i], cf.z, f2v); fma4p(w[i], cf.w, f3v);
+                fma4s(w[i], cf.x, f0v); fma4s(w[i], cf.y, f1v); fma4s(w[i], cf.z, f2v); fma4s(w[i], cf.w, f3v);
             }
         }
 #pragma unroll
@@ -396,7 +387,7 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
             const float4 f2v = sfilt[(4 * g + 2) * 32 + lane], f3v = sfilt[(4 * g + 3) * 32 + lane];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                fma4p(w[i], cf[i].x, f0v); fma4p(w[i], cf[i].y, f1v); fma4p(w[i], cf[i].z, f2v); fma4p(w[i], cf[i].w, f3v);
+                fma4s(w[i], cf[i].x, f0v); fma4s(w[i], cf[i].y, f1v); fma4s(w[i], cf[i].z, f2v); fma4s(w[i], cf[i].w, f3v);
             }
         }
 #pragma unroll
@@ -423,7 +414,7 @@ f2v_bwd_blocked_kernel(int64_t Nf, int CV, int K, const int32_t* __restrict__ fa
             for (int fl = 0; fl < nf_tile; ++fl) {
                 const float4 c = scoef[fl * KG + warp];
                 const float4 t = st[fl * 32 + lane];
-                fma4p(acc[0], c.x, t); fma4p(acc[1], c.y, t); fma4p(acc[2], c.z, t); fma4p(acc[3], c.w, t);
+                fma4s(acc[0], c.x, t); fma4s(acc[1], c.y, t); fma4s(acc[2], c.z, t); fma4s(acc[3], c.w, t);
             }
         }
     }
