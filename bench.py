@@ -457,7 +457,7 @@ def run_ours(args):
 
     e2e = None
     if not args.no_e2e:
-        for _ in range(2):
+        for _ in range(max(args.warmup, 3)):
             step_e2e()
         e_steps = max(2, min(args.steps, 5))
         ems, _ = timed(step_e2e, e_steps)
