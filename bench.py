@@ -39,6 +39,8 @@ from picassoplus_b200 import synth  # noqa: E402
 
 METRIC = "mesh_conv_block_fwd_bwd_faces_per_sec"
 UNIT = "faces/s"
+# max|a-b| / max|b| per tensor that each precision mode of facet2facet must meet
+GATES = {"fp32": 1e-4, "fp32_tf32x3": 1e-4, "tf32": 2e-3, "bf16": 2e-2}
 
 
 def parse_args():
@@ -48,7 +50,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS))
-    ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
+    ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_tf32x3", "tf32", "bf16"])
     ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--graph", action="store_true", help="also time the step replayed from a CUDA graph "
@@ -58,6 +60,7 @@ def parse_args():
                          "0 = one group per 256 MB of host input, at most 4")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
     return ap.parse_args()
 
@@ -72,18 +75,36 @@ def workload_name(cfg, total_meshes):
 
 # ------------------------------------------------------------------------------ inputs
 def host_inputs(cfg, first, count, seed_shift=0):
-    """Host-side batch of meshes [first, first+count) with features, texture samples and
-    the upstream gradient, all seeded per mesh range."""
+    """Host-side batch of meshes [first, first+count).  Features and texture samples are seeded
+    PER MESH (by the mesh's index in the whole batch), so a mesh carries the same data whatever
+    the number of ranks or mesh groups it is dealt to."""
     mb = synth.make_batch(cfg, count, first)
     L = cfg["L"]
     K = (L + 1) ** 2
-    counts, bary_xyz = synth.texture_samples(mb.num_faces, cfg["seed"] * 7919 + first)
-    g = torch.Generator().manual_seed(cfg["seed"] * 104729 + first + seed_shift)
-    x = torch.randn(mb.num_vertices, cfg["cin"], generator=g)
+    counts, bary_xyz, xs = [], [], []
+    for j in range(count):
+        i = first + j
+        cj, bj = synth.texture_samples(int(mb.mf[j]), cfg["seed"] * 7919 + i)
+        counts.append(cj)
+        bary_xyz.append(bj)
+        g = torch.Generator().manual_seed(cfg["seed"] * 104729 + i + seed_shift)
+        xs.append(torch.randn(int(mb.nv[j]), cfg["cin"], generator=g))
+    counts = np.concatenate(counts)
+    bary_xyz = np.concatenate(bary_xyz)
     return dict(vertex=torch.from_numpy(mb.vertex), face=torch.from_numpy(mb.face),
                 counts=torch.from_numpy(counts), cum=torch.cumsum(torch.from_numpy(counts), 0, dtype=torch.int32),
-                bary_xyz=torch.from_numpy(bary_xyz), x=x, K=K, L=L,
-                Nv=mb.num_vertices, Nf=mb.num_faces, NiK=int(counts.sum()), nmesh=count)
+                bary_xyz=torch.from_numpy(bary_xyz), x=torch.cat(xs), K=K, L=L,
+                Nv=mb.num_vertices, Nf=mb.num_faces, NiK=int(counts.sum()), nmesh=count,
+                nv=[int(v) for v in mb.nv], mf=[int(f) for f in mb.mf])
+
+
+def upstream_gradient(cfg, first, nv_per_mesh, dev):
+    """The block's upstream gradient, seeded per mesh like the inputs (device generator)."""
+    parts = []
+    for j, nv in enumerate(nv_per_mesh):
+        gen = torch.Generator(device=dev).manual_seed(cfg["seed"] * 31 + first + j)
+        parts.append(torch.randn(nv, cfg["cout"], generator=gen, device=dev))
+    return torch.cat(parts)
 
 
 def make_params(cfg):
@@ -282,8 +303,7 @@ def run_ours(args):
     pin = {k: h[k].pin_memory() for k in ("vertex", "face", "x", "cum", "bary_xyz")}
     d = {k: v.to(dev) for k, v in pin.items()}
     vt_map = torch.arange(h["Nv"], dtype=torch.int32, device=dev)
-    gen = torch.Generator(device=dev).manual_seed(cfg["seed"] * 31 + first)
-    G = torch.randn(h["Nv"], cfg["cout"], generator=gen, device=dev)
+    G = upstream_gradient(cfg, first, h["nv"], dev)
     params = [w.to(dev).requires_grad_() for w in (Wv, Wf, Wo)]
     allreduce = FilterGradAllReduce(params)
     sh_eye = sph_harm_coeff(L, torch.eye(3, device=dev))
@@ -309,7 +329,8 @@ def run_ours(args):
     # End to end: the rank's meshes are fed from pinned host memory in groups; the copy of
     # group g+1 overlaps the fwd+bwd of group g (filter gradients accumulate over the groups).
     host_bytes = sum(h[k].numel() * h[k].element_size() for k in ("vertex", "face", "x", "cum", "bary_xyz"))
-    want_groups = args.e2e_groups if args.e2e_groups > 0 else min(4, host_bytes // (256 << 20))
+    # at least two groups whenever the rank holds two meshes, so that a copy always has compute to hide behind
+    want_groups = args.e2e_groups if args.e2e_groups > 0 else max(2, min(4, host_bytes // (256 << 20)))
     ngroups = max(1, min(want_groups, count))
     feed = None
     if not args.no_e2e:
@@ -317,15 +338,19 @@ def run_ours(args):
         for gfirst, gcount in [(first + a, b) for a, b in partition_meshes([1] * count, ngroups) if b > 0]:
             hg = h if ngroups == 1 else host_inputs(cfg, gfirst, gcount)
             pinned_groups.append({k: hg[k].pin_memory() for k in ("vertex", "face", "x", "cum", "bary_xyz")})
-            gg = torch.Generator(device=dev).manual_seed(cfg["seed"] * 31 + gfirst)
-            group_G.append(torch.randn(hg["Nv"], cfg["cout"], generator=gg, device=dev))
+            group_G.append(upstream_gradient(cfg, gfirst, hg["nv"], dev))
         feed = HostBatchFeed(pinned_groups, dev, depth=2)
     h2d_bytes = feed.bytes_per_pass if feed is not None else 0
     # step after step over the same pinned groups: the first group of the next step is copied while
     # the last group of the current one is computed
     feed_cycle = feed.cycle() if feed is not None else None
 
+    from picassoplus_b200 import topology
+
     def step_e2e():
+        # index validation without a host round trip per group: the status words of the CSR builds are
+        # read after the step's own synchronisation (the loss read-back)
+        topology.set_validation("deferred")
         for p in params:
             p.grad = None
         total = torch.zeros((), device=dev)
@@ -343,7 +368,10 @@ def run_ours(args):
             loss.backward()
             total = total + loss.detach()
         allreduce()
-        return float(total.item())
+        out = float(total.item())
+        topology.check_deferred()
+        topology.set_validation("sync")
+        return out
 
     def barrier():
         if world > 1:
@@ -378,6 +406,15 @@ def run_ours(args):
     ms_per_step = ms / args.steps
     value = faces_total / (ms_per_step / 1e3)
 
+    if _lib.async_error():
+        raise SystemExit(f"a tensor-core kernel gave up waiting (code {_lib.async_error()}): the timed steps are invalid")
+    # checksum of the all-reduced filter gradients of the last step: the batch is seeded per mesh, so
+    # the values agree across GPU counts up to fp32 re-association of the sum over meshes
+    gsum = sum(float(p.grad.double().sum().item()) for p in params)
+    gl2 = float(sum(float((p.grad.double() ** 2).sum().item()) for p in params) ** 0.5)
+    checksum = dict(sum=gsum, l2=gl2, note="sum and L2 norm over the three all-reduced filter gradients "
+                    "(fp64 accumulation of the fp32 results)")
+
     # per-kernel durations of the same step, measured live with CUDA events on the launch stream
     prof_steps = min(args.steps, 3)
     _lib.prof_reset()
@@ -393,7 +430,6 @@ def run_ours(args):
 
     # per-batch preparation, reported apart (amortised over the convolutions of a level): nfCount,
     # triangle geometry, the two SH bases and the vertex CSR build with its index validation
-    from picassoplus_b200 import topology
     prep_ms = []
     for _ in range(3):
         topology.clear_cache()
@@ -424,6 +460,35 @@ def run_ours(args):
             variants[vname] = dict(value=faces_total / (vms / vsteps / 1e3), unit=UNIT, ms_per_step=vms / vsteps,
                                    note=notes[vname])
         conv3d.set_f2f_precision(args.precision)
+
+    # accuracy of the timed precision mode on this batch's first mesh (outside every timed region):
+    # the whole block in the timed mode against the library's fp32 FFMA path on identical inputs
+    parity = None
+    if rank == 0 and not args.no_parity:
+        nv0, mf0 = h["nv"][0], h["mf"][0]
+        nik0 = int(h["cum"][mf0 - 1])
+        sl = dict(x=d["x"][:nv0].detach(), face=d["face"][:mf0], cum=d["cum"][:mf0], bary=bary_sh[:nik0],
+                  coeff=coeff[:mf0], nfc=nfc[:nv0], vt=vt_map[:nv0], G=G[:nv0])
+
+        def one_mesh(mode):
+            conv3d.set_f2f_precision(mode)
+            x0 = sl["x"].clone().requires_grad_()
+            ws = [p.detach().clone().requires_grad_() for p in params]
+            o = conv_block(x0, ws[0], ws[1], ws[2], sl["face"], sl["cum"], sl["bary"], sl["coeff"], sl["nfc"], sl["vt"],
+                           sh_eye)
+            o.backward(sl["G"])
+            return [o.detach(), x0.grad] + [w.grad for w in ws]
+
+        got, want = one_mesh(args.precision), one_mesh("fp32_ffma")
+        conv3d.set_f2f_precision(args.precision)
+        names = ["out", "grad_x", "grad_Wv", "grad_Wf", "grad_Wo"]
+        parity = {"mode": args.precision, "against": "fp32_ffma path of the same library, same inputs",
+                  "sample": f"first mesh of the batch ({mf0} faces)", "gate_max_rel": GATES[args.precision]}
+        for n, a, b in zip(names, got, want):
+            diff = (a.double() - b.double())
+            parity[n] = dict(max_rel=float(diff.abs().max() / b.double().abs().max()),
+                             rms_rel=float((diff ** 2).mean().sqrt() / (b.double() ** 2).mean().sqrt()))
+        parity["ok"] = all(parity[n]["max_rel"] <= GATES[args.precision] for n in names)
 
     # launch-bound batches: the same resident step captured once into a CUDA graph and replayed
     graph = None
@@ -479,12 +544,13 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload_name(cfg, total_meshes), "name": args.config,
-                       "faces": int(faces_total), "vertices": int(nf_all[1].item()),
-                       "texture_samples": int(nf_all[2].item()), "f2f_precision": args.precision,
-                       "parallelism": f"mesh-dp{world}", "meshes_per_gpu": count,
-                       "l2_policy": "inputs larger than L2 (no flush)" if h["Nf"] * cfg["cin"] * 4 > 256e6
-                       else "inputs smaller than L2, no flush"},
+            "config": {"workload": workload_name(cfg, total_meshes), "name": args.config},
+            "workload_detail": {"faces": int(faces_total), "vertices": int(nf_all[1].item()),
+                                "texture_samples": int(nf_all[2].item()), "f2f_precision": args.precision,
+                                "parallelism": f"mesh-dp{world}", "meshes_per_gpu": count,
+                                "l2_policy": "inputs larger than L2 (no flush)" if h["Nf"] * cfg["cin"] * 4 > 256e6
+                                else "inputs smaller than L2, no flush"},
+            "parity": parity, "grad_checksum": checksum,
             "roofline": roof, "cpu_baseline": cpu, "e2e": e2e, "graph_replay": graph, "prepare": prep, "gpu_launches": int(launches),
             "clocks": clocks, "variants": variants, "kernels": table[:12],
             "allreduce_bytes": allreduce.nbytes if world > 1 else 0,

@@ -3,9 +3,13 @@
  * spherical-harmonic basis, and the adjacency they need, as CUDA kernels for sm_100a.
  *
  * Conventions
- *   - every pointer is a DEVICE pointer owned by the caller; the library never allocates
- *     or frees device memory.  Scratch memory is passed in as `workspace` and sized by the
- *     matching `*_workspace_bytes` query.
+ *   - every pointer is a DEVICE pointer owned by the caller; no call allocates or frees
+ *     device memory.  Scratch memory is passed in as `workspace` and sized by the matching
+ *     `*_workspace_bytes` query.  Two fixed resources belong to the library itself: a 4 MiB
+ *     `__device__` array in the library image (scratch of pb200_vertex2facet_backward_static,
+ *     resident on every GPU that loads the library) and one small block of pinned, mapped HOST
+ *     memory for the asynchronous error words below, allocated by the first facet2facet call of
+ *     the process that takes a tensor-core path -- make that first call outside stream capture.
  *   - features are fp32, row-major, contiguous; indices are int32.
  *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).  All work
  *     is enqueued on it; no call synchronises unless its comment says so.
@@ -37,17 +41,39 @@ extern "C" {
 /* contraction precision for facet2facet (fp32 accumulation in every mode) */
 #define PB200_PREC_FP32     0   /* every operand as bf16 hi + bf16 lo, three tensor-core products
                                    per term (FFMA where the shape has no tensor-core kernel):
-                                   about 1e-5 relative error, meets the 1e-4 gate.  With the
-                                   environment variable PB200_FP32_TF32_SPLIT set the split is
-                                   tf32 hi + lo instead (about 2e-6, a quarter slower).        */
+                                   about 1e-5 relative error, meets the 1e-4 gate            */
 #define PB200_PREC_TF32     1   /* tf32 operands on the tensor cores                       */
 #define PB200_PREC_BF16     2   /* bf16 operands on the tensor cores (2e-2 relative gate)  */
 #define PB200_PREC_FP32_FFMA 3  /* fp32 FFMA path (no tensor cores), every shape            */
+#define PB200_PREC_FP32_TF32X3 4 /* every operand as tf32 hi + tf32 lo, three products per term:
+                                   about 2e-6 relative error, as close to fp64 as the reference's
+                                   own FFMA kernels; about a quarter slower than PB200_PREC_FP32 */
 
 int         pb200_version(void);
 const char* pb200_last_error(void);
 /* number of kernel launches issued by this library in this process so far */
 int64_t     pb200_launch_count(void);
+
+/* ---- asynchronous errors of the tensor-core kernels ------------------------------------
+ * Every wait inside the facet2facet tensor-core kernels is bounded (about one second of GPU
+ * clocks; such a wait can only run out if the GPU is preempted for that long or a kernel has a
+ * defect).  A kernel whose wait runs out unwinds, frees its tensor memory and raises a word in
+ * mapped host memory, one word per device.  The call that launched it has already returned
+ * PB200_OK and its outputs are invalid.  While the word of the current device is raised, every
+ * later facet2facet call on that device fails with PB200_ECUDA.  pb200_async_error() reads the
+ * word of the current device (0 = none; 1/2/3 = forward / input-gradient / filter-gradient
+ * kernel) -- call it after synchronising the stream to learn whether the step's results are
+ * good; pb200_clear_async_error() re-arms the device.  pb200_set_wait_budget() changes the
+ * budget of later launches (clocks; <= 0 restores the default).  A cudaDeviceReset() by the host
+ * invalidates nothing here, but it does invalidate the device address that
+ * pb200_vertex2facet_backward_static caches: do not reset a device between calls of that entry. */
+int  pb200_async_error(void);
+void pb200_clear_async_error(void);
+void pb200_set_wait_budget(int64_t clocks);
+/* Test switch: while on, the forward kernel's filter stream issues no copies, so the kernel's
+ * waits run out after the wait budget and the error path above is exercised.  Never set it
+ * outside a test. */
+void pb200_test_silence_filter_stream(int on);
 
 /* ---- per-kernel timing (for benchmarks) -------------------------------------------
  * When enabled, every launch is bracketed by CUDA events on its stream.  pb200_prof_read
@@ -154,7 +180,11 @@ int pb200_facet2vertex_backward(int64_t Nf, int64_t NvIn, int64_t NvOut, int C, 
  * numInterior[f-1] .. numInterior[f]-1 (numInterior = inclusive cumulative sample count).
  * Replaces facet2facetConv3dLauncher (mesh_conv3d_gpu.cu:6-37,136-143; binding
  * mesh_conv3d.cpp:192-228).  input (NiK,Cin), filter (Cout,Cin,F), bary (NiK,F),
- * output (Nf,Cout).  F <= 50 as in the reference (mesh_conv3d.cpp:211). */
+ * output (Nf,Cout).  F <= 50 as in the reference (mesh_conv3d.cpp:211).
+ * numInterior is trusted, as in the reference: it must be non-decreasing, lie in [0, NiK] and end
+ * at NiK; pb200_check_num_interior verifies that on the device (status = 0 or PB200_EINDEX; run it
+ * once per numInterior array, e.g. alongside the CSR build, and read `status` after a sync). */
+int pb200_check_num_interior(int64_t Nf, int64_t NiK, const int32_t* numInterior, int32_t* status, void* stream);
 size_t pb200_facet2facet_forward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision);
 int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input,
                               const float* filter, const float* bary, const int32_t* numInterior,

@@ -156,7 +156,7 @@ def vertex2facet_forward(inp, filt, face):
     """mesh_conv3d_gpu.cu:176-195: out[f, c*r+m] = sum_k filter[k,c,m] * in[face[f,k], c]."""
     face = face.to(torch.long)
     _, C, r = filt.shape
-    out = torch.zeros(face.shape[0], C, r, dtype=inp.dtype)
+    out = torch.zeros(face.shape[0], C, r, dtype=inp.dtype, device=inp.device)
     for k in range(3):
         out += filt[k].unsqueeze(0) * inp[face[:, k]].unsqueeze(-1)
     return out.reshape(face.shape[0], C * r)
@@ -189,7 +189,7 @@ def facet2vertex_forward(inp, filt, coeff, face, nf_count, vt_map):
     K, C, r = filt.shape
     nv_out = nf_count.shape[0]
     wx = _f2v_terms(coeff, filt) * inp.unsqueeze(-1)          # (Nf, C, r)
-    out = torch.zeros(nv_out, C, r, dtype=inp.dtype)
+    out = torch.zeros(nv_out, C, r, dtype=inp.dtype, device=inp.device)
     vmap = vt_map.to(torch.long)
     nf = nf_count.to(inp.dtype)
     for j in range(3):
@@ -208,7 +208,7 @@ def facet2vertex_backward(gout, inp, filt, coeff, face, nf_count, vt_map):
     vmap = vt_map.to(torch.long)
     nf = nf_count.to(inp.dtype)
     g = gout.reshape(-1, C, r)
-    gt = torch.zeros(face.shape[0], C, r, dtype=inp.dtype)
+    gt = torch.zeros(face.shape[0], C, r, dtype=inp.dtype, device=inp.device)
     for j in range(3):
         vo = vmap[face[:, j]]
         ok = vo >= 0
@@ -224,15 +224,15 @@ def facet2vertex_backward(gout, inp, filt, coeff, face, nf_count, vt_map):
 # ------------------------------------------------------------------------------ F2F
 def _f2f_segments(cum, n_samples):
     cum = cum.to(torch.long)
-    counts = torch.diff(cum, prepend=torch.zeros(1, dtype=torch.long))
-    fid = torch.repeat_interleave(torch.arange(cum.shape[0]), counts, output_size=n_samples)
+    counts = torch.diff(cum, prepend=torch.zeros(1, dtype=torch.long, device=cum.device))
+    fid = torch.repeat_interleave(torch.arange(cum.shape[0], device=cum.device), counts, output_size=n_samples)
     return counts, fid
 
 
 def _f2f_A(inp, bary, counts, fid, f0, f1, k0, k1):
     """A[f,d,ci] = (1/T_f) sum_{k in f} bary[k,d]*in[k,ci] for faces [f0,f1)."""
     F = bary.shape[1]
-    A = torch.zeros(f1 - f0, F, inp.shape[1], dtype=inp.dtype)
+    A = torch.zeros(f1 - f0, F, inp.shape[1], dtype=inp.dtype, device=inp.device)
     if k1 > k0:
         A.index_add_(0, fid[k0:k1] - f0, bary[k0:k1].unsqueeze(-1) * inp[k0:k1].unsqueeze(1))
     T = counts[f0:f1].to(inp.dtype).clamp(min=1).reshape(-1, 1, 1)
@@ -255,7 +255,7 @@ def facet2facet_forward(inp, filt, bary, cum, chunk=8192):
     (cum = inclusive cumulative sample count); a face with no samples gives 0."""
     Cout = filt.shape[0]
     counts, fid = _f2f_segments(cum, inp.shape[0])
-    out = torch.zeros(cum.shape[0], Cout, dtype=inp.dtype)
+    out = torch.zeros(cum.shape[0], Cout, dtype=inp.dtype, device=inp.device)
     Wt = filt.permute(2, 1, 0).reshape(-1, Cout)             # [(d,ci), co]
     for f0, f1, k0, k1 in _face_chunks(cum, chunk):
         A = _f2f_A(inp, bary, counts, fid, f0, f1, k0, k1)
@@ -269,7 +269,7 @@ def facet2facet_backward(gout, inp, filt, bary, cum, chunk=8192):
     Cout, Cin, F = filt.shape
     counts, fid = _f2f_segments(cum, inp.shape[0])
     gin = torch.zeros_like(inp)
-    gfl = torch.zeros(F * Cin, Cout, dtype=inp.dtype)
+    gfl = torch.zeros(F * Cin, Cout, dtype=inp.dtype, device=inp.device)
     Wt = filt.permute(2, 1, 0).reshape(-1, Cout)
     for f0, f1, k0, k1 in _face_chunks(cum, chunk):
         A = _f2f_A(inp, bary, counts, fid, f0, f1, k0, k1)

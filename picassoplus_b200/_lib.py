@@ -13,8 +13,9 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libpicasso_b200.so")
 
 OK, EINVAL, EWORKSPACE, ECUDA, EINDEX = 0, -1, -2, -3, -4
-PREC_FP32, PREC_TF32, PREC_BF16, PREC_FP32_FFMA = 0, 1, 2, 3
-PRECISIONS = {"fp32": PREC_FP32, "tf32": PREC_TF32, "bf16": PREC_BF16, "fp32_ffma": PREC_FP32_FFMA}
+PREC_FP32, PREC_TF32, PREC_BF16, PREC_FP32_FFMA, PREC_FP32_TF32X3 = 0, 1, 2, 3, 4
+PRECISIONS = {"fp32": PREC_FP32, "tf32": PREC_TF32, "bf16": PREC_BF16, "fp32_ffma": PREC_FP32_FFMA,
+              "fp32_tf32x3": PREC_FP32_TF32X3}
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
@@ -38,6 +39,11 @@ SIGNATURES = {
     "pb200_prof_enable": (None, [i32]),
     "pb200_prof_reset": (None, []),
     "pb200_prof_read": (i32, [C.POINTER(ProfRecord), i32]),
+    "pb200_async_error": (i32, []),
+    "pb200_clear_async_error": (None, []),
+    "pb200_set_wait_budget": (None, [i64]),
+    "pb200_test_silence_filter_stream": (None, [i32]),
+    "pb200_check_num_interior": (i32, [i64, i64, vp, vp, vp]),
     "pb200_count_vertex_adjface": (i32, [i64, i64, i64, vp, vp, vp, vp]),
     "pb200_vertex_csr_workspace_bytes": (sz, [i64, i64]),
     "pb200_build_vertex_csr": (i32, [i64, i64, i64, vp, vp, vp, vp, vp, vp, sz, vp]),
@@ -103,3 +109,12 @@ def prof_read(cap: int = 64):
     buf = (ProfRecord * cap)()
     n = _lib.pb200_prof_read(buf, cap)
     return [(buf[i].name.decode(), int(buf[i].launches), float(buf[i].total_ms)) for i in range(min(n, cap))]
+
+
+def async_error() -> int:
+    """0, or the code of the tensor-core kernel that gave up on the current device (after a sync)."""
+    return int(_lib.pb200_async_error())
+
+
+def clear_async_error() -> None:
+    _lib.pb200_clear_async_error()

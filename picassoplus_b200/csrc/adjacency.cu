@@ -176,6 +176,7 @@ __global__ void expand_rows_fwd_kernel(int64_t Nf, int64_t NiK, int CVn, const f
         int64_t f = i / CVn;
         int c = (int)(i - f * CVn);
         int k0 = f > 0 ? __ldg(cum + f - 1) : 0, k1 = __ldg(cum + f);
+        if (k0 < 0) k0 = 0;
         if (k1 > NiK) k1 = (int)NiK;
         if (VEC == 4) {
             float4 v = __ldg(reinterpret_cast<const float4*>(in) + i);
@@ -188,7 +189,7 @@ __global__ void expand_rows_fwd_kernel(int64_t Nf, int64_t NiK, int CVn, const f
 }
 
 template <int VEC>
-__global__ void expand_rows_bwd_kernel(int64_t Nf, int CVn, const float* __restrict__ gout,
+__global__ void expand_rows_bwd_kernel(int64_t Nf, int64_t NiK, int CVn, const float* __restrict__ gout,
                                        const int32_t* __restrict__ cum, float* __restrict__ gin) {
     int64_t total = Nf * CVn;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -196,6 +197,8 @@ __global__ void expand_rows_bwd_kernel(int64_t Nf, int CVn, const float* __restr
         int64_t f = i / CVn;
         int c = (int)(i - f * CVn);
         int k0 = f > 0 ? cum[f - 1] : 0, k1 = cum[f];
+        if (k0 < 0) k0 = 0;
+        if (k1 > NiK) k1 = (int)NiK;
         if (VEC == 4) {
             float4 acc = zero4();
             for (int k = k0; k < k1; ++k)
@@ -207,6 +210,17 @@ __global__ void expand_rows_bwd_kernel(int64_t Nf, int CVn, const float* __restr
             gin[i] = acc;
         }
     }
+}
+
+// numInterior must be a non-decreasing running count inside [0, NiK] that ends at NiK
+__global__ void check_running_count_kernel(int64_t Nf, int64_t NiK, const int32_t* __restrict__ cum,
+                                           int32_t* __restrict__ status) {
+    bool bad = false;
+    for (int64_t f = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; f < Nf; f += (int64_t)gridDim.x * blockDim.x) {
+        const int k1 = cum[f], k0 = f > 0 ? cum[f - 1] : 0;
+        if (k0 < 0 || k1 < k0 || k1 > NiK || (f == Nf - 1 && k1 != NiK)) bad = true;
+    }
+    if (bad) *status = PB200_EINDEX;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -290,6 +304,17 @@ int pb200_triangle_geometry(int64_t Nf, int64_t Nv, int vstride, const float* ve
     return PB200_OK;
 }
 
+int pb200_check_num_interior(int64_t Nf, int64_t NiK, const int32_t* numInterior, int32_t* status, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && NiK >= 0 && NiK < (1LL << 31), PB200_EINVAL, "check_num_interior: bad sizes");
+    PB_REQUIRE(status && (Nf == 0 || numInterior), PB200_EINVAL, "check_num_interior: null pointer");
+    PB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    if (Nf == 0) return PB200_OK;
+    PB_LAUNCH("check_running_count", check_running_count_kernel, persistent_blocks(Nf, 256, 8), 256, 0, stream,
+              Nf, NiK, numInterior, status);
+    return PB200_OK;
+}
+
 int pb200_expand_rows_forward(int64_t Nf, int64_t NiK, int C, const float* in, const int32_t* cum, float* out,
                               void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
@@ -313,8 +338,8 @@ int pb200_expand_rows_backward(int64_t Nf, int64_t NiK, int C, const float* gout
     bool vec = (C % 4 == 0) && aligned16(gout) && aligned16(gin);
     int CVn = vec ? C / 4 : C;
     int grid = persistent_blocks(Nf * CVn, 256, 16);
-    if (vec) PB_LAUNCH("expand_rows_bwd", expand_rows_bwd_kernel<4>, grid, 256, 0, stream, Nf, CVn, gout, cum, gin);
-    else     PB_LAUNCH("expand_rows_bwd", expand_rows_bwd_kernel<1>, grid, 256, 0, stream, Nf, CVn, gout, cum, gin);
+    if (vec) PB_LAUNCH("expand_rows_bwd", expand_rows_bwd_kernel<4>, grid, 256, 0, stream, Nf, NiK, CVn, gout, cum, gin);
+    else     PB_LAUNCH("expand_rows_bwd", expand_rows_bwd_kernel<1>, grid, 256, 0, stream, Nf, NiK, CVn, gout, cum, gin);
     return PB200_OK;
 }
 

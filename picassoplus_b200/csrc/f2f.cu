@@ -69,7 +69,7 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
     cudaStream_t stream = (cudaStream_t)stream_;
     PB_REQUIRE(f2f_sizes_ok(Nf, NiK, Cin, Cout, F), PB200_EINVAL,
                "facet2facet_forward: bad sizes (F must be in 1..50)");
-    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_FFMA, PB200_EINVAL,
+    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_TF32X3, PB200_EINVAL,
                "facet2facet_forward: unknown precision %d", precision);
     if (Nf == 0) return PB200_OK;
     PB_REQUIRE(filter && numInterior && output && (NiK == 0 || (input && bary)), PB200_EINVAL,
@@ -102,7 +102,7 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
     cudaStream_t stream = (cudaStream_t)stream_;
     PB_REQUIRE(f2f_sizes_ok(Nf, NiK, Cin, Cout, F), PB200_EINVAL,
                "facet2facet_backward: bad sizes (F must be in 1..50)");
-    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_FFMA, PB200_EINVAL,
+    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_TF32X3, PB200_EINVAL,
                "facet2facet_backward: unknown precision %d", precision);
     PB_REQUIRE(gradFilter, PB200_EINVAL, "facet2facet_backward: null pointer");
     if (Nf == 0) {

@@ -25,8 +25,7 @@
 // raises the library's asynchronous error word.
 #include "common.cuh"
 #include "tc_ptx.cuh"
-
-#include <mutex>
+#include "tc_runtime.cuh"
 
 namespace pb {
 namespace tc {
@@ -42,34 +41,6 @@ constexpr int FACE_TILE_BYTES = TILE_F * 64;
 constexpr int FILT_TILE_BYTES = UM * 64;
 constexpr int TREG = 4;                     // samples per face whose inputs stay in registers
 constexpr int TMEM_COLS = 256;
-
-// ---- asynchronous error word (pinned, mapped host memory; written by a kernel that gave up)
-static int* g_async_err_host = nullptr;
-static std::mutex g_async_mu;
-
-int* async_error_word() {
-    std::lock_guard<std::mutex> lk(g_async_mu);
-    if (!g_async_err_host) {
-        int* p = nullptr;
-        if (cudaHostAlloc((void**)&p, sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
-            cudaGetLastError();
-            return nullptr;
-        }
-        *p = 0;
-        g_async_err_host = p;
-    }
-    return g_async_err_host;
-}
-
-int check_async_error(const char* where) {
-    int* p = g_async_err_host;
-    if (p && *(volatile int*)p != 0) {
-        set_error("%s: an earlier tensor-core kernel of this library gave up waiting (code %d); results of that "
-                  "call are invalid", where, *(volatile int*)p);
-        return PB200_ECUDA;
-    }
-    return PB200_OK;
-}
 
 // ---- bf16 filter image: Wimg[kb][split][co 0..127][32 bf16, 64B-swizzled], kb = c16*ceil(F/2) + dp,
 //      element (co, j*16 + kk) = filter[co][c16*16 + kk][2*dp + j]  (0 for a basis >= F)
@@ -142,6 +113,8 @@ struct FwdParams {
     const uint8_t* wimg;
     float* out;
     int* async_err;
+    int wait_budget;      // bounded waits give up after this many units of 1024 clocks
+    int silent_filter;    // test switch: the filter stream issues nothing, so every wait runs out
 };
 
 __host__ __device__ inline size_t fwd_stage_bytes(int nsplit) {
@@ -171,7 +144,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(&full[s], PWARPS + 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = p.wait_budget;
         fence_barrier_init();
     }
     if (warp == PWARPS) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
@@ -374,6 +348,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
             for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x) {
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(&empty[s], ph ^ 1u, abort_flag)) { alive = false; break; }
+                    if (p.silent_filter) continue;          // test switch: `full` never completes
                     mbar_arrive_expect_tx(&full[s], bytes);
                     bulk_g2s(stages + (size_t)s * stage_bytes + (size_t)NSPLIT * FACE_TILE_BYTES,
                              p.wimg + (size_t)kb * bytes, bytes, &full[s]);
@@ -442,10 +417,9 @@ bool fwd_supported(int Cin, int Cout, int F) { return Cin % KS == 0 && Cout >= 1
 
 FwdPlan fwd_plan(int Cin, int Cout, int F, int precision) {
     FwdPlan pl;
-    // fp32: bf16 hi+lo operands (three MMAs); tf32: tf32 operands; bf16: bf16 operands
-    static const bool fp32_as_tf32 = getenv("PB200_FP32_TF32_SPLIT") != nullptr;   // the tf32 hi+lo variant of fp32
-    pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
-    pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
+    const OperandMode om = operand_mode(precision);
+    pl.nsplit = om.nsplit;
+    pl.bf = om.bf;
     pl.nkb = (Cin / KS) * (pl.bf ? (F + 1) / 2 : F);
     pl.nstages = pl.nsplit == 2 ? 2 : 4;
     const int FP = ((F + 3) / 4 * 4) | 4;
@@ -485,6 +459,8 @@ int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* inpu
     p.nstages = pl.nstages; p.smaxw = pl.smaxw; p.bpitch = pl.bpitch;
     p.in = input; p.bary = bary; p.cum = cum; p.wimg = wimg; p.out = output;
     p.async_err = async_error_word();
+    p.wait_budget = wait_budget_kclocks();
+    p.silent_filter = test_skip_filter_stream();
     int64_t ntiles = ceil_div(Nf, TILE_F);
     int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
 #define PB_FWD_LAUNCH(NS, BFV)                                                                                      \

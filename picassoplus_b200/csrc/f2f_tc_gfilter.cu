@@ -26,15 +26,13 @@
 // times, and that traffic (about 123 KB per stage) is the floor.
 // At the end the accumulator is drained once into partial[chunk] (final gradFilter layout);
 // a second kernel adds the chunks in order, so the result is deterministic.
-// Modes: 1 split (tf32 operands) or 2 splits (tf32 hi+lo, three MMAs per k-step).
+// Modes: 1 split (bf16 or tf32 operands) or 2 splits (bf16 or tf32 hi+lo, three MMAs per k-step).
 #include "common.cuh"
 #include "tc_ptx.cuh"
+#include "tc_runtime.cuh"
 
 namespace pb {
 namespace tc {
-
-int* async_error_word();
-int check_async_error(const char* where);
 
 namespace gfilter {
 
@@ -164,6 +162,7 @@ struct Params {
     const int32_t* cum;
     float* partial;           // [nchunks][Cout*Cin*F]
     int* async_err;
+    int wait_budget;          // bounded waits give up after this many units of 1024 clocks
 };
 
 template <int NSPLIT, bool BF>
@@ -196,7 +195,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // announces the bulk-copy bytes
         for (int r = 0; r < NRAW; ++r) { mbar_init(&raw_ready[r], 33); mbar_init(&raw_free[r], CWARPS); }
         mbar_init(acc_done, 1);
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = p.wait_budget;
         fence_barrier_init();
     }
     // Pad rows and pad columns of the raw buffers are read (their products are masked) but never
@@ -521,10 +521,9 @@ bool supported(int Cin, int Cout, int F) {
 
 Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     Plan pl;
-    // fp32: bf16 hi+lo operands (three MMAs); tf32: tf32 operands; bf16: bf16 operands
-    static const bool fp32_as_tf32 = getenv("PB200_FP32_TF32_SPLIT") != nullptr;   // the tf32 hi+lo variant of fp32
-    pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
-    pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
+    const OperandMode om = operand_mode(precision);
+    pl.nsplit = om.nsplit;
+    pl.bf = om.bf;
     pl.ncg = Cin / CG;
     int64_t total_stages = ceil_div(Nf > 0 ? Nf : 1, KF);
     int nch = sm_count() / pl.ncg;
@@ -567,6 +566,7 @@ int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, con
     p.gout = gout; p.in = input; p.cum = cum; p.partial = (float*)ws;
     p.bary = bary_p;
     p.async_err = async_error_word();
+    p.wait_budget = wait_budget_kclocks();
     int grid = pl.ncg * pl.nchunks;
 #define PB_GF_LAUNCH(NS, BFV)                                                                                       \
     do {                                                                                                              \

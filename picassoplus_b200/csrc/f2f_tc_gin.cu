@@ -20,12 +20,10 @@
 // All waits are bounded; on a time-out the block unwinds and raises the async error word.
 #include "common.cuh"
 #include "tc_ptx.cuh"
+#include "tc_runtime.cuh"
 
 namespace pb {
 namespace tc {
-
-int* async_error_word();
-int check_async_error(const char* where);
 
 namespace gin {
 
@@ -169,6 +167,7 @@ struct Params {
     const uint8_t* wimg;
     float* gin;
     int* async_err;
+    int wait_budget;                 // bounded waits give up after this many units of 1024 clocks
 };
 
 // BF: operands as bf16 (a 64-byte operand row holds 32 output channels, MMAs of kind::f16 at
@@ -204,7 +203,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
         for (int b = 0; b < 2; ++b) { mbar_init(&g_full[b], GWARPS); mbar_init(&g_empty[b], 1); }
         mbar_init(b_ready, EWARPS);
         mbar_init(b_free, EWARPS);
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = p.wait_budget;
         fence_barrier_init();
     }
     if (warp == EWARPS) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
@@ -592,10 +592,9 @@ bool supported(int Cin, int Cout, int F) {
 
 Plan plan(int Cin, int Cout, int F, int precision) {
     Plan pl;
-    // fp32: bf16 hi+lo operands (three MMAs); tf32: tf32 operands; bf16: bf16 operands
-    static const bool fp32_as_tf32 = getenv("PB200_FP32_TF32_SPLIT") != nullptr;   // the tf32 hi+lo variant of fp32
-    pl.nsplit = precision == PB200_PREC_FP32 ? 2 : 1;
-    pl.bf = (precision == PB200_PREC_BF16 || (precision == PB200_PREC_FP32 && !fp32_as_tf32)) ? 1 : 0;
+    const OperandMode om = operand_mode(precision);
+    pl.nsplit = om.nsplit;
+    pl.bf = om.bf;
     pl.nq = NCOLS / F;
     if (pl.nq > Cin) pl.nq = Cin;
     pl.nslices = (Cin + pl.nq - 1) / pl.nq;
@@ -670,6 +669,7 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
     p.nstages = pl.nstages; p.gbufs = pl.gbufs; p.bary_rows = pl.bary_rows; p.bpitch = pl.bpitch;
     p.gout = gout; p.bary = bary; p.bary_p = bary_p; p.Fp = Fp; p.cum = cum; p.wimg = wimg; p.gin = gin;
     p.async_err = async_error_word();
+    p.wait_budget = wait_budget_kclocks();
     int64_t ntiles = ceil_div(Nf, TILE_M);
     int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
     if (pl.bf) return pl.nsplit == 2 ? launch_f<2, true>(F, p, grid, pl.smem, stream) : launch_f<1, true>(F, p, grid, pl.smem, stream);

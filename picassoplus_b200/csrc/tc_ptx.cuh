@@ -36,8 +36,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// about one second at 2 GHz; far above any legitimate wait of these kernels
-constexpr long long WAIT_CLOCK_BUDGET = 2000000000LL;
+// Default wait budget in units of 1024 clocks: about one second at 2 GHz, far above any
+// legitimate wait of these kernels.  A block keeps two ints in shared memory: abort_flag[0]
+// is the flag, abort_flag[1] the budget (set once by thread 0 before the first wait).
+constexpr int WAIT_BUDGET_KCLOCKS = 2000000;
 
 // Bounded wait on one phase of an mbarrier.  Returns false (and raises *abort_flag) on
 // time-out, or as soon as another thread of the block has raised the flag.
@@ -50,8 +52,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         __nanosleep(i < 8 ? 20 : 100);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 63u) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_CLOCK_BUDGET) { *abort_flag = 1; return false; }
+            if (abort_flag[0]) return false;
+            if (((clock64() - t0) >> 10) > (long long)abort_flag[1]) { abort_flag[0] = 1; return false; }
         }
     }
 }

@@ -1,26 +1,44 @@
 """Per-topology device structures shared by the operators: the vertex -> (face, corner)
-CSR and its cache.
+CSR, its cache, and the validation of index arrays.
 
 A level's `face` / `vtMap` tensors are reused by every convolution of that level (4 to 16
 operator calls per step in the reference's encoder blocks,
 picasso/networks/pi2_blocks.py:88-92), so the CSR is built once per (face, vtMap) pair
-and looked up afterwards.  Cache entries hold a reference to the index tensors they were
-built from, so the memory behind a cached key cannot be recycled while the entry lives;
-an in-place edit of an index tensor bumps its version counter and misses the cache.
+and looked up afterwards.
+
+Cache policy.  A slot is named by the storage of the index tensors (device, data pointer,
+length); the slot remembers the tensors' version counters.  A lookup whose versions differ
+(the tensors were overwritten in place, as a streaming loader does with its device buffers)
+rebuilds the CSR and REPLACES the slot, so stale entries never pile up.  Slots hold a
+reference to their index tensors, so the memory behind a key cannot be recycled while the
+slot lives.  The cache is bounded by bytes (`set_cache_budget`, default 2 GiB of CSR arrays
+per process) and evicts least-recently-used slots; `set_cache_budget(0)` turns it off.
+Callers that manage topologies themselves can pass a prebuilt `VertexCSR` to the operator
+wrappers (`csr=`) and skip the cache altogether.
+
+Validation.  Building a CSR validates every index of `face` / `vtMap` on the device.  In the
+default mode the status word is read back right after the build (ONE device synchronisation
+per cache miss, which also answers whether `vtMap` is the identity) and a bad index raises
+RuntimeError.  `set_validation("deferred")` removes that synchronisation: status words are
+kept and `check_deferred()` reads them all at a point where the caller synchronises anyway
+(the end of a step).  Bad indices are never dereferenced in either mode.
 """
 from __future__ import annotations
 
 import threading
 from collections import OrderedDict
-from typing import Optional
+from typing import List, Optional
 
 import torch
 
 from . import _lib
 
-_CACHE_CAPACITY = 32
+_budget_bytes = 2 << 30
 _cache: "OrderedDict[tuple, VertexCSR]" = OrderedDict()
+_cache_bytes = 0
 _lock = threading.Lock()
+_validation = "sync"
+_deferred: List[tuple] = []          # (status tensor, message)
 
 
 def stream_ptr(device) -> int:
@@ -31,64 +49,174 @@ def ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+def set_cache_budget(nbytes: int) -> None:
+    """Upper bound on the bytes of CSR arrays the cache keeps (0 = no caching)."""
+    global _budget_bytes
+    with _lock:
+        _budget_bytes = int(nbytes)
+        _evict_locked()
+
+
+def set_validation(mode: str) -> None:
+    """'sync' (default): raise on a bad index at build time, one device sync per cache miss.
+    'deferred': no sync; call check_deferred() after the step's own synchronisation."""
+    global _validation
+    if mode not in ("sync", "deferred"):
+        raise ValueError(mode)
+    _validation = mode
+
+
+def check_deferred() -> None:
+    """Reads every status word collected in deferred mode (synchronises); raises RuntimeError
+    for the first bad one."""
+    with _lock:
+        items = list(_deferred)
+        _deferred.clear()
+    if not items:
+        return
+    codes = torch.stack([s.reshape(-1)[0] for s, _ in items]).tolist()
+    for code, (_, msg) in zip(codes, items):
+        if code != 0:
+            raise RuntimeError(msg)
+
+
 class VertexCSR:
     """rowptr (NvOut+1,), entries (3*Nf,) int32: row v lists (f << 2 | corner) ascending."""
 
-    def __init__(self, rowptr, entries, keep):
+    def __init__(self, rowptr, entries, keep, versions=None, shared=False):
         self.rowptr = rowptr
         self.entries = entries
         self._keep = keep
+        self._versions = versions
+        self.nbytes = 0 if shared else rowptr.numel() * 4 + entries.numel() * 4
 
 
-def _key(face, vt_map, nv_in, nv_out):
-    vk = None if vt_map is None else (vt_map.data_ptr(), vt_map._version, vt_map.shape[0])
-    return (face.device.index, face.data_ptr(), face._version, face.shape[0], vk, int(nv_in), int(nv_out))
+def _slot(face, vt_map, nv_in, nv_out):
+    vk = None if vt_map is None else (vt_map.data_ptr(), vt_map.shape[0])
+    return (face.device.index, face.data_ptr(), face.shape[0], vk, int(nv_in), int(nv_out))
+
+
+def _versions(face, vt_map):
+    return (face._version, None if vt_map is None else vt_map._version)
+
+
+def _evict_locked():
+    global _cache_bytes
+    while _cache and _cache_bytes > _budget_bytes:
+        _, old = _cache.popitem(last=False)
+        _cache_bytes -= old.nbytes
+
+
+def _launch_build(face, vt_map, nv_in, nv_out):
+    dev = face.device
+    nf = face.shape[0]
+    rowptr = torch.empty(nv_out + 1, dtype=torch.int32, device=dev)
+    entries = torch.empty(max(3 * nf, 1), dtype=torch.int32, device=dev)
+    status = torch.empty(1, dtype=torch.int32, device=dev)
+    wbytes = _lib.query("pb200_vertex_csr_workspace_bytes", nf, nv_out)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+    _lib.call("pb200_build_vertex_csr", nf, nv_in, nv_out, ptr(face), ptr(vt_map), ptr(rowptr),
+              ptr(entries), ptr(status), ptr(ws), wbytes, stream_ptr(dev))
+    return rowptr, entries, status
+
+
+def _bad_index_message(nv_in, nv_out):
+    return f"face / vtMap hold an index outside the vertex range (NvIn={nv_in}, NvOut={nv_out})"
 
 
 def build_vertex_csr(face: torch.Tensor, vt_map: Optional[torch.Tensor], nv_in: int, nv_out: int) -> VertexCSR:
-    """Uncached build; validates every index and raises RuntimeError on an out-of-range one
-    (one device synchronisation per topology)."""
-    dev = face.device
-    nf = face.shape[0]
-    with torch.cuda.device(dev):
-        rowptr = torch.empty(nv_out + 1, dtype=torch.int32, device=dev)
-        entries = torch.empty(max(3 * nf, 1), dtype=torch.int32, device=dev)
-        status = torch.empty(1, dtype=torch.int32, device=dev)
-        wbytes = _lib.query("pb200_vertex_csr_workspace_bytes", nf, nv_out)
-        ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
-        _lib.call("pb200_build_vertex_csr", nf, nv_in, nv_out, ptr(face), ptr(vt_map), ptr(rowptr),
-                  ptr(entries), ptr(status), ptr(ws), wbytes, stream_ptr(dev))
-        code = int(status.item())
-    if code != 0:
-        raise RuntimeError("face / vtMap hold an index outside the vertex range "
-                           f"(NvIn={nv_in}, NvOut={nv_out})")
-    return VertexCSR(rowptr, entries, (face, vt_map))
+    """Uncached build.  Validates every index: in 'sync' mode a bad one raises RuntimeError here
+    (one device synchronisation), in 'deferred' mode at the next check_deferred()."""
+    with torch.cuda.device(face.device):
+        rowptr, entries, status = _launch_build(face, vt_map, nv_in, nv_out)
+        if _validation == "deferred":
+            with _lock:
+                _deferred.append((status, _bad_index_message(nv_in, nv_out)))
+        elif int(status.item()) != 0:
+            raise RuntimeError(_bad_index_message(nv_in, nv_out))
+    return VertexCSR(rowptr, entries, (face, vt_map), _versions(face, vt_map))
+
+
+def _lookup(slot, versions):
+    with _lock:
+        hit = _cache.get(slot)
+        if hit is not None and hit._versions == versions:
+            _cache.move_to_end(slot)
+            return hit
+    return None
+
+
+def _store(slot, csr):
+    global _cache_bytes
+    with _lock:
+        old = _cache.pop(slot, None)
+        if old is not None:
+            _cache_bytes -= old.nbytes
+        if _budget_bytes > 0:
+            _cache[slot] = csr
+            _cache_bytes += csr.nbytes
+            _evict_locked()
 
 
 def vertex_csr(face: torch.Tensor, vt_map: Optional[torch.Tensor], nv_in: int, nv_out: int) -> VertexCSR:
     """Cached CSR keyed by output vertex vo = vtMap[face[f][j]] (identity when vt_map is None).
-    An identity vtMap over nv_in == nv_out vertices shares the entry of vt_map=None."""
-    key = _key(face, vt_map, nv_in, nv_out)
-    with _lock:
-        hit = _cache.get(key)
-        if hit is not None:
-            _cache.move_to_end(key)
-            return hit
+    In 'sync' mode an identity vtMap over nv_in == nv_out vertices shares the arrays of
+    vt_map=None (the identity test rides on the build's one synchronisation); in 'deferred'
+    mode nothing is read back and the CSR is built from vtMap as given."""
+    slot = _slot(face, vt_map, nv_in, nv_out)
+    versions = _versions(face, vt_map)
+    hit = _lookup(slot, versions)
+    if hit is not None:
+        return hit
     csr = None
-    if vt_map is not None and nv_in == nv_out and vt_map.shape[0] == nv_in:
-        ident = torch.arange(nv_in, dtype=vt_map.dtype, device=vt_map.device)
-        if bool(torch.equal(vt_map, ident)):
-            base = vertex_csr(face, None, nv_in, nv_out)
-            csr = VertexCSR(base.rowptr, base.entries, (face, vt_map))
+    may_be_identity = vt_map is not None and nv_in == nv_out and vt_map.shape[0] == nv_in
+    if may_be_identity and _validation == "sync":
+        base_slot = _slot(face, None, nv_in, nv_out)
+        base = _lookup(base_slot, _versions(face, None))
+        with torch.cuda.device(face.device):
+            ident = (vt_map == torch.arange(nv_in, dtype=vt_map.dtype, device=vt_map.device)).all().to(torch.int32)
+            if base is None:
+                # build the identity CSR and test vtMap in the same synchronisation
+                rowptr, entries, status = _launch_build(face, None, nv_in, nv_out)
+                code, is_ident = torch.stack([status[0], ident]).tolist()
+                if code != 0:
+                    raise RuntimeError(_bad_index_message(nv_in, nv_out))
+                base = VertexCSR(rowptr, entries, (face, None), _versions(face, None))
+                _store(base_slot, base)
+            else:
+                is_ident = int(ident.item())
+        if is_ident:
+            csr = VertexCSR(base.rowptr, base.entries, (face, vt_map), versions, shared=True)
     if csr is None:
         csr = build_vertex_csr(face, vt_map, nv_in, nv_out)
-    with _lock:
-        _cache[key] = csr
-        while len(_cache) > _CACHE_CAPACITY:
-            _cache.popitem(last=False)
+    _store(slot, csr)
     return csr
 
 
+def check_num_interior(num_interior: torch.Tensor, nik: int) -> None:
+    """Validates a running sample count (non-decreasing, inside [0, nik], ends at nik) on the
+    device: raises in 'sync' mode, queues the status word in 'deferred' mode.  The facet2facet
+    kernels trust numInterior as the reference does; run this once per array."""
+    dev = num_interior.device
+    with torch.cuda.device(dev):
+        status = torch.empty(1, dtype=torch.int32, device=dev)
+        _lib.call("pb200_check_num_interior", num_interior.shape[0], int(nik), ptr(num_interior), ptr(status),
+                  stream_ptr(dev))
+        msg = f"numInterior is not a running count that ends at NiK={nik}"
+        if _validation == "deferred":
+            with _lock:
+                _deferred.append((status, msg))
+        elif int(status.item()) != 0:
+            raise RuntimeError(msg)
+
+
+def cache_stats():
+    with _lock:
+        return {"slots": len(_cache), "bytes": _cache_bytes, "budget": _budget_bytes}
+
+
 def clear_cache() -> None:
+    global _cache_bytes
     with _lock:
         _cache.clear()
+        _cache_bytes = 0

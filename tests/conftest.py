@@ -24,14 +24,14 @@ def pytest_collection_modifyitems(config, items):
 
 def rel_err(a, b):
     """max|a-b| / max|b| per tensor: the gate of the fp32 parity tests."""
-    a = torch.as_tensor(a).double().cpu()
-    b = torch.as_tensor(b).double().cpu()
+    a = torch.as_tensor(a).detach().double().cpu()
+    b = torch.as_tensor(b).detach().double().cpu()
     if b.numel() == 0:
         return 0.0
     return float((a - b).abs().max() / (b.abs().max() + 1e-30))
 
 
 def max_abs(a, b):
-    a = torch.as_tensor(a).double().cpu()
-    b = torch.as_tensor(b).double().cpu()
+    a = torch.as_tensor(a).detach().double().cpu()
+    b = torch.as_tensor(b).detach().double().cpu()
     return float((a - b).abs().max()) if b.numel() else 0.0
