@@ -217,6 +217,51 @@ int pb200_sph_harm_coeff(int64_t N, int L, const float* xyz, float* out, void* s
 int pb200_triangle_geometry(int64_t Nf, int64_t Nv, int vstride, const float* vertex,
                             const int32_t* face, float* geometry, void* stream);
 
+/* ---- mesh pooling / unpooling over decimation clusters ------------------------------------
+ * Cluster encoding of the fine level (picasso/mesh/pi_modules/decimate.py:23-28): vtReplace[v] < 0
+ * names the representative -vtReplace[v] that v was contracted into; a representative holds its
+ * cluster size minus one; vtMap[representative] is the coarse vertex id, vtMap of every other
+ * vertex is -1.
+ *
+ * pb200_build_cluster_csr turns the encoding into the two structures the kernels pull through:
+ * key[v] = coarse id of the cluster of fine vertex v (or -1), and a CSR coarse vertex -> member
+ * fine vertices in ascending order (rowptr NvOut+1 ints, members NvIn ints).  `status` is set to 0
+ * or PB200_EINDEX (a representative outside [0,NvIn) or a vtMap value outside [-1,NvOut); such
+ * vertices get key -1 and are never dereferenced).  The reference has no such structure: it
+ * scatters with compare-and-swap / float atomics (mesh_pool3d_gpu.cu:6-17,62,130; mesh_unpool3d_gpu.cu:43). */
+size_t pb200_cluster_csr_workspace_bytes(int64_t NvIn, int64_t NvOut);
+int pb200_build_cluster_csr(int64_t NvIn, int64_t NvOut, const int32_t* vtReplace, const int32_t* vtMap,
+                            int32_t* key, int32_t* rowptr, int32_t* members, int32_t* status,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* output[vo,c] = max over the members v of cluster vo of input[v,c]; maxIndex[vo,c] = the member that
+ * attains it (the smallest id among ties; the reference leaves ties to its thread order).  Replaces
+ * maxPool3dLauncher (mesh_pool3d_gpu.cu:20-88,162-169; binding mesh_pool3d.cpp MeshMaxPool3d).
+ * input (NvIn,C), output (NvOut,C), maxIndex (NvOut,C) int32. */
+int pb200_mesh_max_pool_forward(int64_t NvIn, int64_t NvOut, int C, const float* input, const int32_t* rowptr,
+                                const int32_t* members, float* output, int32_t* maxIndex, void* stream);
+/* gradInput = 0 except gradInput[maxIndex[vo,c], c] = gradOutput[vo,c].  Replaces maxPool3dGradLauncher
+ * (mesh_pool3d_gpu.cu:93-105,171-177; binding MeshMaxPool3dGrad). */
+int pb200_mesh_max_pool_backward(int64_t NvIn, int64_t NvOut, int C, const int32_t* maxIndex, const float* gradOutput,
+                                 float* gradInput, void* stream);
+/* output[vo,c] = sum over members of input[v,c] / (vtReplace[representative] + 1).  Replaces
+ * avgPool3dLauncher (mesh_pool3d_gpu.cu:112-132,179-185; binding MeshAvgPool3d). */
+int pb200_mesh_avg_pool_forward(int64_t NvIn, int64_t NvOut, int C, const float* input, const int32_t* vtReplace,
+                                const int32_t* rowptr, const int32_t* members, float* output, void* stream);
+/* gradInput[v,c] = gradOutput[key[v],c] / count for cluster members, 0 elsewhere.  Replaces
+ * avgPool3dGradLauncher (mesh_pool3d_gpu.cu:138-158,187-193; binding MeshAvgPool3dGrad). */
+int pb200_mesh_avg_pool_backward(int64_t NvIn, int64_t NvOut, int C, const float* gradOutput, const int32_t* vtReplace,
+                                 const int32_t* key, float* gradInput, void* stream);
+/* Interpolation coarse -> fine: output[v,c] = input[key[v],c] for every fine vertex of a cluster, 0
+ * elsewhere; key / rowptr / members are the fine level's cluster structures.  Replaces
+ * interpolateLauncher (mesh_unpool3d_gpu.cu:5-26,49-55; binding mesh_unpool3d.cpp MeshInterpolate). */
+int pb200_mesh_unpool_forward(int64_t NvCoarse, int64_t NvFine, int C, const float* input, const int32_t* key,
+                              float* output, void* stream);
+/* gradInput[vo,c] = sum over the members v of cluster vo of gradOutput[v,c], ascending v.  Replaces
+ * interpolateGradLauncher (mesh_unpool3d_gpu.cu:29-46,57-63; binding MeshInterpolateGrad). */
+int pb200_mesh_unpool_backward(int64_t NvCoarse, int64_t NvFine, int C, const float* gradOutput, const int32_t* rowptr,
+                               const int32_t* members, float* gradInput, void* stream);
+
 /* ---- row expansion (benchmark block glue) ----------------------------------------------
  * forward:  out[k,:] = in[f,:] for every sample k of face f (numInterior as above);
  * backward: gradIn[f,:] = sum over the samples k of f of gradOut[k,:] (fixed order).

@@ -28,6 +28,9 @@ def lib():
     return _LIB
 
 
+C_int = C.c_int
+
+
 def _p(a):
     return a.ctypes.data_as(C.c_void_p)
 
@@ -131,3 +134,51 @@ def triangle_geometry(vertex, face):
     out = np.zeros((face.shape[0], 5), np.float32)
     lib().oracle_triangle_geometry(C.c_int(face.shape[0]), C.c_int(vertex.shape[1]), _p(vertex), _p(face), _p(out))
     return out
+
+
+def max_pool_forward(inp, vt_replace, vt_map, nv_out):
+    inp, vt_replace, vt_map = _f32(inp), _i32(vt_replace), _i32(vt_map)
+    C = inp.shape[1]
+    out, idx = np.zeros((nv_out, C), np.float32), np.zeros((nv_out, C), np.int32)
+    lib().oracle_max_pool_forward(C_int(inp.shape[0]), C_int(nv_out), C_int(C), _p(vt_replace), _p(vt_map), _p(inp),
+                                  _p(out), _p(idx))
+    return out, idx
+
+
+def max_pool_backward(gout, nv_in, max_index):
+    gout, max_index = _f32(gout), _i32(max_index)
+    gin = np.zeros((nv_in, gout.shape[1]), np.float32)
+    lib().oracle_max_pool_backward(C_int(nv_in), C_int(gout.shape[0]), C_int(gout.shape[1]), _p(max_index), _p(gout),
+                                   _p(gin))
+    return gin
+
+
+def avg_pool_forward(inp, vt_replace, vt_map, nv_out):
+    inp, vt_replace, vt_map = _f32(inp), _i32(vt_replace), _i32(vt_map)
+    out = np.zeros((nv_out, inp.shape[1]), np.float32)
+    lib().oracle_avg_pool_forward(C_int(inp.shape[0]), C_int(nv_out), C_int(inp.shape[1]), _p(vt_replace), _p(vt_map),
+                                  _p(inp), _p(out))
+    return out
+
+
+def avg_pool_backward(gout, vt_replace, vt_map):
+    gout, vt_replace, vt_map = _f32(gout), _i32(vt_replace), _i32(vt_map)
+    gin = np.zeros((vt_replace.shape[0], gout.shape[1]), np.float32)
+    lib().oracle_avg_pool_backward(C_int(vt_replace.shape[0]), C_int(gout.shape[1]), _p(vt_replace), _p(vt_map),
+                                   _p(gout), _p(gin))
+    return gin
+
+
+def unpool_forward(inp, vt_replace, vt_map):
+    inp, vt_replace, vt_map = _f32(inp), _i32(vt_replace), _i32(vt_map)
+    out = np.zeros((vt_map.shape[0], inp.shape[1]), np.float32)
+    lib().oracle_unpool_forward(C_int(vt_map.shape[0]), C_int(inp.shape[1]), _p(vt_replace), _p(vt_map), _p(inp), _p(out))
+    return out
+
+
+def unpool_backward(gout, nv_coarse, vt_replace, vt_map):
+    gout, vt_replace, vt_map = _f32(gout), _i32(vt_replace), _i32(vt_map)
+    gin = np.zeros((nv_coarse, gout.shape[1]), np.float32)
+    lib().oracle_unpool_backward(C_int(vt_map.shape[0]), C_int(nv_coarse), C_int(gout.shape[1]), _p(vt_replace),
+                                 _p(vt_map), _p(gout), _p(gin))
+    return gin

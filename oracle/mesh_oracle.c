@@ -229,3 +229,88 @@ void oracle_triangle_geometry(int Nf, int vstride, const float* vertex, const in
     }
 }
 #endif
+
+/* ---- mesh pool / unpool.  mapid = -vtReplace[v] for a contracted vertex, else v; the cluster's
+ * coarse id is vtMap[mapid] (picasso/mesh/pi_modules/source/mesh_pool3d_gpu.cu:49-58). */
+#ifndef ORACLE_ACC_DOUBLE
+static int cluster_of(int v, const int32_t* vtReplace, const int32_t* vtMap) {
+    int mapid = vtReplace[v] < 0 ? -vtReplace[v] : v;
+    return vtMap[mapid];
+}
+
+/* mesh_pool3d_gpu.cu:20-88 (init, forward, index); the argmax is the smallest member id */
+void oracle_max_pool_forward(int nvIn, int nvOut, int C, const int32_t* vtReplace, const int32_t* vtMap,
+                             const float* in, float* out, int32_t* maxIndex) {
+    memset(out, 0, sizeof(float) * (size_t)nvOut * C);
+    memset(maxIndex, 0, sizeof(int32_t) * (size_t)nvOut * C);
+    for (int v = 0; v < nvIn; ++v)
+        if (vtMap[v] >= 0)
+            for (int c = 0; c < C; ++c) out[(int64_t)vtMap[v] * C + c] = in[(int64_t)v * C + c];
+    for (int v = 0; v < nvIn; ++v) {
+        int vo = cluster_of(v, vtReplace, vtMap);
+        if (vo < 0) continue;
+        for (int c = 0; c < C; ++c) out[(int64_t)vo * C + c] = fmaxf(out[(int64_t)vo * C + c], in[(int64_t)v * C + c]);
+    }
+    for (int v = nvIn - 1; v >= 0; --v) {          /* descending: the smallest id is written last */
+        int vo = cluster_of(v, vtReplace, vtMap);
+        if (vo < 0) continue;
+        for (int c = 0; c < C; ++c)
+            if (fabsf(in[(int64_t)v * C + c] - out[(int64_t)vo * C + c]) < 1e-16F) maxIndex[(int64_t)vo * C + c] = v;
+    }
+}
+
+/* mesh_pool3d_gpu.cu:93-105 */
+void oracle_max_pool_backward(int nvIn, int nvOut, int C, const int32_t* maxIndex, const float* gout, float* gin) {
+    memset(gin, 0, sizeof(float) * (size_t)nvIn * C);
+    for (int vo = 0; vo < nvOut; ++vo)
+        for (int c = 0; c < C; ++c) gin[(int64_t)maxIndex[(int64_t)vo * C + c] * C + c] = gout[(int64_t)vo * C + c];
+}
+
+/* mesh_pool3d_gpu.cu:112-132 */
+void oracle_avg_pool_forward(int nvIn, int nvOut, int C, const int32_t* vtReplace, const int32_t* vtMap,
+                             const float* in, float* out) {
+    memset(out, 0, sizeof(float) * (size_t)nvOut * C);
+    for (int v = 0; v < nvIn; ++v) {
+        int mapid = vtReplace[v] < 0 ? -vtReplace[v] : v;
+        int vo = vtMap[mapid];
+        if (vo < 0) continue;
+        int count = vtReplace[mapid] + 1;
+        for (int c = 0; c < C; ++c) out[(int64_t)vo * C + c] += in[(int64_t)v * C + c] / count;
+    }
+}
+
+/* mesh_pool3d_gpu.cu:138-158 */
+void oracle_avg_pool_backward(int nvIn, int C, const int32_t* vtReplace, const int32_t* vtMap, const float* gout,
+                              float* gin) {
+    memset(gin, 0, sizeof(float) * (size_t)nvIn * C);
+    for (int v = 0; v < nvIn; ++v) {
+        int mapid = vtReplace[v] < 0 ? -vtReplace[v] : v;
+        int vo = vtMap[mapid];
+        if (vo < 0) continue;
+        int count = vtReplace[mapid] + 1;
+        for (int c = 0; c < C; ++c) gin[(int64_t)v * C + c] = gout[(int64_t)vo * C + c] / count;
+    }
+}
+
+/* mesh_unpool3d_gpu.cu:5-26 */
+void oracle_unpool_forward(int nvFine, int C, const int32_t* vtReplace, const int32_t* vtMap, const float* in,
+                           float* out) {
+    memset(out, 0, sizeof(float) * (size_t)nvFine * C);
+    for (int v = 0; v < nvFine; ++v) {
+        int vi = cluster_of(v, vtReplace, vtMap);
+        if (vi < 0) continue;
+        for (int c = 0; c < C; ++c) out[(int64_t)v * C + c] = in[(int64_t)vi * C + c];
+    }
+}
+
+/* mesh_unpool3d_gpu.cu:29-46 */
+void oracle_unpool_backward(int nvFine, int nvCoarse, int C, const int32_t* vtReplace, const int32_t* vtMap,
+                            const float* gout, float* gin) {
+    memset(gin, 0, sizeof(float) * (size_t)nvCoarse * C);
+    for (int v = 0; v < nvFine; ++v) {
+        int vi = cluster_of(v, vtReplace, vtMap);
+        if (vi < 0) continue;
+        for (int c = 0; c < C; ++c) gin[(int64_t)vi * C + c] += gout[(int64_t)v * C + c];
+    }
+}
+#endif

@@ -282,6 +282,87 @@ def facet2facet_backward(gout, inp, filt, bary, cum, chunk=8192):
     return gin, gf
 
 
+# ----------------------------------------------------------------- mesh pool / unpool
+def _cluster_key(vt_replace, vt_map):
+    """Coarse id of every fine vertex, -1 outside every cluster (the index arithmetic shared by all
+    kernels of mesh_pool3d_gpu.cu and mesh_unpool3d_gpu.cu: mapid = -vtReplace[v] for a contracted
+    vertex, else v; the cluster's coarse id is vtMap[mapid])."""
+    v = torch.arange(vt_replace.shape[0], device=vt_replace.device)
+    rep = vt_replace.to(torch.long)
+    mapid = torch.where(rep < 0, -rep, v)
+    return vt_map.to(torch.long)[mapid], mapid
+
+
+def mesh_max_pool_forward(inp, vt_replace, vt_map, nv_out):
+    """mesh_pool3d_gpu.cu:20-88: output[vo] = max over the cluster's members; maxIndex = a member that
+    attains it (the smallest id here; the reference takes whichever thread wrote last)."""
+    key, _ = _cluster_key(vt_replace, vt_map)
+    C = inp.shape[1]
+    out = torch.zeros(nv_out, C, dtype=inp.dtype, device=inp.device)
+    idx = torch.zeros(nv_out, C, dtype=torch.int32, device=inp.device)
+    ok = key >= 0
+    members = torch.nonzero(ok).flatten()
+    if members.numel():
+        k = key[members]
+        out_m = torch.full((nv_out, C), -float("inf"), dtype=inp.dtype, device=inp.device)
+        out_m.scatter_reduce_(0, k.unsqueeze(1).expand(-1, C), inp[members], reduce="amax")
+        hit = inp[members] == out_m[k]
+        cand = torch.where(hit, members.unsqueeze(1).expand(-1, C), torch.full_like(hit, 2 ** 31 - 1, dtype=torch.long))
+        first = torch.full((nv_out, C), 2 ** 31 - 1, dtype=torch.long, device=inp.device)
+        first.scatter_reduce_(0, k.unsqueeze(1).expand(-1, C), cand, reduce="amin")
+        has = torch.zeros(nv_out, dtype=torch.bool, device=inp.device)
+        has[k] = True
+        out[has] = out_m[has]
+        idx[has] = first[has].to(torch.int32)
+    return out, idx
+
+
+def mesh_max_pool_backward(gout, nv_in, max_index):
+    """mesh_pool3d_gpu.cu:93-105: gradInput[maxIndex[vo,c], c] = gradOutput[vo,c], zero elsewhere."""
+    C = gout.shape[1]
+    gin = torch.zeros(nv_in, C, dtype=gout.dtype, device=gout.device)
+    gin.scatter_(0, max_index.to(torch.long), gout)
+    return gin
+
+
+def mesh_avg_pool_forward(inp, vt_replace, vt_map, nv_out):
+    """mesh_pool3d_gpu.cu:112-132: output[vo] += input[v] / (vtReplace[mapid] + 1)."""
+    key, mapid = _cluster_key(vt_replace, vt_map)
+    count = (vt_replace.to(torch.long)[mapid] + 1).to(inp.dtype)
+    out = torch.zeros(nv_out, inp.shape[1], dtype=inp.dtype, device=inp.device)
+    ok = key >= 0
+    out.index_add_(0, key[ok], inp[ok] / count[ok].unsqueeze(1))
+    return out
+
+
+def mesh_avg_pool_backward(gout, vt_replace, vt_map):
+    """mesh_pool3d_gpu.cu:138-158: gradInput[v] = gradOutput[vo] / count for cluster members."""
+    key, mapid = _cluster_key(vt_replace, vt_map)
+    count = (vt_replace.to(torch.long)[mapid] + 1).to(gout.dtype)
+    gin = torch.zeros(vt_replace.shape[0], gout.shape[1], dtype=gout.dtype, device=gout.device)
+    ok = key >= 0
+    gin[ok] = gout[key[ok]] / count[ok].unsqueeze(1)
+    return gin
+
+
+def mesh_unpool_forward(inp, vt_replace, vt_map):
+    """mesh_unpool3d_gpu.cu:5-26: output[v] = input[vtMap[mapid]] for every fine vertex of a cluster."""
+    key, _ = _cluster_key(vt_replace, vt_map)
+    out = torch.zeros(vt_map.shape[0], inp.shape[1], dtype=inp.dtype, device=inp.device)
+    ok = key >= 0
+    out[ok] = inp[key[ok]]
+    return out
+
+
+def mesh_unpool_backward(gout, nv_coarse, vt_replace, vt_map):
+    """mesh_unpool3d_gpu.cu:29-46: gradInput[vtMap[mapid]] += gradOutput[v]."""
+    key, _ = _cluster_key(vt_replace, vt_map)
+    gin = torch.zeros(nv_coarse, gout.shape[1], dtype=gout.dtype, device=gout.device)
+    ok = key >= 0
+    gin.index_add_(0, key[ok], gout[ok])
+    return gin
+
+
 # ------------------------------------------------------------- autograd wrappers (CPU)
 class _V2F(torch.autograd.Function):
     @staticmethod

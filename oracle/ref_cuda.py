@@ -103,3 +103,54 @@ def count_vertex_adjface(face, vt_map, nv_out):
     out = torch.zeros(nv_out, dtype=torch.int32, device=face.device)
     _chk(lib().ref_count_vertex_adjface(face.shape[0], _p(face), _p(vt_map), _p(out)))
     return out
+
+
+# ---- mesh pool / unpool (mesh_pool3d_gpu.cu, mesh_unpool3d_gpu.cu); output allocation as the
+# bindings do it (mesh_pool3d.cpp, mesh_unpool3d.cpp: zero-initialised)
+def max_pool_forward(inp, vt_replace, vt_map, nv_out):
+    _sync_in()
+    C = inp.shape[1]
+    out = torch.zeros(nv_out, C, dtype=inp.dtype, device=inp.device)
+    idx = torch.zeros(nv_out, C, dtype=torch.int32, device=inp.device)
+    _chk(lib().ref_max_pool_forward(inp.shape[0], C, _p(vt_replace), _p(vt_map), _p(inp), _p(out), _p(idx)))
+    return out, idx
+
+
+def max_pool_backward(gout, nv_in, max_index):
+    _sync_in()
+    C = gout.shape[1]
+    gin = torch.zeros(nv_in, C, dtype=gout.dtype, device=gout.device)
+    _chk(lib().ref_max_pool_backward(gout.shape[0], C, _p(max_index), _p(gout), _p(gin)))
+    return gin
+
+
+def avg_pool_forward(inp, vt_replace, vt_map, nv_out):
+    _sync_in()
+    C = inp.shape[1]
+    out = torch.zeros(nv_out, C, dtype=inp.dtype, device=inp.device)
+    _chk(lib().ref_avg_pool_forward(inp.shape[0], C, _p(vt_replace), _p(vt_map), _p(inp), _p(out)))
+    return out
+
+
+def avg_pool_backward(gout, vt_replace, vt_map):
+    _sync_in()
+    C = gout.shape[1]
+    gin = torch.zeros(vt_replace.shape[0], C, dtype=gout.dtype, device=gout.device)
+    _chk(lib().ref_avg_pool_backward(vt_replace.shape[0], C, _p(vt_replace), _p(vt_map), _p(gout), _p(gin)))
+    return gin
+
+
+def unpool_forward(inp, vt_replace, vt_map):
+    _sync_in()
+    C = inp.shape[1]
+    out = torch.zeros(vt_map.shape[0], C, dtype=inp.dtype, device=inp.device)
+    _chk(lib().ref_unpool_forward(inp.shape[0], C, vt_map.shape[0], _p(vt_replace), _p(vt_map), _p(inp), _p(out)))
+    return out
+
+
+def unpool_backward(gout, nv_coarse, vt_replace, vt_map):
+    _sync_in()
+    C = gout.shape[1]
+    gin = torch.zeros(nv_coarse, C, dtype=gout.dtype, device=gout.device)
+    _chk(lib().ref_unpool_backward(nv_coarse, C, vt_map.shape[0], _p(vt_replace), _p(vt_map), _p(gout), _p(gin)))
+    return gin

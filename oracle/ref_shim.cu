@@ -2,8 +2,9 @@
 // the unmodified reference CUDA kernels through ctypes.  TEST INFRASTRUCTURE ONLY.
 // This file holds declarations and forwarding calls only; the kernels themselves are
 // compiled from the reference tree where it lies (see oracle/Makefile, target `ref`).
-// Launcher signatures: picasso/mesh/pi_modules/source/mesh_conv3d.cpp:9-23 and
-// picasso/mesh/pi_modules/source/decimate.cpp (countVertexAdjfaceLauncher).
+// Launcher signatures: picasso/mesh/pi_modules/source/mesh_conv3d.cpp:9-23,
+// picasso/mesh/pi_modules/source/decimate.cpp (countVertexAdjfaceLauncher),
+// mesh_pool3d.cpp:8-15 and mesh_unpool3d.cpp:8-11.
 #include <cuda_runtime.h>
 
 void facet2vertexConv3dLauncher(int NfIn, int C, int r, int K, const int* vtMap, const int* nfCount, const int* face,
@@ -21,6 +22,16 @@ void facet2facetConv3dGradLauncher(int NfIn, int F, int Cin, int Cout, const int
                                    const float* input, const float* filter, const float* gradOutput,
                                    float* gradInput, float* gradFilter);
 void countVertexAdjfaceLauncher(int NfIn, const int* face, const int* vtMap, int* nfCount);
+void maxPool3dLauncher(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* input, float* output,
+                       int* maxIndex);
+void maxPool3dGradLauncher(int nvOut, int C, const int* maxIndex, const float* gradOutput, float* gradInput);
+void avgPool3dLauncher(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* input, float* output);
+void avgPool3dGradLauncher(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* gradOutput,
+                           float* gradInput);
+void interpolateLauncher(int nvIn, int C, int nvOut, const int* vtReplace, const int* vtMap, const float* input,
+                         float* output);
+void interpolateGradLauncher(int nvIn, int C, int nvOut, const int* vtReplace, const int* vtMap, const float* gradOutput,
+                             float* gradInput);
 
 // The reference launches on the legacy default stream and never checks errors; each
 // doorway synchronises the device and returns the CUDA status so a test can assert on it.
@@ -66,6 +77,34 @@ int ref_f2f_backward(int NfIn, int F, int Cin, int Cout, const int* numInterior,
 }
 int ref_count_vertex_adjface(int NfIn, const int* face, const int* vtMap, int* nfCount) {
     countVertexAdjfaceLauncher(NfIn, face, vtMap, nfCount);
+    return finish();
+}
+int ref_max_pool_forward(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* input, float* output,
+                         int* maxIndex) {
+    maxPool3dLauncher(nvIn, C, vtReplace, vtMap, input, output, maxIndex);
+    return finish();
+}
+int ref_max_pool_backward(int nvOut, int C, const int* maxIndex, const float* gradOutput, float* gradInput) {
+    maxPool3dGradLauncher(nvOut, C, maxIndex, gradOutput, gradInput);
+    return finish();
+}
+int ref_avg_pool_forward(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* input, float* output) {
+    avgPool3dLauncher(nvIn, C, vtReplace, vtMap, input, output);
+    return finish();
+}
+int ref_avg_pool_backward(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* gradOutput,
+                          float* gradInput) {
+    avgPool3dGradLauncher(nvIn, C, vtReplace, vtMap, gradOutput, gradInput);
+    return finish();
+}
+int ref_unpool_forward(int nvIn, int C, int nvOut, const int* vtReplace, const int* vtMap, const float* input,
+                       float* output) {
+    interpolateLauncher(nvIn, C, nvOut, vtReplace, vtMap, input, output);
+    return finish();
+}
+int ref_unpool_backward(int nvIn, int C, int nvOut, const int* vtReplace, const int* vtMap, const float* gradOutput,
+                        float* gradInput) {
+    interpolateGradLauncher(nvIn, C, nvOut, vtReplace, vtMap, gradOutput, gradInput);
     return finish();
 }
 }

@@ -86,6 +86,41 @@ __global__ void corner_fill_kernel(int64_t ncorner, int64_t NvIn, int64_t NvOut,
     entries[pos] = (int32_t)((f << 2) | (i - 3 * f));
 }
 
+// --------------------------------------------------------------------- vertex clusters
+// Decimation encodes clusters as (picasso/mesh/pi_modules/decimate.py:23-28): vtReplace[v] < 0 names
+// the representative -vtReplace[v] a contracted vertex merged into; the representative holds the
+// cluster size minus one (0 for a singleton); vtMap[representative] is the coarse vertex id, -1 for
+// contracted or dropped vertices.  key[v] = coarse id of v's cluster, or -1.
+__device__ __forceinline__ int cluster_key(int64_t v, int64_t NvIn, int64_t NvOut, const int32_t* __restrict__ vtReplace,
+                                           const int32_t* __restrict__ vtMap, bool* bad) {
+    int rep = vtReplace[v];
+    int64_t m = rep < 0 ? -(int64_t)rep : v;
+    if (m >= NvIn) { *bad = true; return -1; }
+    int vo = vtMap[m];
+    if (vo >= NvOut || vo < -1) { *bad = true; return -1; }
+    return vo;
+}
+
+__global__ void cluster_count_kernel(int64_t NvIn, int64_t NvOut, const int32_t* __restrict__ vtReplace,
+                                     const int32_t* __restrict__ vtMap, int32_t* __restrict__ key,
+                                     int32_t* __restrict__ cnt, int32_t* __restrict__ status) {
+    int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= NvIn) return;
+    bool bad = false;
+    int vo = cluster_key(v, NvIn, NvOut, vtReplace, vtMap, &bad);
+    if (bad) *status = PB200_EINDEX;
+    key[v] = vo;
+    if (vo >= 0) atomicAdd(&cnt[vo], 1);
+}
+
+__global__ void cluster_fill_kernel(int64_t NvIn, const int32_t* __restrict__ key, int32_t* __restrict__ cursor,
+                                    int32_t* __restrict__ members) {
+    int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= NvIn) return;
+    int vo = key[v];
+    if (vo >= 0) members[atomicAdd(&cursor[vo], 1)] = (int32_t)v;
+}
+
 // Rows come out of the atomic fill in arbitrary order; sorting each row ascending makes
 // the CSR (and every reduction that walks it) independent of scheduling.
 constexpr int SHORT_ROW = 32;
@@ -289,6 +324,54 @@ int pb200_build_vertex_csr(int64_t Nf, int64_t NvIn, int64_t NvOut, const int32_
                   NvOut, (const int32_t*)rowptr, entries, long_rows, n_long);
         PB_LAUNCH("sort_long_rows", sort_long_rows_kernel, 2 * sm_count(), 256, 0, stream,
                   (const int32_t*)rowptr, entries, (const int32_t*)long_rows, (const int32_t*)n_long, tmp);
+    }
+    return PB200_OK;
+}
+
+size_t pb200_cluster_csr_workspace_bytes(int64_t NvIn, int64_t NvOut) {
+    if (NvIn < 0 || NvOut < 0) return 0;
+    size_t cursor = align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    size_t tiles = align_up(sizeof(int32_t) * (size_t)(ceil_div(NvOut + 1, SCAN_TILE) + 1), 256);
+    size_t longs = align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    size_t tmp = align_up(sizeof(int32_t) * (size_t)(NvIn + 1), 256);
+    return cursor + tiles + longs + tmp + 256;
+}
+
+int pb200_build_cluster_csr(int64_t NvIn, int64_t NvOut, const int32_t* vtReplace, const int32_t* vtMap,
+                            int32_t* key, int32_t* rowptr, int32_t* members, int32_t* status,
+                            void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(NvIn >= 0 && NvOut >= 0 && NvIn < (1LL << 31) - 1 && NvOut < (1LL << 31) - 1, PB200_EINVAL,
+               "build_cluster_csr: bad sizes");
+    PB_REQUIRE(rowptr && status && (NvIn == 0 || (vtReplace && vtMap && key && members)), PB200_EINVAL,
+               "build_cluster_csr: null pointer");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_cluster_csr_workspace_bytes(NvIn, NvOut), PB200_EWORKSPACE,
+               "build_cluster_csr: workspace too small");
+    char* w = (char*)workspace;
+    int32_t* cursor = (int32_t*)w;  w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int ntiles = (int)ceil_div(NvOut + 1, SCAN_TILE);
+    int32_t* tile_sum = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(ntiles + 1), 256);
+    int32_t* long_rows = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int32_t* tmp = (int32_t*)w;      w += align_up(sizeof(int32_t) * (size_t)(NvIn + 1), 256);
+    int32_t* n_long = (int32_t*)w;
+    PB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    PB_CUDA(cudaMemsetAsync(cursor, 0, sizeof(int32_t) * (NvOut + 1), stream));
+    PB_CUDA(cudaMemsetAsync(n_long, 0, sizeof(int32_t), stream));
+    if (NvIn > 0)
+        PB_LAUNCH("cluster_count", cluster_count_kernel, (unsigned)ceil_div(NvIn, 256), 256, 0, stream,
+                  NvIn, NvOut, vtReplace, vtMap, key, cursor, status);
+    PB_LAUNCH("scan_tiles", scan_tiles_kernel, ntiles, SCAN_THREADS, 0, stream,
+              (const int32_t*)cursor, NvOut + 1, rowptr, tile_sum);
+    PB_LAUNCH("scan_tile_sums", scan_tile_sums_kernel, 1, 32, 0, stream, tile_sum, ntiles, tile_sum + ntiles);
+    PB_LAUNCH("scan_finish", scan_finish_kernel, (unsigned)ceil_div(NvOut + 1, 256), 256, 0, stream,
+              rowptr, NvOut + 1, (const int32_t*)tile_sum, cursor);
+    if (NvIn > 0 && NvOut > 0) {
+        PB_LAUNCH("cluster_fill", cluster_fill_kernel, (unsigned)ceil_div(NvIn, 256), 256, 0, stream,
+                  NvIn, (const int32_t*)key, cursor, members);
+        PB_LAUNCH("sort_short_rows", sort_short_rows_kernel, (unsigned)ceil_div(NvOut, 128), 128, 0, stream,
+                  NvOut, (const int32_t*)rowptr, members, long_rows, n_long);
+        PB_LAUNCH("sort_long_rows", sort_long_rows_kernel, 2 * sm_count(), 256, 0, stream,
+                  (const int32_t*)rowptr, members, (const int32_t*)long_rows, (const int32_t*)n_long, tmp);
     }
     return PB200_OK;
 }

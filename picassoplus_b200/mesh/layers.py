@@ -1,5 +1,6 @@
-"""Layer modules of the mesh convolutions with the reference's class names, constructor
-arguments, parameter names and parameter shapes (picasso/mesh/layers.py:10-195,331-356),
+"""Layer modules of the mesh convolutions (and of mesh pooling / unpooling) with the reference's
+class names, constructor arguments, parameter names and parameter shapes
+(picasso/mesh/layers.py:10-195,263-298,331-356),
 so reference checkpoints load unchanged.  Each module = one operator from
 pi_modules.conv3d followed by the pointwise stage: matmul -> + bias -> activation ->
 BatchNorm1d(eps=1e-3)  (batch norm AFTER the activation, as in the reference)."""
@@ -10,7 +11,7 @@ from typing import List
 import torch
 import torch.nn as nn
 
-from .pi_modules import conv3d
+from .pi_modules import conv3d, pool3d, unpool3d
 from ..math_utils import sph_harm_coeff
 
 
@@ -124,3 +125,28 @@ class V2VConv3d(nn.Module):
 
     def forward(self, inputs, face, nf_count, vt_map, filt_coeff):
         return self.F2V_conv3d(self.V2F_conv3d(inputs, face), face, nf_count, vt_map, filt_coeff)
+
+
+class Pool3d(nn.Module):
+    """Mesh pooling over decimation clusters, 'max' (default) or 'avg' (reference:
+    picasso/mesh/layers.py:263-284)."""
+
+    def __init__(self, method='max'):
+        super().__init__()
+        self.method = method
+
+    def forward(self, inputs, vt_replace, vt_map, vt_out):
+        if self.method == 'max':
+            return pool3d.maxPool(inputs, vt_replace, vt_map, vt_out)
+        if self.method == 'avg':
+            return pool3d.avgPool(inputs, vt_replace, vt_map, vt_out)
+        raise ValueError("Unknow pooling method %s." % self.method)
+
+
+class Unpool3d(nn.Module):
+    """Mesh unpooling: every fine vertex takes the feature of its cluster's coarse vertex
+    (reference: picasso/mesh/layers.py:287-298)."""
+
+    @staticmethod
+    def forward(inputs, vt_replace, vt_map):
+        return unpool3d.interpolate(inputs, vt_replace, vt_map)

@@ -17,8 +17,9 @@ _f2f_precision = _lib.PREC_FP32
 
 
 def set_f2f_precision(name: str) -> None:
-    """Operand precision of the facet2facet contraction: 'fp32' (default, meets the 1e-4
-    relative gate), 'tf32' or 'bf16' (tensor-core operands; fp32 accumulation always)."""
+    """Operand precision of the facet2facet contraction: 'fp32' (default: bf16 hi+lo operands,
+    meets the 1e-4 relative gate), 'fp32_tf32x3' (tf32 hi+lo operands, about 2e-6), 'tf32' or
+    'bf16' (single tensor-core operands), 'fp32_ffma' (no tensor cores); fp32 accumulation always."""
     global _f2f_precision
     _f2f_precision = _lib.PRECISIONS[name]
 

@@ -193,6 +193,50 @@ def vertex_csr(face: torch.Tensor, vt_map: Optional[torch.Tensor], nv_in: int, n
     return csr
 
 
+class ClusterCSR:
+    """Decimation clusters of a fine level: key (NvIn,) = coarse id of each fine vertex or -1;
+    rowptr (NvOut+1,), members (NvIn,) = member fine vertices of every coarse vertex, ascending."""
+
+    def __init__(self, key, rowptr, members, keep, versions):
+        self.key = key
+        self.rowptr = rowptr
+        self.members = members
+        self._keep = keep
+        self._versions = versions
+        self.nbytes = 4 * (key.numel() + rowptr.numel() + members.numel())
+
+
+def cluster_csr(vt_replace: torch.Tensor, vt_map: torch.Tensor, nv_out: int) -> ClusterCSR:
+    """Cached cluster structures of (vtReplace, vtMap) (same cache, budget and validation modes as
+    vertex_csr).  One pooling level is used by a pool in the encoder and an unpool in the decoder,
+    forward and backward: four lookups per step, one build."""
+    nv_in = vt_replace.shape[0]
+    slot = ("cluster", vt_replace.device.index, vt_replace.data_ptr(), vt_map.data_ptr(), nv_in, int(nv_out))
+    versions = (vt_replace._version, vt_map._version)
+    hit = _lookup(slot, versions)
+    if hit is not None:
+        return hit
+    dev = vt_replace.device
+    with torch.cuda.device(dev):
+        key = torch.empty(max(nv_in, 1), dtype=torch.int32, device=dev)
+        rowptr = torch.empty(nv_out + 1, dtype=torch.int32, device=dev)
+        members = torch.empty(max(nv_in, 1), dtype=torch.int32, device=dev)
+        status = torch.empty(1, dtype=torch.int32, device=dev)
+        wbytes = _lib.query("pb200_cluster_csr_workspace_bytes", nv_in, nv_out)
+        ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        _lib.call("pb200_build_cluster_csr", nv_in, nv_out, ptr(vt_replace), ptr(vt_map), ptr(key), ptr(rowptr),
+                  ptr(members), ptr(status), ptr(ws), wbytes, stream_ptr(dev))
+        msg = f"vtReplace / vtMap hold an index outside the vertex range (NvIn={nv_in}, NvOut={nv_out})"
+        if _validation == "deferred":
+            with _lock:
+                _deferred.append((status, msg))
+        elif int(status.item()) != 0:
+            raise RuntimeError(msg)
+    csr = ClusterCSR(key, rowptr, members, (vt_replace, vt_map), versions)
+    _store(slot, csr)
+    return csr
+
+
 def check_num_interior(num_interior: torch.Tensor, nik: int) -> None:
     """Validates a running sample count (non-decreasing, inside [0, nik], ends at nik) on the
     device: raises in 'sync' mode, queues the status word in 'deferred' mode.  The facet2facet

@@ -70,3 +70,40 @@ GOLDEN_CASES = {
     "ico1x2_c5_r2_k9": ("ico1x2", 5, 2, 9, 7, 12),
     "grid9x1_c4_r1_k25": ("grid9x1", 4, 1, 25, 4, 13),
 }
+
+
+def cluster_inputs(nv_in: int, nv_out: int, C: int, seed: int, drop_frac: float = 0.1, ties: bool = False):
+    """A random decimation clustering in the reference's encoding (picasso/mesh/pi_modules/
+    decimate.py:23-28) plus features and upstream gradients, as CPU torch tensors.
+    nv_out representatives keep their order (vtMap counts them from 0); every other vertex is
+    contracted into a random representative (vtReplace = -representative, vtMap = -1) or, with
+    probability drop_frac, belongs to no cluster (vtReplace = 0, vtMap = -1).  Vertex 0 is never a
+    contraction target (-0 cannot be told from 0).  ties=True quantises the features so that equal
+    maxima occur inside clusters."""
+    rng = np.random.default_rng(seed)
+    reps = np.sort(rng.choice(nv_in, size=nv_out, replace=False))
+    is_rep = np.zeros(nv_in, bool)
+    is_rep[reps] = True
+    vt_map = np.full(nv_in, -1, np.int32)
+    vt_map[reps] = np.arange(nv_out, dtype=np.int32)
+    vt_replace = np.zeros(nv_in, np.int32)
+    targets = reps[reps > 0]
+    for v in np.nonzero(~is_rep)[0]:
+        if targets.size and rng.random() >= drop_frac:
+            r = int(targets[rng.integers(targets.size)])
+            vt_replace[v] = -r
+            vt_replace[r] += 1
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(nv_in, C, generator=g)
+    if ties:
+        x = torch.round(x * 2) / 2
+    return dict(vt_replace=torch.from_numpy(vt_replace), vt_map=torch.from_numpy(vt_map), nv_in=nv_in, nv_out=nv_out,
+                x=x, g_coarse=torch.randn(nv_out, C, generator=g), x_coarse=torch.randn(nv_out, C, generator=g),
+                g_fine=torch.randn(nv_in, C, generator=g))
+
+
+POOL_GOLDEN_CASES = {
+    # name: (NvIn, NvOut, C, seed)
+    "pool_n300_m90_c8": (300, 90, 8, 31),
+    "pool_n257_m64_c5": (257, 64, 5, 32),
+}

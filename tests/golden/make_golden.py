@@ -4,10 +4,10 @@ operators (oracle/_ref, see oracle/Makefile target `ref`) on a CUDA device:
     python tests/golden/make_golden.py [output_dir]
 
 For every case of tests/cases.py:GOLDEN_CASES it stores the inputs and the reference's
-outputs (all three operators forward and backward, and nfCount) in <case>.npz.  The
-spherical-harmonic basis has no fixture here: the reference's Python modules cannot be
-imported without packages that are absent (torch_scatter, scipy.special.sph_harm), so
-that function is pinned by analytic values in the CPU tests instead.
+outputs (all three operators forward and backward, and nfCount) in <case>.npz, and for
+every case of POOL_GOLDEN_CASES the reference's mesh pooling / unpooling outputs.  The parts
+of the path that are plain Python in the reference (spherical-harmonic basis, triangle
+geometry, layer modules) have their own generator, make_golden_modules.py.
 """
 from __future__ import annotations
 
@@ -21,7 +21,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from cases import GOLDEN_CASES, conv_inputs  # noqa: E402
+from cases import GOLDEN_CASES, POOL_GOLDEN_CASES, cluster_inputs, conv_inputs  # noqa: E402
 from oracle import ref_cuda  # noqa: E402
 
 
@@ -44,6 +44,22 @@ def main(out_dir):
         arrays = {("in_" + k): v.numpy() for k, v in d.items() if isinstance(v, torch.Tensor)}
         arrays.update({("ref_" + k): v.cpu().numpy() for k, v in out.items()})
         arrays["nv_out"] = np.array(d["nv_out"])
+        np.savez_compressed(os.path.join(out_dir, name + ".npz"), **arrays)
+        print("wrote", name, {k: tuple(v.shape) for k, v in arrays.items() if k.startswith("ref_")})
+    # mesh pool / unpool (mesh_pool3d_gpu.cu, mesh_unpool3d_gpu.cu); inputs without ties, so the
+    # reference's max index does not depend on its thread order
+    for name, (nv_in, nv_out, C, seed) in POOL_GOLDEN_CASES.items():
+        d = cluster_inputs(nv_in, nv_out, C, seed)
+        c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+        out = {}
+        out["max_out"], out["max_index"] = ref_cuda.max_pool_forward(c["x"], c["vt_replace"], c["vt_map"], nv_out)
+        out["max_gin"] = ref_cuda.max_pool_backward(c["g_coarse"], nv_in, out["max_index"])
+        out["avg_out"] = ref_cuda.avg_pool_forward(c["x"], c["vt_replace"], c["vt_map"], nv_out)
+        out["avg_gin"] = ref_cuda.avg_pool_backward(c["g_coarse"], c["vt_replace"], c["vt_map"])
+        out["unpool_out"] = ref_cuda.unpool_forward(c["x_coarse"], c["vt_replace"], c["vt_map"])
+        out["unpool_gin"] = ref_cuda.unpool_backward(c["g_fine"], nv_out, c["vt_replace"], c["vt_map"])
+        arrays = {("in_" + k): v.numpy() for k, v in d.items() if isinstance(v, torch.Tensor)}
+        arrays.update({("ref_" + k): v.cpu().numpy() for k, v in out.items()})
         np.savez_compressed(os.path.join(out_dir, name + ".npz"), **arrays)
         print("wrote", name, {k: tuple(v.shape) for k, v in arrays.items() if k.startswith("ref_")})
 

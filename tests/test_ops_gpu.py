@@ -12,6 +12,7 @@ from cases import conv_inputs
 pytestmark = pytest.mark.gpu
 
 TOL = 1e-4
+ARB_FP32 = 32.0      # bf16 hi+lo operands against the reference's fp32 FFMA, both measured against fp64
 
 CASES = [
     # topology, C, r, K, Cout
@@ -129,6 +130,124 @@ def test_facet2facet_fp32(mods, kind, C, r, K, cout):
         assert rel_err(out, r_out) <= TOL
         r_gin, r_gf = ref.f2f_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
         assert rel_err(gin, r_gin) <= TOL and rel_err(gf, r_gf) <= TOL
+        # The fp64 oracle arbitrates.  The default fp32 mode keeps 16 mantissa bits per operand (bf16
+        # hi+lo), so it may sit up to ARB_FP32 times further from fp64 than the reference's FFMA
+        # kernels; the tf32 hi+lo mode and the FFMA path must be as close as the reference (factor 4
+        # covers the different summation order).  The floor term covers tensors the reference gets
+        # exactly right.
+        for mode, k in (("fp32", ARB_FP32), ("fp32_tf32x3", 4.0), ("fp32_ffma", 4.0)):
+            conv3d.set_f2f_precision(mode)
+            o_m = conv3d.facet2facet_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+            gi_m, gf_m = conv3d.facet2facet_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+            for name, ours, theirs, truth in (("out", o_m, r_out, want), ("gin", gi_m, r_gin, wgin), ("gf", gf_m, r_gf, wgf)):
+                floor = 2e-6 * float(truth.abs().max()) if truth.numel() else 0.0
+                assert max_abs(ours, truth) <= k * max_abs(theirs, truth) + floor, (mode, name, max_abs(ours, truth),
+                                                                                   max_abs(theirs, truth))
+        conv3d.set_f2f_precision("fp32")
+
+
+def _ref_block(ref, x, Wv, Wf, Wo, face, counts, cum, bary_sh, coeff, nfc, vt_map, sh_eye, G):
+    """The benchmark block chained by hand through the reference's own CUDA kernels (forward and
+    backward), with torch for the glue the reference leaves to user code."""
+    cin = x.shape[1]
+    spatial = (sh_eye @ Wv).reshape(3, cin, 1).contiguous()
+    y = ref.v2f_forward(x, spatial, face)
+    tex = torch.repeat_interleave(y, counts.long(), dim=0)
+    z = ref.f2f_forward(tex, Wf, bary_sh, cum)
+    o = ref.f2v_forward(z, Wo, coeff, face, nfc, vt_map)
+    gz, gWo = ref.f2v_backward(G, z, Wo, coeff, face, nfc, vt_map)
+    gtex, gWf = ref.f2f_backward(gz, tex, Wf, bary_sh, cum)
+    fid = torch.repeat_interleave(torch.arange(face.shape[0], device=x.device), counts.long())
+    gy = torch.zeros_like(y).index_add_(0, fid, gtex)
+    gx, gsp = ref.v2f_backward(gy, x, spatial, face)
+    gWv = sh_eye.t() @ gsp.reshape(3, cin)
+    return o, gx, [gWv, gWf, gWo]
+
+
+def test_baseline_config_c1_block_exact(mods):
+    """BASELINE configuration 1 as written: 4 icospheres of level 4 (2562 vertices, 5120 faces each),
+    radial jitter N(0, 0.02), 32 -> 64 channels, L = 3, whole V2F -> F2F -> F2V block forward and
+    backward, against the reference's live CUDA kernels and against the fp64 oracle."""
+    conv3d, _, mo, ref = mods
+    from picassoplus_b200 import synth
+    from picassoplus_b200.block import conv_block
+    from picassoplus_b200.math_utils import sph_harm_coeff
+    cfg = synth.CONFIGS["c1"]
+    L, cin, cout = cfg["L"], cfg["cin"], cfg["cout"]
+    K = (L + 1) ** 2
+    mb = synth.make_batch(cfg)
+    assert mb.num_vertices == 4 * 2562 and mb.num_faces == 4 * 5120
+    counts_np, bary_xyz = synth.texture_samples(mb.num_faces, seed=101)
+    g = torch.Generator().manual_seed(102)
+    rng = __import__("numpy").random.default_rng(103)
+    x = torch.randn(mb.num_vertices, cin, generator=g)
+    Wv = torch.from_numpy(synth.xavier_normal((K, cin), rng))
+    Wf = torch.from_numpy(synth.xavier_normal((cout, cin, K), rng))
+    Wo = torch.from_numpy(synth.xavier_normal((K, cout, 1), rng))
+    G = torch.randn(mb.num_vertices, cout, generator=g)
+    vertex, face = torch.from_numpy(mb.vertex), torch.from_numpy(mb.face)
+    counts = torch.from_numpy(counts_np)
+    cum = torch.cumsum(counts, 0, dtype=torch.int32)
+    vt_map = torch.arange(mb.num_vertices, dtype=torch.int32)
+    nfc = mo.count_vertex_adjface(face, vt_map, mb.num_vertices)
+    coeff = mo.sph_harm_coeff(L, mo.triangle_geometry(vertex, face)[:, :3])
+    bary_sh = mo.sph_harm_coeff(L, torch.from_numpy(bary_xyz))
+    sh_eye = mo.sph_harm_coeff(L, torch.eye(3))
+
+    xo = x.double().requires_grad_()
+    wo = [w.double().requires_grad_() for w in (Wv, Wf, Wo)]
+    oo = mo.conv_block(xo, wo[0], wo[1], wo[2], face, counts, cum, bary_sh.double(), coeff.double(), nfc, vt_map,
+                       sh_eye.double())
+    (oo * G.double()).sum().backward()
+    truth = [oo.detach(), xo.grad] + [w.grad for w in wo]
+
+    conv3d.set_f2f_precision("fp32")
+    xd = x.cuda().requires_grad_()
+    wd = [w.cuda().requires_grad_() for w in (Wv, Wf, Wo)]
+    o = conv_block(xd, wd[0], wd[1], wd[2], face.cuda(), cum.cuda(), bary_sh.cuda(), coeff.cuda(), nfc.cuda(),
+                   vt_map.cuda(), sh_eye.cuda())
+    o.backward(G.cuda())
+    ours = [o.detach(), xd.grad] + [w.grad for w in wd]
+    names = ["out", "grad_x", "grad_Wv", "grad_Wf", "grad_Wo"]
+    for n, a, b in zip(names, ours, truth):
+        assert rel_err(a, b) <= TOL, (n, rel_err(a, b))
+    if ref.available():
+        ro, rgx, rgw = _ref_block(ref, x.cuda(), Wv.cuda(), Wf.cuda(), Wo.cuda(), face.cuda(), counts.cuda(), cum.cuda(),
+                                  bary_sh.cuda(), coeff.cuda(), nfc.cuda(), vt_map.cuda(), sh_eye.cuda(), G.cuda())
+        for n, a, b, t in zip(names, ours, [ro, rgx] + rgw, truth):
+            assert rel_err(a, b) <= TOL, (n, rel_err(a, b))
+            assert rel_err(b, t) <= TOL, ("reference vs fp64", n, rel_err(b, t))
+
+
+def test_one_benchmark_mesh_against_fp64(mods):
+    """One 360 x 360 heightfield mesh of the headline configuration (128 -> 128 channels, L = 4,
+    ~232 k faces): facet2facet forward and backward in every tensor-core mode against the fp64
+    formulas of the oracle (evaluated with torch in fp64 on the device, in face chunks)."""
+    conv3d, _, mo, _ = mods
+    from picassoplus_b200 import synth
+    cfg = synth.CONFIGS["c5"]
+    mb = synth.make_batch(cfg, 1, 0)
+    counts_np, _ = synth.texture_samples(mb.num_faces, 3)
+    g = torch.Generator().manual_seed(5)
+    cum = torch.cumsum(torch.from_numpy(counts_np), 0, dtype=torch.int32).cuda()
+    nik = int(counts_np.sum())
+    C, F, cout = cfg["cin"], (cfg["L"] + 1) ** 2, cfg["cout"]
+    tex = torch.randn(nik, C, generator=g).cuda()
+    bary = torch.randn(nik, F, generator=g).cuda()
+    W = (torch.randn(cout, C, F, generator=g) / (C * F) ** 0.5).cuda()
+    go = torch.randn(mb.num_faces, cout, generator=g).cuda()
+    want = mo.facet2facet_forward(tex.double(), W.double(), bary.double(), cum, chunk=16384)
+    wgin, wgf = mo.facet2facet_backward(go.double(), tex.double(), W.double(), bary.double(), cum, chunk=16384)
+    gates = {"fp32": 1e-4, "fp32_tf32x3": 1e-4, "tf32": 2e-3, "bf16": 2e-2}
+    try:
+        for mode, gate in gates.items():
+            conv3d.set_f2f_precision(mode)
+            out = conv3d.facet2facet_forward(tex, W, bary, cum)
+            gin, gf = conv3d.facet2facet_backward(go, tex, W, bary, cum)
+            errs = dict(out=rel_err(out, want), gin=rel_err(gin, wgin), gf=rel_err(gf, wgf))
+            assert max(errs.values()) <= gate, (mode, errs)
+    finally:
+        conv3d.set_f2f_precision("fp32")
 
 
 def test_autograd_functions_match_oracle_block(mods):
