@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS) + ["c4"])
     ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_tf32x3", "tf32", "bf16"])
     ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -560,6 +560,125 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------- encoder stack (config c4)
+C4 = dict(n=700, batch=2, levels=4, channels=[64, 128, 256, 384], L=3, seed=3)
+
+
+def c4_hierarchy(cfg):
+    """The batch's mesh hierarchy on the host: per level the concatenated (vertex, face), per
+    transition the concatenated cluster encoding (ids re-based to the batch)."""
+    per_mesh = [synth.heightfield_hierarchy(cfg["n"], cfg["seed"] * 1000 + i, cfg["levels"]) for i in range(cfg["batch"])]
+    levels, trans = [], []
+    for lvl in range(cfg["levels"]):
+        levels.append(synth.concat_meshes([pm[0][lvl] for pm in per_mesh]))
+    for t in range(cfg["levels"] - 1):
+        reps, maps, voff, coff = [], [], 0, 0
+        for pm in per_mesh:
+            r, m = pm[1][t]
+            reps.append(np.where(r < 0, r - voff, r).astype(np.int32))       # -(representative + offset)
+            maps.append(np.where(m >= 0, m + coff, m).astype(np.int32))
+            voff += r.shape[0]
+            coff += int(m.max()) + 1
+        trans.append((np.concatenate(reps), np.concatenate(maps)))
+    return levels, trans
+
+
+def run_c4(args):
+    """BASELINE configuration 4: encoder stack over four mesh levels, forward + backward.  Per level
+    one V2VConv3d module (vertex2facet -> pointwise -> facet2vertex -> pointwise, ReLU, batch norm in
+    training mode) followed by a max pool to the next level; channels 64 -> 128 -> 256 -> 384, L = 3.
+    The hierarchy comes from synth.heightfield_hierarchy (grid halving, face ratios 1 / 0.25 / 0.062 /
+    0.015), which stands in for the reference's GPU decimation; indices are built once and held fixed."""
+    from picassoplus_b200 import _lib, topology
+    from picassoplus_b200.mesh.layers import Pool3d, V2VConv3d
+    from picassoplus_b200.mesh.pi_modules import conv3d
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for --impl ours)")
+    assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "config c4 is a single-GPU measurement"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = C4
+    conv3d.set_f2f_precision(args.precision)
+    levels, trans = c4_hierarchy(cfg)
+    L, ch = cfg["L"], cfg["channels"]
+    rng = np.random.default_rng(cfg["seed"] + 77)
+    v0 = levels[0].vertex
+    xyz = (v0 - v0.min(0)) / (v0.max(0) - v0.min(0) + 1e-9)
+    feats6 = np.concatenate([xyz, rng.uniform(0, 1, size=xyz.shape)], axis=1).astype(np.float32)
+    x0 = torch.from_numpy(feats6 @ synth.xavier_normal((6, ch[0]), rng)).to(dev).requires_grad_()
+    torch.manual_seed(cfg["seed"])
+    convs = [V2VConv3d(ch[i], [ch[i + 1], ch[i + 1]], L, [1, 1]).to(dev).train() for i in range(3)]
+    pool = Pool3d("max")
+    lv = []
+    for mb in levels:
+        vertex, face = torch.from_numpy(mb.vertex).to(dev), torch.from_numpy(mb.face).to(dev)
+        vt = torch.arange(mb.num_vertices, dtype=torch.int32, device=dev)
+        prep = topology.prepare_level(vertex, face, vt, mb.num_vertices, L, want_geometry=False)
+        lv.append(dict(vertex=vertex, face=face, vt=vt, nfc=prep["nf_count"], coeff=prep["coeff"]))
+    tr = [(torch.from_numpy(r).to(dev), torch.from_numpy(m).to(dev)) for r, m in trans]
+    G = torch.randn(levels[3].num_vertices, ch[3], device=dev, generator=torch.Generator(device=dev).manual_seed(9))
+    params = [p for c in convs for p in c.parameters()]
+
+    def step():
+        for p in params:
+            p.grad = None
+        x0.grad = None
+        x = x0
+        for i in range(3):
+            x = convs[i](x, lv[i]["face"], lv[i]["nfc"], lv[i]["vt"], lv[i]["coeff"])
+            x = pool(x, tr[i][0], tr[i][1], lv[i + 1]["vertex"])
+        x.backward(G)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    with ClockSampler(gpu_uuid(dev)) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0 = _lib.launch_count()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = _lib.launch_count() - n0
+    _lib.prof_reset()
+    _lib.prof_enable(True)
+    step()
+    torch.cuda.synchronize()
+    _lib.prof_enable(False)
+    records = _lib.prof_read(64)
+    _lib.prof_reset()
+    lib_ms = sum(r[2] for r in records)
+    faces = levels[0].num_faces
+    # algorithmic bytes of the library's operators per level (the formulas of kernel_models), summed
+    peaks = load_peaks()
+    alg = 0
+    for i in range(3):
+        Nv, Nf, Ci, Co, K = levels[i].num_vertices, levels[i].num_faces, ch[i], ch[i + 1], (L + 1) ** 2
+        alg += 12 * Ci * Nv + 8 * Ci * Nf + 24 * Nf                                         # V2F fwd+bwd
+        alg += 12 * Co * Nf + 8 * K * Nf + 24 * Nf + 8 * Co * Nv + 16 * Nv                  # F2V fwd+bwd
+        alg += 4 * Co * (2 * Nv + 3 * levels[i + 1].num_vertices)                           # max pool fwd+bwd
+    line = {
+        "metric": METRIC, "value": faces / (ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"encoder stack, {cfg['batch']} heightfield meshes {cfg['n']}x{cfg['n']} over 4 levels "
+                               f"(faces {[m.num_faces for m in levels]}), channels 64->128->256->384, L=3", "name": "c4"},
+        "workload_detail": {"faces_level0": faces, "vertices_per_level": [m.num_vertices for m in levels],
+                            "hierarchy": "synthetic grid halving (stands in for the reference's GPU decimation)",
+                            "pointwise_stage": "torch.matmul + bias + ReLU + BatchNorm1d (cuBLAS / torch kernels)"},
+        "roofline": {"bound": "hbm", "achieved": alg / (lib_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": alg / (lib_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "note": "all library operator kernels of one step together: algorithmic bytes of V2F, F2V and max "
+                             "pool over the three conv levels / their summed duration", "peak_source": peaks["source"]},
+        "library_kernel_ms_per_step": lib_ms, "other_ms_per_step": ms - lib_ms,
+        "gpu_launches": int(launches), "clocks": clk.summary(),
+        "kernels": [dict(kernel=n, launches_per_step=c, ms_per_step=t) for n, c, t in records[:14]],
+    }
+    print(json.dumps(line))
+
+
 # ------------------------------------------------------------------- CPU oracle timing
 def _oracle_step_fn(cfg, n_or_level, seed_shift=0):
     """One mesh of the configuration's kind (heightfield n x n or icosphere level) and a
@@ -663,5 +782,7 @@ if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.config == "c4":
+        run_c4(a)
     else:
         run_ours(a)

@@ -217,6 +217,23 @@ int pb200_sph_harm_coeff(int64_t N, int L, const float* xyz, float* out, void* s
 int pb200_triangle_geometry(int64_t Nf, int64_t Nv, int vstride, const float* vertex,
                             const int32_t* face, float* geometry, void* stream);
 
+/* Per-level preparation in one call: for every face the triangle geometry (as pb200_triangle_geometry;
+ * `geometry` may be NULL), the normal the filter coefficients are taken from -- the geometric normal,
+ * or with orient != 0 the normal flipped towards the origin as viewpoint
+ * (picasso/networks/scene_seg.py:117-124: sign = sign(sum(-center*normal)), every sign above -1 set to
+ * +1; `normals` (Nf,3) may be NULL) -- and coeff (Nf,(L+1)^2) = its spherical-harmonic basis (as
+ * pb200_sph_harm_coeff); for the vertices nfCount (as pb200_count_vertex_adjface) and the vertex CSR
+ * (as pb200_build_vertex_csr, same workspace size, same `status`).  The faces are read once: one
+ * kernel does geometry, orientation, basis and corner counting.  Replaces, per mesh level, the
+ * sequence compute_triangle_geometry_ (decimate.py:70-85), get_oriented_normals, SphHarmCoeff
+ * (layers.py:341-356) and count_vertex_adjface (decimate_gpu.cu:813-836): about 60 small torch and
+ * CUDA kernels in the reference. */
+int pb200_level_prepare(int64_t Nf, int64_t NvIn, int64_t NvOut, int vstride, const float* vertex,
+                        const int32_t* face, const int32_t* vtMap, int L, int orient,
+                        float* geometry, float* normals, float* coeff, int32_t* nfCount,
+                        int32_t* rowptr, int32_t* entries, int32_t* status,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- mesh pooling / unpooling over decimation clusters ------------------------------------
  * Cluster encoding of the fine level (picasso/mesh/pi_modules/decimate.py:23-28): vtReplace[v] < 0
  * names the representative -vtReplace[v] that v was contracted into; a representative holds its

@@ -143,6 +143,18 @@ def triangle_geometry(vertex: torch.Tensor, face: torch.Tensor) -> torch.Tensor:
     return torch.cat([normal, d, area], dim=-1)
 
 
+def oriented_normals(geometry: torch.Tensor, vertex: torch.Tensor, face: torch.Tensor) -> torch.Tensor:
+    """picasso/networks/scene_seg.py:117-124 (get_oriented_normals): flip a face normal when it points
+    away from the origin taken as viewpoint; sign = sign(sum(-center*normal)) with every sign above -1
+    set to +1, so only a strictly negative dot product flips."""
+    face = face.to(torch.long)
+    normals = geometry[:, :3]
+    center = (vertex[face[:, 0], :3] + vertex[face[:, 1], :3] + vertex[face[:, 2], :3]) / 3
+    sign = torch.sign(torch.sum(-center * normals, dim=-1, keepdim=True))
+    sign = torch.where(sign > -1, torch.ones_like(sign), sign)
+    return normals * sign
+
+
 def count_vertex_adjface(face: torch.Tensor, vt_map: torch.Tensor, nv_out: int) -> torch.Tensor:
     """picasso/mesh/pi_modules/source/decimate_gpu.cu:813-831: one count per face corner
     whose mapped vertex id is non-negative."""

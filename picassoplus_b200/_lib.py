@@ -61,6 +61,7 @@ SIGNATURES = {
     "pb200_facet2facet_forward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_facet2facet_backward_workspace_bytes": (sz, [i64, i64, i32, i32, i32, i32]),
     "pb200_facet2facet_backward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
+    "pb200_level_prepare": (i32, [i64, i64, i64, i32, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_cluster_csr_workspace_bytes": (sz, [i64, i64]),
     "pb200_build_cluster_csr": (i32, [i64, i64, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_mesh_max_pool_forward": (i32, [i64, i64, i32, vp, vp, vp, vp, vp, vp]),

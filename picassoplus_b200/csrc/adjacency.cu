@@ -2,6 +2,7 @@
 // scatter-shaped kernel pulls through, triangle geometry, and row expansion by sample
 // counts.  All integer work; results are bit-exact and independent of scheduling.
 #include "common.cuh"
+#include "sph_core.cuh"
 
 namespace pb {
 
@@ -198,6 +199,83 @@ __global__ void triangle_geometry_kernel(int64_t Nf, int64_t Nv, int vstride, co
     g[4] = l2 / 2.f;
 }
 
+// ------------------------------------------------------------- fused per-level preparation
+// One pass over the faces of a mesh level: triangle geometry (normal, plane intercept, area), the
+// optionally re-oriented normal (flipped when it points away from the origin as viewpoint,
+// reference: picasso/networks/scene_seg.py:117-124), its spherical-harmonic coefficients, and the
+// per-vertex corner counts that seed the vertex CSR (= the reference's nfCount).  The vertex rows of
+// a face are read once for all of it; the K coefficients are staged through shared memory so the
+// global store is coalesced.
+constexpr int PREP_BLOCK = 128;
+
+__global__ void __launch_bounds__(PREP_BLOCK)
+level_prepare_kernel(int64_t Nf, int64_t NvIn, int64_t NvOut, int vstride, const float* __restrict__ vertex,
+                     const int32_t* __restrict__ face, const int32_t* __restrict__ vtMap, int L, int orient, SphConst cst,
+                     float* __restrict__ geom, float* __restrict__ normal_out, float* __restrict__ coeff,
+                     int32_t* __restrict__ cnt, int32_t* __restrict__ status) {
+    extern __shared__ float stage[];            // [PREP_BLOCK][K+1]
+    const int K = (L + 1) * (L + 1), KP = K + 1;
+    const int64_t base = (int64_t)blockIdx.x * PREP_BLOCK;
+    const int64_t f = base + threadIdx.x;
+    if (f < Nf) {
+        const int i0 = face[3 * f], i1 = face[3 * f + 1], i2 = face[3 * f + 2];
+        float nx = 0.f, ny = 0.f, nz = 0.f, dd = 0.f, area = 0.f;
+        const bool ok = !(i0 < 0 || i1 < 0 || i2 < 0 || i0 >= NvIn || i1 >= NvIn || i2 >= NvIn);
+        if (ok) {
+            const float* a = vertex + (int64_t)i0 * vstride;
+            const float* b = vertex + (int64_t)i1 * vstride;
+            const float* c = vertex + (int64_t)i2 * vstride;
+            const float ax = a[0], ay = a[1], az = a[2];
+            const float bx = b[0], by = b[1], bz = b[2], cx = c[0], cy = c[1], cz = c[2];
+            const float ux = bx - ax, uy = by - ay, uz = bz - az;
+            const float vx = cx - ax, vy = cy - ay, vz = cz - az;
+            nx = __fsub_rn(__fmul_rn(uy, vz), __fmul_rn(uz, vy));
+            ny = __fsub_rn(__fmul_rn(uz, vx), __fmul_rn(ux, vz));
+            nz = __fsub_rn(__fmul_rn(ux, vy), __fmul_rn(uy, vx));
+            const float l2 = sqrtf(__fadd_rn(__fadd_rn(__fmul_rn(nx, nx), __fmul_rn(ny, ny)), __fmul_rn(nz, nz)));
+            const float den = l2 + 1e-10f;
+            nx = nx / den; ny = ny / den; nz = nz / den;
+            dd = -__fadd_rn(__fadd_rn(__fmul_rn(nx, ax), __fmul_rn(ny, ay)), __fmul_rn(nz, az));
+            area = l2 / 2.f;
+            if (geom) { float* g = geom + f * 5; g[0] = nx; g[1] = ny; g[2] = nz; g[3] = dd; g[4] = area; }
+            if (orient) {
+                // sign(sum(-center * normal)) with every value above -1 set to +1: only a strictly
+                // negative dot product flips the normal
+                const float mx = __fadd_rn(__fadd_rn(ax, bx), cx) / 3.f, my = __fadd_rn(__fadd_rn(ay, by), cy) / 3.f,
+                            mz = __fadd_rn(__fadd_rn(az, bz), cz) / 3.f;
+                const float dot = __fadd_rn(__fadd_rn(__fmul_rn(-mx, nx), __fmul_rn(-my, ny)), __fmul_rn(-mz, nz));
+                if (dot < 0.f) { nx = -nx; ny = -ny; nz = -nz; }
+            }
+        } else {
+            if (status) *status = PB200_EINDEX;
+            if (geom) { float* g = geom + f * 5; g[0] = g[1] = g[2] = g[3] = g[4] = 0.f; }
+        }
+        if (normal_out) { normal_out[3 * f] = nx; normal_out[3 * f + 1] = ny; normal_out[3 * f + 2] = nz; }
+        sph_eval(nx, ny, nz, L, cst.c, stage + threadIdx.x * KP);
+        if (cnt && ok) {
+            const int vi[3] = {i0, i1, i2};
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const int vo = vtMap ? vtMap[vi[j]] : vi[j];
+                if (vo >= NvOut || vo < -1) { if (status) *status = PB200_EINDEX; }
+                else if (vo >= 0) atomicAdd(&cnt[vo], 1);
+            }
+        }
+    }
+    __syncthreads();
+    const int64_t nfb = Nf - base < PREP_BLOCK ? Nf - base : PREP_BLOCK;
+    float* dst = coeff + base * K;
+    for (int64_t j = threadIdx.x; j < nfb * K; j += PREP_BLOCK) {
+        const int p = (int)(j / K), k = (int)(j - (int64_t)p * K);
+        dst[j] = stage[p * KP + k];
+    }
+}
+
+__global__ void copy_counts_kernel(int64_t n, const int32_t* __restrict__ src, int32_t* __restrict__ dst) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[i];
+}
+
 // ------------------------------------------------------------------------ row expansion
 // The samples of face f are rows cum[f-1] .. cum[f]-1 (cum = inclusive running count).
 // forward: one item per (face, channel group); the face's row is read once and written to
@@ -260,6 +338,28 @@ __global__ void check_running_count_kernel(int64_t Nf, int64_t NiK, const int32_
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// second half of the vertex-CSR build: exclusive scan of the corner counts in cursor[0..NvOut]
+// (last slot 0) -> rowptr, atomic-cursor fill, per-row sort
+static int finish_vertex_csr(int64_t Nf, int64_t NvIn, int64_t NvOut, const int32_t* face, const int32_t* vtMap,
+                             int32_t* rowptr, int32_t* entries, int32_t* cursor, int32_t* tile_sum, int32_t* long_rows,
+                             int32_t* tmp, int32_t* n_long, cudaStream_t stream) {
+    const int ntiles = (int)ceil_div(NvOut + 1, SCAN_TILE);
+    PB_LAUNCH("scan_tiles", scan_tiles_kernel, ntiles, SCAN_THREADS, 0, stream,
+              (const int32_t*)cursor, NvOut + 1, rowptr, tile_sum);
+    PB_LAUNCH("scan_tile_sums", scan_tile_sums_kernel, 1, 32, 0, stream, tile_sum, ntiles, tile_sum + ntiles);
+    PB_LAUNCH("scan_finish", scan_finish_kernel, (unsigned)ceil_div(NvOut + 1, 256), 256, 0, stream,
+              rowptr, NvOut + 1, (const int32_t*)tile_sum, cursor);
+    if (Nf > 0 && NvOut > 0) {
+        PB_LAUNCH("corner_fill", corner_fill_kernel, (unsigned)ceil_div(3 * Nf, 256), 256, 0, stream,
+                  3 * Nf, NvIn, NvOut, face, vtMap, cursor, entries);
+        PB_LAUNCH("sort_short_rows", sort_short_rows_kernel, (unsigned)ceil_div(NvOut, 128), 128, 0, stream,
+                  NvOut, (const int32_t*)rowptr, entries, long_rows, n_long);
+        PB_LAUNCH("sort_long_rows", sort_long_rows_kernel, 2 * sm_count(), 256, 0, stream,
+                  (const int32_t*)rowptr, entries, (const int32_t*)long_rows, (const int32_t*)n_long, tmp);
+    }
+    return PB200_OK;
+}
+
 }  // namespace pb
 
 using namespace pb;
@@ -311,21 +411,44 @@ int pb200_build_vertex_csr(int64_t Nf, int64_t NvIn, int64_t NvOut, const int32_
     if (Nf > 0)
         PB_LAUNCH("corner_count", corner_count_kernel, (unsigned)ceil_div(3 * Nf, 256), 256, 0, stream,
                   3 * Nf, NvIn, NvOut, face, vtMap, cursor, status);
-    // exclusive scan of cursor[0..NvOut] (last slot is 0) -> rowptr[0..NvOut]
-    PB_LAUNCH("scan_tiles", scan_tiles_kernel, ntiles, SCAN_THREADS, 0, stream,
-              (const int32_t*)cursor, NvOut + 1, rowptr, tile_sum);
-    PB_LAUNCH("scan_tile_sums", scan_tile_sums_kernel, 1, 32, 0, stream, tile_sum, ntiles, tile_sum + ntiles);
-    PB_LAUNCH("scan_finish", scan_finish_kernel, (unsigned)ceil_div(NvOut + 1, 256), 256, 0, stream,
-              rowptr, NvOut + 1, (const int32_t*)tile_sum, cursor);
-    if (Nf > 0 && NvOut > 0) {
-        PB_LAUNCH("corner_fill", corner_fill_kernel, (unsigned)ceil_div(3 * Nf, 256), 256, 0, stream,
-                  3 * Nf, NvIn, NvOut, face, vtMap, cursor, entries);
-        PB_LAUNCH("sort_short_rows", sort_short_rows_kernel, (unsigned)ceil_div(NvOut, 128), 128, 0, stream,
-                  NvOut, (const int32_t*)rowptr, entries, long_rows, n_long);
-        PB_LAUNCH("sort_long_rows", sort_long_rows_kernel, 2 * sm_count(), 256, 0, stream,
-                  (const int32_t*)rowptr, entries, (const int32_t*)long_rows, (const int32_t*)n_long, tmp);
+    return pb::finish_vertex_csr(Nf, NvIn, NvOut, face, vtMap, rowptr, entries, cursor, tile_sum, long_rows, tmp, n_long,
+                                 stream);
+}
+
+int pb200_level_prepare(int64_t Nf, int64_t NvIn, int64_t NvOut, int vstride, const float* vertex, const int32_t* face,
+                        const int32_t* vtMap, int L, int orient, float* geometry, float* normals, float* coeff,
+                        int32_t* nfCount, int32_t* rowptr, int32_t* entries, int32_t* status,
+                        void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && NvIn >= 0 && NvOut >= 0 && Nf < (1LL << 29) && NvOut < (1LL << 31) - 1 && vstride >= 3,
+               PB200_EINVAL, "level_prepare: bad sizes");
+    PB_REQUIRE(L >= 0 && L <= 5, PB200_EINVAL, "level_prepare: degree L=%d not supported (0..5)", L);
+    PB_REQUIRE(rowptr && status && nfCount && (Nf == 0 || (face && entries && vertex && coeff)), PB200_EINVAL,
+               "level_prepare: null pointer");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_vertex_csr_workspace_bytes(Nf, NvOut), PB200_EWORKSPACE,
+               "level_prepare: workspace too small");
+    char* w = (char*)workspace;
+    int32_t* cursor = (int32_t*)w;  w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int ntiles = (int)ceil_div(NvOut + 1, SCAN_TILE);
+    int32_t* tile_sum = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(ntiles + 1), 256);
+    int32_t* long_rows = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int32_t* tmp = (int32_t*)w;      w += align_up(sizeof(int32_t) * (size_t)(3 * Nf + 1), 256);
+    int32_t* n_long = (int32_t*)w;
+    PB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    PB_CUDA(cudaMemsetAsync(cursor, 0, sizeof(int32_t) * (NvOut + 1), stream));
+    PB_CUDA(cudaMemsetAsync(n_long, 0, sizeof(int32_t), stream));
+    if (Nf > 0) {
+        static const SphConst cst = make_sph_const();
+        const int K = (L + 1) * (L + 1);
+        PB_LAUNCH("level_prepare", level_prepare_kernel, (unsigned)ceil_div(Nf, PREP_BLOCK), PREP_BLOCK,
+                  sizeof(float) * PREP_BLOCK * (K + 1), stream, Nf, NvIn, NvOut, vstride, vertex, face, vtMap, L, orient, cst,
+                  geometry, normals, coeff, cursor, status);
     }
-    return PB200_OK;
+    if (NvOut > 0)      // the corner counts are the reference's nfCount; the scan below overwrites the cursor
+        PB_LAUNCH("copy_counts", copy_counts_kernel, (unsigned)ceil_div(NvOut, 256), 256, 0, stream, NvOut,
+                  (const int32_t*)cursor, nfCount);
+    return pb::finish_vertex_csr(Nf, NvIn, NvOut, face, vtMap, rowptr, entries, cursor, tile_sum, long_rows, tmp, n_long,
+                                 stream);
 }
 
 size_t pb200_cluster_csr_workspace_bytes(int64_t NvIn, int64_t NvOut) {

@@ -45,11 +45,14 @@ constexpr int WAIT_BUDGET_KCLOCKS = 2000000;
 // time-out, or as soon as another thread of the block has raised the flag.
 // A failed probe backs off with a short sleep so that a waiting role (the MMA issuer, the
 // bulk-copy thread) does not take issue slots from the warps it is waiting for.
+#ifndef PB_WAIT_SPIN
+#define PB_WAIT_SPIN 0          // probes without a sleep in between before the back-off starts
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 0;; ++i) {
-        __nanosleep(i < 8 ? 20 : 100);
+        if (i >= PB_WAIT_SPIN) __nanosleep(i < PB_WAIT_SPIN + 8 ? 20 : 100);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 63u) == 63u) {
             if (abort_flag[0]) return false;

@@ -110,6 +110,47 @@ def heightfield(n: int, seed: int, delete_frac: float = 0.10) -> Tuple[np.ndarra
     return v, f[keep].astype(np.int32)
 
 
+def heightfield_hierarchy(n: int, seed: int, levels: int = 4, delete_frac: float = 0.10):
+    """A heightfield mesh and `levels - 1` coarser versions of it, with the cluster encoding that
+    mesh decimation produces (picasso/mesh/pi_modules/decimate.py:23-28), standing in for the
+    reference's GPU decimation: level l+1 keeps every second grid vertex in both directions (face
+    ratio about 0.25 per level: 1, 0.25, 0.0625, 0.016 over four levels); the up to four fine
+    vertices of a 2x2 cell form one cluster whose representative is the kept vertex.  Returns
+    [(vertex, face)] per level and [(vt_replace, vt_map)] per transition (arrays over the finer
+    level's vertices).  Cells whose representative is vertex 0 stay singletons (a representative is
+    named by its negated id, which vertex 0 does not have); their other vertices belong to no
+    cluster, like the vertices decimation drops."""
+    rng = np.random.default_rng(seed)
+    z = _value_noise(n, rng)
+    meshes, maps = [], []
+    step, m = 1, n
+    for lvl in range(levels):
+        zi = z[::step, ::step]
+        m = zi.shape[0]
+        ys, xs = np.meshgrid(np.linspace(0, 1, n)[::step], np.linspace(0, 1, n)[::step], indexing="ij")
+        v = np.stack([xs, ys, zi], axis=-1).reshape(-1, 3).astype(np.float32)
+        idx = np.arange(m * m, dtype=np.int64).reshape(m, m)
+        a, b, c, d = idx[:-1, :-1].ravel(), idx[:-1, 1:].ravel(), idx[1:, :-1].ravel(), idx[1:, 1:].ravel()
+        f = np.stack([np.stack([a, b, c], 1), np.stack([b, d, c], 1)], axis=1).reshape(-1, 3)
+        keep = rng.random(f.shape[0]) >= delete_frac
+        meshes.append((v, f[keep].astype(np.int32)))
+        if lvl + 1 < levels:
+            mc = (m + 1) // 2                                   # coarse grid size
+            ii, jj = np.meshgrid(np.arange(m), np.arange(m), indexing="ij")
+            rep = ((ii // 2) * 2 * m + (jj // 2) * 2).ravel()   # fine id of the cell's kept vertex
+            me = np.arange(m * m)
+            is_rep = rep == me
+            vt_map = np.full(m * m, -1, np.int32)
+            vt_map[is_rep] = ((ii // 2) * mc + (jj // 2)).ravel()[is_rep]
+            vt_replace = np.zeros(m * m, np.int32)
+            member = (~is_rep) & (rep > 0)
+            vt_replace[member] = -rep[member]
+            np.add.at(vt_replace, rep[member], 1)
+            maps.append((vt_replace, vt_map))
+        step *= 2
+    return meshes, maps
+
+
 # ------------------------------------------------------------------------------ batches
 @dataclass
 class MeshBatch:

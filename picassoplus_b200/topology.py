@@ -193,6 +193,47 @@ def vertex_csr(face: torch.Tensor, vt_map: Optional[torch.Tensor], nv_in: int, n
     return csr
 
 
+def prepare_level(vertex: torch.Tensor, face: torch.Tensor, vt_map: Optional[torch.Tensor], nv_out: int, L: int,
+                  orient: bool = False, want_geometry: bool = True, want_normals: bool = False):
+    """Everything a mesh level's convolutions need, in one library call: triangle geometry
+    (picasso/mesh/pi_modules/decimate.py:70-85), the (optionally origin-oriented,
+    picasso/networks/scene_seg.py:117-124) face normals, their spherical-harmonic filter coefficients
+    (picasso/mesh/layers.py:341-356), nfCount (decimate_gpu.cu:813-836) and the vertex CSR, which is
+    put into the cache for the operator calls that follow.  Returns a dict with keys geometry (Nf,5)
+    or None, normals (Nf,3) or None, coeff (Nf,(L+1)^2), nf_count (NvOut,), csr."""
+    if L >= 6 or L < 0:
+        raise NotImplementedError
+    if not (vertex.is_cuda and face.is_cuda) or vertex.dtype != torch.float32 or face.dtype != torch.int32:
+        raise RuntimeError("vertex must be a float32 and face an int32 CUDA tensor")
+    if vertex.dim() != 2 or vertex.shape[1] < 3 or face.dim() != 2 or face.shape[1] != 3:
+        raise RuntimeError("vertex must have shape (Nv, >=3) and face (Nf, 3)")
+    vertex, face = vertex.contiguous(), face.contiguous()
+    nv_in, nf = vertex.shape[0], face.shape[0]
+    dev = face.device
+    K = (L + 1) ** 2
+    with torch.cuda.device(dev):
+        geometry = torch.empty(nf, 5, dtype=torch.float32, device=dev) if want_geometry else None
+        normals = torch.empty(nf, 3, dtype=torch.float32, device=dev) if want_normals else None
+        coeff = torch.empty(nf, K, dtype=torch.float32, device=dev)
+        nf_count = torch.empty(nv_out, dtype=torch.int32, device=dev)
+        rowptr = torch.empty(nv_out + 1, dtype=torch.int32, device=dev)
+        entries = torch.empty(max(3 * nf, 1), dtype=torch.int32, device=dev)
+        status = torch.empty(1, dtype=torch.int32, device=dev)
+        wbytes = _lib.query("pb200_vertex_csr_workspace_bytes", nf, nv_out)
+        ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        _lib.call("pb200_level_prepare", nf, nv_in, nv_out, vertex.shape[1], ptr(vertex), ptr(face), ptr(vt_map), L,
+                  1 if orient else 0, ptr(geometry), ptr(normals), ptr(coeff), ptr(nf_count), ptr(rowptr), ptr(entries),
+                  ptr(status), ptr(ws), wbytes, stream_ptr(dev))
+        if _validation == "deferred":
+            with _lock:
+                _deferred.append((status, _bad_index_message(nv_in, nv_out)))
+        elif int(status.item()) != 0:
+            raise RuntimeError(_bad_index_message(nv_in, nv_out))
+    csr = VertexCSR(rowptr, entries, (face, vt_map), _versions(face, vt_map))
+    _store(_slot(face, vt_map, nv_in, nv_out), csr)
+    return dict(geometry=geometry, normals=normals, coeff=coeff, nf_count=nf_count, csr=csr)
+
+
 class ClusterCSR:
     """Decimation clusters of a fine level: key (NvIn,) = coarse id of each fine vertex or -1;
     rowptr (NvOut+1,), members (NvIn,) = member fine vertices of every coarse vertex, ascending."""

@@ -120,3 +120,35 @@ def test_bad_cluster_indices_are_reported(mods):
     with pytest.raises(RuntimeError):
         pool3d.avg_forward(c["x"], bad, c["vt_map"], torch.zeros(30, 3, device="cuda"))
     assert torch.isfinite(pool3d.avg_forward(c["x"], c["vt_replace"], c["vt_map"], torch.zeros(30, 3, device="cuda"))).all()
+
+
+@pytest.mark.parametrize("kind,L,orient", [("grid17x2", 4, False), ("grid17x2+drop", 3, True), ("ico2x3", 2, True),
+                                           ("tet+iso", 5, True)])
+def test_level_prepare_matches_the_separate_calls(kind, L, orient):
+    """pb200_level_prepare (one fused pass per mesh level) against the separate entry points, the
+    oracle, and the CSR built by pb200_build_vertex_csr: geometry and basis bit-identical to the
+    separate kernels, nfCount and CSR bit-exact."""
+    from cases import conv_inputs
+    from oracle import mesh_oracle as mo
+    from picassoplus_b200 import topology
+    from picassoplus_b200.math_utils import sph_harm_coeff
+    from picassoplus_b200.mesh.pi_modules import decimate
+    d = conv_inputs(kind, 4, 1, 4, 2, seed=33)
+    vertex = (d["vertex"] - 0.5).cuda()             # centre the meshes on the origin so both orientations occur
+    face, vt_map = d["face"].cuda(), d["vt_map"].cuda()
+    topology.clear_cache()
+    got = topology.prepare_level(vertex, face, vt_map, d["nv_out"], L, orient=orient, want_normals=True)
+    geo = decimate.compute_triangle_geometry_(vertex, face)
+    assert torch.equal(got["geometry"], geo)
+    want_n = mo.oriented_normals(geo.cpu(), vertex.cpu(), d["face"]) if orient else geo[:, :3].cpu()
+    assert torch.equal(got["normals"].cpu(), want_n)
+    if orient:
+        assert (want_n != geo[:, :3].cpu()).any()            # the case does flip some normals
+    assert torch.equal(got["coeff"], sph_harm_coeff(L, got["normals"]))
+    assert max_abs(got["coeff"], mo.sph_harm_coeff(L, want_n)) <= 2e-6
+    assert torch.equal(got["nf_count"].cpu(), mo.count_vertex_adjface(d["face"], d["vt_map"], d["nv_out"]))
+    ref_csr = topology.build_vertex_csr(face, vt_map, d["vt_map"].shape[0], d["nv_out"])
+    assert torch.equal(got["csr"].rowptr, ref_csr.rowptr)
+    n = int(ref_csr.rowptr[-1])
+    assert torch.equal(got["csr"].entries[:n], ref_csr.entries[:n])
+    assert topology.vertex_csr(face, vt_map, d["vt_map"].shape[0], d["nv_out"]) is got["csr"]     # served from the cache
