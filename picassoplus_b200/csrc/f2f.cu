@@ -12,7 +12,7 @@ int f2f_simt_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const f
                       void* ws, cudaStream_t stream, bool want_gin, bool want_gfilter);
 namespace tc {
 bool fwd_supported(int Cin, int Cout, int F);
-size_t fwd_workspace_bytes(int Cin, int Cout, int F, int precision);
+size_t fwd_workspace_bytes(int64_t NiK, int Cin, int Cout, int F, int precision);
 int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input, const float* filter,
             const float* bary, const int32_t* cum, float* output, int precision, void* ws, cudaStream_t stream);
 int check_async_error(const char* where);
@@ -34,6 +34,9 @@ int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, con
 int padded_F(int F);
 size_t padded_bary_bytes(int64_t NiK, int F);
 int pad_bary(int64_t NiK, int F, const float* bary, float* dst, cudaStream_t stream);
+int padded_channels(int Cin);
+size_t padded_input_bytes(int64_t NiK, int Cin);
+int pad_input(int64_t NiK, int Cin, const float* input, float* dst, cudaStream_t stream);
 }  // namespace tc
 }  // namespace pb
 
@@ -59,7 +62,7 @@ extern "C" {
 
 size_t pb200_facet2facet_forward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
     if (!f2f_sizes_ok(Nf, NiK, Cin, Cout, F)) return 0;
-    if (use_tc_fwd(Cin, Cout, F, precision)) return tc::fwd_workspace_bytes(Cin, Cout, F, precision);
+    if (use_tc_fwd(Cin, Cout, F, precision)) return tc::fwd_workspace_bytes(NiK, Cin, Cout, F, precision);
     return f2f_simt_fwd_ws(Nf, Cin, Cout, F);
 }
 
@@ -92,6 +95,7 @@ size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int C
     if (tg) n += tc::gin::workspace_bytes(Cin, Cout, F, precision);
     if (tf) n += tc::gfilter::workspace_bytes(Nf, Cin, Cout, F, precision);
     if (tg || tf) n += tc::padded_bary_bytes(NiK, F);
+    if (tf) n += tc::padded_input_bytes(NiK, Cin);
     return n;
 }
 
@@ -139,7 +143,17 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
         w += tc::gin::workspace_bytes(Cin, Cout, F, precision);
     }
     if (tf) {
-        int rc = tc::gfilter::backward_filter(Nf, Cin, Cout, F, gradOutput, input, bary_p, Fp, numInterior, gradFilter,
+        // the filter-gradient kernel reads 16 input channels per CTA with 16-byte copies: channel counts that
+        // are not a multiple of 16 go through a zero-padded copy at the end of the workspace
+        const float* input_p = input;
+        if (Cin % 16 != 0 && NiK > 0) {
+            char* wx = (char*)workspace + pb200_facet2facet_backward_workspace_bytes(Nf, NiK, Cin, Cout, F, precision) -
+                       tc::padded_input_bytes(NiK, Cin);
+            int rc = tc::pad_input(NiK, Cin, input, (float*)wx, stream);
+            if (rc) return rc;
+            input_p = (const float*)wx;
+        }
+        int rc = tc::gfilter::backward_filter(Nf, Cin, Cout, F, gradOutput, input_p, bary_p, Fp, numInterior, gradFilter,
                                               precision, w, stream);
         if (rc) return rc;
     }

@@ -44,8 +44,10 @@ constexpr int TMEM_COLS = 256;
 
 // ---- bf16 filter image: Wimg[kb][split][co 0..127][32 bf16, 64B-swizzled], kb = c16*ceil(F/2) + dp,
 //      element (co, j*16 + kk) = filter[co][c16*16 + kk][2*dp + j]  (0 for a basis >= F)
-__global__ void f2f_tc_prep_filter_bf16_kernel(int F, int Cin, int Cout, int nsplit, const float* __restrict__ filter,
-                                               uint8_t* __restrict__ wimg) {
+//      Cin = channels padded to 16 (CinF = channels of the filter; padded ones are 0); the image holds
+//      output channels co0 .. co0 + Cout - 1 of the filter.
+__global__ void f2f_tc_prep_filter_bf16_kernel(int F, int Cin, int CinF, int co0, int Cout, int nsplit,
+                                               const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
     const int nd2 = (F + 1) / 2;
     const int nkb = (Cin / 16) * nd2;
     int64_t total = (int64_t)nkb * 128 * 4;
@@ -62,7 +64,7 @@ __global__ void f2f_tc_prep_filter_bf16_kernel(int F, int Cin, int Cout, int nsp
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int ci = c16 * 16 + (c & 1) * 8 + 2 * j + e;
-                v[e] = (co < Cout && d < F) ? __ldg(filter + ((int64_t)co * Cin + ci) * F + d) : 0.f;
+                v[e] = (co < Cout && d < F && ci < CinF) ? __ldg(filter + ((int64_t)(co0 + co) * CinF + ci) * F + d) : 0.f;
             }
             if (nsplit == 1) { hi[j] = pack_bf16x2(v[0], v[1]); lo[j] = 0u; }
             else split_bf16x2(v[0], v[1], hi[j], lo[j]);
@@ -76,8 +78,8 @@ __global__ void f2f_tc_prep_filter_bf16_kernel(int F, int Cin, int Cout, int nsp
 
 // ---- filter image: Wimg[kb][split][co 0..127][16 floats, 64B-swizzled], kb = c16*F + d,
 //      element (co, kk) = filter[co][c16*16 + kk][d]
-__global__ void f2f_tc_prep_filter_kernel(int F, int Cin, int Cout, int nsplit, const float* __restrict__ filter,
-                                          uint8_t* __restrict__ wimg) {
+__global__ void f2f_tc_prep_filter_kernel(int F, int Cin, int CinF, int co0, int Cout, int nsplit,
+                                          const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
     const int nkb = (Cin / KS) * F;
     int64_t total = (int64_t)nkb * UM * 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -89,7 +91,8 @@ __global__ void f2f_tc_prep_filter_kernel(int F, int Cin, int Cout, int nsplit, 
         float v[4], hi[4], lo[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            v[j] = co < Cout ? __ldg(filter + ((int64_t)co * Cin + c16 * KS + c * 4 + j) * F + d) : 0.f;
+            const int ci = c16 * KS + c * 4 + j;
+            v[j] = (co < Cout && ci < CinF) ? __ldg(filter + ((int64_t)(co0 + co) * CinF + ci) * F + d) : 0.f;
             if (nsplit == 1) { hi[j] = to_tf32_rna(v[j]); lo[j] = 0.f; }
             else { hi[j] = tf32_hi(v[j]); lo[j] = v[j] - hi[j]; }
         }
@@ -111,7 +114,8 @@ struct FwdParams {
     const float* bary;
     const int32_t* cum;
     const uint8_t* wimg;
-    float* out;
+    float* out;           // first output channel of this launch's chunk
+    int out_stride;       // floats per output row (all output channels of the operator)
     int* async_err;
     int wait_budget;      // bounded waits give up after this many units of 1024 clocks
     int silent_filter;    // test switch: the filter stream issues nothing, so every wait runs out
@@ -332,7 +336,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         int64_t fo = f0 + col + j;
-                        if (fo < p.Nf) __stcs(p.out + fo * Cout + co, __uint_as_float(r[j]));
+                        if (fo < p.Nf) __stcs(p.out + fo * p.out_stride + co, __uint_as_float(r[j]));
                     }
                 }
             }
@@ -410,10 +414,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
     }
 }
 
+// rows of C floats -> rows of Cp >= C floats, pad columns zero (thread = one float of the padded row)
+__global__ void pad_rows_kernel(int64_t n, int C, int Cp, const float* __restrict__ src, float* __restrict__ dst) {
+    const int64_t total = n * Cp;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / Cp;
+        const int c = (int)(i - r * Cp);
+        dst[i] = c < C ? __ldg(src + r * C + c) : 0.f;
+    }
+}
+
+int padded_channels(int Cin) { return (Cin + KS - 1) / KS * KS; }
+size_t padded_input_bytes(int64_t NiK, int Cin) {
+    return Cin % KS == 0 ? 0 : align_up((size_t)(NiK > 0 ? NiK : 1) * padded_channels(Cin) * sizeof(float), 256);
+}
+int pad_input(int64_t NiK, int Cin, const float* input, float* dst, cudaStream_t stream) {
+    if (NiK <= 0) return PB200_OK;
+    const int Cp = padded_channels(Cin);
+    PB_LAUNCH("f2f_pad_input", pad_rows_kernel, persistent_blocks(NiK * Cp, 256, 8), 256, 0, stream, NiK, Cin, Cp, input, dst);
+    return PB200_OK;
+}
+
 // ---------------------------------------------------------------------------- host side
 struct FwdPlan { int nsplit, bf, nkb, nstages, smaxw, bpitch; size_t smem; size_t wimg_bytes; };
 
-bool fwd_supported(int Cin, int Cout, int F) { return Cin % KS == 0 && Cout >= 1 && Cout <= UM && F >= 1 && F <= 50; }
+// every channel count: input channels are zero-padded to a multiple of 16 (a copy in the workspace),
+// output channels are walked in chunks of 128 (one launch each over the same input)
+bool fwd_supported(int Cin, int Cout, int F) { return Cin >= 1 && Cout >= 1 && F >= 1 && F <= 50; }
 
 FwdPlan fwd_plan(int Cin, int Cout, int F, int precision) {
     FwdPlan pl;
@@ -435,45 +462,54 @@ FwdPlan fwd_plan(int Cin, int Cout, int F, int precision) {
     return pl;
 }
 
-size_t fwd_workspace_bytes(int Cin, int Cout, int F, int precision) {
-    return align_up(fwd_plan(Cin, Cout, F, precision).wimg_bytes, 256);
+size_t fwd_workspace_bytes(int64_t NiK, int Cin, int Cout, int F, int precision) {
+    return align_up(fwd_plan(padded_channels(Cin), Cout, F, precision).wimg_bytes, 256) + padded_input_bytes(NiK, Cin);
 }
 
 int forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* input, const float* filter,
             const float* bary, const int32_t* cum, float* output, int precision, void* ws, cudaStream_t stream) {
-    (void)NiK;
     int rc = check_async_error("facet2facet_forward");
     if (rc) return rc;
-    FwdPlan pl = fwd_plan(Cin, Cout, F, precision);
+    const int CinP = padded_channels(Cin);
+    FwdPlan pl = fwd_plan(CinP, Cout, F, precision);
     uint8_t* wimg = (uint8_t*)ws;
-    int64_t prep_items = (int64_t)pl.nkb * UM * 4;
-    if (pl.bf) {
-        PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_bf16_kernel, persistent_blocks(prep_items, 256, 8), 256, 0,
-                  stream, F, Cin, Cout, pl.nsplit, filter, wimg);
-    } else {
-        PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_kernel, persistent_blocks(prep_items, 256, 8), 256, 0, stream,
-                  F, Cin, Cout, pl.nsplit, filter, wimg);
+    if (CinP != Cin) {
+        float* xp = (float*)((char*)ws + align_up(pl.wimg_bytes, 256));
+        rc = pad_input(NiK, Cin, input, xp, stream);
+        if (rc) return rc;
+        input = xp;
     }
-    FwdParams p;
-    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F;
-    p.nstages = pl.nstages; p.smaxw = pl.smaxw; p.bpitch = pl.bpitch;
-    p.in = input; p.bary = bary; p.cum = cum; p.wimg = wimg; p.out = output;
-    p.async_err = async_error_word();
-    p.wait_budget = wait_budget_kclocks();
-    p.silent_filter = test_skip_filter_stream();
-    int64_t ntiles = ceil_div(Nf, TILE_F);
-    int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
+    const int64_t prep_items = (int64_t)pl.nkb * UM * 4;
+    const int64_t ntiles = ceil_div(Nf, TILE_F);
+    const int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
+    for (int co0 = 0; co0 < Cout; co0 += UM) {
+        const int cchunk = Cout - co0 < UM ? Cout - co0 : UM;
+        if (pl.bf) {
+            PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_bf16_kernel, persistent_blocks(prep_items, 256, 8), 256, 0,
+                      stream, F, CinP, Cin, co0, cchunk, pl.nsplit, filter, wimg);
+        } else {
+            PB_LAUNCH("f2f_tc_prep_filter", f2f_tc_prep_filter_kernel, persistent_blocks(prep_items, 256, 8), 256, 0, stream,
+                      F, CinP, Cin, co0, cchunk, pl.nsplit, filter, wimg);
+        }
+        FwdParams p;
+        p.Nf = Nf; p.Cin = CinP; p.Cout = cchunk; p.F = F;
+        p.nstages = pl.nstages; p.smaxw = pl.smaxw; p.bpitch = pl.bpitch;
+        p.in = input; p.bary = bary; p.cum = cum; p.wimg = wimg; p.out = output + co0; p.out_stride = Cout;
+        p.async_err = async_error_word();
+        p.wait_budget = wait_budget_kclocks();
+        p.silent_filter = test_skip_filter_stream();
 #define PB_FWD_LAUNCH(NS, BFV)                                                                                      \
     do {                                                                                                              \
         PB_CUDA(cudaFuncSetAttribute(f2f_fwd_tc_kernel<NS, BFV>, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
                                      (int)pl.smem));                                                                  \
         PB_LAUNCH("f2f_fwd_tc", (f2f_fwd_tc_kernel<NS, BFV>), grid, NTHREADS, pl.smem, stream, p);                    \
     } while (0)
-    if (pl.nsplit == 2 && pl.bf) PB_FWD_LAUNCH(2, true);
-    else if (pl.nsplit == 2) PB_FWD_LAUNCH(2, false);
-    else if (pl.bf) PB_FWD_LAUNCH(1, true);
-    else PB_FWD_LAUNCH(1, false);
+        if (pl.nsplit == 2 && pl.bf) PB_FWD_LAUNCH(2, true);
+        else if (pl.nsplit == 2) PB_FWD_LAUNCH(2, false);
+        else if (pl.bf) PB_FWD_LAUNCH(1, true);
+        else PB_FWD_LAUNCH(1, false);
 #undef PB_FWD_LAUNCH
+    }
     return PB200_OK;
 }
 

@@ -149,7 +149,8 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 
 struct Params {
     int64_t Nf;
-    int Cin, Cout, F;
+    int Cin, Cout, F;         // Cin: channels of `in` (a multiple of 16); Cout: output channels of this launch's chunk
+    int CinF, CoutF, co0;     // channels of the filter gradient, and the chunk's first output channel
     int Fp;                   // floats per row of the padded bary copy (F rounded up to 4)
     int ncg;                  // channel groups = Cin / 16
     int nchunks;              // face chunks
@@ -322,8 +323,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             u = zero4(); w = zero4();
             const int64_t f = (st0 + st) * KF + 2 * warp;
             if (st >= nst || 4 * lane >= Cout) return;
-            if (f < p.Nf) u = ldg4(reinterpret_cast<const float4*>(p.gout + f * Cout) + lane);
-            if (f + 1 < p.Nf) w = ldg4(reinterpret_cast<const float4*>(p.gout + (f + 1) * Cout) + lane);
+            if (f < p.Nf) u = ldg4(reinterpret_cast<const float4*>(p.gout + f * p.CoutF + p.co0) + lane);
+            if (f + 1 < p.Nf) w = ldg4(reinterpret_cast<const float4*>(p.gout + (f + 1) * p.CoutF + p.co0) + lane);
         };
         float4 gu0, gw0, gu1, gw1;                            // stages st and st + 1
         load_g(0, gu0, gw0);
@@ -410,7 +411,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             tc_fence_after();
             const int q = warp & 3, hcol = warp >> 2;       // TMEM lane quadrant, half of the 32-column groups
             const int co = q * 32 + lane;
-            float* out = p.partial + (int64_t)chunk * Cout * Cin * F;
+            float* out = p.partial + (int64_t)chunk * p.CoutF * p.CinF * F;
             const int ngroups = (NR + 31) / 32;
             for (int gi = hcol; gi < ngroups; gi += CWARPS / 4) {
                 uint32_t r[32];
@@ -421,8 +422,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                     for (int j = 0; j < 32; ++j) {
                         int col = gi * 32 + j;
                         if (col < NR) {
-                            const int d = col / CG, kk = col - d * CG;
-                            out[((int64_t)co * Cin + cgp * CG + kk) * F + d] = nst > 0 ? __uint_as_float(r[j]) : 0.f;
+                            const int d = col / CG, kk = col - d * CG, ci = cgp * CG + kk;
+                            if (ci < p.CinF)
+                                out[((int64_t)(p.co0 + co) * p.CinF + ci) * F + d] = nst > 0 ? __uint_as_float(r[j]) : 0.f;
                         }
                     }
                 }
@@ -515,8 +517,10 @@ __global__ void pad_bary_kernel(int64_t n, int F, int Fp, const float* __restric
 // ---------------------------------------------------------------------------- host side
 struct Plan { int nsplit, bf, ncg, nchunks, nstages, nraw; int64_t stages_per_chunk; size_t smem, partial_bytes; };
 
+// every channel count: `input` must come with its channels padded to a multiple of 16 (tc::pad_input),
+// output channels are walked in chunks of 128; rows of gradOutput are read 16 bytes at a time
 bool supported(int Cin, int Cout, int F) {
-    return Cin % CG == 0 && Cout % 4 == 0 && Cout >= 4 && Cout <= UM && F >= 1 && F <= 32;   // F*16 <= 512 columns
+    return Cin >= 1 && Cout % 4 == 0 && Cout >= 4 && F >= 1 && F <= 32;   // F*16 <= 512 columns
 }
 
 Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
@@ -524,7 +528,7 @@ Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     const OperandMode om = operand_mode(precision);
     pl.nsplit = om.nsplit;
     pl.bf = om.bf;
-    pl.ncg = Cin / CG;
+    pl.ncg = (Cin + CG - 1) / CG;
     int64_t total_stages = ceil_div(Nf > 0 ? Nf : 1, KF);
     int nch = sm_count() / pl.ncg;
     if (nch < 1) nch = 1;
@@ -553,17 +557,19 @@ size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision) {
     return align_up(plan(Nf, Cin, Cout, F, precision).partial_bytes, 256);
 }
 
-// `bary_p`: bary with rows of `Fp` floats (F rounded up to 4, pad columns zero; see tc::pad_bary)
-int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* input, const float* bary_p,
+// `bary_p`: bary with rows of `Fp` floats (F rounded up to 4, pad columns zero; see tc::pad_bary);
+// `input_p`: input with rows of Cin rounded up to 16 floats (pad channels zero; see tc::pad_input)
+int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* input_p, const float* bary_p,
                     int Fp, const int32_t* cum, float* gfilter, int precision, void* ws, cudaStream_t stream) {
     int rc = check_async_error("facet2facet_backward");
     if (rc) return rc;
     Plan pl = plan(Nf, Cin, Cout, F, precision);
     Params p;
-    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout; p.F = F; p.Fp = Fp;
+    p.Nf = Nf; p.Cin = pl.ncg * CG; p.F = F; p.Fp = Fp;
+    p.CinF = Cin; p.CoutF = Cout;
     p.ncg = pl.ncg; p.nchunks = pl.nchunks; p.stages_per_chunk = pl.stages_per_chunk;
     p.nstages = pl.nstages; p.nraw = pl.nraw;
-    p.gout = gout; p.in = input; p.cum = cum; p.partial = (float*)ws;
+    p.gout = gout; p.in = input_p; p.cum = cum; p.partial = (float*)ws;
     p.bary = bary_p;
     p.async_err = async_error_word();
     p.wait_budget = wait_budget_kclocks();
@@ -574,10 +580,14 @@ int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, con
                                      (int)pl.smem));                                                                  \
         PB_LAUNCH("f2f_bwd_gfilter_tc", (f2f_bwd_gfilter_tc_kernel<NS, BFV>), grid, NTHREADS, pl.smem, stream, p);    \
     } while (0)
-    if (pl.nsplit == 2 && pl.bf) PB_GF_LAUNCH(2, true);
-    else if (pl.nsplit == 2) PB_GF_LAUNCH(2, false);
-    else if (pl.bf) PB_GF_LAUNCH(1, true);
-    else PB_GF_LAUNCH(1, false);
+    for (int co0 = 0; co0 < Cout; co0 += UM) {          // every launch writes its rows of every face chunk's partial
+        p.co0 = co0;
+        p.Cout = Cout - co0 < UM ? Cout - co0 : UM;
+        if (pl.nsplit == 2 && pl.bf) PB_GF_LAUNCH(2, true);
+        else if (pl.nsplit == 2) PB_GF_LAUNCH(2, false);
+        else if (pl.bf) PB_GF_LAUNCH(1, true);
+        else PB_GF_LAUNCH(1, false);
+    }
 #undef PB_GF_LAUNCH
     return reduce_partials((const float*)ws, pl.nchunks, (int64_t)Cout * Cin * F, gfilter, stream);
 }

@@ -91,7 +91,8 @@ __device__ __forceinline__ void tmem_ld_row(uint32_t taddr, float* v) {
 
 // ---- filter image: Wimg[slice][kst][split][row 0..255][16 floats, 64B-swizzled];
 //      row = cil*F + d, element (row, kk) = filter[co = kst*16 + kk][ci = slice*NQ + cil][d]
-__global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int Cout, int nq, int nslices, int kst, int nsplit,
+//      (co counts from the chunk's first output channel co0)
+__global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int co0, int Cout, int nq, int nslices, int kst, int nsplit,
                                               const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
     int64_t total = (int64_t)nslices * kst * NCOLS * 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -107,7 +108,7 @@ __global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int Cout, int nq, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             int co = ks * KS + c * 4 + j;
-            float v = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)co * Cin + ci) * F + d) : 0.f;
+            float v = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)(co0 + co) * Cin + ci) * F + d) : 0.f;
             if (nsplit == 1) { hi[j] = to_tf32_rna(v); lo[j] = 0.f; }
             else { hi[j] = tf32_hi(v); lo[j] = v - hi[j]; }
         }
@@ -121,8 +122,9 @@ __global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int Cout, int nq, 
 
 // ---- bf16 filter image: Wimg[slice][kst][split][row 0..255][32 bf16, 64B-swizzled];
 //      row = cil*F + d, element (row, kk) = filter[co = kst*32 + kk][ci = slice*NQ + cil][d]
-__global__ void f2f_tc_gin_prep_filter_bf16_kernel(int F, int Cin, int Cout, int nq, int nslices, int kst, int nsplit,
-                                                   const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
+__global__ void f2f_tc_gin_prep_filter_bf16_kernel(int F, int Cin, int co0, int Cout, int nq, int nslices, int kst,
+                                                   int nsplit, const float* __restrict__ filter,
+                                                   uint8_t* __restrict__ wimg) {
     int64_t total = (int64_t)nslices * kst * NCOLS * 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -140,7 +142,7 @@ __global__ void f2f_tc_gin_prep_filter_bf16_kernel(int F, int Cin, int Cout, int
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 int co = ks * 32 + c * 8 + 2 * j + e;
-                v[e] = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)co * Cin + ci) * F + d) : 0.f;
+                v[e] = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)(co0 + co) * Cin + ci) * F + d) : 0.f;
             }
             if (nsplit == 1) { hi[j] = pack_bf16x2(v[0], v[1]); lo[j] = 0u; }
             else split_bf16x2(v[0], v[1], hi[j], lo[j]);
@@ -159,7 +161,9 @@ struct Params {
     int nstages;                     // filter ring depth
     int gbufs;                       // gradOutput tile buffers (2 = the copy runs a tile ahead)
     int bary_rows, bpitch;           // staged bary rows per tile (0 = read from global), row pitch in floats
-    const float* gout;
+    const float* gout;               // first output channel of this launch's chunk
+    int g_stride;                    // floats per gradOutput row (all output channels of the operator)
+    int accumulate;                  // 0: gradInput = result; 1: gradInput += result (later output-channel chunks)
     const float* bary;
     const float* bary_p;             // bary with rows padded to Fp floats (pad columns zero)
     int Fp;
@@ -303,7 +307,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                 // those pairs, two samples and two channels at a time, no shared-memory traffic at all.
                 if (lean) {
                     const int ci0 = slice * p.nq;
-                    const bool vec = ((ci0 | Cin) & 1) == 0;           // float2 stores stay 8-byte aligned
                     // accumulator columns of the first channel pair; later pairs are requested as soon as
                     // the registers of the previous one are free, so the loads overlap the sums and stores
                     float2 va[FH], vb[FH];
@@ -361,15 +364,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                                 // four channels (a scattered store costs the same pass whatever its width)
                                 if ((ci & 2) == 0) { h0 = g0; h1 = g1; }
                                 else {
-                                    if (on0) *reinterpret_cast<float4*>(d0 - 2) = make_float4(h0.x, h0.y, g0.x, g0.y);
-                                    if (on1) *reinterpret_cast<float4*>(d1 - 2) = make_float4(h1.x, h1.y, g1.x, g1.y);
+                                    float4 v0 = make_float4(h0.x, h0.y, g0.x, g0.y), v1 = make_float4(h1.x, h1.y, g1.x, g1.y);
+                                    if (p.accumulate) {
+                                        if (on0) add4(v0, *reinterpret_cast<const float4*>(d0 - 2));
+                                        if (on1) add4(v1, *reinterpret_cast<const float4*>(d1 - 2));
+                                    }
+                                    if (on0) *reinterpret_cast<float4*>(d0 - 2) = v0;
+                                    if (on1) *reinterpret_cast<float4*>(d1 - 2) = v1;
                                 }
-                            } else if (vec && has_b) {
-                                if (on0) *reinterpret_cast<float2*>(d0) = g0;
-                                if (on1) *reinterpret_cast<float2*>(d1) = g1;
                             } else {
-                                if (on0) { d0[0] = g0.x; if (has_b) d0[1] = g0.y; }
-                                if (on1) { d1[0] = g1.x; if (has_b) d1[1] = g1.y; }
+                                const float a0 = p.accumulate && on0 ? d0[0] : 0.f, a1 = p.accumulate && on1 ? d1[0] : 0.f;
+                                const float b0 = p.accumulate && on0 && has_b ? d0[1] : 0.f;
+                                const float b1 = p.accumulate && on1 && has_b ? d1[1] : 0.f;
+                                if (on0) { d0[0] = g0.x + a0; if (has_b) d0[1] = g0.y + b0; }
+                                if (on1) { d1[0] = g1.x + a1; if (has_b) d1[1] = g1.y + b1; }
                             }
                         }
                     }
@@ -414,8 +422,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                             }
                             const int64_t idx = (int64_t)(k0 + t) * Cin + ci;
                             float* dst = p.gin + idx;
-                            if (has_b && ((idx & 1) == 0)) *reinterpret_cast<float2*>(dst) = make_float2(ga * invT, gb * invT);
-                            else { dst[0] = ga * invT; if (has_b) dst[1] = gb * invT; }
+                            const float olda = p.accumulate ? dst[0] : 0.f, oldb = (p.accumulate && has_b) ? dst[1] : 0.f;
+                            dst[0] = ga * invT + olda;
+                            if (has_b) dst[1] = gb * invT + oldb;
                         }
                     }
                 }
@@ -458,7 +467,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
                     const int idx = base + j * GWARPS * 32 + gt;
                     const int rr = idx / cpr, c = idx - rr * cpr;
                     const int64_t fr = f0 + rr;
-                    const float4* src = reinterpret_cast<const float4*>(p.gout + fr * Cout);
+                    const float4* src = reinterpret_cast<const float4*>(p.gout + fr * p.g_stride);
                     u[j] = zero4(); w[j] = zero4();
                     if (BF) {
                         if (idx < ntasks && fr < p.Nf && c * 8 < Cout) u[j] = ldg4(src + 2 * c);
@@ -586,12 +595,15 @@ struct Plan { int nsplit, bf, nq, nslices, kst, nmma, nstages, gbufs, bary_rows,
 
 static bool f_templated(int F) { return F == 4 || F == 9 || F == 16 || F == 25 || F == 36; }
 
+// output channels beyond 256 are walked in chunks of 256; chunks after the first add to gradInput
+constexpr int MAX_COUT = 256;
 bool supported(int Cin, int Cout, int F) {
-    return f_templated(F) && Cout % 4 == 0 && Cout >= 4 && Cout <= 256 && Cin >= 1;
+    return f_templated(F) && Cout % 4 == 0 && Cout >= 4 && Cin >= 1;
 }
 
-Plan plan(int Cin, int Cout, int F, int precision) {
+Plan plan(int Cin, int CoutAll, int F, int precision) {
     Plan pl;
+    const int Cout = CoutAll < MAX_COUT ? CoutAll : MAX_COUT;          // the widest chunk sizes the buffers
     const OperandMode om = operand_mode(precision);
     pl.nsplit = om.nsplit;
     pl.bf = om.bf;
@@ -655,25 +667,32 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
     if (rc) return rc;
     Plan pl = plan(Cin, Cout, F, precision);
     uint8_t* wimg = (uint8_t*)ws;
-    int64_t items = (int64_t)pl.nslices * pl.kst * NCOLS * 4;
-    if (pl.bf) {
-        PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_bf16_kernel, persistent_blocks(items, 256, 8), 256, 0,
-                  stream, F, Cin, Cout, pl.nq, pl.nslices, pl.kst, pl.nsplit, filter, wimg);
-    } else {
-        PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_kernel, persistent_blocks(items, 256, 8), 256, 0,
-                  stream, F, Cin, Cout, pl.nq, pl.nslices, pl.kst, pl.nsplit, filter, wimg);
+    const int64_t ntiles = ceil_div(Nf, TILE_M);
+    const int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
+    for (int co0 = 0; co0 < Cout; co0 += MAX_COUT) {
+        const int cchunk = Cout - co0 < MAX_COUT ? Cout - co0 : MAX_COUT;
+        const int kst = pl.bf ? (cchunk + 31) / 32 : (cchunk + KS - 1) / KS;
+        const int64_t items = (int64_t)pl.nslices * kst * NCOLS * 4;
+        if (pl.bf) {
+            PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_bf16_kernel, persistent_blocks(items, 256, 8), 256, 0,
+                      stream, F, Cin, co0, cchunk, pl.nq, pl.nslices, kst, pl.nsplit, filter, wimg);
+        } else {
+            PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_kernel, persistent_blocks(items, 256, 8), 256, 0,
+                      stream, F, Cin, co0, cchunk, pl.nq, pl.nslices, kst, pl.nsplit, filter, wimg);
+        }
+        Params p;
+        p.Nf = Nf; p.Cin = Cin; p.Cout = cchunk;
+        p.nq = pl.nq; p.nslices = pl.nslices; p.kst = kst; p.nmma = pl.nmma;
+        p.nstages = pl.nstages; p.gbufs = pl.gbufs; p.bary_rows = pl.bary_rows; p.bpitch = pl.bpitch;
+        p.gout = gout + co0; p.g_stride = Cout; p.accumulate = co0 > 0 ? 1 : 0;
+        p.bary = bary; p.bary_p = bary_p; p.Fp = Fp; p.cum = cum; p.wimg = wimg; p.gin = gin;
+        p.async_err = async_error_word();
+        p.wait_budget = wait_budget_kclocks();
+        if (pl.bf) rc = pl.nsplit == 2 ? launch_f<2, true>(F, p, grid, pl.smem, stream) : launch_f<1, true>(F, p, grid, pl.smem, stream);
+        else rc = pl.nsplit == 2 ? launch_f<2, false>(F, p, grid, pl.smem, stream) : launch_f<1, false>(F, p, grid, pl.smem, stream);
+        if (rc) return rc;
     }
-    Params p;
-    p.Nf = Nf; p.Cin = Cin; p.Cout = Cout;
-    p.nq = pl.nq; p.nslices = pl.nslices; p.kst = pl.kst; p.nmma = pl.nmma;
-    p.nstages = pl.nstages; p.gbufs = pl.gbufs; p.bary_rows = pl.bary_rows; p.bpitch = pl.bpitch;
-    p.gout = gout; p.bary = bary; p.bary_p = bary_p; p.Fp = Fp; p.cum = cum; p.wimg = wimg; p.gin = gin;
-    p.async_err = async_error_word();
-    p.wait_budget = wait_budget_kclocks();
-    int64_t ntiles = ceil_div(Nf, TILE_M);
-    int grid = (int)(ntiles < sm_count() ? ntiles : sm_count());
-    if (pl.bf) return pl.nsplit == 2 ? launch_f<2, true>(F, p, grid, pl.smem, stream) : launch_f<1, true>(F, p, grid, pl.smem, stream);
-    return pl.nsplit == 2 ? launch_f<2, false>(F, p, grid, pl.smem, stream) : launch_f<1, false>(F, p, grid, pl.smem, stream);
+    return PB200_OK;
 }
 
 }  // namespace gin

@@ -221,8 +221,10 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // hi = bf16(v), lo = bf16(v - hi) for two values at once
 __device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& lo) {
     hi = pack_bf16x2(a, b);
-    const float ah = __uint_as_float(hi << 16), bh = __uint_as_float(hi & 0xFFFF0000u);
-    lo = pack_bf16x2(a - ah, b - bh);
+    // both remainders with one packed FMA: (a, b) - (hi_a, hi_b)
+    const float2 h2 = make_float2(__uint_as_float(hi << 16), __uint_as_float(hi & 0xFFFF0000u));
+    const float2 r = __ffma2_rn(h2, make_float2(-1.f, -1.f), make_float2(a, b));
+    lo = pack_bf16x2(r.x, r.y);
 }
 
 // Shared-memory matrix descriptor of an MN-major operand tile of 16-bit elements with the

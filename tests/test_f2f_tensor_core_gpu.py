@@ -22,6 +22,9 @@ SHAPES = [
     ("grid17x2", 64, 9, 128, 9),       # faces with more samples than stay in registers / staged rows
     ("ico1x2", 48, 4, 100, 2),         # Cout not a multiple of 32, Cin = 3 groups
     ("tri", 16, 16, 16, 3),            # a single face
+    ("ico2x3", 3, 16, 32, 4),          # the reference networks' texture entry (RGB in, 32 out): channels padded to 16
+    ("grid17x2", 40, 25, 200, 4),      # channels padded 40 -> 48, output channels in two chunks (128 + 72)
+    ("grid9x1", 256, 16, 384, 3),      # output channels in three chunks; input gradient accumulates over 256 + 128
 ]
 
 
@@ -81,10 +84,32 @@ def test_forward_many_tiles_vs_ffma_path(mods):
 
 
 BWD_SHAPES = SHAPES + [
-    ("grid17x2", 7, 36, 12, 4),        # odd channel count, F = 36 (7 channels per slice), Cout = 12
-    ("grid17x2", 40, 25, 200, 4),      # Cout above 128: forward falls back, input gradient still tensor-core
-    ("ico2x3", 3, 16, 32, 4),          # the reference networks' texture entry: RGB in, 32 out
+    ("grid17x2", 7, 36, 12, 4),        # odd channel count, F = 36 (7 channels per slice; filter gradient on the FFMA path)
 ]
+
+
+@pytest.mark.parametrize("kind,C,K,cout,tmax", [("ico2x3", 3, 16, 32, 4), ("grid17x2", 40, 25, 200, 4),
+                                                ("grid9x1", 256, 16, 384, 3), ("grid33x2", 128, 25, 128, 4)])
+def test_every_channel_count_runs_on_the_tensor_cores(mods, kind, C, K, cout, tmax):
+    """Channel counts that are no multiple of 16 and output widths above 128 / 256 still take the three
+    tcgen05 kernels (the library's per-kernel timing table names what was launched), never the FFMA path."""
+    conv3d, _ = mods
+    from picassoplus_b200 import _lib
+    c = _dev(conv_inputs(kind, C, 1, K, cout, seed=47, max_per_face=tmax))
+    conv3d.set_f2f_precision("fp32")
+    _lib.prof_reset()
+    _lib.prof_enable(True)
+    try:
+        conv3d.facet2facet_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+        conv3d.facet2facet_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
+        torch.cuda.synchronize()
+    finally:
+        _lib.prof_enable(False)
+    names = {n for n, _, _ in _lib.prof_read(64)}
+    _lib.prof_reset()
+    assert {"f2f_fwd_tc", "f2f_bwd_gin_tc", "f2f_bwd_gfilter_tc"} <= names, names
+    assert not any("sgemm" in n or n.startswith("f2f_build_A") or n == "f2f_gin_from_gA" for n in names), names
+
 
 
 @pytest.mark.parametrize("mode", MODES)

@@ -136,9 +136,11 @@ def test_facet2facet_fp32(mods, kind, C, r, K, cout):
         # The FFMA path must be as close as the reference (factor 4 covers the different summation
         # order).  The tensor-core modes of "fp32" keep 16 (bf16 hi+lo) or 21 (tf32 hi+lo) mantissa bits
         # per operand and drop the lo*lo product, so they sit further from fp64 than an FFMA chain
-        # while staying inside the 1e-4 gate: bounded by the factors below.  The floor term covers
-        # tensors the reference gets exactly right.
-        for mode, k in (("fp32", ARB_FP32), ("fp32_tf32x3", ARB_TF32X3), ("fp32_ffma", 4.0)):
+        # while staying inside the 1e-4 gate: bounded by the factors below, with a floor of 2e-5 of the
+        # tensor's largest value (operand rounding does not shrink with the length of the sum, the
+        # reference's accumulation error does).  The FFMA path's floor covers tensors the reference
+        # gets exactly right.
+        for mode, k, flo in (("fp32", ARB_FP32, 2e-5), ("fp32_tf32x3", ARB_TF32X3, 2e-5), ("fp32_ffma", 4.0, 2e-6)):
             conv3d.set_f2f_precision(mode)
             o_m = conv3d.facet2facet_forward(c["tex"], c["filt_f2f"], c["bary"], c["cum"])
             gi_m, gf_m = conv3d.facet2facet_backward(c["g_f2f"], c["tex"], c["filt_f2f"], c["bary"], c["cum"])
