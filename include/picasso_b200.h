@@ -279,6 +279,36 @@ int pb200_mesh_unpool_forward(int64_t NvCoarse, int64_t NvFine, int C, const flo
 int pb200_mesh_unpool_backward(int64_t NvCoarse, int64_t NvFine, int C, const float* gradOutput, const int32_t* rowptr,
                                const int32_t* members, float* gradInput, void* stream);
 
+/* ---- point-cloud depthwise convolution (the SPH3D kernel of the dual point / mesh blocks) ------
+ * Neighbour pairs p = (nnIndex[p][0] = output point, nnIndex[p][1] = input point), Nout of them;
+ * nnCount[o] = neighbours of output point o; a pair's filter bin is binIndex[p] (hard assignment,
+ * binCoeff = NULL, T = 1) or the T bins binIndex[p][t] with weights binCoeff[p][t] (fuzzy).
+ *   output[o, c*r+m] = sum over the pairs of o of input[in_p, c] * w_p[c*r+m] / nnCount[o],
+ *   w_p[co] = filter[bin_p, co]  or  sum_t binCoeff[p][t] * filter[binIndex[p][t], co].
+ * Replaces depthwiseConv3dLauncher / fuzzyDepthwiseConv3dLauncher and their Grad launchers
+ * (picasso/point/pi_modules/source/pcloud_conv3d_gpu.cu:8-193,197-268; bindings pcloud_conv3d.cpp
+ * SPH3D_forward/backward, fuzzySPH3D_forward/backward).  input (Np,C), filter (F,C,r), output (Mp,C*r).
+ * The pairs are pulled through two groupings built with pb200_build_key_csr: by output point
+ * (key = nnIndex, stride 2) for the forward pass, by input point (key = nnIndex + 1, stride 2) for the
+ * input gradient.  Indices outside their range contribute nothing. */
+
+/* Generic grouping of N items by key[i * key_stride] in [-1, NvOut): rowptr (NvOut+1), members (N)
+ * = item ids of every row in ascending order; `status` = 0 or PB200_EINDEX.  Workspace as
+ * pb200_cluster_csr_workspace_bytes(N, NvOut). */
+int pb200_build_key_csr(int64_t N, int64_t NvOut, const int32_t* key, int key_stride, int32_t* rowptr,
+                        int32_t* members, int32_t* status, void* workspace, size_t workspace_bytes, void* stream);
+int pb200_pcloud_conv3d_forward(int64_t Np, int64_t Mp, int64_t Nout, int F, int C, int r, int T,
+                                const float* input, const float* filter, const int32_t* nnCount,
+                                const int32_t* nnIndex, const int32_t* binIndex, const float* binCoeff,
+                                const int32_t* rowptr_out, const int32_t* members_out, float* output, void* stream);
+size_t pb200_pcloud_conv3d_backward_workspace_bytes(int64_t Nout, int F, int C, int r);
+int pb200_pcloud_conv3d_backward(int64_t Np, int64_t Mp, int64_t Nout, int F, int C, int r, int T,
+                                 const float* gradOutput, const float* input, const float* filter,
+                                 const int32_t* nnCount, const int32_t* nnIndex, const int32_t* binIndex,
+                                 const float* binCoeff, const int32_t* rowptr_in, const int32_t* members_in,
+                                 float* gradInput, float* gradFilter, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+
 /* ---- row expansion (benchmark block glue) ----------------------------------------------
  * forward:  out[k,:] = in[f,:] for every sample k of face f (numInterior as above);
  * backward: gradIn[f,:] = sum over the samples k of f of gradOut[k,:] (fixed order).

@@ -182,3 +182,28 @@ def unpool_backward(gout, nv_coarse, vt_replace, vt_map):
     lib().oracle_unpool_backward(C_int(vt_map.shape[0]), C_int(nv_coarse), C_int(gout.shape[1]), _p(vt_replace),
                                  _p(vt_map), _p(gout), _p(gin))
     return gin
+
+
+def pcloud_forward(inp, filt, nn_count, nn_index, bin_index, bin_coeff=None):
+    inp, filt, nn_count, nn_index, bin_index = _f32(inp), _f32(filt), _i32(nn_count), _i32(nn_index), _i32(bin_index)
+    F, Cc, r = filt.shape
+    T = 1 if bin_coeff is None else bin_index.shape[1]
+    coeff = None if bin_coeff is None else _f32(bin_coeff)
+    out = np.zeros((nn_count.shape[0], Cc * r), np.float32)
+    lib().oracle_pcloud_forward(C_int(nn_count.shape[0]), C_int(nn_index.shape[0]), C_int(Cc), C_int(r), C_int(T),
+                                _p(nn_count), _p(nn_index), _p(bin_index), None if coeff is None else _p(coeff), _p(inp),
+                                _p(filt), _p(out))
+    return out
+
+
+def pcloud_backward(gout, inp, filt, nn_count, nn_index, bin_index, bin_coeff=None):
+    gout, inp, filt = _f32(gout), _f32(inp), _f32(filt)
+    nn_count, nn_index, bin_index = _i32(nn_count), _i32(nn_index), _i32(bin_index)
+    F, Cc, r = filt.shape
+    T = 1 if bin_coeff is None else bin_index.shape[1]
+    coeff = None if bin_coeff is None else _f32(bin_coeff)
+    gin, gf = np.zeros_like(inp), np.zeros_like(filt)
+    lib().oracle_pcloud_backward(C_int(inp.shape[0]), C_int(nn_index.shape[0]), C_int(F), C_int(Cc), C_int(r), C_int(T),
+                                 _p(nn_count), _p(nn_index), _p(bin_index), None if coeff is None else _p(coeff), _p(inp),
+                                 _p(filt), _p(gout), _p(gin), _p(gf))
+    return gin, gf

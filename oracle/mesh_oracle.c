@@ -313,4 +313,43 @@ void oracle_unpool_backward(int nvFine, int nvCoarse, int C, const int32_t* vtRe
         for (int c = 0; c < C; ++c) gin[(int64_t)vi * C + c] += gout[(int64_t)v * C + c];
     }
 }
+
+/* ---- point-cloud depthwise convolution, hard (coeff == NULL, T = 1) or fuzzy bin assignment;
+ * picasso/point/pi_modules/source/pcloud_conv3d_gpu.cu:8-27,94-118 (forward), 30-48,121-147 (input
+ * gradient), 51-88,150-193 (filter gradient); pairs in ascending order */
+static float pcloud_weight(int p, int co, int Cr, int T, const int32_t* bin, const float* coeff, const float* filter) {
+    if (!coeff) return filter[(int64_t)bin[p] * Cr + co];
+    float w = 0;
+    for (int t = 0; t < T; ++t) w += coeff[p * T + t] * filter[(int64_t)bin[p * T + t] * Cr + co];
+    return w;
+}
+
+void oracle_pcloud_forward(int Mp, int Nout, int C, int r, int T, const int32_t* nnCount, const int32_t* nnIndex,
+                           const int32_t* bin, const float* coeff, const float* in, const float* filter, float* out) {
+    int Cr = C * r;
+    memset(out, 0, sizeof(float) * (size_t)Mp * Cr);
+    for (int p = 0; p < Nout; ++p) {
+        int o = nnIndex[2 * p], i = nnIndex[2 * p + 1];
+        for (int co = 0; co < Cr; ++co)
+            out[(int64_t)o * Cr + co] += in[(int64_t)i * C + co / r] * pcloud_weight(p, co, Cr, T, bin, coeff, filter) / nnCount[o];
+    }
+}
+
+void oracle_pcloud_backward(int Np, int Nout, int F, int C, int r, int T, const int32_t* nnCount, const int32_t* nnIndex,
+                            const int32_t* bin, const float* coeff, const float* in, const float* filter,
+                            const float* gout, float* gin, float* gfilter) {
+    int Cr = C * r;
+    memset(gin, 0, sizeof(float) * (size_t)Np * C);
+    memset(gfilter, 0, sizeof(float) * (size_t)F * Cr);
+    for (int p = 0; p < Nout; ++p) {
+        int o = nnIndex[2 * p], i = nnIndex[2 * p + 1];
+        for (int co = 0; co < Cr; ++co) {
+            float g = gout[(int64_t)o * Cr + co];
+            gin[(int64_t)i * C + co / r] += g * pcloud_weight(p, co, Cr, T, bin, coeff, filter) / nnCount[o];
+            float d = g * in[(int64_t)i * C + co / r] / nnCount[o];
+            if (!coeff) gfilter[(int64_t)bin[p] * Cr + co] += d;
+            else for (int t = 0; t < T; ++t) gfilter[(int64_t)bin[p * T + t] * Cr + co] += coeff[p * T + t] * d;
+        }
+    }
+}
 #endif

@@ -375,6 +375,46 @@ def mesh_unpool_backward(gout, nv_coarse, vt_replace, vt_map):
     return gin
 
 
+# ------------------------------------------------------- point-cloud depthwise convolution
+def _pair_weights(filt, bin_index, bin_coeff):
+    """w[p, c, m]: filter[bin[p]] (hard assignment) or sum_t coeff[p,t]*filter[bin[p,t]] (fuzzy);
+    picasso/point/pi_modules/source/pcloud_conv3d_gpu.cu:24,108-116."""
+    if bin_coeff is None:
+        return filt[bin_index.to(torch.long)]
+    return (bin_coeff.unsqueeze(-1).unsqueeze(-1) * filt[bin_index.to(torch.long)]).sum(1)
+
+
+def pcloud_conv3d_forward(inp, filt, nn_count, nn_index, bin_index, bin_coeff=None):
+    """pcloud_conv3d_gpu.cu:8-27 (hard) / 94-118 (fuzzy): output[out_p, c*r+m] += input[in_p, c] *
+    w_p[c, m] / nnCount[out_p] over the neighbour pairs p = (out_p, in_p)."""
+    F, C, r = filt.shape
+    o, i = nn_index[:, 0].to(torch.long), nn_index[:, 1].to(torch.long)
+    w = _pair_weights(filt, bin_index, bin_coeff)
+    term = inp[i].unsqueeze(-1) * w / nn_count.to(inp.dtype)[o].reshape(-1, 1, 1)
+    out = torch.zeros(nn_count.shape[0], C, r, dtype=inp.dtype, device=inp.device)
+    out.index_add_(0, o, term)
+    return out.reshape(-1, C * r)
+
+
+def pcloud_conv3d_backward(gout, inp, filt, nn_count, nn_index, bin_index, bin_coeff=None):
+    """pcloud_conv3d_gpu.cu:30-88 (hard) / 121-193 (fuzzy): gIn[in_p, c] += sum_m gOut[out_p, c*r+m] *
+    w_p[c,m] / nnCount[out_p];  gF[f, c, m] += coeff * gOut[out_p, c*r+m] * input[in_p, c] / nnCount[out_p]."""
+    F, C, r = filt.shape
+    o, i = nn_index[:, 0].to(torch.long), nn_index[:, 1].to(torch.long)
+    w = _pair_weights(filt, bin_index, bin_coeff)
+    g = gout.reshape(-1, C, r)[o] / nn_count.to(inp.dtype)[o].reshape(-1, 1, 1)
+    gin = torch.zeros_like(inp)
+    gin.index_add_(0, i, (g * w).sum(-1))
+    d = g * inp[i].unsqueeze(-1)
+    gf = torch.zeros_like(filt)
+    if bin_coeff is None:
+        gf.index_add_(0, bin_index.to(torch.long), d)
+    else:
+        for t in range(bin_index.shape[1]):
+            gf.index_add_(0, bin_index[:, t].to(torch.long), bin_coeff[:, t].reshape(-1, 1, 1) * d)
+    return gin, gf
+
+
 # ------------------------------------------------------------- autograd wrappers (CPU)
 class _V2F(torch.autograd.Function):
     @staticmethod

@@ -154,3 +154,25 @@ def unpool_backward(gout, nv_coarse, vt_replace, vt_map):
     gin = torch.zeros(nv_coarse, C, dtype=gout.dtype, device=gout.device)
     _chk(lib().ref_unpool_backward(nv_coarse, C, vt_map.shape[0], _p(vt_replace), _p(vt_map), _p(gout), _p(gin)))
     return gin
+
+
+# ---- point-cloud depthwise convolution (pcloud_conv3d_gpu.cu); bin_coeff None = hard assignment
+def pcloud_forward(inp, filt, nn_count, nn_index, bin_index, bin_coeff=None):
+    _sync_in()
+    F, Cc, r = filt.shape
+    T = 1 if bin_coeff is None else bin_index.shape[1]
+    out = torch.zeros(nn_count.shape[0], Cc * r, dtype=inp.dtype, device=inp.device)
+    _chk(lib().ref_pcloud_forward(inp.shape[0], nn_count.shape[0], nn_index.shape[0], F, Cc, r, T, _p(nn_count), _p(nn_index),
+                                  _p(bin_index), None if bin_coeff is None else _p(bin_coeff), _p(inp), _p(filt), _p(out)))
+    return out
+
+
+def pcloud_backward(gout, inp, filt, nn_count, nn_index, bin_index, bin_coeff=None):
+    _sync_in()
+    F, Cc, r = filt.shape
+    T = 1 if bin_coeff is None else bin_index.shape[1]
+    gin, gf = torch.zeros_like(inp), torch.zeros_like(filt)
+    _chk(lib().ref_pcloud_backward(inp.shape[0], nn_count.shape[0], nn_index.shape[0], F, Cc, r, T, _p(nn_count),
+                                   _p(nn_index), _p(bin_index), None if bin_coeff is None else _p(bin_coeff), _p(inp),
+                                   _p(filt), _p(gout), _p(gin), _p(gf)))
+    return gin, gf

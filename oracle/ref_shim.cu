@@ -4,7 +4,7 @@
 // compiled from the reference tree where it lies (see oracle/Makefile, target `ref`).
 // Launcher signatures: picasso/mesh/pi_modules/source/mesh_conv3d.cpp:9-23,
 // picasso/mesh/pi_modules/source/decimate.cpp (countVertexAdjfaceLauncher),
-// mesh_pool3d.cpp:8-15 and mesh_unpool3d.cpp:8-11.
+// mesh_pool3d.cpp:8-15, mesh_unpool3d.cpp:8-11 and picasso/point/pi_modules/source/pcloud_conv3d.cpp:8-21.
 #include <cuda_runtime.h>
 
 void facet2vertexConv3dLauncher(int NfIn, int C, int r, int K, const int* vtMap, const int* nfCount, const int* face,
@@ -32,6 +32,17 @@ void interpolateLauncher(int nvIn, int C, int nvOut, const int* vtReplace, const
                          float* output);
 void interpolateGradLauncher(int nvIn, int C, int nvOut, const int* vtReplace, const int* vtMap, const float* gradOutput,
                              float* gradInput);
+void depthwiseConv3dLauncher(int Np, int Mp, int Nout, int F, int C, int r, const int* nnCount, const int* nnIndex,
+                             const int* binIndex, const float* input, const float* filter, float* output);
+void depthwiseConv3dGradLauncher(int Np, int Mp, int Nout, int F, int C, int r, const int* nnCount, const int* nnIndex,
+                                 const int* binIndex, const float* input, const float* filter, const float* gradOutput,
+                                 float* gradInput, float* gradFilter);
+void fuzzyDepthwiseConv3dLauncher(int Np, int Mp, int Nout, int F, int C, int r, int T, const int* nnCount,
+                                  const int* nnIndex, const int* binIndex, const float* binCoeff, const float* input,
+                                  const float* filter, float* output);
+void fuzzyDepthwiseConv3dGradLauncher(int Np, int Mp, int Nout, int F, int C, int r, int T, const int* nnCount,
+                                      const int* nnIndex, const int* binIndex, const float* binCoeff, const float* input,
+                                      const float* filter, const float* gradOutput, float* gradInput, float* gradFilter);
 
 // The reference launches on the legacy default stream and never checks errors; each
 // doorway synchronises the device and returns the CUDA status so a test can assert on it.
@@ -105,6 +116,23 @@ int ref_unpool_forward(int nvIn, int C, int nvOut, const int* vtReplace, const i
 int ref_unpool_backward(int nvIn, int C, int nvOut, const int* vtReplace, const int* vtMap, const float* gradOutput,
                         float* gradInput) {
     interpolateGradLauncher(nvIn, C, nvOut, vtReplace, vtMap, gradOutput, gradInput);
+    return finish();
+}
+int ref_pcloud_forward(int Np, int Mp, int Nout, int F, int C, int r, int T, const int* nnCount, const int* nnIndex,
+                       const int* binIndex, const float* binCoeff, const float* input, const float* filter, float* output) {
+    if (binCoeff) fuzzyDepthwiseConv3dLauncher(Np, Mp, Nout, F, C, r, T, nnCount, nnIndex, binIndex, binCoeff, input, filter, output);
+    else depthwiseConv3dLauncher(Np, Mp, Nout, F, C, r, nnCount, nnIndex, binIndex, input, filter, output);
+    return finish();
+}
+int ref_pcloud_backward(int Np, int Mp, int Nout, int F, int C, int r, int T, const int* nnCount, const int* nnIndex,
+                        const int* binIndex, const float* binCoeff, const float* input, const float* filter,
+                        const float* gradOutput, float* gradInput, float* gradFilter) {
+    if (binCoeff)
+        fuzzyDepthwiseConv3dGradLauncher(Np, Mp, Nout, F, C, r, T, nnCount, nnIndex, binIndex, binCoeff, input, filter,
+                                         gradOutput, gradInput, gradFilter);
+    else
+        depthwiseConv3dGradLauncher(Np, Mp, Nout, F, C, r, nnCount, nnIndex, binIndex, input, filter, gradOutput, gradInput,
+                                    gradFilter);
     return finish();
 }
 }

@@ -70,6 +70,11 @@ SIGNATURES = {
     "pb200_mesh_avg_pool_backward": (i32, [i64, i64, i32, vp, vp, vp, vp, vp]),
     "pb200_mesh_unpool_forward": (i32, [i64, i64, i32, vp, vp, vp, vp]),
     "pb200_mesh_unpool_backward": (i32, [i64, i64, i32, vp, vp, vp, vp, vp]),
+    "pb200_build_key_csr": (i32, [i64, i64, vp, i32, vp, vp, vp, vp, sz, vp]),
+    "pb200_pcloud_conv3d_forward": (i32, [i64, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
+    "pb200_pcloud_conv3d_backward_workspace_bytes": (sz, [i64, i32, i32, i32]),
+    "pb200_pcloud_conv3d_backward": (i32, [i64, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                                           vp, sz, vp]),
     "pb200_sph_harm_coeff": (i32, [i64, i32, vp, vp, vp]),
     "pb200_triangle_geometry": (i32, [i64, i64, i32, vp, vp, vp, vp]),
     "pb200_expand_rows_forward": (i32, [i64, i64, i32, vp, vp, vp, vp]),

@@ -114,6 +114,24 @@ __global__ void cluster_count_kernel(int64_t NvIn, int64_t NvOut, const int32_t*
     if (vo >= 0) atomicAdd(&cnt[vo], 1);
 }
 
+// generic grouping: item i belongs to row key[i * stride] (-1 = no row)
+__global__ void key_count_kernel(int64_t N, int64_t NvOut, const int32_t* __restrict__ key, int stride,
+                                 int32_t* __restrict__ cnt, int32_t* __restrict__ status) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int k = key[i * stride];
+    if (k >= NvOut || k < -1) { *status = PB200_EINDEX; return; }
+    if (k >= 0) atomicAdd(&cnt[k], 1);
+}
+
+__global__ void key_fill_kernel(int64_t N, int64_t NvOut, const int32_t* __restrict__ key, int stride,
+                                int32_t* __restrict__ cursor, int32_t* __restrict__ members) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const int k = key[i * stride];
+    if (k >= 0 && k < NvOut) members[atomicAdd(&cursor[k], 1)] = (int32_t)i;
+}
+
 __global__ void cluster_fill_kernel(int64_t NvIn, const int32_t* __restrict__ key, int32_t* __restrict__ cursor,
                                     int32_t* __restrict__ members) {
     int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -491,6 +509,43 @@ int pb200_build_cluster_csr(int64_t NvIn, int64_t NvOut, const int32_t* vtReplac
     if (NvIn > 0 && NvOut > 0) {
         PB_LAUNCH("cluster_fill", cluster_fill_kernel, (unsigned)ceil_div(NvIn, 256), 256, 0, stream,
                   NvIn, (const int32_t*)key, cursor, members);
+        PB_LAUNCH("sort_short_rows", sort_short_rows_kernel, (unsigned)ceil_div(NvOut, 128), 128, 0, stream,
+                  NvOut, (const int32_t*)rowptr, members, long_rows, n_long);
+        PB_LAUNCH("sort_long_rows", sort_long_rows_kernel, 2 * sm_count(), 256, 0, stream,
+                  (const int32_t*)rowptr, members, (const int32_t*)long_rows, (const int32_t*)n_long, tmp);
+    }
+    return PB200_OK;
+}
+
+int pb200_build_key_csr(int64_t N, int64_t NvOut, const int32_t* key, int key_stride, int32_t* rowptr,
+                        int32_t* members, int32_t* status, void* workspace, size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(N >= 0 && NvOut >= 0 && N < (1LL << 31) - 1 && NvOut < (1LL << 31) - 1 && key_stride >= 1, PB200_EINVAL,
+               "build_key_csr: bad sizes");
+    PB_REQUIRE(rowptr && status && (N == 0 || (key && members)), PB200_EINVAL, "build_key_csr: null pointer");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_cluster_csr_workspace_bytes(N, NvOut), PB200_EWORKSPACE,
+               "build_key_csr: workspace too small");
+    char* w = (char*)workspace;
+    int32_t* cursor = (int32_t*)w;  w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int ntiles = (int)ceil_div(NvOut + 1, SCAN_TILE);
+    int32_t* tile_sum = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(ntiles + 1), 256);
+    int32_t* long_rows = (int32_t*)w; w += align_up(sizeof(int32_t) * (size_t)(NvOut + 1), 256);
+    int32_t* tmp = (int32_t*)w;      w += align_up(sizeof(int32_t) * (size_t)(N + 1), 256);
+    int32_t* n_long = (int32_t*)w;
+    PB_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), stream));
+    PB_CUDA(cudaMemsetAsync(cursor, 0, sizeof(int32_t) * (NvOut + 1), stream));
+    PB_CUDA(cudaMemsetAsync(n_long, 0, sizeof(int32_t), stream));
+    if (N > 0)
+        PB_LAUNCH("key_count", key_count_kernel, (unsigned)ceil_div(N, 256), 256, 0, stream, N, NvOut, key, key_stride,
+                  cursor, status);
+    PB_LAUNCH("scan_tiles", scan_tiles_kernel, ntiles, SCAN_THREADS, 0, stream,
+              (const int32_t*)cursor, NvOut + 1, rowptr, tile_sum);
+    PB_LAUNCH("scan_tile_sums", scan_tile_sums_kernel, 1, 32, 0, stream, tile_sum, ntiles, tile_sum + ntiles);
+    PB_LAUNCH("scan_finish", scan_finish_kernel, (unsigned)ceil_div(NvOut + 1, 256), 256, 0, stream,
+              rowptr, NvOut + 1, (const int32_t*)tile_sum, cursor);
+    if (N > 0 && NvOut > 0) {
+        PB_LAUNCH("key_fill", key_fill_kernel, (unsigned)ceil_div(N, 256), 256, 0, stream, N, NvOut, key, key_stride,
+                  cursor, members);
         PB_LAUNCH("sort_short_rows", sort_short_rows_kernel, (unsigned)ceil_div(NvOut, 128), 128, 0, stream,
                   NvOut, (const int32_t*)rowptr, members, long_rows, n_long);
         PB_LAUNCH("sort_long_rows", sort_long_rows_kernel, 2 * sm_count(), 256, 0, stream,

@@ -278,6 +278,48 @@ def cluster_csr(vt_replace: torch.Tensor, vt_map: torch.Tensor, nv_out: int) -> 
     return csr
 
 
+class PairCSR:
+    """Neighbour pairs grouped by one column of nnIndex: rowptr (rows+1,), members (pairs,) = pair ids
+    of every row, ascending."""
+
+    def __init__(self, rowptr, members, keep, versions):
+        self.rowptr = rowptr
+        self.members = members
+        self._keep = keep
+        self._versions = versions
+        self.nbytes = 4 * (rowptr.numel() + members.numel())
+
+
+def pair_csr(nn_index: torch.Tensor, column: int, n_rows: int) -> PairCSR:
+    """Cached grouping of the neighbour pairs of a point-cloud convolution by their output point
+    (column 0) or input point (column 1); same cache, budget and validation modes as vertex_csr."""
+    npairs = nn_index.shape[0]
+    slot = ("pairs", nn_index.device.index, nn_index.data_ptr(), npairs, int(column), int(n_rows))
+    versions = (nn_index._version,)
+    hit = _lookup(slot, versions)
+    if hit is not None:
+        return hit
+    dev = nn_index.device
+    with torch.cuda.device(dev):
+        rowptr = torch.empty(n_rows + 1, dtype=torch.int32, device=dev)
+        members = torch.empty(max(npairs, 1), dtype=torch.int32, device=dev)
+        status = torch.empty(1, dtype=torch.int32, device=dev)
+        wbytes = _lib.query("pb200_cluster_csr_workspace_bytes", npairs, n_rows)
+        ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
+        key_ptr = None if npairs == 0 else nn_index.data_ptr() + 4 * column
+        _lib.call("pb200_build_key_csr", npairs, n_rows, key_ptr, 2, ptr(rowptr), ptr(members), ptr(status), ptr(ws), wbytes,
+                  stream_ptr(dev))
+        msg = f"nn_index column {column} holds an index outside [0, {n_rows})"
+        if _validation == "deferred":
+            with _lock:
+                _deferred.append((status, msg))
+        elif int(status.item()) != 0:
+            raise RuntimeError(msg)
+    csr = PairCSR(rowptr, members, (nn_index,), versions)
+    _store(slot, csr)
+    return csr
+
+
 def check_num_interior(num_interior: torch.Tensor, nik: int) -> None:
     """Validates a running sample count (non-decreasing, inside [0, nik], ends at nik) on the
     device: raises in 'sync' mode, queues the status word in 'deferred' mode.  The facet2facet

@@ -107,3 +107,40 @@ POOL_GOLDEN_CASES = {
     "pool_n300_m90_c8": (300, 90, 8, 31),
     "pool_n257_m64_c5": (257, 64, 5, 32),
 }
+
+
+def pcloud_inputs(Np: int, Mp: int, knn: int, F: int, C: int, r: int, T: int, seed: int, shuffle: bool = False):
+    """Neighbour pairs of a point-cloud convolution as a neighbour search would emit them (grouped by
+    output point unless shuffle=True), filter bins (T = 0: hard assignment; T > 0: T fuzzy bins with
+    weights that sum to 1), features, filter and upstream gradient, as CPU torch tensors.  Some output
+    points have no neighbour at all."""
+    rng = np.random.default_rng(seed)
+    counts = rng.integers(0, knn + 1, size=Mp)
+    counts[rng.integers(0, Mp)] = knn
+    out_idx = np.repeat(np.arange(Mp), counts)
+    in_idx = rng.integers(0, Np, size=out_idx.shape[0])
+    if shuffle:
+        perm = rng.permutation(out_idx.shape[0])
+        out_idx, in_idx = out_idx[perm], in_idx[perm]
+    nn_index = np.stack([out_idx, in_idx], 1).astype(np.int32)
+    nn_count = np.maximum(counts, 1).astype(np.int32)            # the reference divides by it: never 0
+    npairs = nn_index.shape[0]
+    g = torch.Generator().manual_seed(seed)
+    d = dict(nn_index=torch.from_numpy(nn_index), nn_count=torch.from_numpy(nn_count),
+             x=torch.randn(Np, C, generator=g), filt=torch.randn(F, C, r, generator=g) / F ** 0.5,
+             g_out=torch.randn(Mp, C * r, generator=g))
+    if T == 0:
+        d["bin_index"] = torch.from_numpy(rng.integers(0, F, size=npairs).astype(np.int32))
+        d["bin_coeff"] = None
+    else:
+        d["bin_index"] = torch.from_numpy(rng.integers(0, F, size=(npairs, T)).astype(np.int32))
+        w = rng.random((npairs, T)).astype(np.float32) + 0.05
+        d["bin_coeff"] = torch.from_numpy(w / w.sum(1, keepdims=True))
+    return d
+
+
+PCLOUD_GOLDEN_CASES = {
+    # name: (Np, Mp, knn, F, C, r, T, seed)
+    "pcloud_hard_n200_m60_c6_r2": (200, 60, 12, 9, 6, 2, 0, 41),
+    "pcloud_fuzzy_n150_m80_c8_r1": (150, 80, 10, 17, 8, 1, 3, 42),
+}

@@ -5,7 +5,8 @@ operators (oracle/_ref, see oracle/Makefile target `ref`) on a CUDA device:
 
 For every case of tests/cases.py:GOLDEN_CASES it stores the inputs and the reference's
 outputs (all three operators forward and backward, and nfCount) in <case>.npz, and for
-every case of POOL_GOLDEN_CASES the reference's mesh pooling / unpooling outputs.  The parts
+every case of POOL_GOLDEN_CASES / PCLOUD_GOLDEN_CASES the reference's mesh pooling / unpooling and
+point-cloud convolution outputs.  The parts
 of the path that are plain Python in the reference (spherical-harmonic basis, triangle
 geometry, layer modules) have their own generator, make_golden_modules.py.
 """
@@ -21,7 +22,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from cases import GOLDEN_CASES, POOL_GOLDEN_CASES, cluster_inputs, conv_inputs  # noqa: E402
+from cases import (GOLDEN_CASES, PCLOUD_GOLDEN_CASES, POOL_GOLDEN_CASES, cluster_inputs, conv_inputs,  # noqa: E402
+                   pcloud_inputs)
 from oracle import ref_cuda  # noqa: E402
 
 
@@ -58,6 +60,17 @@ def main(out_dir):
         out["avg_gin"] = ref_cuda.avg_pool_backward(c["g_coarse"], c["vt_replace"], c["vt_map"])
         out["unpool_out"] = ref_cuda.unpool_forward(c["x_coarse"], c["vt_replace"], c["vt_map"])
         out["unpool_gin"] = ref_cuda.unpool_backward(c["g_fine"], nv_out, c["vt_replace"], c["vt_map"])
+        arrays = {("in_" + k): v.numpy() for k, v in d.items() if isinstance(v, torch.Tensor)}
+        arrays.update({("ref_" + k): v.cpu().numpy() for k, v in out.items()})
+        np.savez_compressed(os.path.join(out_dir, name + ".npz"), **arrays)
+        print("wrote", name, {k: tuple(v.shape) for k, v in arrays.items() if k.startswith("ref_")})
+    # point-cloud depthwise convolution, hard and fuzzy bins (pcloud_conv3d_gpu.cu)
+    for name, args in PCLOUD_GOLDEN_CASES.items():
+        d = pcloud_inputs(*args)
+        c = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+        out = {"out": ref_cuda.pcloud_forward(c["x"], c["filt"], c["nn_count"], c["nn_index"], c["bin_index"], c["bin_coeff"])}
+        out["gin"], out["gf"] = ref_cuda.pcloud_backward(c["g_out"], c["x"], c["filt"], c["nn_count"], c["nn_index"],
+                                                         c["bin_index"], c["bin_coeff"])
         arrays = {("in_" + k): v.numpy() for k, v in d.items() if isinstance(v, torch.Tensor)}
         arrays.update({("ref_" + k): v.cpu().numpy() for k, v in out.items()})
         np.savez_compressed(os.path.join(out_dir, name + ".npz"), **arrays)
