@@ -61,6 +61,8 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-fusion", action="store_true", help="config c4: run the layer modules as operator + separate "
+                    "pointwise kernels instead of the fused operator + pointwise kernels")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
     return ap.parse_args()
 
@@ -590,11 +592,14 @@ def run_c4(args):
     The hierarchy comes from synth.heightfield_hierarchy (grid halving, face ratios 1 / 0.25 / 0.062 /
     0.015), which stands in for the reference's GPU decimation; indices are built once and held fixed."""
     from picassoplus_b200 import _lib, topology
+    from picassoplus_b200.mesh import layers as mesh_layers
     from picassoplus_b200.mesh.layers import Pool3d, V2VConv3d
-    from picassoplus_b200.mesh.pi_modules import conv3d
+    from picassoplus_b200.mesh.pi_modules import conv3d, fused
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for --impl ours)")
     assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "config c4 is a single-GPU measurement"
+    mesh_layers.set_fusion(not args.no_fusion)
+    fused.set_pointwise_precision("bf16" if args.precision == "bf16" else "fp32")
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     cfg = C4
@@ -667,7 +672,11 @@ def run_c4(args):
                                f"(faces {[m.num_faces for m in levels]}), channels 64->128->256->384, L=3", "name": "c4"},
         "workload_detail": {"faces_level0": faces, "vertices_per_level": [m.num_vertices for m in levels],
                             "hierarchy": "synthetic grid halving (stands in for the reference's GPU decimation)",
-                            "pointwise_stage": "torch.matmul + bias + ReLU + BatchNorm1d (cuBLAS / torch kernels)"},
+                            "pointwise_stage": ("torch.matmul + bias + ReLU (cuBLAS / torch kernels), BatchNorm1d in torch"
+                                                if args.no_fusion else
+                                                "fused with the operator in one tcgen05 kernel (forward; "
+                                                f"{'bf16' if args.precision == 'bf16' else 'bf16 hi+lo'} operands), "
+                                                "BatchNorm1d in torch; backward = recompute + matmuls + operator backward")},
         "roofline": {"bound": "hbm", "achieved": alg / (lib_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": alg / (lib_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
                      "note": "all library operator kernels of one step together: algorithmic bytes of V2F, F2V and max "

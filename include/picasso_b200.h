@@ -61,8 +61,8 @@ int64_t     pb200_launch_count(void);
  * mapped host memory, one word per device.  The call that launched it has already returned
  * PB200_OK and its outputs are invalid.  While the word of the current device is raised, every
  * later facet2facet call on that device fails with PB200_ECUDA.  pb200_async_error() reads the
- * word of the current device (0 = none; 1/2/3 = forward / input-gradient / filter-gradient
- * kernel) -- call it after synchronising the stream to learn whether the step's results are
+ * word of the current device (0 = none; 1/2/3 = facet2facet forward / input-gradient /
+ * filter-gradient kernel, 4 = fused operator + pointwise kernel) -- call it after synchronising the stream to learn whether the step's results are
  * good; pb200_clear_async_error() re-arms the device.  pb200_set_wait_budget() changes the
  * budget of later launches (clocks; <= 0 restores the default).  A cudaDeviceReset() by the host
  * invalidates nothing here, but it does invalidate the device address that
@@ -173,6 +173,30 @@ int pb200_facet2vertex_backward(int64_t Nf, int64_t NvIn, int64_t NvOut, int C, 
                                 const float* coeff, const int32_t* face, const int32_t* nfCount,
                                 const int32_t* vtMap, float* gradInput, float* gradFilter,
                                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- operator + pointwise stage in one kernel (module-level fusion) ----------------------
+ * output[row, co] = act( sum_c feat[row, c] * depthWeights[c, co] + bias[co] ), act = ReLU if relu != 0,
+ * where feat is the operator's output for depth multiplier 1 and is never written to memory:
+ *   vertex2facet:  feat = pb200_vertex2facet_forward(input, filter (3,C,1), face)           rows = faces
+ *   facet2vertex:  feat = pb200_facet2vertex_forward(input, filter (K,C,1), coeff, CSR)     rows = output vertices
+ * The product runs on the tensor cores (tcgen05, fp32 accumulation): PB200_PREC_FP32 = bf16 hi+lo
+ * operands, three products per term (about 1e-5 relative); PB200_PREC_BF16 = bf16 operands.
+ * Replaces, inside V2FConv3d.forward / F2VConv3d.forward (picasso/mesh/layers.py:109-120,166-175), the
+ * sequence operator -> torch.matmul(., depth_weights) -> + biases -> ReLU and the (rows, C) round trip
+ * through memory between them.  depthWeights (C, Cout) row-major, bias (Cout) or NULL, C % 8 == 0,
+ * input / filter / workspace 16-byte aligned.  The facet2vertex workspace also holds the per-face
+ * products (Nf, C).  The first call of the process allocates the asynchronous error words (see above). */
+size_t pb200_vertex2facet_pointwise_workspace_bytes(int C, int precision);
+int pb200_vertex2facet_pointwise_forward(int64_t Nf, int64_t Nv, int C, int Cout, const float* input,
+                                         const float* filter, const int32_t* face, const float* depthWeights,
+                                         const float* bias, int relu, float* output, int precision,
+                                         void* workspace, size_t workspace_bytes, void* stream);
+size_t pb200_facet2vertex_pointwise_workspace_bytes(int64_t Nf, int C, int precision);
+int pb200_facet2vertex_pointwise_forward(int64_t Nf, int64_t NvOut, int C, int K, int Cout, const float* input,
+                                         const float* filter, const float* coeff, const int32_t* nfCount,
+                                         const int32_t* rowptr, const int32_t* entries,
+                                         const float* depthWeights, const float* bias, int relu, float* output,
+                                         int precision, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- facet2facet --------------------------------------------------------------------
  * A[f,d,ci] = (1/T_f) sum_{k in samples(f)} bary[k,d]*input[k,ci];

@@ -57,6 +57,11 @@ SIGNATURES = {
     "pb200_facet2vertex_backward_workspace_bytes": (sz, [i64, i32, i32, i32]),
     "pb200_facet2vertex_backward": (i32, [i64, i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                           vp, sz, vp]),
+    "pb200_vertex2facet_pointwise_workspace_bytes": (sz, [i32, i32]),
+    "pb200_vertex2facet_pointwise_forward": (i32, [i64, i64, i32, i32, vp, vp, vp, vp, vp, i32, vp, i32, vp, sz, vp]),
+    "pb200_facet2vertex_pointwise_workspace_bytes": (sz, [i64, i32, i32]),
+    "pb200_facet2vertex_pointwise_forward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32,
+                                                   vp, sz, vp]),
     "pb200_facet2facet_forward_workspace_bytes": (sz, [i64, i64, i32, i32, i32, i32]),
     "pb200_facet2facet_forward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_facet2facet_backward_workspace_bytes": (sz, [i64, i64, i32, i32, i32, i32]),

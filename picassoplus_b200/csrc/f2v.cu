@@ -505,6 +505,33 @@ static F2VBwdPlan f2v_bwd_plan(int64_t Nf, int C, int r, int K) {
     return p;
 }
 
+// The per-face stage of the vectorised forward pass on its own: wx[f, :] = (coeff[f] @ filter) * input[f]
+// (r = 1, C % 4 == 0); used by pb200_facet2vertex_forward and by the fused facet2vertex + pointwise entry.
+bool f2v_face_products_supported(int C, int K) { return vec_ok(C, 1) && kt_ok(K); }
+
+int f2v_face_products(int64_t Nf, int C, int K, const float* input, const float* filter, const float* coeff, float* wx_,
+                      cudaStream_t stream) {
+    const int CV = C / 4;
+    float4* wx = (float4*)wx_;
+    if (Nf <= 0) return PB200_OK;
+    if (CV % 32 == 0 && K <= 32) {
+        const int KPb = (K + 3) / 4 * 4;
+        const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + 2 * F2VF_TF * (KPb / 4));
+        dim3 gridf(persistent_blocks(Nf, F2VF_TF, 4), (unsigned)(CV / 32));
+        PB_LAUNCH("f2v_fwd_face", f2v_fwd_face_blocked_kernel, gridf, 256, smemb, stream, Nf, CV, K, coeff,
+                  (const float4*)input, (const float4*)filter, wx);
+    } else {
+        const int KP = (K + 3) / 4 * 4 + 4;
+        size_t smem = sizeof(float4) * 32 * (size_t)K + sizeof(float) * F2VF_TF * KP;
+        dim3 gridf(persistent_blocks(Nf, F2VF_TF, 6), (unsigned)ceil_div(CV, 32));
+        if (smem > 48 * 1024)
+            PB_CUDA(cudaFuncSetAttribute(f2v_fwd_face_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PB_LAUNCH("f2v_fwd_face", f2v_fwd_face_kernel, gridf, 256, smem, stream, Nf, CV, K, coeff,
+                  (const float4*)input, (const float4*)filter, wx);
+    }
+    return PB200_OK;
+}
+
 }  // namespace pb
 
 using namespace pb;
@@ -534,21 +561,8 @@ int pb200_facet2vertex_forward(int64_t Nf, int64_t NvOut, int C, int r, int K, c
     if (vec) {
         int CV = C / 4;
         float4* wx = (float4*)workspace;
-        if (Nf > 0 && CV % 32 == 0 && K <= 32) {
-            const int KPb = (K + 3) / 4 * 4;
-            const size_t smemb = sizeof(float4) * ((size_t)KPb * 32 + 2 * F2VF_TF * (KPb / 4));
-            dim3 gridf(persistent_blocks(Nf, F2VF_TF, 4), (unsigned)(CV / 32));
-            PB_LAUNCH("f2v_fwd_face", f2v_fwd_face_blocked_kernel, gridf, 256, smemb, stream, Nf, CV, K, coeff,
-                      (const float4*)input, (const float4*)filter, wx);
-        } else if (Nf > 0) {
-            const int KP = (K + 3) / 4 * 4 + 4;
-            size_t smem = sizeof(float4) * 32 * (size_t)K + sizeof(float) * F2VF_TF * KP;
-            dim3 gridf(persistent_blocks(Nf, F2VF_TF, 6), (unsigned)ceil_div(CV, 32));
-            if (smem > 48 * 1024)
-                PB_CUDA(cudaFuncSetAttribute(f2v_fwd_face_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            PB_LAUNCH("f2v_fwd_face", f2v_fwd_face_kernel, gridf, 256, smem, stream, Nf, CV, K, coeff,
-                      (const float4*)input, (const float4*)filter, wx);
-        }
+        int rc = f2v_face_products(Nf, C, K, input, filter, coeff, (float*)wx, stream);
+        if (rc) return rc;
         TeamGeom g = team_geom(CV);
         dim3 grid(persistent_blocks(NvOut, g.teams, 8), g.chunks);
         PB_DISPATCH_TL(g.TL, PB_LAUNCH("f2v_fwd_gather", f2v_fwd_gather_kernel<TL>, grid, 256, 0, stream, NvOut, CV,

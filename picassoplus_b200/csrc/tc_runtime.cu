@@ -41,7 +41,8 @@ int check_async_error(const char* where) {
     const int code = *(volatile int*)(base + current_device());
     if (code != 0) {
         set_error("%s: an earlier tensor-core kernel of this library gave up waiting on this device (kernel %d: "
-                  "1 forward, 2 input gradient, 3 filter gradient); the results of that call are invalid. "
+                  "1 facet2facet forward, 2 input gradient, 3 filter gradient, 4 pointwise fusion); the results of that call "
+                  "are invalid. "
                   "pb200_clear_async_error() re-arms the device.", where, code);
         return PB200_ECUDA;
     }

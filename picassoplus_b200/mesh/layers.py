@@ -11,8 +11,19 @@ from typing import List
 import torch
 import torch.nn as nn
 
-from .pi_modules import conv3d, pool3d, unpool3d
+from .pi_modules import conv3d, fused, pool3d, unpool3d
 from ..math_utils import sph_harm_coeff
+
+
+_fusion = True
+
+
+def set_fusion(on: bool) -> None:
+    """V2FConv3d / F2VConv3d run operator + depth_weights product + bias + ReLU as ONE kernel where the
+    shapes allow it (depth multiplier 1, channels a multiple of 8, ReLU or no activation); off = the
+    reference's sequence of separate kernels.  Batch norm stays a torch module either way."""
+    global _fusion
+    _fusion = bool(on)
 
 
 def _filter_variable_(shape, stddev=1.0, use_xavier=True):
@@ -48,6 +59,12 @@ class _PointwiseTail(nn.Module):
         if self.with_bn:
             x = self.BatchNorm(x)
         return x
+
+    def _fusable(self, x, channels, multiplier):
+        return _fusion and fused.eligible(x, channels, multiplier, self.activation_fn)
+
+    def _after_fused(self, x):
+        return self.BatchNorm(x) if self.with_bn else x
 
 
 class F2FConv3d(_PointwiseTail):
@@ -88,6 +105,9 @@ class V2FConv3d(_PointwiseTail):
     def forward(self, inputs, face):
         corners = sph_harm_coeff(self.L, torch.eye(3, device=inputs.device))
         spatial = (corners @ self.spatial_weights).reshape(3, self.in_channels, self.multiplier)
+        if self._fusable(inputs, self.in_channels, self.multiplier):
+            return self._after_fused(fused.vertex2facet_pointwise(inputs, spatial, face, self.depth_weights, self.biases,
+                                                                  self.activation_fn is not None))
         feats = conv3d.vertex2facet(inputs, spatial, face)
         return self._tail(feats @ self.depth_weights)
 
@@ -108,6 +128,10 @@ class F2VConv3d(_PointwiseTail):
         self._init_tail(out_channels, activation_fn, with_bn, bn_momentum)
 
     def forward(self, inputs, face, nf_count, vt_map, filt_coeff):
+        if self._fusable(inputs, self.in_channels, self.multiplier):
+            return self._after_fused(fused.facet2vertex_pointwise(inputs, self.spatial_weights, filt_coeff, face, nf_count,
+                                                                  vt_map, self.depth_weights, self.biases,
+                                                                  self.activation_fn is not None))
         feats = conv3d.facet2vertex(inputs, self.spatial_weights, filt_coeff, face, nf_count, vt_map)
         return self._tail(feats @ self.depth_weights)
 

@@ -1,0 +1,116 @@
+"""Operator + pointwise stage as one autograd Function each (no counterpart in the reference, whose
+modules run operator -> torch.matmul -> + bias -> ReLU as separate kernels,
+picasso/mesh/layers.py:109-120,166-175).  Forward: one fused tensor-core kernel; the operator's
+(rows, C) output never exists in memory.  Backward: the operator's output is recomputed with the
+stand-alone forward kernel (cheaper than having stored it), the pointwise gradients are two matrix
+products, and the operator gradient is the stand-alone backward kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from ... import _lib
+from ...topology import ptr, stream_ptr, vertex_csr
+from . import conv3d
+
+_precision = _lib.PREC_FP32
+
+
+def set_pointwise_precision(name: str) -> None:
+    """'fp32' (default: bf16 hi+lo operands, about 1e-5 relative) or 'bf16'."""
+    global _precision
+    if name not in ("fp32", "bf16"):
+        raise ValueError(name)
+    _precision = _lib.PRECISIONS[name]
+
+
+def eligible(x: torch.Tensor, channels: int, multiplier: int, activation_fn) -> bool:
+    """The fused kernels take depth multiplier 1, channels that are a multiple of 8, and ReLU or no
+    activation."""
+    return (x.is_cuda and x.dtype == torch.float32 and multiplier == 1 and channels % 8 == 0 and
+            (activation_fn is None or isinstance(activation_fn, torch.nn.ReLU)))
+
+
+def _pointwise_backward(grad_out, out, feats, depth_weights, relu):
+    g = grad_out * (out > 0) if relu else grad_out
+    return g @ depth_weights.t(), feats.t() @ g, g.sum(0, keepdim=True)
+
+
+class V2FPointwiseFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, filter, face, depth_weights, biases, relu):
+        face.requires_grad = False
+        conv3d._check(input, "input", 2, torch.float32)
+        conv3d._check(filter, "filter", 3, torch.float32)
+        conv3d._check(face, "face", 2, torch.int32)
+        conv3d._check(depth_weights, "depth_weights", 2, torch.float32)
+        Nv, C = input.shape
+        Nf, Cout = face.shape[0], depth_weights.shape[1]
+        if tuple(filter.shape) != (3, C, 1) or depth_weights.shape[0] != C:
+            raise RuntimeError("filter must have shape (3, C, 1) and depth_weights (C, out_channels)")
+        dev = input.device
+        input, filter = conv3d._aligned16(input), conv3d._aligned16(filter)
+        bias = None if biases is None else biases.reshape(-1).contiguous()
+        with torch.cuda.device(dev):
+            out = torch.empty(Nf, Cout, dtype=input.dtype, device=dev)
+            nb = _lib.query("pb200_vertex2facet_pointwise_workspace_bytes", C, _precision)
+            ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=dev)
+            _lib.call("pb200_vertex2facet_pointwise_forward", Nf, Nv, C, Cout, ptr(input), ptr(filter), ptr(face),
+                      ptr(depth_weights), ptr(bias), 1 if relu else 0, ptr(out), _precision, ptr(ws), nb, stream_ptr(dev))
+        ctx.relu = relu
+        ctx.has_bias = biases is not None
+        ctx.save_for_backward(input, filter, face, depth_weights, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        input, filter, face, depth_weights, out = ctx.saved_tensors
+        feats = conv3d.vertex2facet_forward(input, filter, face)
+        g_feats, g_w, g_b = _pointwise_backward(grad_out.contiguous(), out, feats, depth_weights, ctx.relu)
+        g_in, g_filter = conv3d.vertex2facet_backward(g_feats.contiguous(), input, filter, face)
+        return g_in, g_filter, None, g_w, (g_b if ctx.has_bias else None), None
+
+
+class F2VPointwiseFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, input, filter, coeff, face, nf_count, vt_map, depth_weights, biases, relu):
+        for t in (coeff, face, nf_count, vt_map):
+            t.requires_grad = False
+        conv3d._f2v_checks(input, filter, coeff, face, nf_count, vt_map)
+        conv3d._check(depth_weights, "depth_weights", 2, torch.float32)
+        Nf, C = input.shape
+        K = filter.shape[0]
+        NvOut, NvIn, Cout = nf_count.shape[0], vt_map.shape[0], depth_weights.shape[1]
+        if filter.shape[2] != 1 or depth_weights.shape[0] != C:
+            raise RuntimeError("filter must have shape (K, C, 1) and depth_weights (C, out_channels)")
+        dev = input.device
+        input, filter = conv3d._aligned16(input), conv3d._aligned16(filter)
+        bias = None if biases is None else biases.reshape(-1).contiguous()
+        with torch.cuda.device(dev):
+            csr = vertex_csr(face, vt_map, NvIn, NvOut)
+            out = torch.empty(NvOut, Cout, dtype=input.dtype, device=dev)
+            nb = _lib.query("pb200_facet2vertex_pointwise_workspace_bytes", Nf, C, _precision)
+            ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=dev)
+            _lib.call("pb200_facet2vertex_pointwise_forward", Nf, NvOut, C, K, Cout, ptr(input), ptr(filter), ptr(coeff),
+                      ptr(nf_count), ptr(csr.rowptr), ptr(csr.entries), ptr(depth_weights), ptr(bias), 1 if relu else 0,
+                      ptr(out), _precision, ptr(ws), nb, stream_ptr(dev))
+        ctx.relu = relu
+        ctx.has_bias = biases is not None
+        ctx.save_for_backward(input, filter, coeff, face, nf_count, vt_map, depth_weights, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        input, filter, coeff, face, nf_count, vt_map, depth_weights, out = ctx.saved_tensors
+        feats = conv3d.facet2vertex_forward(input, filter, coeff, face, nf_count, vt_map)
+        g_feats, g_w, g_b = _pointwise_backward(grad_out.contiguous(), out, feats, depth_weights, ctx.relu)
+        g_in, g_filter = conv3d.facet2vertex_backward(g_feats.contiguous(), input, filter, coeff, face, nf_count, vt_map)
+        return g_in, g_filter, None, None, None, None, g_w, (g_b if ctx.has_bias else None), None
+
+
+def vertex2facet_pointwise(input, filter, face, depth_weights, biases, relu):
+    return V2FPointwiseFunction.apply(input, filter, face, depth_weights, biases, relu)
+
+
+def facet2vertex_pointwise(input, filter, coeff, face, nf_count, vt_map, depth_weights, biases, relu):
+    return F2VPointwiseFunction.apply(input, filter, coeff, face, nf_count, vt_map, depth_weights, biases, relu)
