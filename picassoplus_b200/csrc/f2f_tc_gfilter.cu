@@ -11,13 +11,14 @@
 //     copy of bary whose rows are padded to a multiple of 4 floats), the other fetches the
 //     CTA's 16 input channels of every sample with 16-byte asynchronous copies into per-face
 //     slots; the sample ranges they need are loaded three stages ahead;
-//   * 8 compute warps build both operands in shared memory, MN-major (128-byte swizzle,
-//     32-byte base): a face is a K-row whose 128-byte pieces hold 32 consecutive output
-//     channels (gradOutput block) or 32 consecutive (basis, channel) columns (A block), so
-//     neither operand is transposed and every store is a 16-byte vector.  Warp w copies the
-//     gradOutput rows of faces 2w, 2w+1 (straight from global memory into registers, two
-//     stages ahead) and builds the A columns of bases 4w..4w+3 (thread = face x 8 channels,
-//     one 16-byte bary load per sample);
+//   * both operands live in shared memory MN-major (128-byte swizzle): a face is a K-row whose
+//     128-byte pieces hold consecutive output channels (gradOutput block) or consecutive
+//     (basis, channel) columns (A block), so neither operand is transposed and every store is
+//     a vector.  8 compute warps build the A block: warp w the columns of bases 4w..4w+3
+//     (thread = face x 8 channels, one 16-byte bary load per sample);
+//   * 4 warps write the gradOutput block: each copies 4 of the stage's 16 rows straight from
+//     global memory (registers, one stage ahead), splits and stores them -- on warps of their
+//     own this work overlaps the compute warps' chains instead of lengthening them (-7 %);
 //   * one thread issues tcgen05.mma (M = 128 output channels, N = F*16 in chunks of <= 256,
 //     K = 8 faces per instruction) and commits the stage back.
 // What bounds it: every 16-byte shared-memory access of a warp costs at least 4 passes of the
@@ -45,7 +46,10 @@ constexpr int CWARPS = 8;                     // compute warps 0..7: two faces x
 constexpr int REC_WARP = CWARPS;              // loader: face records + bary block
 constexpr int X_WARP = CWARPS + 1;            // loader: sample rows
 constexpr int MMA_WARP = CWARPS + 2;
-constexpr int NTHREADS = (CWARPS + 3) * 32;
+constexpr int G_WARP = CWARPS + 3;            // first of the warps that write the gradOutput operand
+constexpr int GWARPS = 4;
+constexpr int GROWS = KF / GWARPS;            // rows of a stage per such warp
+constexpr int NTHREADS = (CWARPS + 3 + GWARPS) * 32;
 static_assert(CWARPS * 16 == UM && CWARPS * 2 == KF, "one 16-channel gradOutput unit and two faces per compute warp");
 constexpr int ATOM_BYTES = 512;               // 4 K-rows x 128 bytes (32 M/N elements)
 constexpr int G_SBO = (UM / 32) * ATOM_BYTES; // gradOutput block: [4-face group][32-channel block][atom]
@@ -191,7 +195,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(&full[s], CWARPS); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(&full[s], CWARPS + GWARPS); mbar_init(&empty[s], 1); }
         // the sample-row warp's 32 asynchronous-copy arrivals + the record warp's arrival that
         // announces the bulk-copy bytes
         for (int r = 0; r < NRAW; ++r) { mbar_init(&raw_ready[r], 33); mbar_init(&raw_free[r], CWARPS); }
@@ -311,30 +315,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // load reads one whole row and the 8 lanes of a quarter warp store 128 consecutive bytes
         // of the face's K-row (16-byte piece l&7 of 32-channel block l>>3).
         // (bf16: 8-byte piece l&15 of 64-channel block l>>4)
-        auto g_row_off = [&](int k) -> uint32_t {
-            if (BF)
-                return (uint32_t)(k >> 3) * BG_SBO + (uint32_t)(k & 7) * 128u + (uint32_t)(lane >> 4) * BATOM_BYTES
-                       + ((((uint32_t)(lane & 15) >> 1) ^ (uint32_t)(k & 7)) << 4) + (uint32_t)(lane & 1) * 8u;
-            return (uint32_t)(k >> 2) * G_SBO + (uint32_t)(k & 3) * 128u + (uint32_t)(lane >> 3) * ATOM_BYTES
-                   + ((((uint32_t)(lane & 7) >> 1) ^ (uint32_t)(k & 3)) << 5) + (uint32_t)(lane & 1) * 16u;
-        };
-        const uint32_t g_off0 = g_row_off(2 * warp), g_off1 = g_row_off(2 * warp + 1);
-        auto load_g = [&](int64_t st, float4& u, float4& w) {
-            u = zero4(); w = zero4();
-            const int64_t f = (st0 + st) * KF + 2 * warp;
-            if (st >= nst || 4 * lane >= Cout) return;
-            if (f < p.Nf) u = ldg4(reinterpret_cast<const float4*>(p.gout + f * p.CoutF + p.co0) + lane);
-            if (f + 1 < p.Nf) w = ldg4(reinterpret_cast<const float4*>(p.gout + (f + 1) * p.CoutF + p.co0) + lane);
-        };
-        float4 gu0, gw0, gu1, gw1;                            // stages st and st + 1
-        load_g(0, gu0, gw0);
-        load_g(1, gu1, gw1);
         int si = 0, rbuf = 0;
         uint32_t sph = 0, rph = 0;
         bool alive = true;
         for (int64_t st = 0; st < nst; ++st) {
-            float4 gu2, gw2;
-            load_g(st + 2, gu2, gw2);
             if (!warp_wait(&raw_ready[rbuf], rph, abort_flag, lane)) { alive = false; break; }
             const uint32_t rb32 = raw32 + (uint32_t)rbuf * RAW_BYTES;
             const int4 rec = lds_i4(rb32 + RAW_REC_OFF + fl * 16);           // {kloc, T, 1/T, first sample}
@@ -343,9 +327,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             const float invT = __int_as_float(rec.z);
             if (!warp_wait(&empty[si], sph ^ 1u, abort_flag, lane)) { alive = false; break; }
             const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes;
-            if (BF) { put4_b16<NSPLIT>(sb32 + g_off0, GT, gu0); put4_b16<NSPLIT>(sb32 + g_off1, GT, gw0); }
-            else { put4<NSPLIT>(sb32 + g_off0, GT, gu0); put4<NSPLIT>(sb32 + g_off1, GT, gw0); }
-            gu0 = gu1; gw0 = gw1; gu1 = gu2; gw1 = gw2;
             if (has_unit && !slow) {
                 // fast path: every face of the stage has at most TREG samples, all of them staged.
                 // (Rows behind a face's last sample belong to other faces or are stale: their weight
@@ -430,6 +411,48 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                 }
             }
             tc_fence_before();
+        }
+    } else if (warp >= G_WARP) {
+        const int gw = warp - G_WARP;
+        // ================================ gradOutput operand ================================
+        // lane l holds channels 4l..4l+3 of the stage's 16 rows (one stage ahead in registers) and writes
+        // them as K-rows of the MN-major operand: 16-byte piece l&7 of 32-channel block l>>3 (tf32),
+        // 8-byte piece l&15 of 64-channel block l>>4 (bf16)
+        auto g_row_off = [&](int k) -> uint32_t {
+            if (BF)
+                return (uint32_t)(k >> 3) * BG_SBO + (uint32_t)(k & 7) * 128u + (uint32_t)(lane >> 4) * BATOM_BYTES
+                       + ((((uint32_t)(lane & 15) >> 1) ^ (uint32_t)(k & 7)) << 4) + (uint32_t)(lane & 1) * 8u;
+            return (uint32_t)(k >> 2) * G_SBO + (uint32_t)(k & 3) * 128u + (uint32_t)(lane >> 3) * ATOM_BYTES
+                   + ((((uint32_t)(lane & 7) >> 1) ^ (uint32_t)(k & 3)) << 5) + (uint32_t)(lane & 1) * 16u;
+        };
+        float4 cur[GROWS], nxt[GROWS];
+        auto load_rows = [&](int64_t st, float4 (&dst)[GROWS]) {
+#pragma unroll
+            for (int k = 0; k < GROWS; ++k) {
+                dst[k] = zero4();
+                const int64_t f = (st0 + st) * KF + gw * GROWS + k;
+                if (st < nst && 4 * lane < Cout && f < p.Nf)
+                    dst[k] = ldg4(reinterpret_cast<const float4*>(p.gout + f * p.CoutF + p.co0) + lane);
+            }
+        };
+        load_rows(0, cur);
+        int si = 0;
+        uint32_t sph = 0;
+        for (int64_t st = 0; st < nst; ++st) {
+            load_rows(st + 1, nxt);
+            if (!warp_wait(&empty[si], sph ^ 1u, abort_flag, lane)) break;
+            const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes;
+#pragma unroll
+            for (int k = 0; k < GROWS; ++k) {
+                if (BF) put4_b16<NSPLIT>(sb32 + g_row_off(gw * GROWS + k), GT, cur[k]);
+                else put4<NSPLIT>(sb32 + g_row_off(gw * GROWS + k), GT, cur[k]);
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[si]);
+#pragma unroll
+            for (int k = 0; k < GROWS; ++k) cur[k] = nxt[k];
+            if (++si == S) { si = 0; sph ^= 1u; }
         }
     } else {
         // ==================================== MMA issuer ====================================

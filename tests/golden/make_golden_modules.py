@@ -6,6 +6,8 @@ Python for the parts of the path that are plain torch code:
   * compute_triangle_geometry_       (picasso/mesh/pi_modules/decimate.py:70-85)
   * V2VConv3d and F2FConv3d, forward and backward with a seeded state_dict
                                      (picasso/mesh/layers.py:18-195)
+  * get_oriented_normals             (picasso/networks/scene_seg.py:117-124)
+  * PCloudConv3d with fuzzy bins, forward and backward (picasso/point/layers.py:19-75)
 
     REF_ROOT=<reference checkout> python tests/golden/make_golden_modules.py [output_dir]
 
@@ -14,8 +16,9 @@ cannot be imported as it is on a machine without its compiled extensions, so thi
 (and only this script) puts stand-ins into sys.modules for what the import needs but the
 recorded functions never call: `torch_scatter` (used by GlobalPool3d only),
 `scipy.special.sph_harm` (imported by math_utils, never called by torch_sph_harm_reorder),
-`mesh_decimation`, `mesh_pool3d`, `mesh_unpool3d` (imported by pi_modules, not called here).
-The one extension the modules do call, `mesh_conv3d`, is bound to the reference's own CUDA
+`mesh_decimation`, `mesh_pool3d`, `mesh_unpool3d`, `open3d` and the point-cloud extensions other than
+`point_conv3d` (imported by pi_modules / utils, not called here).
+The extensions the modules do call, `mesh_conv3d` and `point_conv3d`, are bound to the reference's own CUDA
 kernels (oracle/_ref, compiled from the reference sources) when a CUDA device is present,
 else to the plain-C restatement in oracle/mesh_oracle.c, which is itself pinned against
 those kernels by tests/golden/*.npz; the fixture records which one ran (`conv_backend`).
@@ -37,7 +40,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from cases import conv_inputs  # noqa: E402
+from cases import conv_inputs, pcloud_inputs  # noqa: E402
 
 
 def _install_stand_ins(use_cuda: bool) -> str:
@@ -47,8 +50,10 @@ def _install_stand_ins(use_cuda: bool) -> str:
     import scipy.special
     if not hasattr(scipy.special, "sph_harm"):
         scipy.special.sph_harm = lambda *a, **k: (_ for _ in ()).throw(RuntimeError("stand-in"))
-    for name in ("mesh_decimation", "mesh_pool3d", "mesh_unpool3d"):
+    for name in ("mesh_decimation", "mesh_pool3d", "mesh_unpool3d", "open3d", "point_buildkernel", "point_nnquery",
+                 "point_pool3d", "point_sample", "point_unpool3d"):
         sys.modules[name] = types.ModuleType(name)
+    pconv = types.ModuleType("point_conv3d")
 
     conv = types.ModuleType("mesh_conv3d")
     if use_cuda:
@@ -59,6 +64,10 @@ def _install_stand_ins(use_cuda: bool) -> str:
         conv.vertex2facet_backward = lambda g, x, w, f: list(rc.v2f_backward(g, x, w, f))
         conv.facet2vertex_forward = rc.f2v_forward
         conv.facet2vertex_backward = lambda g, x, w, c, f, n, m: list(rc.f2v_backward(g, x, w, c, f, n, m))
+        pconv.SPH3D_forward = lambda x, w, c, i, b: rc.pcloud_forward(x, w, c, i, b)
+        pconv.SPH3D_backward = lambda g, x, w, c, i, b: list(rc.pcloud_backward(g, x, w, c, i, b))
+        pconv.fuzzySPH3D_forward = lambda x, w, c, i, b, k: rc.pcloud_forward(x, w, c, i, b, k)
+        pconv.fuzzySPH3D_backward = lambda g, x, w, c, i, b, k: list(rc.pcloud_backward(g, x, w, c, i, b, k))
         backend = "reference CUDA kernels (oracle/_ref)"
     else:
         from oracle import c_oracle as co
@@ -71,10 +80,16 @@ def _install_stand_ins(use_cuda: bool) -> str:
         conv.facet2vertex_forward = lambda x, w, c, f, nf, m: t(co.f2v_forward(n(x), n(w), n(c), n(f), n(nf), n(m)))
         conv.facet2vertex_backward = lambda g, x, w, c, f, nf, m: [
             t(a) for a in co.f2v_backward(n(g), n(x), n(w), n(c), n(f), n(nf), n(m))]
+        pconv.SPH3D_forward = lambda x, w, c, i, b: t(co.pcloud_forward(n(x), n(w), n(c), n(i), n(b)))
+        pconv.SPH3D_backward = lambda g, x, w, c, i, b: [t(a) for a in co.pcloud_backward(n(g), n(x), n(w), n(c), n(i), n(b))]
+        pconv.fuzzySPH3D_forward = lambda x, w, c, i, b, k: t(co.pcloud_forward(n(x), n(w), n(c), n(i), n(b), n(k)))
+        pconv.fuzzySPH3D_backward = lambda g, x, w, c, i, b, k: [
+            t(a) for a in co.pcloud_backward(n(g), n(x), n(w), n(c), n(i), n(b), n(k))]
         backend = "plain-C restatement (oracle/mesh_oracle.c), fp32 accumulators"
         orig = torch.Tensor.get_device
         torch.Tensor.get_device = lambda self: orig(self) if self.is_cuda else "cpu"
     sys.modules["mesh_conv3d"] = conv
+    sys.modules["point_conv3d"] = pconv
     return backend
 
 
@@ -151,6 +166,32 @@ def main(out_dir: str) -> None:
         out["f2f_grad/" + n_] = p_.grad.cpu().numpy()
     for n_, b_ in f2f.named_buffers():
         out["f2f_buffer/" + n_] = b_.detach().cpu().numpy()
+
+    # ---- oriented normals (origin as viewpoint) on meshes centred on the origin, so that both signs occur
+    from picasso.networks.scene_seg import PicassoNetII
+    dn = conv_inputs("grid17x2", 4, 1, 4, 2, seed=74)
+    vert_c = (dn["vertex"] - 0.5).to(dev)
+    geo_c = ref_decimate.compute_triangle_geometry_(vert_c, dn["face"].to(dev))
+    out.update(orient_vertex=vert_c.cpu().numpy(), orient_face=dn["face"].numpy(), orient_geometry=geo_c.cpu().numpy(),
+               orient_normals=PicassoNetII.get_oriented_normals(None, geo_c, vert_c, dn["face"].to(dev)).cpu().numpy())
+
+    # ---- PCloudConv3d with fuzzy filter bins, depth multiplier 2
+    from picasso.point import layers as ref_point_layers
+    pc_args = (120, 70, 8, 9, 6, 2, 3, 75)                      # Np, Mp, knn, F, C, r, T, seed
+    dp = pcloud_inputs(*pc_args)
+    torch.manual_seed(9)
+    pconv = ref_point_layers.PCloudConv3d(6, 10, 9, depth_multiplier=2).to(dev)
+    pconv.train()
+    xp = dp["x"].clone().to(dev).requires_grad_()
+    Gp = torch.randn(70, 10, generator=g)
+    yp = pconv(xp, dp["nn_count"].to(dev), dp["nn_index"].to(dev), dp["bin_index"].to(dev), dp["bin_coeff"].to(dev))
+    (yp * Gp.to(dev)).sum().backward()
+    out.update(pc_args=np.array(pc_args), pc_G=Gp.numpy(), pc_out=yp.detach().cpu().numpy(), pc_grad_x=xp.grad.cpu().numpy())
+    for n_, p_ in pconv.named_parameters():
+        out["pc_param/" + n_] = p_.detach().cpu().numpy()
+        out["pc_grad/" + n_] = p_.grad.cpu().numpy()
+    for n_, b_ in pconv.named_buffers():
+        out["pc_buffer/" + n_] = b_.detach().cpu().numpy()
 
     os.makedirs(out_dir, exist_ok=True)
     path = os.path.join(out_dir, "modules_ref_python.npz")

@@ -56,3 +56,27 @@ def test_f2f_module_matches_reference_python():
     assert rel_err(tex.grad, FX["f2f_grad_tex"]) <= 1e-4
     for name, g in group(FX, "f2f_grad").items():
         assert rel_err(params[name].grad, g) <= 1e-4, name
+
+
+def test_oriented_normals_match_reference_python():
+    geo, vertex = torch.from_numpy(FX["orient_geometry"]), torch.from_numpy(FX["orient_vertex"])
+    face, want = torch.from_numpy(FX["orient_face"]), torch.from_numpy(FX["orient_normals"])
+    assert max_abs(mo.triangle_geometry(vertex, face), geo) <= 1e-6
+    got = mo.oriented_normals(geo, vertex, face)
+    assert torch.equal(got, want)
+    assert (want != geo[:, :3]).any() and (want == geo[:, :3]).any()       # both orientations occur
+
+
+def test_pcloud_module_matches_reference_python():
+    from cases import pcloud_inputs
+    d = pcloud_inputs(*[int(v) for v in FX["pc_args"]])
+    params = {k: v.double().requires_grad_() for k, v in group(FX, "pc_param").items()}
+    x = d["x"].double().requires_grad_()
+    from module_oracle import tail
+    f = mo.pcloud_conv3d_forward(x, params["spatial_weights"], d["nn_count"], d["nn_index"], d["bin_index"],
+                                 d["bin_coeff"].double())
+    out = tail(f @ params["depth_weights"], params["biases"], params["BatchNorm.weight"], params["BatchNorm.bias"])
+    (out * torch.from_numpy(FX["pc_G"]).double()).sum().backward()
+    assert rel_err(out, FX["pc_out"]) <= 1e-4 and rel_err(x.grad, FX["pc_grad_x"]) <= 1e-4
+    for name, g in group(FX, "pc_grad").items():
+        assert rel_err(params[name].grad, g) <= 1e-4, name

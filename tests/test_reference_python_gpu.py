@@ -79,3 +79,32 @@ def test_f2f_module_matches_reference_python():
     params = dict(mod.named_parameters())
     for name, g in group(FX, "f2f_grad").items():
         assert rel_err(params[name].grad, g) <= 1e-4, name
+
+
+def test_level_prepare_orientation_matches_reference_python():
+    from picassoplus_b200 import topology
+    vertex, face = torch.from_numpy(FX["orient_vertex"]).cuda(), torch.from_numpy(FX["orient_face"]).cuda()
+    vt = torch.arange(vertex.shape[0], dtype=torch.int32, device="cuda")
+    got = topology.prepare_level(vertex, face, vt, vertex.shape[0], 3, orient=True, want_normals=True)
+    assert max_abs(got["geometry"], FX["orient_geometry"]) <= 1e-6
+    assert max_abs(got["normals"], FX["orient_normals"]) <= 1e-6
+    flipped_ref = FX["orient_normals"] != FX["orient_geometry"][:, :3]
+    flipped = (got["normals"] != got["geometry"][:, :3]).cpu().numpy()
+    assert (flipped == flipped_ref).all()                               # the same faces are re-oriented
+
+
+def test_pcloud_module_matches_reference_python():
+    from cases import pcloud_inputs
+    from picassoplus_b200.point.layers import PCloudConv3d
+    Np, Mp, knn, F, C, r, T, seed = [int(v) for v in FX["pc_args"]]
+    d = pcloud_inputs(Np, Mp, knn, F, C, r, T, seed)
+    mod = PCloudConv3d(C, FX["pc_out"].shape[1], F, depth_multiplier=r)
+    _load(mod, "pc")
+    mod = mod.cuda().train()
+    x = d["x"].cuda().requires_grad_()
+    out = mod(x, d["nn_count"].cuda(), d["nn_index"].cuda(), d["bin_index"].cuda(), d["bin_coeff"].cuda())
+    (out * torch.from_numpy(FX["pc_G"]).cuda()).sum().backward()
+    assert rel_err(out, FX["pc_out"]) <= 1e-4 and rel_err(x.grad, FX["pc_grad_x"]) <= 1e-4
+    params = dict(mod.named_parameters())
+    for name, g in group(FX, "pc_grad").items():
+        assert rel_err(params[name].grad, g) <= 1e-4, name
