@@ -320,6 +320,9 @@ int pb200_vertex2facet_backward_static(int64_t Nf, int64_t Nv, int C, int r, con
                "vertex2facet_backward_static: this shape needs %zu bytes of scratch, the built-in array holds %u; "
                "use pb200_vertex2facet_backward with a caller-provided workspace",
                need, (unsigned)PB200_STATIC_SCRATCH_BYTES);
+    // argument checks before the first-call set-up, so that a bad call never triggers it
+    PB_REQUIRE(gradFilter && (Nf == 0 || (gradOutput && input && filter && face && rowptr && entries && gradInput)),
+               PB200_EINVAL, "vertex2facet_backward_static: null pointer");
     void* scratch = nullptr;
     int rc = static_scratch_for_current_device(&scratch);
     if (rc != PB200_OK) return rc;
