@@ -333,6 +333,39 @@ int pb200_pcloud_conv3d_backward(int64_t Np, int64_t Mp, int64_t Nout, int F, in
                                  float* gradInput, float* gradFilter, void* workspace, size_t workspace_bytes,
                                  void* stream);
 
+/* ---- mesh decimation (one pass) and cluster merge ----------------------------------------
+ * pb200_mesh_simplify replaces meshDecimationLauncher (picasso/mesh/pi_modules/source/decimate_gpu.cu:618-747;
+ * binding decimate.cpp MeshDecimation, Python module function `simplify`): one pass of quadric-error vertex
+ * clustering over a batch of B meshes.  nvIn / mfIn (B) are the running totals of vertices / faces per sample
+ * (the last ones equal Nv / Nf), nv2Remove (B) the vertices to remove per sample; vertexIn (Nv,D>=3),
+ * faceIn (Nf,3), planeIn (Nf,5) = unit normal, plane intercept, area.  Outputs as the reference's:
+ * vertexOut (Nv,D) (cluster means; zero rows for contracted vertices), faceOut (Nf,3) (relabelled to output
+ * ids where not degenerate), isDegenerate (Nf) bytes, vtReplace (Nv) (negative = contracted into that vertex,
+ * positive = cluster size - 1, 0 = untouched), vtMap (Nv) (output id or -1), nvOut / mfOut (B).
+ * Everything runs on the device; the reference's per-sample host loop and its sequential clustering sweeps
+ * (decimate_gpu.cu:561-614) are computed as parallel rounds with the same result.  Where the reference adds
+ * floats with atomics, the order here is fixed: quadrics by ascending (face, corner), cluster means by
+ * ascending vertex id, and no multiply-add is fused, so the result is reproducible bit for bit.  Candidates
+ * with equal cost keep their (lower vertex, higher vertex) order; -0 counts as +0, NaN costs come last.
+ * Edges of a face that names a vertex twice are no candidates.
+ * edgeCost (3*Nf floats, may be NULL) receives the cost of every distinct edge in (lower, higher) order;
+ * info (HOST pointer to 4 int64, may be NULL) = {distinct edges, matching rounds run on the whole grid, edges
+ * handed to the single-block finish, 0}.  The call synchronises the stream a few times (it reads back three
+ * counters and the 2*B sample totals) and returns PB200_EINDEX for a vertex id outside [0, Nv). */
+size_t pb200_mesh_simplify_workspace_bytes(int64_t B, int64_t Nv, int64_t Nf);
+int pb200_mesh_simplify(int useArea, float wgtBnd, int64_t B, int64_t D, int64_t Nv, int64_t Nf,
+                        const int32_t* nvIn, const int32_t* mfIn, const int32_t* nv2Remove, const float* vertexIn,
+                        const int32_t* faceIn, const float* planeIn, int32_t* nvOut, int32_t* mfOut, float* vertexOut,
+                        int32_t* faceOut, int32_t* vtReplace, int32_t* vtMap, uint8_t* isDegenerate, float* edgeCost,
+                        int64_t* info, void* workspace, size_t workspace_bytes, void* stream);
+/* Clusters of a mesh A (repA, mapA over its nvA vertices) merged with the clusters of its decimated
+ * version B (repB, mapB over nvB vertices) into clusters of A over the vertices B kept.  Replaces
+ * combineClustersLauncher (decimate_gpu.cu:750-812; binding CombineClusters, `combine_clusters`).
+ * Workspace: (nvB + 1) int32; `status` = 0 or PB200_EINDEX (an id out of range, skipped). */
+int pb200_combine_clusters(int64_t nvA, int64_t nvB, const int32_t* repA, const int32_t* mapA, const int32_t* repB,
+                           const int32_t* mapB, int32_t* repOut, int32_t* mapOut, int32_t* status, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* ---- row expansion (benchmark block glue) ----------------------------------------------
  * forward:  out[k,:] = in[f,:] for every sample k of face f (numInterior as above);
  * backward: gradIn[f,:] = sum over the samples k of f of gradOut[k,:] (fixed order).

@@ -207,3 +207,37 @@ def pcloud_backward(gout, inp, filt, nn_count, nn_index, bin_index, bin_coeff=No
                                  _p(nn_count), _p(nn_index), _p(bin_index), None if coeff is None else _p(coeff), _p(inp),
                                  _p(filt), _p(gout), _p(gin), _p(gf))
     return gin, gf
+
+
+def mesh_simplify(vertex, face, geometry, nv_cum, mf_cum, nv2remove, use_area=True, wgt_bnd=5.0):
+    """One decimation pass (decimate_oracle.c).  nv_cum / mf_cum are the running totals per sample.
+    Returns a dict with the reference's seven outputs plus the candidate costs in edge order."""
+    vertex, face, geometry = _f32(vertex), _i32(face), _f32(geometry)
+    nv_cum, mf_cum, nv2remove = _i32(nv_cum), _i32(mf_cum), _i32(nv2remove)
+    Nv, D = vertex.shape
+    Nf, B = face.shape[0], nv_cum.shape[0]
+    out = dict(vertexOut=np.zeros((Nv, D), np.float32), faceOut=np.zeros((Nf, 3), np.int32),
+               isDegenerate=np.zeros(Nf, np.uint8), vtReplace=np.zeros(Nv, np.int32), vtMap=np.zeros(Nv, np.int32),
+               nvOut=np.zeros(B, np.int32), mfOut=np.zeros(B, np.int32))
+    cost = np.zeros(max(3 * Nf, 1), np.float32)
+    fn = lib().oracle_mesh_simplify
+    fn.restype = C.c_int
+    nu = fn(C.c_int(int(bool(use_area))), C.c_float(float(wgt_bnd)), C.c_int(B), C.c_int(D), C.c_int(Nv), C.c_int(Nf),
+            _p(nv_cum), _p(mf_cum), _p(nv2remove), _p(vertex), _p(face), _p(geometry), _p(out["nvOut"]), _p(out["mfOut"]),
+            _p(out["vertexOut"]), _p(out["faceOut"]), _p(out["vtReplace"]), _p(out["vtMap"]), _p(out["isDegenerate"]),
+            _p(cost))
+    if nu < 0:
+        raise MemoryError("oracle_mesh_simplify")
+    out["isDegenerate"] = out["isDegenerate"].astype(bool)
+    out["edgeCost"] = cost[:nu]
+    return out
+
+
+def combine_clusters(rep_a, map_a, rep_b, map_b):
+    rep_a, map_a, rep_b, map_b = _i32(rep_a), _i32(map_a), _i32(rep_b), _i32(map_b)
+    rep_out, map_out = np.zeros_like(rep_a), np.zeros_like(map_a)
+    fn = lib().oracle_combine_clusters
+    fn.restype = None
+    fn(C.c_int(rep_a.shape[0]), C.c_int(rep_b.shape[0]), _p(rep_a), _p(map_a), _p(rep_b), _p(map_b), _p(rep_out),
+       _p(map_out))
+    return rep_out, map_out

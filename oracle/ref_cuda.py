@@ -176,3 +176,31 @@ def pcloud_backward(gout, inp, filt, nn_count, nn_index, bin_index, bin_coeff=No
                                    _p(nn_index), _p(bin_index), None if bin_coeff is None else _p(bin_coeff), _p(inp),
                                    _p(filt), _p(gout), _p(gin), _p(gf)))
     return gin, gf
+
+
+def mesh_simplify(vertex, face, geometry, nv_cum, mf_cum, nv2remove, use_area=True, wgt_bnd=5.0):
+    """One pass of the reference's decimation (decimate_gpu.cu:618-747; outputs allocated as
+    decimate.cpp:57-63 does).  The reference keeps a per-vertex array on the host stack: small meshes only."""
+    assert vertex.shape[0] <= 200_000
+    _sync_in()
+    Nv, D = vertex.shape
+    Nf, B = face.shape[0], nv_cum.shape[0]
+    dev = vertex.device
+    out = dict(vertexOut=torch.zeros(Nv, D, dtype=torch.float32, device=dev),
+               faceOut=torch.zeros(Nf, 3, dtype=torch.int32, device=dev),
+               isDegenerate=torch.zeros(Nf, dtype=torch.bool, device=dev),
+               vtReplace=torch.zeros(Nv, dtype=torch.int32, device=dev), vtMap=torch.zeros(Nv, dtype=torch.int32, device=dev),
+               nvOut=torch.zeros(B, dtype=torch.int32, device=dev), mfOut=torch.zeros(B, dtype=torch.int32, device=dev))
+    _chk(lib().ref_mesh_simplify(int(bool(use_area)), C.c_float(float(wgt_bnd)), B, D, Nv, Nf, _p(nv_cum), _p(mf_cum),
+                                 _p(nv2remove), _p(vertex), _p(face), _p(geometry), _p(out["nvOut"]), _p(out["mfOut"]),
+                                 _p(out["vertexOut"]), _p(out["faceOut"]), _p(out["vtReplace"]), _p(out["vtMap"]),
+                                 _p(out["isDegenerate"])))
+    return out
+
+
+def combine_clusters(rep_a, map_a, rep_b, map_b):
+    _sync_in()
+    rep_out, map_out = torch.zeros_like(rep_a), torch.zeros_like(map_a)
+    _chk(lib().ref_combine_clusters(rep_a.shape[0], rep_b.shape[0], _p(rep_a), _p(map_a), _p(rep_b), _p(map_b),
+                                    _p(rep_out), _p(map_out)))
+    return rep_out, map_out

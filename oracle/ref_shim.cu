@@ -3,7 +3,8 @@
 // This file holds declarations and forwarding calls only; the kernels themselves are
 // compiled from the reference tree where it lies (see oracle/Makefile, target `ref`).
 // Launcher signatures: picasso/mesh/pi_modules/source/mesh_conv3d.cpp:9-23,
-// picasso/mesh/pi_modules/source/decimate.cpp (countVertexAdjfaceLauncher),
+// picasso/mesh/pi_modules/source/decimate.cpp:9-17 (meshDecimationLauncher, combineClustersLauncher,
+// countVertexAdjfaceLauncher),
 // mesh_pool3d.cpp:8-15, mesh_unpool3d.cpp:8-11 and picasso/point/pi_modules/source/pcloud_conv3d.cpp:8-21.
 #include <cuda_runtime.h>
 
@@ -22,6 +23,12 @@ void facet2facetConv3dGradLauncher(int NfIn, int F, int Cin, int Cout, const int
                                    const float* input, const float* filter, const float* gradOutput,
                                    float* gradInput, float* gradFilter);
 void countVertexAdjfaceLauncher(int NfIn, const int* face, const int* vtMap, int* nfCount);
+void meshDecimationLauncher(const bool useArea, const float wgtBnd, const int B, const int D, const int Nv, const int Nf,
+                            const int* nvIn, const int* mfIn, const int* nv2Remove, const float* vertexIn,
+                            const int* faceIn, const float* planeIn, int* nvOut, int* mfOut, float* vertexOut,
+                            int* faceOut, int* vtReplace, int* vtMap, bool* isDegenerate);
+void combineClustersLauncher(const int nvA, const int nvB, const int* repA, const int* mapA, const int* repB,
+                             const int* mapB, int* repOut, int* mapOut);
 void maxPool3dLauncher(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* input, float* output,
                        int* maxIndex);
 void maxPool3dGradLauncher(int nvOut, int C, const int* maxIndex, const float* gradOutput, float* gradInput);
@@ -88,6 +95,20 @@ int ref_f2f_backward(int NfIn, int F, int Cin, int Cout, const int* numInterior,
 }
 int ref_count_vertex_adjface(int NfIn, const int* face, const int* vtMap, int* nfCount) {
     countVertexAdjfaceLauncher(NfIn, face, vtMap, nfCount);
+    return finish();
+}
+// The reference keeps one int per vertex in an array on the host stack (decimate_gpu.cu:663):
+// callers keep Nv small.
+int ref_mesh_simplify(int useArea, float wgtBnd, int B, int D, int Nv, int Nf, const int* nvIn, const int* mfIn,
+                      const int* nv2Remove, const float* vertexIn, const int* faceIn, const float* planeIn, int* nvOut,
+                      int* mfOut, float* vertexOut, int* faceOut, int* vtReplace, int* vtMap, bool* isDegenerate) {
+    meshDecimationLauncher(useArea != 0, wgtBnd, B, D, Nv, Nf, nvIn, mfIn, nv2Remove, vertexIn, faceIn, planeIn, nvOut,
+                           mfOut, vertexOut, faceOut, vtReplace, vtMap, isDegenerate);
+    return finish();
+}
+int ref_combine_clusters(int nvA, int nvB, const int* repA, const int* mapA, const int* repB, const int* mapB,
+                         int* repOut, int* mapOut) {
+    combineClustersLauncher(nvA, nvB, repA, mapA, repB, mapB, repOut, mapOut);
     return finish();
 }
 int ref_max_pool_forward(int nvIn, int C, const int* vtReplace, const int* vtMap, const float* input, float* output,

@@ -24,7 +24,7 @@ if not os.path.exists(LIB_PATH):
 
 _lib = C.CDLL(LIB_PATH)
 
-i64, i32, vp, sz = C.c_int64, C.c_int, C.c_void_p, C.c_size_t
+i64, i32, vp, sz, f32 = C.c_int64, C.c_int, C.c_void_p, C.c_size_t, C.c_float
 
 
 class ProfRecord(C.Structure):
@@ -80,6 +80,10 @@ SIGNATURES = {
     "pb200_pcloud_conv3d_backward_workspace_bytes": (sz, [i64, i32, i32, i32]),
     "pb200_pcloud_conv3d_backward": (i32, [i64, i64, i64, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                            vp, sz, vp]),
+    "pb200_mesh_simplify_workspace_bytes": (sz, [i64, i64, i64]),
+    "pb200_mesh_simplify": (i32, [i32, f32, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                                  vp, sz, vp]),
+    "pb200_combine_clusters": (i32, [i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_sph_harm_coeff": (i32, [i64, i32, vp, vp, vp]),
     "pb200_triangle_geometry": (i32, [i64, i64, i32, vp, vp, vp, vp]),
     "pb200_expand_rows_forward": (i32, [i64, i64, i32, vp, vp, vp, vp]),

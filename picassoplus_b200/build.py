@@ -26,6 +26,11 @@ NVCC_FLAGS = [
 ]
 
 
+# Per-file flags.  The decimation kernels round every float operation on its own (no fused
+# multiply-add) so that their edge costs, and with them the clustering, are reproducible by plain C.
+FILE_FLAGS = {"decimate.cu": ["--fmad=false"]}
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", "nvcc"):
         if cand and (os.path.isabs(cand) and os.path.exists(cand) or not os.path.isabs(cand)):
@@ -54,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(OBJ, src[:-3] + ".o")
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hm):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [nvcc] + NVCC_FLAGS + FILE_FLAGS.get(src, []) + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append(cmd)
 
     def run(cmd):

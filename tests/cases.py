@@ -144,3 +144,60 @@ PCLOUD_GOLDEN_CASES = {
     "pcloud_hard_n200_m60_c6_r2": (200, 60, 12, 9, 6, 2, 0, 41),
     "pcloud_fuzzy_n150_m80_c8_r1": (150, 80, 10, 17, 8, 1, 3, 42),
 }
+
+
+def decimate_inputs(meshes, remove_frac: float, D: int, seed: int, noise: float = 0.0):
+    """A batch for one decimation pass, as CPU torch tensors: `meshes` is a list of ("heightfield", n, seed)
+    / ("icosphere", level) descriptions, remove_frac the share of every sample's vertices to remove,
+    D >= 3 the vertex row width (columns past xyz are random features), noise the standard deviation of
+    a random displacement of every vertex.  Height fields have boundary edges and holes, spheres are
+    closed.  Without noise the meshes are regular and many candidate edges have exactly equal costs;
+    with noise the costs are well separated."""
+    import numpy as _np
+    from picassoplus_b200 import synth
+    from oracle import c_oracle
+    rng = _np.random.default_rng(seed)
+    vs, fs, nv, mf, off = [], [], [], [], 0
+    for m in meshes:
+        v, f = synth.heightfield(m[1], seed=m[2]) if m[0] == "heightfield" else synth.icosphere(m[1])
+        v = v.astype(_np.float32)
+        if noise > 0:
+            v = v + (noise * rng.standard_normal(v.shape)).astype(_np.float32)
+        vs.append(v)
+        fs.append(f.astype(_np.int32) + off)
+        off += v.shape[0]
+        nv.append(v.shape[0])
+        mf.append(f.shape[0])
+    V = _np.concatenate(vs)
+    if D > 3:
+        V = _np.concatenate([V, rng.standard_normal((V.shape[0], D - 3)).astype(_np.float32)], axis=1)
+    F = _np.concatenate(fs)
+    geo = c_oracle.triangle_geometry(V[:, :3].copy(), F)
+    nv, mf = _np.array(nv, _np.int32), _np.array(mf, _np.int32)
+    remove = _np.floor(nv * remove_frac).astype(_np.int32)
+    t = torch.from_numpy
+    return dict(vertex=t(_np.ascontiguousarray(V)), face=t(F), geometry=t(geo), nv=t(nv), mf=t(mf),
+                nv_cum=t(_np.cumsum(nv).astype(_np.int32)), mf_cum=t(_np.cumsum(mf).astype(_np.int32)),
+                remove=t(remove))
+
+
+# one decimation pass, library against the sequential restatement (bit for bit):
+# name: (meshes, remove_frac, D, seed, noise, useArea, wgtBnd)
+DECIMATE_CASES = {
+    "two_sweeps": ([("heightfield", 24, 1), ("icosphere", 2), ("heightfield", 17, 3)], 0.75, 3, 51, 0.0, True, 5.0),
+    "early_stop": ([("icosphere", 3), ("heightfield", 20, 7)], 0.15, 6, 52, 0.0, False, 0.0),
+    "plain_weight": ([("heightfield", 30, 9)], 0.5, 4, 53, 0.0, False, 3.0),
+    "one_sample_skipped": ([("heightfield", 16, 2), ("icosphere", 2), ("heightfield", 12, 4)], 0.6, 3, 54, 0.02, True, 5.0),
+    "larger": ([("heightfield", 90, 11), ("heightfield", 70, 12), ("icosphere", 4)], 0.7, 3, 55, 0.01, True, 5.0),
+}
+
+# fixtures recorded from the reference's own kernels: small meshes with displaced vertices, where the
+# candidate costs are far enough apart that neither the order of the reference's float atomics nor its
+# fused multiply-adds change the clustering:
+# name: (meshes, remove_frac, D, seed, noise, useArea, wgtBnd)
+DECIMATE_GOLDEN_CASES = {
+    "decim_two_sweeps": ([("heightfield", 8, 1), ("icosphere", 1), ("heightfield", 10, 2)], 0.75, 3, 5, 0.05, True, 5.0),
+    "decim_early_stop": ([("heightfield", 8, 1), ("icosphere", 1), ("heightfield", 10, 2)], 0.2, 5, 5, 0.05, True, 5.0),
+    "decim_medium": ([("heightfield", 12, 3), ("icosphere", 2)], 0.6, 3, 6, 0.03, True, 5.0),
+    "decim_closed_plain": ([("icosphere", 2), ("icosphere", 1)], 0.5, 3, 7, 0.05, False, 0.0),
+}

@@ -6,7 +6,8 @@ operators (oracle/_ref, see oracle/Makefile target `ref`) on a CUDA device:
 For every case of tests/cases.py:GOLDEN_CASES it stores the inputs and the reference's
 outputs (all three operators forward and backward, and nfCount) in <case>.npz, and for
 every case of POOL_GOLDEN_CASES / PCLOUD_GOLDEN_CASES the reference's mesh pooling / unpooling and
-point-cloud convolution outputs.  The parts
+point-cloud convolution outputs, for every case of DECIMATE_GOLDEN_CASES two passes of the reference's
+mesh decimation and the merge of their clusters.  The parts
 of the path that are plain Python in the reference (spherical-harmonic basis, triangle
 geometry, layer modules) have their own generator, make_golden_modules.py.
 """
@@ -22,8 +23,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-from cases import (GOLDEN_CASES, PCLOUD_GOLDEN_CASES, POOL_GOLDEN_CASES, cluster_inputs, conv_inputs,  # noqa: E402
-                   pcloud_inputs)
+from cases import (DECIMATE_GOLDEN_CASES, GOLDEN_CASES, PCLOUD_GOLDEN_CASES, POOL_GOLDEN_CASES, cluster_inputs,  # noqa: E402
+                   conv_inputs, decimate_inputs, pcloud_inputs)
+from oracle import c_oracle  # noqa: E402
 from oracle import ref_cuda  # noqa: E402
 
 
@@ -75,6 +77,35 @@ def main(out_dir):
         arrays.update({("ref_" + k): v.cpu().numpy() for k, v in out.items()})
         np.savez_compressed(os.path.join(out_dir, name + ".npz"), **arrays)
         print("wrote", name, {k: tuple(v.shape) for k, v in arrays.items() if k.startswith("ref_")})
+    # mesh decimation (decimate_gpu.cu): two passes as decimate.py:30-46 chains them, and the cluster merge
+    names = ("vertexOut", "faceOut", "isDegenerate", "vtReplace", "vtMap", "nvOut", "mfOut")
+    for name, (meshes, frac, D, seed, noise, use_area, wgt_bnd) in DECIMATE_GOLDEN_CASES.items():
+        d = decimate_inputs(meshes, frac, D, seed, noise)
+        c = {k: v.to(dev) for k, v in d.items()}
+        arrays = {("in_" + k): v.numpy() for k, v in d.items()}
+        arrays["use_area"], arrays["wgt_bnd"] = np.array(use_area), np.array(wgt_bnd, np.float32)
+        r1 = ref_cuda.mesh_simplify(c["vertex"], c["face"], c["geometry"], c["nv_cum"], c["mf_cum"], c["remove"],
+                                    use_area, wgt_bnd)
+        again = ref_cuda.mesh_simplify(c["vertex"], c["face"], c["geometry"], c["nv_cum"], c["mf_cum"], c["remove"],
+                                       use_area, wgt_bnd)
+        assert all(torch.equal(r1[k], again[k]) for k in names if k != "vertexOut"), "reference not repeatable on " + name
+        arrays.update({("ref1_" + k): r1[k].cpu().numpy() for k in names})
+        # second pass on the compacted mesh: every sample sheds a third of what it has left
+        face2 = r1["faceOut"][~r1["isDegenerate"]].contiguous()
+        vertex2 = r1["vertexOut"][r1["vtMap"] >= 0].contiguous()
+        geo2 = torch.from_numpy(c_oracle.triangle_geometry(vertex2[:, :3].cpu().numpy().copy(), face2.cpu().numpy())).to(dev)
+        nv2, mf2 = r1["nvOut"], r1["mfOut"]
+        nv_cum2 = torch.cumsum(nv2, 0, dtype=torch.int32)
+        mf_cum2 = torch.cumsum(mf2, 0, dtype=torch.int32)
+        remove2 = (nv2 // 3).to(torch.int32)
+        r2 = ref_cuda.mesh_simplify(vertex2, face2, geo2, nv_cum2, mf_cum2, remove2, use_area, wgt_bnd)
+        arrays.update(in2_vertex=vertex2.cpu().numpy(), in2_face=face2.cpu().numpy(), in2_geometry=geo2.cpu().numpy(),
+                      in2_nv_cum=nv_cum2.cpu().numpy(), in2_mf_cum=mf_cum2.cpu().numpy(), in2_remove=remove2.cpu().numpy())
+        arrays.update({("ref2_" + k): r2[k].cpu().numpy() for k in names})
+        rep, mp = ref_cuda.combine_clusters(r1["vtReplace"], r1["vtMap"], r2["vtReplace"], r2["vtMap"])
+        arrays["ref_comb_rep"], arrays["ref_comb_map"] = rep.cpu().numpy(), mp.cpu().numpy()
+        np.savez_compressed(os.path.join(out_dir, name + ".npz"), **arrays)
+        print("wrote", name, "nvOut", r1["nvOut"].tolist(), "->", r2["nvOut"].tolist())
 
 
 if __name__ == "__main__":
