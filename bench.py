@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS) + ["c4"])
+    ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS) + ["c4", "decimate"])
     ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_tf32x3", "tf32", "bf16"])
     ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -61,6 +61,9 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--hierarchy", default="decimate", choices=["decimate", "grid"],
+                    help="config c4: mesh levels by the library's quadric-error decimation (stride 4 per level) or by "
+                         "halving the height-field grid")
     ap.add_argument("--no-fusion", action="store_true", help="config c4: run the layer modules as operator + separate "
                     "pointwise kernels instead of the fused operator + pointwise kernels")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="target CPU time of one baseline step")
@@ -589,8 +592,9 @@ def run_c4(args):
     """BASELINE configuration 4: encoder stack over four mesh levels, forward + backward.  Per level
     one V2VConv3d module (vertex2facet -> pointwise -> facet2vertex -> pointwise, ReLU, batch norm in
     training mode) followed by a max pool to the next level; channels 64 -> 128 -> 256 -> 384, L = 3.
-    The hierarchy comes from synth.heightfield_hierarchy (grid halving, face ratios 1 / 0.25 / 0.062 /
-    0.015), which stands in for the reference's GPU decimation; indices are built once and held fixed."""
+    The levels come from the library's quadric-error decimation (stride 4 per level; --hierarchy grid
+    halves the height-field grid instead: face ratios 1 / 0.25 / 0.062 / 0.015 either way); they are
+    built once, timed on their own (hierarchy_build_ms), and held fixed over the steps."""
     from picassoplus_b200 import _lib, topology
     from picassoplus_b200.mesh import layers as mesh_layers
     from picassoplus_b200.mesh.layers import Pool3d, V2VConv3d
@@ -604,7 +608,25 @@ def run_c4(args):
     torch.cuda.set_device(dev)
     cfg = C4
     conv3d.set_f2f_precision(args.precision)
-    levels, trans = c4_hierarchy(cfg)
+    hierarchy_ms = None
+    if args.hierarchy == "grid":
+        levels, trans = c4_hierarchy(cfg)
+    else:
+        # levels by decimation, as the reference's networks build them per batch (picasso/mesh/utils.py:32-58,
+        # networks/scene_seg.py:131): stride 4 per level, the reference's hyper-parameters (scene_seg.py:23)
+        from picassoplus_b200.mesh.utils import MeshHierarchy
+        mb0 = synth.concat_meshes([synth.heightfield(cfg["n"], cfg["seed"] * 1000 + i) for i in range(cfg["batch"])])
+        t_in = [torch.from_numpy(a).to(dev) for a in (mb0.vertex, mb0.face, mb0.nv.astype(np.int32), mb0.mf.astype(np.int32))]
+        build = MeshHierarchy([4] * (cfg["levels"] - 1), [16] * (cfg["levels"] - 1), True, 1.0)
+        build(*t_in)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        hier = build(*t_in)
+        torch.cuda.synchronize()
+        hierarchy_ms = (time.perf_counter() - t0) * 1e3
+        levels = [synth.MeshBatch(h[0][:, :3].cpu().numpy(), h[1].cpu().numpy(), h[3].cpu().numpy(), h[4].cpu().numpy())
+                  for h in hier]
+        trans = [(h[5].cpu().numpy(), h[6].cpu().numpy()) for h in hier[1:]]
     L, ch = cfg["L"], cfg["channels"]
     rng = np.random.default_rng(cfg["seed"] + 77)
     v0 = levels[0].vertex
@@ -671,7 +693,9 @@ def run_c4(args):
         "config": {"workload": f"encoder stack, {cfg['batch']} heightfield meshes {cfg['n']}x{cfg['n']} over 4 levels "
                                f"(faces {[m.num_faces for m in levels]}), channels 64->128->256->384, L=3", "name": "c4"},
         "workload_detail": {"faces_level0": faces, "vertices_per_level": [m.num_vertices for m in levels],
-                            "hierarchy": "synthetic grid halving (stands in for the reference's GPU decimation)",
+                            "hierarchy": ("grid halving of the height fields" if args.hierarchy == "grid" else
+                                          "quadric-error decimation by the library, stride 4 per level (pb200_mesh_simplify)"),
+                            "hierarchy_build_ms": hierarchy_ms,
                             "pointwise_stage": ("torch.matmul + bias + ReLU (cuBLAS / torch kernels), BatchNorm1d in torch"
                                                 if args.no_fusion else
                                                 "fused with the operator in one tcgen05 kernel (forward; "
@@ -686,6 +710,188 @@ def run_c4(args):
         "kernels": [dict(kernel=n, launches_per_step=c, ms_per_step=t) for n, c, t in records[:14]],
     }
     print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------ decimation
+DECIMATE = dict(n=360, batch=32, stride=4, seed=5, use_area=True, wgt_bnd=1.0)
+DECIMATE_METRIC, DECIMATE_UNIT = "mesh_decimation_input_faces_per_sec", "faces/s"
+
+
+def decimate_batch(cfg, meshes):
+    mb = synth.concat_meshes([synth.heightfield(cfg["n"], cfg["seed"] * 1000 + i) for i in range(meshes)])
+    return mb, (mb.nv // cfg["stride"]).astype(np.int32)
+
+
+def decimate_workload(cfg, meshes, mb):
+    return (f"decimation of {meshes} heightfield meshes {cfg['n']}x{cfg['n']} ({mb.num_vertices} vertices, {mb.num_faces} "
+            f"faces) to 1/{cfg['stride']} of their vertices: triangle geometry + all passes of the quadric-error "
+            "clustering + cluster merges")
+
+
+def run_decimate(args):
+    """One step = the whole decimation of the batch to a quarter of its vertices (geometry, every pass of
+    pb200_mesh_simplify, compaction, cluster merges), as the reference's networks run it once per batch and
+    level (picasso/mesh/utils.py:42-58).  The workload (4.1 M vertices) is larger than L2."""
+    from picassoplus_b200 import _lib
+    from picassoplus_b200.mesh.pi_modules import decimate as dm
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for --impl ours)")
+    assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "config decimate is a single-GPU measurement"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = DECIMATE
+    meshes = args.meshes or cfg["batch"]
+    mb, target = decimate_batch(cfg, meshes)
+    host = [torch.from_numpy(a).pin_memory() for a in (mb.vertex, mb.face, mb.nv.astype(np.int32), mb.mf.astype(np.int32), target)]
+    resident = [t.to(dev) for t in host]
+
+    def step(inputs):
+        vertex, face, nv, mf, nv_out = inputs
+        geo = dm.compute_triangle_geometry_(vertex, face)
+        return dm.mesh_decimation_(vertex, face, geo, nv, mf, nv_out, cfg["use_area"], cfg["wgt_bnd"])
+
+    def step_e2e():
+        res = step([t.to(dev, non_blocking=True) for t in host])
+        return res[3].cpu(), res[4].cpu()
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        res = step(resident)
+    torch.cuda.synchronize()
+    with ClockSampler(gpu_uuid(dev)) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n0 = _lib.launch_count()
+        e0.record()
+        for _ in range(args.steps):
+            res = step(resident)
+        e1.record()
+        torch.cuda.synchronize()
+        launches = _lib.launch_count() - n0
+    ms = e0.elapsed_time(e1) / args.steps
+    for _ in range(2):
+        step_e2e()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        nv_res, mf_res = step_e2e()
+    torch.cuda.synchronize()
+    ms_e2e = (time.perf_counter() - t0) * 1e3 / args.steps
+    # the dominant kernel of the first (largest) pass: the radix-sort scatter
+    vertex, face, nv, mf, nv_out = resident
+    geo = dm.compute_triangle_geometry_(vertex, face)
+    nv_cum, mf_cum = torch.cumsum(nv, 0, dtype=torch.int32), torch.cumsum(mf, 0, dtype=torch.int32)
+    _lib.prof_reset()
+    _lib.prof_enable(True)
+    _, info, _ = dm.simplify(vertex, face, geo, nv_cum, mf_cum, (nv - nv_out).to(torch.int32), cfg["use_area"], cfg["wgt_bnd"],
+                             return_info=True)
+    torch.cuda.synchronize()
+    _lib.prof_enable(False)
+    records = _lib.prof_read(64)
+    _lib.prof_reset()
+    peaks = load_peaks()
+    Nv, Nf, nu = mb.num_vertices, mb.num_faces, int(info[0])
+    edge_passes = -(-2 * max(Nv, 1).bit_length() // 8)
+    cost_passes = -(-(32 + meshes.bit_length()) // 8)
+    scatter_bytes = 24 * (edge_passes * 3 * Nf + cost_passes * nu)            # key + payload, read and written
+    scatter = [r for r in records if r[0] == "dec_sort_scatter"]
+    sc_ms = scatter[0][2] if scatter else float("nan")
+    pass_ms = sum(r[2] for r in records)
+    line = {
+        "metric": DECIMATE_METRIC, "value": Nf / (ms / 1e3), "unit": DECIMATE_UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": decimate_workload(cfg, meshes, mb), "name": "decimate", "l2": "inputs larger than L2"},
+        "e2e": dict(value=Nf / (ms_e2e / 1e3), unit=DECIMATE_UNIT, ms_per_step=ms_e2e,
+                    h2d_bytes_per_step=int(sum(t.numel() * t.element_size() for t in host)),
+                    d2h_bytes_per_step=int(nv_res.numel() * 4 + mf_res.numel() * 4)),
+        "roofline": {"bound": "hbm", "achieved": scatter_bytes / (sc_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": scatter_bytes / (sc_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "kernel": "dec_sort_scatter", "launches": scatter[0][1] if scatter else 0,
+                     "note": "first pass only: (key 8 B + payload 4 B) read and written per element and radix pass, "
+                             f"{edge_passes} passes over {3 * Nf} edge instances + {cost_passes} over {nu} candidates",
+                     "peak_source": peaks["source"]},
+        "first_pass": {"kernel_ms": pass_ms, "distinct_edges": nu, "grid_rounds": int(info[1]), "tail_edges": int(info[2])},
+        "result": {"vertices_out": int(res[3].sum()), "faces_out": int(res[4].sum())},
+        "gpu_launches": int(launches), "clocks": clk.summary(),
+        "kernels": [dict(kernel=n, launches=c, ms=t, share=t / pass_ms) for n, c, t in records[:12]],
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = decimate_cpu_baseline(cfg, min(meshes, 8))
+    print(json.dumps(line))
+
+
+def decimate_cpu_baseline(cfg, meshes):
+    """The sequential C restatement of the same loop on one host core, on `meshes` meshes of the workload."""
+    from oracle import c_oracle
+    mb, target = decimate_batch(cfg, meshes)
+    vertex, face, nv, mf = mb.vertex, mb.face, mb.nv.astype(np.int32), mb.mf.astype(np.int32)
+    t0 = time.perf_counter()
+    geo = c_oracle.triangle_geometry(vertex, face)
+    remove = nv - target
+    rep, mp = np.zeros(vertex.shape[0], np.int32), np.arange(vertex.shape[0], dtype=np.int32)
+    while (remove > 0).any():
+        o = c_oracle.mesh_simplify(vertex, face, geo, np.cumsum(nv).astype(np.int32), np.cumsum(mf).astype(np.int32),
+                                   remove.astype(np.int32), cfg["use_area"], cfg["wgt_bnd"])
+        if not ((nv - o["nvOut"]) > 0).any():
+            break
+        face, vertex = o["faceOut"][~o["isDegenerate"]], o["vertexOut"][o["vtMap"] >= 0]
+        geo = c_oracle.triangle_geometry(vertex[:, :3].copy(), face)
+        remove = remove - (nv - o["nvOut"])
+        rep, mp = c_oracle.combine_clusters(rep, mp, o["vtReplace"], o["vtMap"])
+        nv, mf = o["nvOut"], o["mfOut"]
+    dt = time.perf_counter() - t0
+    return dict(value=mb.num_faces / dt, unit=DECIMATE_UNIT, cores=1, kind="port", seconds=dt,
+                sample=f"{meshes} of the workload's meshes ({mb.num_faces} faces), the whole loop, sequential C restatement")
+
+
+def run_reference_decimate(args):
+    """Reference arm of config decimate.  The reference's decimation is a CUDA program with a host loop; where its
+    sources were compiled (oracle/_ref) and a GPU is present it is run unmodified on a sample its per-vertex host
+    stack array allows (decimate_gpu.cu:663), otherwise the sequential C restatement is timed on the host."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cfg = DECIMATE
+    from oracle import ref_cuda
+    if ref_cuda.available():
+        from oracle import c_oracle
+        sub = dict(cfg, n=200)
+        mb, target = decimate_batch(sub, 4)
+        dev = torch.device("cuda", 0)
+        geo = torch.from_numpy(c_oracle.triangle_geometry(mb.vertex, mb.face)).to(dev)
+        vertex, face = torch.from_numpy(mb.vertex).to(dev), torch.from_numpy(mb.face).to(dev)
+        nv_cum = torch.from_numpy(np.cumsum(mb.nv).astype(np.int32)).to(dev)
+        mf_cum = torch.from_numpy(np.cumsum(mb.mf).astype(np.int32)).to(dev)
+        remove = torch.from_numpy((mb.nv - target).astype(np.int32)).to(dev)
+
+        def step():
+            ref_cuda.mesh_simplify(vertex, face, geo, nv_cum, mf_cum, remove, cfg["use_area"], cfg["wgt_bnd"])
+        kind, cores = "reference", 1
+        sample = (f"first pass only on 4 heightfield meshes 200x200 ({mb.num_faces} faces): the reference's own CUDA kernels "
+                  "and host loop, unmodified, on this GPU (its per-vertex host stack array bounds the size)")
+        nf = mb.num_faces
+    else:
+        def step():
+            step.out = decimate_cpu_baseline(cfg, 4)
+        kind, cores, nf = "port", 1, None
+        sample = "4 of the workload's meshes, the whole loop, sequential C restatement on one host core"
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    if kind == "reference":
+        torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / args.steps
+    if nf is None:
+        nf = decimate_batch(cfg, 4)[0].num_faces
+    value = nf / dt
+    print(json.dumps({
+        "impl": "reference", "metric": DECIMATE_METRIC, "value": value, "unit": DECIMATE_UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": {"name": "decimate", "workload": sample},
+        "cpu_baseline": dict(value=value, unit=DECIMATE_UNIT, cores=cores, kind=kind, sample=sample),
+        "e2e": dict(value=value, unit=DECIMATE_UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+    }))
 
 
 # ------------------------------------------------------------------- CPU oracle timing
@@ -789,8 +995,12 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.impl == "reference" and a.config == "decimate":
+        run_reference_decimate(a)
+    elif a.impl == "reference":
         run_reference(a)
+    elif a.config == "decimate":
+        run_decimate(a)
     elif a.config == "c4":
         run_c4(a)
     else:
