@@ -493,7 +493,29 @@ def run_ours(args):
             diff = (a.double() - b.double())
             parity[n] = dict(max_rel=float(diff.abs().max() / b.double().abs().max()),
                              rms_rel=float((diff ** 2).mean().sqrt() / (b.double() ** 2).mean().sqrt()))
-        parity["ok"] = all(parity[n]["max_rel"] <= GATES[args.precision] for n in names)
+        # the filter gradients sum over every face of the batch: check them on the rank's whole batch too
+        # (a sum that long is where an accumulator that truncates would show)
+
+        def whole_batch(mode):
+            conv3d.set_f2f_precision(mode)
+            ws = [p.detach().clone().requires_grad_() for p in params]
+            x0 = d["x"].detach().clone().requires_grad_()
+            o = conv_block(x0, ws[0], ws[1], ws[2], d["face"], d["cum"], bary_sh, coeff, nfc, vt_map, sh_eye)
+            o.backward(G)
+            return [w.grad for w in ws]
+
+        got_b, want_b = whole_batch(args.precision), whole_batch("fp32_ffma")
+        conv3d.set_f2f_precision(args.precision)
+        parity["whole_batch"] = {"sample": f"the rank's whole batch ({h['Nf']} faces)"}
+        for n, a, b in zip(names[2:], got_b, want_b):
+            diff = (a.double() - b.double())
+            parity["whole_batch"][n] = dict(
+                max_rel=float(diff.abs().max() / b.double().abs().max()),
+                rms_rel=float((diff ** 2).mean().sqrt() / (b.double() ** 2).mean().sqrt()),
+                scale=float((a.double() * b.double()).sum() / (b.double() ** 2).sum()) - 1.0)
+        del got_b, want_b
+        parity["ok"] = (all(parity[n]["max_rel"] <= GATES[args.precision] for n in names) and
+                        all(parity["whole_batch"][n]["max_rel"] <= GATES[args.precision] for n in names[2:]))
 
     # launch-bound batches: the same resident step captured once into a CUDA graph and replayed
     graph = None

@@ -25,8 +25,10 @@
 // load/store pipe, so the layout of every access is chosen to touch 512 distinct bytes; in
 // the hi+lo mode the three MMAs per product read their operands from shared memory three
 // times, and that traffic (about 123 KB per stage) is the floor.
-// At the end the accumulator is drained once into partial[chunk] (final gradFilter layout);
-// a second kernel adds the chunks in order, so the result is deterministic.
+// Every 256 stages the accumulator is added to a running sum in global memory and restarted (the
+// tensor core's adder truncates; see FLUSH_STAGES).  At the end accumulator + running sum go to
+// partial[chunk] (final gradFilter layout); a second kernel adds the chunks in order, so the result
+// is deterministic.
 // Modes: 1 split (bf16 or tf32 operands) or 2 splits (bf16 or tf32 hi+lo, three MMAs per k-step).
 #include "common.cuh"
 #include "tc_ptx.cuh"
@@ -55,6 +57,14 @@ constexpr int ATOM_BYTES = 512;               // 4 K-rows x 128 bytes (32 M/N el
 constexpr int G_SBO = (UM / 32) * ATOM_BYTES; // gradOutput block: [4-face group][32-channel block][atom]
 constexpr int G_TILE_BYTES = (KF / 4) * G_SBO;
 constexpr int TREG = 4;                       // samples per face on the fast path
+// The tensor core adds into its accumulator with truncation, so a long chain of accumulating
+// products drifts towards zero (measured: -1.2e-3 relative over the 26 000 stages a CTA walks on a
+// 7.4 M-face batch, -1.2e-5 over 256).  Every FLUSH_STAGES stages the accumulator is therefore added
+// (round-to-nearest, CUDA cores) to a running sum of the CTA in global memory and restarted.
+#ifndef PB_GF_FLUSH_STAGES
+#define PB_GF_FLUSH_STAGES 256
+#endif
+constexpr int FLUSH_STAGES = PB_GF_FLUSH_STAGES;
 __host__ __device__ constexpr int at_blocks(int F) { return (F * CG + 31) / 32; }   // 32-column blocks of the A operand
 
 // one raw buffer: what a stage needs from global memory, as it lies there
@@ -151,6 +161,26 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
     return ok != 0;
 }
 
+// One compute warp's share of a flush: its TMEM lane quadrant, every second group of 32 accumulator
+// columns, added to (or, the first time, stored as) the CTA's running sum.  Kept out of line so that its
+// 32 staging registers do not count against the operand-building loop it is called from.
+__device__ __noinline__ void flush_accumulator(uint32_t tmem_quadrant, float* run, int first_group, int ngroups,
+                                               bool add) {
+    for (int gi = first_group; gi < ngroups; gi += CWARPS / 4) {
+        uint32_t r[32];
+        tmem_ld32(tmem_quadrant + (uint32_t)(gi * 32), r);
+        tmem_ld_wait();
+        float* dst = run + (size_t)(gi * 32) * UM;
+        if (add) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dst[(size_t)j * UM] += __uint_as_float(r[j]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) dst[(size_t)j * UM] = __uint_as_float(r[j]);
+        }
+    }
+}
+
 struct Params {
     int64_t Nf;
     int Cin, Cout, F;         // Cin: channels of `in` (a multiple of 16); Cout: output channels of this launch's chunk
@@ -166,6 +196,7 @@ struct Params {
     const float* bary;        // padded copy: [samples][Fp], pad columns zero
     const int32_t* cum;
     float* partial;           // [nchunks][Cout*Cin*F]
+    float* running;           // [CTA][accumulator columns rounded up to 32][128 output channels]
     int* async_err;
     int wait_budget;          // bounded waits give up after this many units of 1024 clocks
 };
@@ -190,8 +221,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     uint64_t* empty = bars + S;                   // [S]    MMA done with the stage
     uint64_t* raw_ready = bars + 2 * S;           // [NRAW] copies of a raw buffer landed, records written
     uint64_t* raw_free = bars + 2 * S + NRAW;     // [NRAW] all compute warps done with a raw buffer
-    uint64_t* acc_done = bars + 2 * S + 2 * NRAW; // all MMAs of the CTA complete
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+    uint64_t* acc_done = bars + 2 * S + 2 * NRAW; // all MMAs issued so far complete (once per flush, once at the end)
+    uint64_t* acc_free = acc_done + 1;            // all compute warps have read the accumulator out
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (tid == 0) {
@@ -200,6 +232,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // announces the bulk-copy bytes
         for (int r = 0; r < NRAW; ++r) { mbar_init(&raw_ready[r], 33); mbar_init(&raw_free[r], CWARPS); }
         mbar_init(acc_done, 1);
+        mbar_init(acc_free, CWARPS);
         abort_flag[0] = 0;
         abort_flag[1] = p.wait_budget;
         fence_barrier_init();
@@ -223,6 +256,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
     if (st1 > total_stages) st1 = total_stages;
     const int64_t nst = st1 > st0 ? st1 - st0 : 0;
     const uint32_t raw32 = smem_u32(raw), stages32 = smem_u32(stages);
+    // The accumulator is flushed after stage b when (b + 1) is a multiple of FLUSH_STAGES.  The compute
+    // warps do it S stages later (before they build stage b + S), so that the operand ring is full
+    // when the products resume; a boundary too close to the end of the chunk is left to the final drain.
+    // (every role counts stages of the chunk in 32 bits: a chunk has fewer than 2^31 stages)
+    const int nst32 = (int)nst;
 
     if (warp == REC_WARP || warp == X_WARP) {
         // ===================================== loaders =====================================
@@ -316,9 +354,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
         // of the face's K-row (16-byte piece l&7 of 32-channel block l>>3).
         // (bf16: 8-byte piece l&15 of 64-channel block l>>4)
         int si = 0, rbuf = 0;
-        uint32_t sph = 0, rph = 0;
-        bool alive = true;
-        for (int64_t st = 0; st < nst; ++st) {
+        uint32_t sph = 0, rph = 0, aph = 0;
+        bool alive = true, flushed = false;
+        const int dq = warp & 3, dhalf = warp >> 2;      // TMEM lane quadrant, half of the 32-column groups
+        const int ngroups = (NR + 31) / 32;
+        float* run = p.running + ((size_t)blockIdx.x * (size_t)(ngroups * 32)) * UM + (dq * 32 + lane);
+        int to_flush = FLUSH_STAGES + S;                 // iterations until the next flush is due here
+        for (int st = 0; st < nst32; ++st) {
+            if (--to_flush == 0) {                       // stage st - S closed a run of FLUSH_STAGES stages
+                to_flush = FLUSH_STAGES;
+                // running sum += accumulator (a thread meets the same addresses at every flush)
+                if (!warp_wait(acc_done, aph, abort_flag, lane)) { alive = false; break; }
+                aph ^= 1u;
+                tc_fence_after();
+                flush_accumulator(tmem_base + ((uint32_t)(dq * 32) << 16), run, dhalf, ngroups, flushed);
+                flushed = true;
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_free);
+            }
             if (!warp_wait(&raw_ready[rbuf], rph, abort_flag, lane)) { alive = false; break; }
             const uint32_t rb32 = raw32 + (uint32_t)rbuf * RAW_BYTES;
             const int4 rec = lds_i4(rb32 + RAW_REC_OFF + fl * 16);           // {kloc, T, 1/T, first sample}
@@ -388,24 +442,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             if (++rbuf == NRAW) { rbuf = 0; rph ^= 1u; }
         }
         // ==================================== drain ====================================
-        if (alive && warp_wait(acc_done, 0u, abort_flag, lane)) {
+        if (alive && warp_wait(acc_done, aph, abort_flag, lane)) {
             tc_fence_after();
-            const int q = warp & 3, hcol = warp >> 2;       // TMEM lane quadrant, half of the 32-column groups
-            const int co = q * 32 + lane;
+            const int co = dq * 32 + lane;
             float* out = p.partial + (int64_t)chunk * p.CoutF * p.CinF * F;
-            const int ngroups = (NR + 31) / 32;
-            for (int gi = hcol; gi < ngroups; gi += CWARPS / 4) {
+            for (int gi = dhalf; gi < ngroups; gi += CWARPS / 4) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(gi * 32), r);
+                tmem_ld32(tmem_base + ((uint32_t)(dq * 32) << 16) + (uint32_t)(gi * 32), r);
                 tmem_ld_wait();
+                const float* src = run + (size_t)(gi * 32) * UM;
                 if (co < Cout) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         int col = gi * 32 + j;
                         if (col < NR) {
                             const int d = col / CG, kk = col - d * CG, ci = cgp * CG + kk;
-                            if (ci < p.CinF)
-                                out[((int64_t)(p.co0 + co) * p.CinF + ci) * F + d] = nst > 0 ? __uint_as_float(r[j]) : 0.f;
+                            if (ci < p.CinF) {
+                                float v = nst > 0 ? __uint_as_float(r[j]) : 0.f;
+                                if (flushed) v += src[(size_t)j * UM];
+                                out[((int64_t)(p.co0 + co) * p.CinF + ci) * F + d] = v;
+                            }
                         }
                     }
                 }
@@ -470,16 +526,24 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             const uint32_t g_kstep = 2 * G_SBO, a_kstep = 2 * at_sbo;
             const uint32_t n_chunk = BF ? 4u * BATOM_BYTES : 8u * ATOM_BYTES;      // 256 columns further on
             int si = 0;
-            uint32_t sph = 0;
-            bool alive = true;
-            for (int64_t st = 0; st < nst; ++st) {
+            uint32_t sph = 0, fph = 0;
+            bool alive = true, fresh = true;                 // fresh: the next product overwrites the accumulator
+            int run_len = 0;                                 // stages added to the accumulator since it was restarted
+            bool wait_free = false;
+            for (int st = 0; st < nst32; ++st) {
                 if (!mbar_wait(&full[si], sph, abort_flag)) { alive = false; break; }
+                if (wait_free) {                             // the compute warps have read the accumulator out
+                    wait_free = false;
+                    if (!mbar_wait(acc_free, fph, abort_flag)) { alive = false; break; }
+                    fph ^= 1u;
+                    fresh = true;
+                }
                 tc_fence_after();
                 const uint64_t soff = (uint64_t)(((uint32_t)si * (uint32_t)stage_bytes) >> 4);
                 const uint64_t dg_hi0 = dbase_g + soff, da_hi0 = dbase_a + soff;
 #pragma unroll
                 for (int k2 = 0; k2 < KSTEPS; ++k2) {
-                    const uint32_t first = (st != 0 || k2 != 0) ? 1u : 0u;
+                    const uint32_t first = (!fresh || k2 != 0) ? 1u : 0u;
                     for (int c = 0; c < (n2 > 0 ? 2 : 1); ++c) {
                         const uint32_t d_tmem = tmem_base + (uint32_t)(c * 256);
                         const uint32_t idesc = c == 0 ? idesc1 : idesc2;
@@ -499,7 +563,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
                         }
                     }
                 }
+                fresh = false;
                 tc_commit(&empty[si]);
+                if (++run_len == FLUSH_STAGES) {
+                    run_len = 0;
+                    if (st + S < nst32) { tc_commit(acc_done); wait_free = true; }
+                }
                 if (++si == S) { si = 0; sph ^= 1u; }
             }
             if (alive) tc_commit(acc_done);
@@ -538,7 +607,7 @@ __global__ void pad_bary_kernel(int64_t n, int F, int Fp, const float* __restric
 }
 
 // ---------------------------------------------------------------------------- host side
-struct Plan { int nsplit, bf, ncg, nchunks, nstages, nraw; int64_t stages_per_chunk; size_t smem, partial_bytes; };
+struct Plan { int nsplit, bf, ncg, nchunks, nstages, nraw; int64_t stages_per_chunk; size_t smem, partial_bytes, running_bytes; };
 
 // every channel count: `input` must come with its channels padded to a multiple of 16 (tc::pad_input),
 // output channels are walked in chunks of 128; rows of gradOutput are read 16 bytes at a time
@@ -568,7 +637,8 @@ Plan plan(int64_t Nf, int Cin, int Cout, int F, int precision) {
     pl.nstages = S;
     pl.nraw = R;
     pl.smem = (size_t)S * stage + (size_t)R * RAW_BYTES + fixed;
-    pl.partial_bytes = (size_t)pl.nchunks * Cout * Cin * F * sizeof(float);
+    pl.partial_bytes = align_up((size_t)pl.nchunks * Cout * Cin * F * sizeof(float), 256);
+    pl.running_bytes = (size_t)pl.ncg * pl.nchunks * (size_t)((F * CG + 31) / 32 * 32) * UM * sizeof(float);
     return pl;
 }
 
@@ -577,7 +647,8 @@ bool fits(int64_t Nf, int Cin, int Cout, int F, int precision) {
 }
 
 size_t workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision) {
-    return align_up(plan(Nf, Cin, Cout, F, precision).partial_bytes, 256);
+    const Plan pl = plan(Nf, Cin, Cout, F, precision);
+    return align_up(pl.partial_bytes + pl.running_bytes, 256);
 }
 
 // `bary_p`: bary with rows of `Fp` floats (F rounded up to 4, pad columns zero; see tc::pad_bary);
@@ -593,6 +664,7 @@ int backward_filter(int64_t Nf, int Cin, int Cout, int F, const float* gout, con
     p.ncg = pl.ncg; p.nchunks = pl.nchunks; p.stages_per_chunk = pl.stages_per_chunk;
     p.nstages = pl.nstages; p.nraw = pl.nraw;
     p.gout = gout; p.in = input_p; p.cum = cum; p.partial = (float*)ws;
+    p.running = (float*)((char*)ws + pl.partial_bytes);
     p.bary = bary_p;
     p.async_err = async_error_word();
     p.wait_budget = wait_budget_kclocks();

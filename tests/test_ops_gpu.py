@@ -255,6 +255,40 @@ def test_one_benchmark_mesh_against_fp64(mods):
         conv3d.set_f2f_precision("fp32")
 
 
+def test_filter_gradient_over_a_long_batch_against_fp64(mods):
+    """Eight meshes of the headline configuration (1.86 M faces): the filter gradient sums over all faces,
+    a CTA of the tensor-core kernel walks 100 000 of them.  The tensor core adds into its accumulator with
+    truncation, so without the periodic flush of the accumulator into a round-to-nearest running sum the result
+    drifts towards zero with the length of that walk (-3.1e-4 here, -1.2e-3 on the 32-mesh batch): the gate
+    must hold at this size too."""
+    conv3d, _, mo, _ = mods
+    from picassoplus_b200 import synth
+    cfg = dict(synth.CONFIGS["c5"])
+    mb = synth.make_batch(cfg, 8, 0)
+    counts_np = np.concatenate([synth.texture_samples(int(m), 11 + i)[0] for i, m in enumerate(mb.mf)])
+    g = torch.Generator(device="cuda").manual_seed(6)
+    cum = torch.cumsum(torch.from_numpy(counts_np), 0, dtype=torch.int32).cuda()
+    nik = int(counts_np.sum())
+    C, F, cout = cfg["cin"], (cfg["L"] + 1) ** 2, cfg["cout"]
+    tex = torch.randn(nik, C, generator=g, device="cuda")
+    bary = torch.randn(nik, F, generator=g, device="cuda")
+    W = torch.randn(cout, C, F, generator=g, device="cuda") / (C * F) ** 0.5
+    go = torch.randn(mb.num_faces, cout, generator=g, device="cuda")
+    # fp64 filter gradient in face chunks (the input gradient has no long sum and is covered elsewhere)
+    _, wgf = mo.facet2facet_backward(go.double(), tex.double(), W.double(), bary.double(), cum, chunk=16384)
+    gates = {"fp32": 1e-4, "tf32": 2e-3, "bf16": 2e-2}
+    try:
+        for mode, gate in gates.items():
+            conv3d.set_f2f_precision(mode)
+            _, gf = conv3d.facet2facet_backward(go, tex, W, bary, cum)
+            err = rel_err(gf, wgf)
+            scale = float((gf.double() * wgf).sum() / (wgf * wgf).sum()) - 1.0
+            assert err <= gate, (mode, err)
+            assert abs(scale) <= 5e-5, (mode, "systematic scale error", scale)
+    finally:
+        conv3d.set_f2f_precision("fp32")
+
+
 def test_autograd_functions_match_oracle_block(mods):
     """The three autograd Functions chained as the benchmark block, against the oracle's
     autograd over the same formula (fp64)."""
