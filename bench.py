@@ -124,23 +124,34 @@ def make_params(cfg):
 
 # ------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    FIELDS = ("uuid,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi in loop mode beside the timed region.  Entering waits until the first sample has arrived
+    (so the sampler is already running when the timed region starts, however short that is), and the summary
+    counts only samples whose own timestamps lie inside the region."""
+    FIELDS = ("timestamp,uuid,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, uuid):
+    def __init__(self, uuid, active=True):
         self.uuid = uuid
+        self.active = active                                   # only rank 0 samples (its own GPU)
         self.lines = []
         self.proc = None
+        self.t0 = self.t1 = None
 
     def __enter__(self):
+        if not self.active:
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            deadline = time.time() + 2.0
+            while not self.lines and time.time() < deadline:
+                time.sleep(0.005)
         except OSError:
             self.proc = None
+        self.t0 = time.time()
         return self
 
     def _pump(self):
@@ -148,32 +159,55 @@ class ClockSampler:
             self.lines.append(line)
 
     def __exit__(self, *exc):
+        self.t1 = time.time()
         if self.proc is not None:
+            time.sleep(0.03)                                   # let the sample taken at the end arrive
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
+    @staticmethod
+    def _stamp(text):
+        import datetime
+        try:
+            return datetime.datetime.strptime(text.strip(), "%Y/%m/%d %H:%M:%S.%f").timestamp()
+        except ValueError:
+            return None
+
     def summary(self):
-        sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 8 or (self.uuid and self.uuid not in parts[0]):
+            if len(parts) < 9 or (self.uuid and self.uuid not in parts[1]):
                 continue
             try:
-                sm.append(float(parts[1]))
-                smax.append(float(parts[2]))
+                rows.append((self._stamp(parts[0]), float(parts[2]), float(parts[3]), parts[5:9]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[4:8]):
+        inside = [r for r in rows if r[0] is not None and self.t0 is not None and self.t0 - 0.005 <= r[0] <= self.t1 + 0.005]
+        note = None
+        if not inside and rows and self.t0 is not None:
+            # a region shorter than the sampling interval: the sample closest to it
+            mid = 0.5 * (self.t0 + self.t1)
+            stamped = [r for r in rows if r[0] is not None]
+            if stamped:
+                inside = [min(stamped, key=lambda r: abs(r[0] - mid))]
+                note = "timed region shorter than the sampling interval: nearest sample"
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        reasons = set()
+        for r in inside:
+            for n, v in zip(names, r[3]):
                 if v == "Active":
                     reasons.add(n)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        out = {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": max(r[2] for r in inside),
+               "reasons": sorted(reasons), "samples": len(inside)}
+        if note:
+            out["note"] = note
+        return out
 
 
 def gpu_uuid(dev):
@@ -334,8 +368,10 @@ def run_ours(args):
     # End to end: the rank's meshes are fed from pinned host memory in groups; the copy of
     # group g+1 overlaps the fwd+bwd of group g (filter gradients accumulate over the groups).
     host_bytes = sum(h[k].numel() * h[k].element_size() for k in ("vertex", "face", "x", "cum", "bary_xyz"))
-    # at least two groups whenever the rank holds two meshes, so that a copy always has compute to hide behind
-    want_groups = args.e2e_groups if args.e2e_groups > 0 else max(2, min(4, host_bytes // (256 << 20)))
+    # one group per 300 MB of host input, at most four.  Every group costs about 0.6 ms of fixed work (preparation,
+    # CSR build, launches), and the feed is double-buffered across steps as well (the first group of the next step
+    # is copied while the last group of this one is computed), so a small shard goes in one piece.
+    want_groups = args.e2e_groups if args.e2e_groups > 0 else max(1, min(4, host_bytes // (300 << 20)))
     ngroups = max(1, min(want_groups, count))
     feed = None
     if not args.no_e2e:
@@ -405,7 +441,7 @@ def run_ours(args):
 
     for _ in range(max(args.warmup, 3)):
         step_resident()
-    with ClockSampler(gpu_uuid(dev)) as clk:
+    with ClockSampler(gpu_uuid(dev), active=(rank == 0)) as clk:
         ms, launches = timed(step_resident, args.steps)
     clocks = clk.summary()
     ms_per_step = ms / args.steps
