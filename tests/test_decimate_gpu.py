@@ -123,6 +123,44 @@ def test_equal_costs_long_chains(n, frac, device):
     assert (g["vtReplace"] < 0).sum() > 0
 
 
+def random_soup(rng, nv, nf, B):
+    """B samples of random triangles over random points: non-manifold edges (shared by three and more faces),
+    duplicate faces, faces that name a vertex twice, isolated vertices, many boundary edges."""
+    vs, fs, nvs, mfs, off = [], [], [], [], 0
+    for _ in range(B):
+        n, m = int(rng.integers(nv // 2, nv + 1)), int(rng.integers(nf // 2, nf + 1))
+        v = rng.standard_normal((n, 3)).astype(np.float32)
+        f = rng.integers(0, n, size=(m, 3)).astype(np.int32)
+        f[: m // 8] = f[m // 8: 2 * (m // 8)]                 # duplicates
+        f[-3:, 1] = f[-3:, 0]                                 # a vertex named twice
+        vs.append(v); fs.append(f + off); nvs.append(n); mfs.append(m); off += n
+    return np.concatenate(vs), np.concatenate(fs), np.array(nvs, np.int32), np.array(mfs, np.int32)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_triangle_soups(seed, device):
+    rng = np.random.default_rng(100 + seed)
+    B = int(rng.integers(1, 5))
+    v, f, nv, mf = random_soup(rng, 120, 300, B)
+    geo = c_oracle.triangle_geometry(v, f)
+    frac = [0.05, 0.3, 0.6, 0.9, 0.5, 0.75][seed]
+    remove = np.floor(nv * frac).astype(np.int32)
+    if B > 1:
+        remove[0] = 0                                          # one sample left alone
+    arrs = [v, f, geo, np.cumsum(nv).astype(np.int32), np.cumsum(mf).astype(np.int32), remove]
+    check_against_oracle(device, arrs, bool(seed % 2), [0.0, 1.0, 5.0][seed % 3])
+
+
+def test_degenerate_sizes(device):
+    # a batch whose second sample has no face at all, nothing to remove anywhere, a single triangle
+    v = np.array([[0, 0, 0], [1, 0, 0], [0, 1, 0], [5, 5, 5], [6, 5, 5]], np.float32)
+    f = np.array([[0, 1, 2]], np.int32)
+    geo = c_oracle.triangle_geometry(v, f)
+    for remove in ([0, 0], [1, 1], [3, 2]):
+        arrs = [v, f, geo, np.array([3, 5], np.int32), np.array([1, 1], np.int32), np.array(remove, np.int32)]
+        check_against_oracle(device, arrs, True, 5.0)
+
+
 def oracle_decimation(d, nv_out, use_area, wgt_bnd):
     """The pass loop of picasso/mesh/pi_modules/decimate.py:30-46 on the restatement."""
     vertex, face, geo = d["vertex"].numpy(), d["face"].numpy(), d["geometry"].numpy()
