@@ -399,9 +399,9 @@ def run_ours(args):
             b = next(feed_cycle)
             nv = b["vertex"].shape[0]
             vt = vt_map[:nv]
-            nfc_ = mesh_utils.count_vertex_adjface(b["face"], vt, b["vertex"])
-            geo = mesh_utils.compute_triangle_geometry(b["vertex"], b["face"])
-            coeff_ = sph_harm_coeff(L, geo[:, :3].contiguous())
+            # nfCount, face normals, their SH coefficients and the vertex CSR in one library call
+            lvl = topology.prepare_level(b["vertex"], b["face"], vt, nv, L, want_geometry=False)
+            nfc_, coeff_ = lvl["nf_count"], lvl["coeff"]
             bary_ = sph_harm_coeff(L, b["bary_xyz"])
             xe = b["x"].detach().requires_grad_()
             o = conv_block(xe, params[0], params[1], params[2], b["face"], b["cum"], bary_, coeff_, nfc_, vt, sh_eye)
