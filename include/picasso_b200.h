@@ -198,6 +198,17 @@ int pb200_facet2vertex_pointwise_forward(int64_t Nf, int64_t NvOut, int C, int K
                                          const float* depthWeights, const float* bias, int relu, float* output,
                                          int precision, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Backward of the pointwise stage on the tensor cores (no counterpart in the reference, whose modules leave it
+ * to autograd): output[row, co] = sum_c g[row, c] * weights[c, co] with g = rows where mask > 0, else 0
+ * (mask = the stage's activated output; NULL = no activation).  rows, mask (Nrows, C), C a multiple of 8;
+ * weights (C, Cout) row-major -- pass depth_weights transposed to get the gradient of the operator output;
+ * maskedRows (Nrows, C), may be NULL, receives g itself (needed for the weight and bias gradients).
+ * Precision PB200_PREC_FP32 (bf16 hi + lo operands, about 1e-5 relative) or PB200_PREC_BF16. */
+size_t pb200_masked_rows_matmul_workspace_bytes(int C, int precision);
+int pb200_masked_rows_matmul(int64_t Nrows, int C, int Cout, const float* rows, const float* mask, const float* weights,
+                             float* output, float* maskedRows, int precision, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
 /* ---- facet2facet --------------------------------------------------------------------
  * A[f,d,ci] = (1/T_f) sum_{k in samples(f)} bary[k,d]*input[k,ci];
  * output[f,co] = sum_{d,ci} A[f,d,ci]*filter[co,ci,d];  samples(f) = rows

@@ -84,6 +84,10 @@ struct Params {
     const int32_t* rowptr;
     const int32_t* entries;
     const int32_t* nfCount;
+    // masked rows (backward of the pointwise stage)
+    const float* rows;        // (Nrows, C) upstream gradient
+    const float* mask;        // (Nrows, C) activated output: the gradient passes where it is > 0; NULL = no mask
+    float* masked_out;        // (Nrows, C) the masked gradient, written as a by-product; NULL = not wanted
     const uint8_t* wimg;
     const float* bias;        // (Cout chunk) or NULL
     float* out;               // first output channel of the chunk
@@ -93,7 +97,7 @@ struct Params {
 
 __host__ __device__ inline size_t stage_bytes(int nsplit) { return (size_t)nsplit * (ROW_TILE_BYTES + W_TILE_BYTES); }
 
-// MODE 0: vertex2facet rows, MODE 1: facet2vertex rows
+// MODE 0: vertex2facet rows, MODE 1: facet2vertex rows, MODE 2: rows of a gradient masked by an activation
 template <int NSPLIT, int MODE>
 __global__ void __launch_bounds__(NTHREADS, 1) rows_pointwise_tc_kernel(Params p) {
     extern __shared__ uint8_t smem_raw[];
@@ -195,6 +199,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) rows_pointwise_tc_kernel(Params p
                                 const float4* f = reinterpret_cast<const float4*>(p.vfilt + (int64_t)k * C + c);
                                 fma4(a0, ldg4(f), ldg4(x));
                                 fma4(a1, ldg4(f + 1), ldg4(x + 1));
+                            }
+                        }
+                    } else if (MODE == 2) {
+                        if (valid) {
+                            const float4* x = reinterpret_cast<const float4*>(p.rows + row * C + c);
+                            a0 = ldg4(x); a1 = ldg4(x + 1);
+                            if (p.mask) {
+                                const float4* mk = reinterpret_cast<const float4*>(p.mask + row * C + c);
+                                const float4 m0 = ldg4(mk), m1 = ldg4(mk + 1);
+                                a0 = make_float4(m0.x > 0.f ? a0.x : 0.f, m0.y > 0.f ? a0.y : 0.f, m0.z > 0.f ? a0.z : 0.f,
+                                                 m0.w > 0.f ? a0.w : 0.f);
+                                a1 = make_float4(m1.x > 0.f ? a1.x : 0.f, m1.y > 0.f ? a1.y : 0.f, m1.z > 0.f ? a1.z : 0.f,
+                                                 m1.w > 0.f ? a1.w : 0.f);
+                            }
+                            if (p.masked_out) {
+                                float4* mo = reinterpret_cast<float4*>(p.masked_out + row * C + c);
+                                mo[0] = a0; mo[1] = a1;
                             }
                         }
                     } else {
@@ -337,7 +358,8 @@ static int run(Params p, int Cout, const float* wd, const float* bias, float* ou
         PB_LAUNCH("pw_prep_weights", pw_prep_weights_kernel, persistent_blocks((int64_t)pl.nkb * UM * 4, 256, 8), 256, 0, stream,
                   p.C, Cout, co0, cchunk, pl.nkb, pl.nsplit, wd, wimg);
         p.Cout = cchunk; p.wimg = wimg; p.bias = bias ? bias + co0 : nullptr; p.out = out + co0;
-        const char* label = MODE == 0 ? "v2f_pointwise_tc" : "f2v_pointwise_tc";
+        const char* label = MODE == 0 ? "v2f_pointwise_tc" : (MODE == 1 ? "f2v_pointwise_tc" : "masked_rows_tc");
+        if (MODE == 2 && co0 > 0) p.masked_out = nullptr;      // the by-product is written by the first chunk's launch
         if (pl.nsplit == 2) {
             PB_CUDA(cudaFuncSetAttribute(rows_pointwise_tc_kernel<2, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl.smem));
             PB_LAUNCH(label, (rows_pointwise_tc_kernel<2, MODE>), grid, NTHREADS, pl.smem, stream, p);
@@ -415,6 +437,31 @@ int pb200_facet2vertex_pointwise_forward(int64_t Nf, int64_t NvOut, int C, int K
     p.Nrows = NvOut; p.C = C; p.relu = relu;
     p.wx = wx; p.rowptr = rowptr; p.entries = entries; p.nfCount = nfCount;
     return pw::run<1>(p, Cout, depthWeights, bias, output, precision, workspace, stream);
+}
+
+size_t pb200_masked_rows_matmul_workspace_bytes(int C, int precision) {
+    if (C <= 0) return 0;
+    return align_up(pw::plan(C, precision).wimg_bytes, 256);
+}
+
+int pb200_masked_rows_matmul(int64_t Nrows, int C, int Cout, const float* rows, const float* mask, const float* weights,
+                             float* output, float* maskedRows, int precision, void* workspace, size_t workspace_bytes,
+                             void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nrows >= 0 && C > 0 && Cout > 0 && C % 8 == 0 && Nrows < (1LL << 31), PB200_EINVAL,
+               "masked_rows_matmul: bad sizes (the row width must be a multiple of 8)");
+    PB_REQUIRE(precision == PB200_PREC_FP32 || precision == PB200_PREC_BF16, PB200_EINVAL,
+               "masked_rows_matmul: precision must be PB200_PREC_FP32 or PB200_PREC_BF16");
+    if (Nrows == 0) return PB200_OK;
+    PB_REQUIRE(rows && weights && output, PB200_EINVAL, "masked_rows_matmul: null pointer");
+    PB_REQUIRE(pw::aligned16(rows) && pw::aligned16(mask) && pw::aligned16(maskedRows) && pw::aligned16(workspace), PB200_EINVAL,
+               "masked_rows_matmul: rows, mask, maskedRows and workspace must be 16-byte aligned");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_masked_rows_matmul_workspace_bytes(C, precision), PB200_EWORKSPACE,
+               "masked_rows_matmul: workspace too small");
+    pw::Params p = {};
+    p.Nrows = Nrows; p.C = C; p.relu = 0;
+    p.rows = rows; p.mask = mask; p.masked_out = maskedRows;
+    return pw::run<2>(p, Cout, weights, nullptr, output, precision, workspace, stream);
 }
 
 }  // extern "C"

@@ -2,8 +2,10 @@
 modules run operator -> torch.matmul -> + bias -> ReLU as separate kernels,
 picasso/mesh/layers.py:109-120,166-175).  Forward: one fused tensor-core kernel; the operator's
 (rows, C) output never exists in memory.  Backward: the operator's output is recomputed with the
-stand-alone forward kernel (cheaper than having stored it), the pointwise gradients are two matrix
-products, and the operator gradient is the stand-alone backward kernel.
+stand-alone forward kernel (cheaper than having stored it); the gradient of the operator output is one
+tensor-core kernel that applies the activation mask on the fly (pb200_masked_rows_matmul) and hands back the
+masked gradient, from which the weight and bias gradients are reduced; the operator gradient is the
+stand-alone backward kernel.
 """
 from __future__ import annotations
 
@@ -32,8 +34,27 @@ def eligible(x: torch.Tensor, channels: int, multiplier: int, activation_fn) -> 
 
 
 def _pointwise_backward(grad_out, out, feats, depth_weights, relu):
-    g = grad_out * (out > 0) if relu else grad_out
-    return g @ depth_weights.t(), feats.t() @ g, g.sum(0, keepdim=True)
+    """Gradients of out = act(feats @ depth_weights + bias): (d feats, d depth_weights, d bias).  The product
+    with depth_weights^T runs on the tensor cores with the activation mask applied on the fly
+    (pb200_masked_rows_matmul), which also hands back the masked gradient for the two reductions."""
+    Nrows, Cout = grad_out.shape
+    C = depth_weights.shape[0]
+    if Cout % 8 != 0 or Nrows == 0:
+        g = grad_out * (out > 0) if relu else grad_out
+        return g @ depth_weights.t(), feats.t() @ g, g.sum(0, keepdim=True)
+    dev = grad_out.device
+    grad_out = conv3d._aligned16(grad_out)
+    with torch.cuda.device(dev):
+        g_feats = torch.empty(Nrows, C, dtype=grad_out.dtype, device=dev)
+        g = torch.empty_like(grad_out) if relu else None
+        wt = depth_weights.t().contiguous()
+        nb = _lib.query("pb200_masked_rows_matmul_workspace_bytes", Cout, _precision)
+        ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=dev)
+        _lib.call("pb200_masked_rows_matmul", Nrows, Cout, C, ptr(grad_out), ptr(out) if relu else None, ptr(wt),
+                  ptr(g_feats), ptr(g), _precision, ptr(ws), nb, stream_ptr(dev))
+    if g is None:
+        g = grad_out
+    return g_feats, feats.t() @ g, g.sum(0, keepdim=True)
 
 
 class V2FPointwiseFunction(torch.autograd.Function):
