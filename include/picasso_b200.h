@@ -209,6 +209,16 @@ int pb200_masked_rows_matmul(int64_t Nrows, int C, int Cout, const float* rows, 
                              float* output, float* maskedRows, int precision, void* workspace, size_t workspace_bytes,
                              void* stream);
 
+/* out[m, n] = sum over rows of A[row, m] * B[row, n] and, if colsum is not NULL, colsum[n] = sum over rows of
+ * B[row, n]: the weight and bias gradients of a pointwise stage (A = its input rows, B = the masked upstream
+ * gradient), which the reference's modules leave to autograd (an fp32 GEMM whose contraction runs over millions
+ * of rows).  A (Nrows, M), B (Nrows, N) row-major, M and N multiples of 4, 16-byte aligned; out (M, N).
+ * Tensor cores with bf16 hi + lo operands (PB200_PREC_FP32, about 1e-5 relative) or bf16 (PB200_PREC_BF16);
+ * at most 4096 rows go through one accumulator chain, the partial results are added in a fixed order. */
+size_t pb200_rows_contract_workspace_bytes(int64_t Nrows, int M, int N);
+int pb200_rows_contract(int64_t Nrows, int M, int N, const float* A, const float* B, float* out, float* colsum,
+                        int precision, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- facet2facet --------------------------------------------------------------------
  * A[f,d,ci] = (1/T_f) sum_{k in samples(f)} bary[k,d]*input[k,ci];
  * output[f,co] = sum_{d,ci} A[f,d,ci]*filter[co,ci,d];  samples(f) = rows

@@ -86,6 +86,8 @@ SIGNATURES = {
     "pb200_combine_clusters": (i32, [i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_masked_rows_matmul_workspace_bytes": (sz, [i32, i32]),
     "pb200_masked_rows_matmul": (i32, [i64, i32, i32, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
+    "pb200_rows_contract_workspace_bytes": (sz, [i64, i32, i32]),
+    "pb200_rows_contract": (i32, [i64, i32, i32, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_sph_harm_coeff": (i32, [i64, i32, vp, vp, vp]),
     "pb200_triangle_geometry": (i32, [i64, i64, i32, vp, vp, vp, vp]),
     "pb200_expand_rows_forward": (i32, [i64, i64, i32, vp, vp, vp, vp]),

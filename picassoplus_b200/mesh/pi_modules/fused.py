@@ -54,7 +54,27 @@ def _pointwise_backward(grad_out, out, feats, depth_weights, relu):
                   ptr(g_feats), ptr(g), _precision, ptr(ws), nb, stream_ptr(dev))
     if g is None:
         g = grad_out
-    return g_feats, feats.t() @ g, g.sum(0, keepdim=True)
+    g_w, g_b = rows_contract(feats, g)
+    return g_feats, g_w, g_b
+
+
+def rows_contract(a, b):
+    """(a^T @ b, column sums of b as a (1, N) row) with the contraction over rows on the tensor cores
+    (pb200_rows_contract); torch for widths that are no multiple of 4."""
+    Nrows, M = a.shape
+    N = b.shape[1]
+    if M % 4 != 0 or N % 4 != 0 or Nrows == 0:
+        return a.t() @ b, b.sum(0, keepdim=True)
+    dev = a.device
+    a, b = conv3d._aligned16(a), conv3d._aligned16(b)
+    with torch.cuda.device(dev):
+        out = torch.empty(M, N, dtype=a.dtype, device=dev)
+        colsum = torch.empty(1, N, dtype=a.dtype, device=dev)
+        nb = _lib.query("pb200_rows_contract_workspace_bytes", Nrows, M, N)
+        ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=dev)
+        _lib.call("pb200_rows_contract", Nrows, M, N, ptr(a), ptr(b), ptr(out), ptr(colsum), _precision, ptr(ws), nb,
+                  stream_ptr(dev))
+    return out, colsum
 
 
 class V2FPointwiseFunction(torch.autograd.Function):

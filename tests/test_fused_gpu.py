@@ -87,3 +87,41 @@ def test_modules_with_and_without_fusion_agree():
         layers.set_fusion(True)
     for a, b in zip(*results):
         assert rel_err(a, b) <= 2e-4
+
+
+@pytest.mark.parametrize("rows,M,N", [(5000, 64, 128), (333, 128, 256), (9000, 256, 384), (70, 8, 12), (4096, 384, 64)])
+@pytest.mark.parametrize("mode", ["fp32", "bf16"])
+def test_rows_contract_and_masked_rows_matmul(rows, M, N, mode):
+    """The two tensor-core kernels of the modules' backward against fp64: a^T b with column sums of b
+    (contraction over rows), and (g masked by an activation) @ w."""
+    from picassoplus_b200 import _lib
+    from picassoplus_b200.mesh.pi_modules import fused
+    from picassoplus_b200.topology import ptr, stream_ptr
+    gate = 1e-4 if mode == "fp32" else 2e-2
+    gen = torch.Generator(device="cuda").manual_seed(rows + M)
+    a = torch.randn(rows, M, device="cuda", generator=gen)
+    b = torch.randn(rows, N, device="cuda", generator=gen)
+    fused.set_pointwise_precision(mode)
+    try:
+        out, colsum = fused.rows_contract(a, b)
+        again, _ = fused.rows_contract(a, b)
+        assert torch.equal(out, again)                                  # fixed-order reduction
+        want = a.double().t() @ b.double()
+        assert rel_err(out, want) <= gate
+        assert rel_err(colsum, b.double().sum(0, keepdim=True)) <= 1e-5
+        if N % 8 == 0:
+            act = torch.randn(rows, N, device="cuda", generator=gen)     # stands for the activated output
+            w = torch.randn(N, M, device="cuda", generator=gen) * 0.1    # depth_weights^T
+            dev = a.device
+            g_feats = torch.empty(rows, M, device=dev)
+            g_masked = torch.empty(rows, N, device=dev)
+            prec = _lib.PRECISIONS[mode]
+            nb = _lib.query("pb200_masked_rows_matmul_workspace_bytes", N, prec)
+            ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=dev)
+            _lib.call("pb200_masked_rows_matmul", rows, N, M, ptr(b), ptr(act), ptr(w), ptr(g_feats), ptr(g_masked), prec,
+                      ptr(ws), nb, stream_ptr(dev))
+            gm = b * (act > 0)
+            assert torch.equal(g_masked, gm)
+            assert rel_err(g_feats, gm.double() @ w.double()) <= gate
+    finally:
+        fused.set_pointwise_precision("fp32")
