@@ -744,6 +744,11 @@ def run_c4(args):
         alg += 12 * Ci * Nv + 8 * Ci * Nf + 24 * Nf                                         # V2F fwd+bwd
         alg += 12 * Co * Nf + 8 * K * Nf + 24 * Nf + 8 * Co * Nv + 16 * Nv                  # F2V fwd+bwd
         alg += 4 * Co * (2 * Nv + 3 * levels[i + 1].num_vertices)                           # max pool fwd+bwd
+        if not args.no_fusion:
+            # backward of the two pointwise stages (rows x C -> Cout): masked product reads gradient + activation,
+            # writes the masked gradient and the operator-output gradient; the contraction over rows reads both
+            for rows, C, Cout in ((Nf, Ci, Co), (Nv, Co, Co)):
+                alg += 4 * rows * (3 * Cout + C) + 4 * rows * (C + Cout)
     line = {
         "metric": METRIC, "value": faces / (ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
@@ -758,11 +763,13 @@ def run_c4(args):
                                                 if args.no_fusion else
                                                 "fused with the operator in one tcgen05 kernel (forward; "
                                                 f"{'bf16' if args.precision == 'bf16' else 'bf16 hi+lo'} operands), "
-                                                "BatchNorm1d in torch; backward = recompute + matmuls + operator backward")},
+                                                "BatchNorm1d in torch; backward = recompute of the operator output + masked product and "
+                                                "contraction over rows on the tensor cores + operator backward")},
         "roofline": {"bound": "hbm", "achieved": alg / (lib_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": alg / (lib_ms / 1e3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
-                     "note": "all library operator kernels of one step together: algorithmic bytes of V2F, F2V and max "
-                             "pool over the three conv levels / their summed duration", "peak_source": peaks["source"]},
+                     "note": "all library kernels of one step together: algorithmic bytes of V2F, F2V, max pool and (fused "
+                             "mode) the two backward products of every pointwise stage over the three conv levels / "
+                             "their summed duration", "peak_source": peaks["source"]},
         "library_kernel_ms_per_step": lib_ms, "other_ms_per_step": ms - lib_ms,
         "gpu_launches": int(launches), "clocks": clk.summary(),
         "kernels": [dict(kernel=n, launches_per_step=c, ms_per_step=t) for n, c, t in records[:14]],
