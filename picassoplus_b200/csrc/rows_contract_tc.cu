@@ -15,8 +15,9 @@
 // K-rows; one thread issues tcgen05.mma (M = 128 columns of A, N <= 256 columns of B, K = 16 rows
 // per instruction, three products per term in the hi+lo mode) into a TMEM accumulator.
 // The tensor core's adder truncates, so one CTA sums at most 4096 rows (768 accumulating
-// instructions, drift 1e-5); the per-CTA partial results are added in CTA order by a second
-// kernel, which also makes the result independent of scheduling.  All waits are bounded.
+// instructions, drift 1e-5), fewer when that gives the GPU more CTAs to run (two per SM); the
+// per-CTA partial results are added in CTA order by a second kernel, which also makes the result
+// independent of scheduling.  All waits are bounded.
 #include "common.cuh"
 #include "tc_ptx.cuh"
 #include "tc_runtime.cuh"
@@ -32,13 +33,14 @@ constexpr int UN = 256;                       // columns of B per launch (UMMA N
 constexpr int RS = 32;                        // rows per stage (two K-steps of 16)
 constexpr int PWARPS = 8;
 constexpr int NTHREADS = (PWARPS + 1) * 32;
-constexpr int ROWS_PER_CTA = 4096;
+constexpr int MAX_ROWS_PER_CTA = 4096;        // longest accumulator chain: 768 instructions
+constexpr int MIN_ROWS_PER_CTA = 256;
 constexpr int ATOM = 1024;                    // 8 K-rows x 128 bytes (64 bf16 columns)
 constexpr int SBO_A = (UM / 64) * ATOM;       // next 8 rows of the A tile
 constexpr int SBO_B = (UN / 64) * ATOM;
 constexpr int A_TILE = (RS / 8) * SBO_A;      // one split of the A tile of a stage
 constexpr int B_TILE = (RS / 8) * SBO_B;
-constexpr int NSTAGES = 4;
+constexpr int NSTAGES = 2;                    // 2 stages -> two CTAs per SM
 
 struct Params {
     int64_t Nrows;
@@ -48,6 +50,7 @@ struct Params {
     const float* B;
     float* partial;           // [gridDim.x][M][N]
     float* colsum_partial;    // [gridDim.x][N] or NULL
+    int rows_per_cta;
     int* async_err;
     int wait_budget;
 };
@@ -78,7 +81,7 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 template <int NSPLIT>
-__global__ void __launch_bounds__(NTHREADS, 1) rows_contract_tc_kernel(Params p) {
+__global__ void __launch_bounds__(NTHREADS, 2) rows_contract_tc_kernel(Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -105,8 +108,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) rows_contract_tc_kernel(Params p)
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t s32 = smem_u32(smem);
 
-    const int64_t row_begin = (int64_t)blockIdx.x * ROWS_PER_CTA;
-    int64_t row_end = row_begin + ROWS_PER_CTA;
+    const int64_t row_begin = (int64_t)blockIdx.x * p.rows_per_cta;
+    int64_t row_end = row_begin + p.rows_per_cta;
     if (row_end > p.Nrows) row_end = p.Nrows;
     const int nst = row_end > row_begin ? (int)((row_end - row_begin + RS - 1) / RS) : 0;
     const int nmma = (p.Nw + 15) / 16 * 16;                  // UMMA N of this launch
@@ -228,6 +231,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) rows_contract_tc_kernel(Params p)
     }
 }
 
+// rows per CTA: enough CTAs to fill the GPU twice over when the rows allow it, never a chain longer than
+// MAX_ROWS_PER_CTA, and not so many CTAs that the partial results outgrow 256 MB
+static int rows_per_cta(int64_t Nrows, int M, int N) {
+    int64_t r = ceil_div(Nrows > 0 ? Nrows : 1, 2 * (int64_t)sm_count());
+    r = ceil_div(r, RS) * RS;
+    if (r < MIN_ROWS_PER_CTA) r = MIN_ROWS_PER_CTA;
+    const int64_t cap_ctas = (256LL << 20) / ((int64_t)M * N * 4);
+    if (cap_ctas > 0 && ceil_div(Nrows, r) > cap_ctas) r = ceil_div(ceil_div(Nrows, cap_ctas), RS) * RS;
+    if (r > MAX_ROWS_PER_CTA) r = MAX_ROWS_PER_CTA;
+    return (int)r;
+}
+
 constexpr size_t smem_bytes(int nsplit) { return NSTAGES * stage_bytes(nsplit) + 256 + PWARPS * UN * 4 + 1024; }
 
 }  // namespace rc
@@ -240,7 +255,7 @@ extern "C" {
 
 size_t pb200_rows_contract_workspace_bytes(int64_t Nrows, int M, int N) {
     if (Nrows < 0 || M <= 0 || N <= 0) return 0;
-    const size_t ctas = (size_t)ceil_div(Nrows > 0 ? Nrows : 1, tc::rc::ROWS_PER_CTA);
+    const size_t ctas = (size_t)ceil_div(Nrows > 0 ? Nrows : 1, tc::rc::rows_per_cta(Nrows, M, N));
     return align_up(sizeof(float) * ctas * (size_t)M * N, 256) + align_up(sizeof(float) * ctas * (size_t)N, 256);
 }
 
@@ -265,8 +280,10 @@ int pb200_rows_contract(int64_t Nrows, int M, int N, const float* A, const float
                "rows_contract: workspace too small");
     int rc = tc::check_async_error("rows_contract");
     if (rc) return rc;
-    const int ctas = (int)ceil_div(Nrows, ROWS_PER_CTA);
+    const int rpc = rows_per_cta(Nrows, M, N);
+    const int ctas = (int)ceil_div(Nrows, rpc);
     Params p;
+    p.rows_per_cta = rpc;
     p.Nrows = Nrows; p.M = M; p.N = N; p.A = A; p.B = B;
     p.partial = (float*)workspace;
     float* cpart = (float*)((char*)workspace + align_up(sizeof(float) * (size_t)ctas * M * N, 256));
