@@ -198,6 +198,13 @@ int pb200_facet2vertex_pointwise_forward(int64_t Nf, int64_t NvOut, int C, int K
                                          const float* depthWeights, const float* bias, int relu, float* output,
                                          int precision, void* workspace, size_t workspace_bytes, void* stream);
 
+/* output[row, co] = act(sum_c rows[row, c] * weights[c, co] + bias[co]) on the tensor cores: the pointwise layer of
+ * the reference's networks (PerItemConv3d, picasso/mesh/layers.py:198-240: torch.matmul, + biases, activation as
+ * separate kernels).  rows (Nrows, C), C a multiple of 8; weights (C, Cout); bias (Cout) or NULL; relu 0/1.
+ * Workspace as pb200_masked_rows_matmul_workspace_bytes(C, precision).  Its backward is the next two entries. */
+int pb200_rows_pointwise_forward(int64_t Nrows, int C, int Cout, const float* rows, const float* weights, const float* bias,
+                                 int relu, float* output, int precision, void* workspace, size_t workspace_bytes,
+                                 void* stream);
 /* Backward of the pointwise stage on the tensor cores (no counterpart in the reference, whose modules leave it
  * to autograd): output[row, co] = sum_c g[row, c] * weights[c, co] with g = rows where mask > 0, else 0
  * (mask = the stage's activated output; NULL = no activation).  rows, mask (Nrows, C), C a multiple of 8;

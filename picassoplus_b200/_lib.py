@@ -84,6 +84,7 @@ SIGNATURES = {
     "pb200_mesh_simplify": (i32, [i32, f32, i64, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                   vp, sz, vp]),
     "pb200_combine_clusters": (i32, [i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
+    "pb200_rows_pointwise_forward": (i32, [i64, i32, i32, vp, vp, vp, i32, vp, i32, vp, sz, vp]),
     "pb200_masked_rows_matmul_workspace_bytes": (sz, [i32, i32]),
     "pb200_masked_rows_matmul": (i32, [i64, i32, i32, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_rows_contract_workspace_bytes": (sz, [i64, i32, i32]),

@@ -444,6 +444,26 @@ size_t pb200_masked_rows_matmul_workspace_bytes(int C, int precision) {
     return align_up(pw::plan(C, precision).wimg_bytes, 256);
 }
 
+int pb200_rows_pointwise_forward(int64_t Nrows, int C, int Cout, const float* rows, const float* weights, const float* bias,
+                                 int relu, float* output, int precision, void* workspace, size_t workspace_bytes,
+                                 void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nrows >= 0 && C > 0 && Cout > 0 && C % 8 == 0 && Nrows < (1LL << 31), PB200_EINVAL,
+               "rows_pointwise_forward: bad sizes (the row width must be a multiple of 8)");
+    PB_REQUIRE(precision == PB200_PREC_FP32 || precision == PB200_PREC_BF16, PB200_EINVAL,
+               "rows_pointwise_forward: precision must be PB200_PREC_FP32 or PB200_PREC_BF16");
+    if (Nrows == 0) return PB200_OK;
+    PB_REQUIRE(rows && weights && output, PB200_EINVAL, "rows_pointwise_forward: null pointer");
+    PB_REQUIRE(pw::aligned16(rows) && pw::aligned16(workspace), PB200_EINVAL,
+               "rows_pointwise_forward: rows and workspace must be 16-byte aligned");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_masked_rows_matmul_workspace_bytes(C, precision), PB200_EWORKSPACE,
+               "rows_pointwise_forward: workspace too small");
+    pw::Params p = {};
+    p.Nrows = Nrows; p.C = C; p.relu = relu;
+    p.rows = rows;
+    return pw::run<2>(p, Cout, weights, bias, output, precision, workspace, stream);
+}
+
 int pb200_masked_rows_matmul(int64_t Nrows, int C, int Cout, const float* rows, const float* mask, const float* weights,
                              float* output, float* maskedRows, int precision, void* workspace, size_t workspace_bytes,
                              void* stream_) {

@@ -1,6 +1,6 @@
 """Layer modules of the mesh convolutions (and of mesh pooling / unpooling) with the reference's
 class names, constructor arguments, parameter names and parameter shapes
-(picasso/mesh/layers.py:10-195,263-298,331-356),
+(picasso/mesh/layers.py:10-356),
 so reference checkpoints load unchanged.  Each module = one operator from
 pi_modules.conv3d followed by the pointwise stage: matmul -> + bias -> activation ->
 BatchNorm1d(eps=1e-3)  (batch norm AFTER the activation, as in the reference)."""
@@ -174,3 +174,74 @@ class Unpool3d(nn.Module):
     @staticmethod
     def forward(inputs, vt_replace, vt_map):
         return unpool3d.interpolate(inputs, vt_replace, vt_map)
+
+
+class PerItemConv3d(nn.Module):
+    """Pointwise layer (per vertex, per facet, per point): matmul -> + biases -> activation -> batch norm, the
+    reference's module of the same name (picasso/mesh/layers.py:198-240), parameters `weights`
+    (in_channels, out_channels), `biases` (1, out_channels), `BatchNorm`.  With fusion on, an input width that is
+    a multiple of 8 and ReLU or no activation, product + bias + activation are one tensor-core kernel, and so are
+    the two products of the backward pass."""
+
+    def __init__(self, in_channels, out_channels, use_xavier=True, stddev=1e-3, activation_fn=nn.ReLU(), with_bn=True,
+                 bn_momentum=0.1):
+        super().__init__()
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.use_xavier, self.stddev = use_xavier, stddev
+        self.with_bn, self.activation_fn = with_bn, activation_fn
+        if with_bn:
+            self.BatchNorm = nn.BatchNorm1d(out_channels, eps=0.001, momentum=bn_momentum)
+        self.weights = _filter_variable_([in_channels, out_channels], stddev=stddev, use_xavier=use_xavier)
+        self.biases = nn.Parameter(torch.zeros(1, out_channels))
+
+    def forward(self, inputs):
+        if _fusion and inputs.dim() == 2 and fused.eligible(inputs, self.in_channels, 1, self.activation_fn):
+            outputs = fused.rows_pointwise(inputs.contiguous(), self.weights, self.biases, self.activation_fn is not None)
+        else:
+            outputs = torch.matmul(inputs, self.weights) + self.biases
+            if self.activation_fn is not None:
+                outputs = self.activation_fn(outputs)
+        return self.BatchNorm(outputs) if self.with_bn else outputs
+
+
+class GlobalPool3d(nn.Module):
+    """Pools all vertices of every sample of a batch into one row ('avg' or 'max'); nv_in (B,) = vertices per
+    sample.  The reference (picasso/mesh/layers.py:242-260) goes through torch_scatter, whose scatter_max returns
+    the pair (values, positions): 'max' returns that pair here as well."""
+
+    def __init__(self, method='avg'):
+        super().__init__()
+        self.method = method
+
+    def forward(self, inputs, nv_in):
+        lengths = nv_in.to(torch.int64)
+        if self.method == 'avg':
+            return torch.segment_reduce(inputs, 'mean', lengths=lengths)
+        if self.method == 'max':
+            values = torch.segment_reduce(inputs, 'max', lengths=lengths)
+            # position of the first vertex that attains the maximum, as an index into `inputs`
+            B = lengths.shape[0]
+            sample = torch.repeat_interleave(torch.arange(B, device=inputs.device), lengths)
+            rows = torch.arange(inputs.shape[0], device=inputs.device).unsqueeze(1).expand_as(inputs)
+            cand = torch.where(inputs == values[sample], rows, torch.full_like(rows, inputs.shape[0]))
+            first = torch.full((B, inputs.shape[1]), inputs.shape[0], dtype=rows.dtype, device=inputs.device)
+            first = first.scatter_reduce(0, sample.unsqueeze(1).expand_as(cand), cand, 'amin')
+            return values, first
+        raise ValueError("Unknow pooling method %s." % self.method)
+
+
+class BuildF2VCoeff(nn.Module):
+    """Fuzzy facet2vertex coefficients from face normals: softmax over `kernel_size` learned unit directions of the
+    cosine between normal and direction, sharpened by 1/tau (picasso/mesh/layers.py:299-328); parameter
+    `centers` (kernel_size, dim)."""
+
+    def __init__(self, kernel_size, tau=0.1, dim=3, stddev=1.0):
+        super().__init__()
+        self.kernel_size, self.tau, self.dim, self.stddev = kernel_size, tau, dim, stddev
+        self.centers = _filter_variable_([kernel_size, dim], stddev=stddev, use_xavier=False)
+
+    def forward(self, face_normals):
+        directions = self.centers / torch.sqrt(torch.sum(self.centers ** 2, dim=-1, keepdim=True))
+        zeta = torch.matmul(face_normals, directions.to(face_normals.device).t()) / self.tau
+        coeff = torch.exp(zeta)
+        return coeff / torch.sum(coeff, dim=-1, keepdim=True)

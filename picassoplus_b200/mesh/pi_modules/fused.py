@@ -149,6 +149,43 @@ class F2VPointwiseFunction(torch.autograd.Function):
         return g_in, g_filter, None, None, None, None, g_w, (g_b if ctx.has_bias else None), None
 
 
+class RowsPointwiseFunction(torch.autograd.Function):
+    """out = act(rows @ weights + biases): the pointwise layer (the reference's PerItemConv3d,
+    picasso/mesh/layers.py:198-240) as one tensor-core kernel forward and two backward."""
+
+    @staticmethod
+    def forward(ctx, rows, weights, biases, relu):
+        conv3d._check(rows, "inputs", 2, torch.float32)
+        conv3d._check(weights, "weights", 2, torch.float32)
+        Nrows, C = rows.shape
+        Cout = weights.shape[1]
+        if weights.shape[0] != C:
+            raise RuntimeError("weights must have shape (in_channels, out_channels)")
+        dev = rows.device
+        rows = conv3d._aligned16(rows)
+        bias = None if biases is None else biases.reshape(-1).contiguous()
+        with torch.cuda.device(dev):
+            out = torch.empty(Nrows, Cout, dtype=rows.dtype, device=dev)
+            nb = _lib.query("pb200_masked_rows_matmul_workspace_bytes", C, _precision)
+            ws = torch.empty(max(nb, 1), dtype=torch.uint8, device=dev)
+            _lib.call("pb200_rows_pointwise_forward", Nrows, C, Cout, ptr(rows), ptr(weights), ptr(bias), 1 if relu else 0,
+                      ptr(out), _precision, ptr(ws), nb, stream_ptr(dev))
+        ctx.relu = relu
+        ctx.has_bias = biases is not None
+        ctx.save_for_backward(rows, weights, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        rows, weights, out = ctx.saved_tensors
+        g_rows, g_w, g_b = _pointwise_backward(grad_out.contiguous(), out, rows, weights, ctx.relu)
+        return g_rows, g_w, (g_b if ctx.has_bias else None), None
+
+
+def rows_pointwise(rows, weights, biases, relu):
+    return RowsPointwiseFunction.apply(rows, weights, biases, relu)
+
+
 def vertex2facet_pointwise(input, filter, face, depth_weights, biases, relu):
     return V2FPointwiseFunction.apply(input, filter, face, depth_weights, biases, relu)
 

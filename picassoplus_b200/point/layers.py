@@ -27,3 +27,7 @@ class PCloudConv3d(_PointwiseTail):
         else:
             feats = conv3d.fuzzyconv3d(inputs, self.spatial_weights, nn_count, nn_index, filt_index, filt_coeff)
         return self._tail(feats @ self.depth_weights)
+
+
+# the pointwise layer is the same module for points, vertices and facets (picasso/point/layers.py:78-119)
+from ..mesh.layers import PerItemConv3d  # noqa: E402,F401

@@ -5,6 +5,7 @@ Python for the parts of the path that are plain torch code:
                                       picasso/math_utils.py:10-62)
   * compute_triangle_geometry_       (picasso/mesh/pi_modules/decimate.py:70-85)
   * V2VConv3d and F2FConv3d, forward and backward with a seeded state_dict
+  * PerItemConv3d (forward and backward) and BuildF2VCoeff, in layers_ref_python.npz
                                      (picasso/mesh/layers.py:18-195)
   * get_oriented_normals             (picasso/networks/scene_seg.py:117-124)
   * PCloudConv3d with fuzzy bins, forward and backward (picasso/point/layers.py:19-75)
@@ -197,6 +198,39 @@ def main(out_dir: str) -> None:
     path = os.path.join(out_dir, "modules_ref_python.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, f"({os.path.getsize(path) / 1024:.0f} KB), mesh_conv3d bound to:", backend)
+
+    # ---- the remaining layer modules, in a file of their own: PerItemConv3d (with and without batch norm /
+    # activation, forward and backward) and BuildF2VCoeff (picasso/mesh/layers.py:198-240, 299-328)
+    more = {}
+    for tag, (cin_p, cout_p, rows_p, kw) in {"pic_bn": (16, 24, 300, {}),
+                                             "pic_plain": (40, 12, 257, dict(with_bn=False, activation_fn=None))}.items():
+        torch.manual_seed(11)
+        pic = ref_layers.PerItemConv3d(cin_p, cout_p, **kw).to(dev)
+        with torch.no_grad():
+            pic.biases.copy_(torch.randn(pic.biases.shape, generator=g) * 0.1)
+        pic.train()
+        xin = torch.randn(rows_p, cin_p, generator=g)
+        xq = xin.clone().to(dev).requires_grad_()
+        Gq = torch.randn(rows_p, cout_p, generator=g)
+        yq = pic(xq)
+        (yq * Gq.to(dev)).sum().backward()
+        more.update({f"{tag}_cfg": np.array([cin_p, cout_p]), f"{tag}_x": xin.numpy(), f"{tag}_G": Gq.numpy(),
+                     f"{tag}_out": yq.detach().cpu().numpy(), f"{tag}_grad_x": xq.grad.cpu().numpy()})
+        for n_, p_ in pic.named_parameters():
+            more[f"{tag}_param/" + n_] = p_.detach().cpu().numpy()
+            more[f"{tag}_grad/" + n_] = p_.grad.cpu().numpy()
+        for n_, b_ in pic.named_buffers():
+            more[f"{tag}_buffer/" + n_] = b_.detach().cpu().numpy()
+    torch.manual_seed(12)
+    if dev.type == "cpu":
+        torch.Tensor.get_device = lambda self: self.device          # the reference asks a CPU tensor for its device
+    f2vc = ref_layers.BuildF2VCoeff(9, tau=0.2).to(dev)
+    normals = torch.nn.functional.normalize(torch.randn(200, 3, generator=g), dim=1)
+    more.update(f2vc_normals=normals.numpy(), f2vc_centers=f2vc.centers.detach().cpu().numpy(),
+                f2vc_out=f2vc(normals.to(dev)).detach().cpu().numpy(), f2vc_cfg=np.array([9, 0.2]))
+    path2 = os.path.join(out_dir, "layers_ref_python.npz")
+    np.savez_compressed(path2, **more)
+    print("wrote", path2, f"({os.path.getsize(path2) / 1024:.0f} KB)")
 
 
 if __name__ == "__main__":

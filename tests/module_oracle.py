@@ -31,10 +31,10 @@ def f2f_forward(tex, params, bary, counts):
     return tail(z, params["biases"], params["BatchNorm.weight"], params["BatchNorm.bias"])
 
 
-def load_fixture():
+def load_fixture(name="modules_ref_python.npz"):
     import os
     import numpy as np
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "modules_ref_python.npz")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", name)
     z = np.load(path)
     return {k: z[k] for k in z.files}
 

@@ -2,6 +2,7 @@
 picasso/mesh/layers.py, picasso/mesh/pi_modules/decimate.py run unmodified by
 tests/golden/make_golden_modules.py): spherical-harmonic basis, triangle geometry, and the
 V2VConv3d / F2FConv3d modules forward + backward."""
+import pytest
 import torch
 
 from conftest import max_abs, rel_err
@@ -80,3 +81,63 @@ def test_pcloud_module_matches_reference_python():
     assert rel_err(out, FX["pc_out"]) <= 1e-4 and rel_err(x.grad, FX["pc_grad_x"]) <= 1e-4
     for name, g in group(FX, "pc_grad").items():
         assert rel_err(params[name].grad, g) <= 1e-4, name
+
+
+LX = load_fixture("layers_ref_python.npz")
+
+
+def _load_layer(module, prefix):
+    sd = group(LX, prefix + "_param")
+    sd.update(group(LX, prefix + "_buffer"))
+    for k in list(sd):                                  # recorded after the reference's step: start from fresh ones
+        if k.endswith("running_mean"):
+            sd[k] = torch.zeros_like(sd[k])
+        elif k.endswith("running_var"):
+            sd[k] = torch.ones_like(sd[k])
+        elif k.endswith("num_batches_tracked"):
+            sd[k] = torch.zeros_like(sd[k])
+    module.load_state_dict(sd, strict=True)
+
+
+@pytest.mark.parametrize("tag,kw", [("pic_bn", {}), ("pic_plain", dict(with_bn=False, activation_fn=None))])
+def test_per_item_conv_matches_reference_python(tag, kw):
+    from picassoplus_b200.mesh.layers import PerItemConv3d
+    cin, cout = [int(v) for v in LX[tag + "_cfg"]]
+    mod = PerItemConv3d(cin, cout, **kw)
+    _load_layer(mod, tag)
+    mod = mod.to("cpu").train()
+    x = torch.from_numpy(LX[tag + "_x"]).to("cpu").requires_grad_()
+    out = mod(x)
+    (out * torch.from_numpy(LX[tag + "_G"]).to("cpu")).sum().backward()
+    assert rel_err(out, LX[tag + "_out"]) <= 1e-4
+    assert rel_err(x.grad, LX[tag + "_grad_x"]) <= 1e-4
+    params = dict(mod.named_parameters())
+    for name, g in group(LX, tag + "_grad").items():
+        assert rel_err(params[name].grad, g) <= 1e-4, name
+    bufs = dict(mod.named_buffers())
+    for name, b in group(LX, tag + "_buffer").items():
+        if b.dtype.is_floating_point:
+            assert rel_err(bufs[name], b) <= 1e-4, name
+
+
+def test_build_f2v_coeff_matches_reference_python():
+    from picassoplus_b200.mesh.layers import BuildF2VCoeff
+    mod = BuildF2VCoeff(int(LX["f2vc_cfg"][0]), tau=float(LX["f2vc_cfg"][1]))
+    mod.load_state_dict({"centers": torch.from_numpy(LX["f2vc_centers"])}, strict=True)
+    out = mod.to("cpu")(torch.from_numpy(LX["f2vc_normals"]).to("cpu"))
+    assert max_abs(out, LX["f2vc_out"]) <= 1e-6
+
+
+def test_global_pool_against_plain_loops():
+    from picassoplus_b200.mesh.layers import GlobalPool3d
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(37, 5, generator=g).to("cpu")
+    nv = torch.tensor([10, 1, 26], dtype=torch.int32, device="cpu")
+    avg = GlobalPool3d("avg")(x, nv)
+    val, pos = GlobalPool3d("max")(x, nv)
+    start = 0
+    for s, n in enumerate([10, 1, 26]):
+        seg = x[start:start + n]
+        assert max_abs(avg[s], seg.mean(0)) <= 1e-6
+        assert torch.equal(val[s], seg.max(0).values) and torch.equal(pos[s].cpu(), seg.argmax(0).cpu() + start)
+        start += n
