@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS) + ["c4", "decimate"])
+    ap.add_argument("--config", default="c5", choices=sorted(synth.CONFIGS) + ["c4", "decimate", "aux"])
     ap.add_argument("--precision", default="fp32", choices=["fp32", "fp32_tf32x3", "tf32", "bf16"])
     ap.add_argument("--meshes", type=int, default=0, help="total meshes of the batch (0 = the configuration's)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -959,6 +959,141 @@ def run_reference_decimate(args):
     }))
 
 
+# ------------------------------------------------------------------ auxiliary kernels
+AUX = dict(n=700, batch=2, C=128, L=3, seed=3, pc_points=1 << 20, pc_out=1 << 18, pc_knn=16, pc_bins=17, pc_fuzzy=3, pc_C=64)
+AUX_METRIC, AUX_UNIT = "aux_kernels_hbm_fraction_geomean", "fraction of measured copy bandwidth"
+
+
+def aux_pcloud_inputs(cfg, dev):
+    """Neighbour pairs as a radius search emits them (grouped by output point, up to knn each), fuzzy bins."""
+    rng = np.random.default_rng(cfg["seed"] + 9)
+    Np, Mp, knn, F, T = cfg["pc_points"], cfg["pc_out"], cfg["pc_knn"], cfg["pc_bins"], cfg["pc_fuzzy"]
+    counts = rng.integers(knn // 2, knn + 1, size=Mp)
+    out_idx = np.repeat(np.arange(Mp), counts)
+    in_idx = rng.integers(0, Np, size=out_idx.shape[0])
+    w = rng.random((out_idx.shape[0], T)).astype(np.float32) + 0.05
+    t = lambda a: torch.from_numpy(a).to(dev)
+    return dict(nn_index=t(np.stack([out_idx, in_idx], 1).astype(np.int32)), nn_count=t(counts.astype(np.int32)),
+                bin_index=t(rng.integers(0, F, size=(out_idx.shape[0], T)).astype(np.int32)),
+                bin_coeff=t(w / w.sum(1, keepdims=True)), npairs=int(out_idx.shape[0]))
+
+
+def aux_cases(cfg, dev, impl):
+    """[(name, callable, algorithmic bytes)] for one level-0 -> level-1 transition of the config-4 hierarchy
+    (980 000 -> 245 000 vertices, C = 128) and a point-cloud convolution; impl = 'ours' or 'reference'."""
+    from picassoplus_b200.mesh.utils import MeshHierarchy
+    mb0 = synth.concat_meshes([synth.heightfield(cfg["n"], cfg["seed"] * 1000 + i) for i in range(cfg["batch"])])
+    t_in = [torch.from_numpy(a).to(dev) for a in (mb0.vertex, mb0.face, mb0.nv.astype(np.int32), mb0.mf.astype(np.int32))]
+    hier = MeshHierarchy([4], [16], True, 1.0)(*t_in)
+    rep, vmap, vout = hier[1][5], hier[1][6], hier[1][0][:, :3].contiguous()
+    nv_in, nv_out, C = rep.shape[0], vout.shape[0], cfg["C"]
+    gen = torch.Generator(device=dev).manual_seed(cfg["seed"])
+    x = torch.randn(nv_in, C, device=dev, generator=gen)
+    xc = torch.randn(nv_out, C, device=dev, generator=gen)
+    pc = aux_pcloud_inputs(cfg, dev)
+    Cp, F, T, Np, Mp, P = cfg["pc_C"], cfg["pc_bins"], cfg["pc_fuzzy"], cfg["pc_points"], cfg["pc_out"], pc["npairs"]
+    xp = torch.randn(Np, Cp, device=dev, generator=gen)
+    gp = torch.randn(Mp, Cp, device=dev, generator=gen)
+    filt = torch.randn(F, Cp, 1, device=dev, generator=gen)
+    if impl == "ours":
+        from picassoplus_b200.mesh.pi_modules import pool3d, unpool3d
+        from picassoplus_b200.point.pi_modules import conv3d as pconv
+        from picassoplus_b200 import topology
+        mx, idx = pool3d.max_forward(x, rep, vmap, vout)
+        L = cfg["L"]
+        vt = torch.arange(nv_in, dtype=torch.int32, device=dev)
+        cases = [
+            ("mesh_max_pool_fwd", lambda: pool3d.max_forward(x, rep, vmap, vout), 4 * C * nv_in + 8 * C * nv_out),
+            ("mesh_max_pool_bwd", lambda: pool3d.max_backward(xc, x, idx), 8 * C * nv_out + 4 * C * nv_in),
+            ("mesh_avg_pool_fwd", lambda: pool3d.avg_forward(x, rep, vmap, vout), 4 * C * nv_in + 4 * C * nv_out),
+            ("mesh_avg_pool_bwd", lambda: pool3d.avg_backward(xc, x, rep, vmap), 4 * C * nv_out + 4 * C * nv_in),
+            ("mesh_unpool_fwd", lambda: unpool3d.forward(xc, rep, vmap), 4 * C * nv_out + 4 * C * nv_in),
+            ("mesh_unpool_bwd", lambda: unpool3d.backward(x, xc, rep, vmap), 4 * C * nv_in + 4 * C * nv_out),
+            ("pcloud_conv_fwd", lambda: pconv.fuzzySPH3D_forward(xp, filt, pc["nn_count"], pc["nn_index"], pc["bin_index"],
+                                                                 pc["bin_coeff"]),
+             4 * Cp * P + 4 * Cp * Mp + (8 + 8 * T) * P),
+            ("pcloud_conv_bwd", lambda: pconv.fuzzySPH3D_backward(gp, xp, filt, pc["nn_count"], pc["nn_index"], pc["bin_index"],
+                                                                  pc["bin_coeff"]),
+             8 * Cp * P + 4 * Cp * Np + (8 + 8 * T) * P),
+            ("level_prepare (geometry + normals + SH + nfCount + CSR)",
+             lambda: topology.prepare_level(t_in[0], t_in[1], vt, nv_in, L, want_geometry=True),
+             12 * nv_in + 12 * mb0.num_faces * 3 + (20 + 4 * (L + 1) ** 2) * mb0.num_faces + 12 * mb0.num_faces),
+        ]
+    else:
+        from oracle import ref_cuda
+        mx, idx = ref_cuda.max_pool_forward(x, rep, vmap, nv_out)
+        cases = [
+            ("mesh_max_pool_fwd", lambda: ref_cuda.max_pool_forward(x, rep, vmap, nv_out), 4 * C * nv_in + 8 * C * nv_out),
+            ("mesh_max_pool_bwd", lambda: ref_cuda.max_pool_backward(xc, nv_in, idx), 8 * C * nv_out + 4 * C * nv_in),
+            ("mesh_avg_pool_fwd", lambda: ref_cuda.avg_pool_forward(x, rep, vmap, nv_out), 4 * C * nv_in + 4 * C * nv_out),
+            ("mesh_avg_pool_bwd", lambda: ref_cuda.avg_pool_backward(xc, rep, vmap), 4 * C * nv_out + 4 * C * nv_in),
+            ("mesh_unpool_fwd", lambda: ref_cuda.unpool_forward(xc, rep, vmap), 4 * C * nv_out + 4 * C * nv_in),
+            ("mesh_unpool_bwd", lambda: ref_cuda.unpool_backward(x, nv_out, rep, vmap), 4 * C * nv_in + 4 * C * nv_out),
+            ("pcloud_conv_fwd", lambda: ref_cuda.pcloud_forward(xp, filt, pc["nn_count"], pc["nn_index"], pc["bin_index"],
+                                                                pc["bin_coeff"]),
+             4 * Cp * P + 4 * Cp * Mp + (8 + 8 * T) * P),
+            ("pcloud_conv_bwd", lambda: ref_cuda.pcloud_backward(gp, xp, filt, pc["nn_count"], pc["nn_index"], pc["bin_index"],
+                                                                 pc["bin_coeff"]),
+             8 * Cp * P + 4 * Cp * Np + (8 + 8 * T) * P),
+        ]
+    what = (f"one level transition of the config-4 hierarchy ({nv_in} -> {nv_out} vertices by the library's decimation, "
+            f"C = {C}) and a fuzzy point-cloud convolution ({Np} -> {Mp} points, {P} pairs, {F} bins x {T}, C = {Cp})")
+    return cases, what
+
+
+def run_aux(args):
+    """Auxiliary kernels around the convolutions (mesh pool / unpool, point-cloud convolution, per-level
+    preparation): each timed alone with CUDA events over `steps` calls (inputs larger than L2), reported with
+    its algorithmic bytes against the measured copy bandwidth.  --impl reference times the reference's own
+    CUDA kernels of the same operators (oracle/_ref) on the same inputs."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py --config aux needs a CUDA device")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    impl = args.impl
+    if impl == "reference":
+        from oracle import ref_cuda
+        if not ref_cuda.available():
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's CUDA sources were not compiled (oracle/_ref missing)"}))
+            return
+    cases, what = aux_cases(AUX, dev, impl)
+    peaks = load_peaks()
+    rows = []
+    warm = max(args.warmup, 3)
+    with ClockSampler(gpu_uuid(dev)) as clk:
+        for name, fn, nbytes in cases:
+            for _ in range(warm):
+                fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / args.steps
+            rows.append(dict(kernel=name, ms=ms, algorithmic_bytes=int(nbytes), gbs=nbytes / (ms / 1e3) / 1e9,
+                             hbm_frac=nbytes / (ms / 1e3) / 1e9 / peaks["hbm_gbs"]))
+    geo = float(np.exp(np.mean([np.log(r["hbm_frac"]) for r in rows])))
+    total_ms = sum(r["ms"] for r in rows)
+    line = {"metric": AUX_METRIC, "value": geo, "unit": AUX_UNIT, "n_gpus": 1, "steps": args.steps, "warmup": warm,
+            "ms_per_step": total_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"name": "aux", "workload": what, "l2": "inputs larger than L2"},
+            "roofline": {"bound": "hbm", "achieved": geo * peaks["hbm_gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": geo, "traffic": None, "note": "geometric mean over the kernels; per-call time includes "
+                         "the host side of the call (allocation of the outputs, cached cluster / pair groupings)",
+                         "peak_source": peaks["source"]},
+            "kernels": rows, "clocks": clk.summary()}
+    if impl == "reference":
+        line["impl"] = "reference"
+        line["cpu_baseline"] = dict(value=geo, unit=AUX_UNIT, cores=1, kind="reference",
+                                    sample="the reference's own CUDA kernels of the same operators on the same inputs and GPU")
+        line["e2e"] = dict(value=geo, unit=AUX_UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0)
+    print(json.dumps(line))
+
+
 # ------------------------------------------------------------------- CPU oracle timing
 def _oracle_step_fn(cfg, n_or_level, seed_shift=0):
     """One mesh of the configuration's kind (heightfield n x n or icosphere level) and a
@@ -1060,7 +1195,9 @@ def run_reference(args):
 
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference" and a.config == "decimate":
+    if a.config == "aux":
+        run_aux(a)
+    elif a.impl == "reference" and a.config == "decimate":
         run_reference_decimate(a)
     elif a.impl == "reference":
         run_reference(a)
