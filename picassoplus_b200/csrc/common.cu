@@ -80,8 +80,44 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, int np
     out[i] = acc;
 }
 
+// Many partials: 32 slices of them are summed side by side (each in ascending order, four loads in flight) and
+// the 32 sums are added in slice order.
+constexpr int RP_SLICES = 32, RP_WIDTH = 32;
+__global__ void __launch_bounds__(RP_WIDTH * RP_SLICES)
+reduce_partials_sliced_kernel(const float* __restrict__ partial, int nparts, int64_t n, float* __restrict__ out) {
+    __shared__ float part[RP_SLICES][RP_WIDTH];
+    const int64_t i = (int64_t)blockIdx.x * RP_WIDTH + threadIdx.x;
+    const int y = threadIdx.y, per = (nparts + RP_SLICES - 1) / RP_SLICES;
+    const int b0 = y * per, b1 = b0 + per < nparts ? b0 + per : nparts;
+    float acc = 0.f;
+    if (i < n) {
+        int b = b0;
+        for (; b + 4 <= b1; b += 4) {
+            const float v0 = partial[(int64_t)b * n + i], v1 = partial[(int64_t)(b + 1) * n + i];
+            const float v2 = partial[(int64_t)(b + 2) * n + i], v3 = partial[(int64_t)(b + 3) * n + i];
+            acc += v0;
+            acc += v1;
+            acc += v2;
+            acc += v3;
+        }
+        for (; b < b1; ++b) acc += partial[(int64_t)b * n + i];
+    }
+    part[y][threadIdx.x] = acc;
+    __syncthreads();
+    if (y == 0 && i < n) {
+        float s = part[0][threadIdx.x];
+        for (int k = 1; k < RP_SLICES; ++k) s += part[k][threadIdx.x];
+        out[i] = s;
+    }
+}
+
 int reduce_partials(const float* partial, int nparts, int64_t n, float* out, cudaStream_t stream) {
     if (n <= 0) return PB200_OK;
+    if (nparts >= 256) {
+        PB_LAUNCH("reduce_partials", reduce_partials_sliced_kernel, (unsigned)ceil_div(n, RP_WIDTH), dim3(RP_WIDTH, RP_SLICES), 0, stream,
+                  partial, nparts, n, out);
+        return PB200_OK;
+    }
     PB_LAUNCH("reduce_partials", reduce_partials_kernel, (unsigned)ceil_div(n, 128), 128, 0, stream,
               partial, nparts, n, out);
     return PB200_OK;

@@ -231,6 +231,293 @@ static bool sizes_ok(int64_t Np, int64_t Mp, int64_t Nout, int F, int C, int r, 
     return Np >= 0 && Mp >= 0 && Nout >= 0 && F > 0 && C > 0 && r > 0 && T > 0 && Np < (1LL << 31) && Mp < (1LL << 31) &&
            Nout < (1LL << 31) && (int64_t)F * C * r * 4 <= 200 * 1024;
 }
+// ------------------------------------------------------------------------ cooperative kernels
+// C of 32, 64 or 128: the CV = C / 4 lanes of a point sit in one warp, so lane j fetches the indices of the j-th
+// pair of a run and the run is walked with shuffles, four pairs at a time: the four row gathers and the bin
+// fetches of a step are in flight together. TT: 1 = one bin per pair, 3 = three weighted bins, 0 = any T.
+// Same order of additions as the vector kernels.
+template <int CV>
+__device__ __forceinline__ unsigned group_mask(int gbase) {
+    return CV == 32 ? 0xffffffffu : (((1u << (CV & 31)) - 1u) << gbase);
+}
+
+template <int TT, int CV>
+__device__ __forceinline__ float4 pair_weight4t(int64_t p, int cg, int F, int T, const int32_t* __restrict__ bin,
+                                                const float* __restrict__ coeff, const float4* __restrict__ sfilt) {
+    if constexpr (TT == 0) {
+        return pair_weight4(p, cg, CV, F, T, bin, coeff, sfilt);
+    } else if constexpr (TT == 1) {
+        const int f = __ldg(bin + p);
+        const bool ok = (unsigned)f < (unsigned)F;
+        const float4 w = sfilt[(ok ? f : 0) * CV + cg];
+        return ok ? w : zero4();
+    } else {
+    int f[3];
+    float c[3];
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        f[t] = __ldg(bin + p * 3 + t);
+        c[t] = __ldg(coeff + p * 3 + t);
+    }
+    float4 w = zero4();
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+        const bool ok = (unsigned)f[t] < (unsigned)F;
+        fma4s(w, ok ? c[t] : 0.f, sfilt[(ok ? f[t] : 0) * CV + cg]);
+    }
+    return w;
+    }
+}
+
+template <int TT, int CV>
+__global__ void __launch_bounds__(256)
+conv_fwd_coop_kernel(int64_t Np, int64_t Mp, int F, int T, const float4* __restrict__ input,
+                     const float4* __restrict__ filter, const int32_t* __restrict__ nnCount,
+                     const int32_t* __restrict__ nnIndex, const int32_t* __restrict__ bin, const float* __restrict__ coeff,
+                     const int32_t* __restrict__ rowptr, const int32_t* __restrict__ members, float4* __restrict__ output) {
+    extern __shared__ float4 sfilt[];
+    for (int i = threadIdx.x; i < F * CV; i += blockDim.x) sfilt[i] = filter[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, cg = lane % CV, gbase = lane - cg;
+    const unsigned mask = group_mask<CV>(gbase);
+    const int64_t stride = (int64_t)gridDim.x * (blockDim.x / CV);
+    for (int64_t o = (int64_t)blockIdx.x * (blockDim.x / CV) + threadIdx.x / CV; o < Mp; o += stride) {
+        const int e0 = __ldg(rowptr + o), e1 = __ldg(rowptr + o + 1);
+        const float rn = 1.f / (float)__ldg(nnCount + o);
+        float4 acc = zero4();
+        for (int e = e0; e < e1; e += CV) {
+            int p_mine = 0, in_mine = -1;
+            if (e + cg < e1) {
+                p_mine = __ldg(members + e + cg);
+                in_mine = __ldg(nnIndex + 2 * (int64_t)p_mine + 1);
+            }
+            const int n = e1 - e < CV ? e1 - e : CV;
+            for (int j = 0; j < n; j += 4) {
+                float4 x[4], w[4];
+                int pp[4];
+                bool ok[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int src = gbase + ((j + u) & (CV - 1));
+                    pp[u] = __shfl_sync(mask, p_mine, src);
+                    const int in = __shfl_sync(mask, in_mine, src);
+                    ok[u] = j + u < n && in >= 0 && in < Np;
+                    x[u] = ok[u] ? ldg4(input + (int64_t)in * CV + cg) : zero4();
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) w[u] = pair_weight4t<TT, CV>(pp[u], cg, F, T, bin, coeff, sfilt);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (ok[u]) fma4(acc, scale4(x[u], rn), w[u]);
+            }
+        }
+        output[o * CV + cg] = acc;
+    }
+}
+
+// The bins and weights of the pair a lane fetched (TT of 1 or 3), handed to the group's lanes by shuffles.
+template <int TT>
+struct LaneBins {
+    int f[TT == 3 ? 3 : 1];
+    float c[TT == 3 ? 3 : 1];
+};
+
+template <int TT>
+__device__ __forceinline__ void load_bins(LaneBins<TT>& b, bool have, int64_t p, const int32_t* __restrict__ bin,
+                                          const float* __restrict__ coeff) {
+#pragma unroll
+    for (int t = 0; t < (TT == 3 ? 3 : 1); ++t) {
+        b.f[t] = have ? __ldg(bin + p * (TT == 3 ? 3 : 1) + t) : -1;
+        b.c[t] = TT == 3 ? (have ? __ldg(coeff + p * 3 + t) : 0.f) : 1.f;
+    }
+}
+
+template <int TT, int CV>
+__device__ __forceinline__ float4 shuffled_weight4(const LaneBins<TT>& b, unsigned mask, int src, int cg, int F,
+                                                   const float4* __restrict__ sfilt) {
+    float4 w = zero4();
+#pragma unroll
+    for (int t = 0; t < (TT == 3 ? 3 : 1); ++t) {
+        const int f = __shfl_sync(mask, b.f[t], src);
+        const float c = TT == 3 ? __shfl_sync(mask, b.c[t], src) : 1.f;
+        const bool ok = (unsigned)f < (unsigned)F;
+        fma4s(w, ok ? c : 0.f, sfilt[(ok ? f : 0) * CV + cg]);
+    }
+    return w;
+}
+
+// one step of the input gradient: up to four pairs whose indices sit in the lanes of the group, slots j .. j + 3
+// of [j, end); the four rows of the output gradient and the bin fetches are in flight together
+template <int TT, int CV>
+__device__ __forceinline__ void bwd_input_step(float4& acc, int j, int end, unsigned mask, int gbase, int cg, int p_mine,
+                                               int o_mine, float rn_mine, const LaneBins<TT>& mybins, int64_t Mp, int F, int T,
+                                               const float4* __restrict__ gout, const int32_t* __restrict__ bin,
+                                               const float* __restrict__ coeff, const float4* __restrict__ sfilt) {
+    float4 x[4], w[4];
+    int pp[4];
+    float rn[4];
+    bool ok[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int src = gbase + ((j + u) & (CV - 1));
+        pp[u] = __shfl_sync(mask, p_mine, src);
+        const int o = __shfl_sync(mask, o_mine, src);
+        rn[u] = __shfl_sync(mask, rn_mine, src);
+        ok[u] = j + u < end && o >= 0 && o < Mp;
+        x[u] = ok[u] ? ldg4(gout + (int64_t)o * CV + cg) : zero4();
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        if constexpr (TT == 0) w[u] = pair_weight4(pp[u], cg, CV, F, T, bin, coeff, sfilt);
+        else w[u] = shuffled_weight4<TT, CV>(mybins, mask, gbase + ((j + u) & (CV - 1)), cg, F, sfilt);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+        if (ok[u]) fma4(acc, scale4(x[u], rn[u]), w[u]);
+}
+
+// A group takes W = CV / 4 consecutive input points per step: their pairs are one contiguous run of the grouping,
+// and when it fits the group's lanes (the usual case: an input point is the neighbour of a few output points) one
+// fetch of the indices serves all W points.
+template <int TT, int CV>
+__global__ void __launch_bounds__(256, 4)
+conv_bwd_input_coop_kernel(int64_t Np, int64_t Mp, int F, int T, const float4* __restrict__ gout,
+                           const float4* __restrict__ filter, const int32_t* __restrict__ nnCount,
+                           const int32_t* __restrict__ nnIndex, const int32_t* __restrict__ bin,
+                           const float* __restrict__ coeff, const int32_t* __restrict__ rowptr,
+                           const int32_t* __restrict__ members, float4* __restrict__ gin) {
+    constexpr int W = CV / 4;
+    extern __shared__ float4 sfilt[];
+    for (int i = threadIdx.x; i < F * CV; i += blockDim.x) sfilt[i] = filter[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, cg = lane % CV, gbase = lane - cg;
+    const unsigned mask = group_mask<CV>(gbase);
+    const int64_t stride = (int64_t)gridDim.x * (blockDim.x / CV) * W;
+    for (int64_t base = ((int64_t)blockIdx.x * (blockDim.x / CV) + threadIdx.x / CV) * W; base < Np; base += stride) {
+        int rp_mine = 0;
+        if (cg <= W) rp_mine = __ldg(rowptr + (base + cg < Np ? base + cg : Np));
+        const int E0 = __shfl_sync(mask, rp_mine, gbase), EW = __shfl_sync(mask, rp_mine, gbase + W);
+        const bool together = EW - E0 <= CV;
+        int p_mine = 0, o_mine = -1;
+        float rn_mine = 0.f;
+        LaneBins<TT> mybins;
+        if (together) {
+            const bool have = E0 + cg < EW;
+            if (have) p_mine = __ldg(members + E0 + cg);
+            if (have) o_mine = __ldg(nnIndex + 2 * (int64_t)p_mine);
+            if constexpr (TT != 0) load_bins<TT>(mybins, have, p_mine, bin, coeff);
+            if (o_mine >= 0 && o_mine < Mp) rn_mine = 1.f / (float)__ldg(nnCount + o_mine);
+        }
+#pragma unroll 1
+        for (int k = 0; k < W; ++k) {
+            const int e0 = __shfl_sync(mask, rp_mine, gbase + k), e1 = __shfl_sync(mask, rp_mine, gbase + k + 1);
+            float4 acc = zero4();
+            if (together) {
+                for (int j = e0 - E0; j < e1 - E0; j += 4)
+                    bwd_input_step<TT, CV>(acc, j, e1 - E0, mask, gbase, cg, p_mine, o_mine, rn_mine, mybins, Mp, F, T, gout, bin,
+                                           coeff, sfilt);
+            } else {
+                for (int e = e0; e < e1; e += CV) {
+                    p_mine = 0, o_mine = -1, rn_mine = 0.f;
+                    const bool have = e + cg < e1;
+                    if (have) p_mine = __ldg(members + e + cg);
+                    if (have) o_mine = __ldg(nnIndex + 2 * (int64_t)p_mine);
+                    if constexpr (TT != 0) load_bins<TT>(mybins, have, p_mine, bin, coeff);
+                    if (o_mine >= 0 && o_mine < Mp) rn_mine = 1.f / (float)__ldg(nnCount + o_mine);
+                    const int n = e1 - e < CV ? e1 - e : CV;
+                    for (int j = 0; j < n; j += 4)
+                        bwd_input_step<TT, CV>(acc, j, n, mask, gbase, cg, p_mine, o_mine, rn_mine, mybins, Mp, F, T, gout, bin,
+                                               coeff, sfilt);
+                }
+            }
+            if (base + k < Np) gin[(base + k) * CV + cg] = acc;
+        }
+    }
+}
+
+// Filter gradient: a block of SUB groups of CV lanes takes a contiguous run of pairs, group g the g-th equal part
+// of it, walked in order into the group's own copy of the [F][C] accumulator in shared memory; copies are added in
+// group order, blocks in block order.
+template <int TT, int CV>
+__global__ void __launch_bounds__(256)
+conv_bwd_filter_coop_kernel(int64_t Np, int64_t Mp, int64_t Nout, int pairs_per_block, int SUB, int F, int T,
+                            const float4* __restrict__ input, const float4* __restrict__ gout,
+                            const int32_t* __restrict__ nnCount, const int32_t* __restrict__ nnIndex,
+                            const int32_t* __restrict__ bin, const float* __restrict__ coeff, float4* __restrict__ partial) {
+    extern __shared__ float4 acc4[];                 // [SUB][F][CV]
+    for (int i = threadIdx.x; i < SUB * F * CV; i += blockDim.x) acc4[i] = zero4();
+    __syncthreads();
+    const int lane = threadIdx.x & 31, cg = lane % CV, gbase = lane - cg, g = threadIdx.x / CV;
+    const unsigned mask = group_mask<CV>(gbase);
+    const int per_group = (pairs_per_block + SUB - 1) / SUB;
+    const int64_t b0 = (int64_t)blockIdx.x * pairs_per_block;
+    int64_t b1 = b0 + pairs_per_block;
+    if (b1 > Nout) b1 = Nout;
+    const int64_t q0 = b0 + (int64_t)g * per_group;
+    int64_t q1 = q0 + per_group;
+    if (q1 > b1) q1 = b1;
+    float4* mine = acc4 + (size_t)g * F * CV;
+    for (int64_t q = q0; q < q1; q += CV) {
+        int o_mine = -1, in_mine = -1;
+        float rn_mine = 0.f;
+        LaneBins<TT> mybins;
+        const bool have = q + cg < q1;
+        if (have) {
+            o_mine = __ldg(nnIndex + 2 * (q + cg));
+            in_mine = __ldg(nnIndex + 2 * (q + cg) + 1);
+        }
+        if constexpr (TT != 0) load_bins<TT>(mybins, have, q + cg, bin, coeff);
+        if (o_mine >= 0 && o_mine < Mp) rn_mine = 1.f / (float)__ldg(nnCount + o_mine);
+        const int n = q1 - q < CV ? (int)(q1 - q) : CV;
+        for (int j = 0; j < n; j += 4) {
+            float4 gr[4], xr[4];
+            float rn[4];
+            bool ok[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int src = gbase + ((j + u) & (CV - 1));
+                const int o = __shfl_sync(mask, o_mine, src);
+                const int in = __shfl_sync(mask, in_mine, src);
+                rn[u] = __shfl_sync(mask, rn_mine, src);
+                ok[u] = j + u < n && o >= 0 && o < Mp && in >= 0 && in < Np;
+                gr[u] = ok[u] ? ldg4(gout + (int64_t)o * CV + cg) : zero4();
+                xr[u] = ok[u] ? ldg4(input + (int64_t)in * CV + cg) : zero4();
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4 d = mul4(scale4(gr[u], rn[u]), xr[u]);
+                if constexpr (TT != 0) {
+                    const int src = gbase + ((j + u) & (CV - 1));
+#pragma unroll
+                    for (int t = 0; t < (TT == 3 ? 3 : 1); ++t) {
+                        const int f = __shfl_sync(mask, mybins.f[t], src);
+                        const float c = TT == 3 ? __shfl_sync(mask, mybins.c[t], src) : 1.f;
+                        if (ok[u] && (unsigned)f < (unsigned)F) fma4s(mine[f * CV + cg], c, d);
+                    }
+                } else if (ok[u]) {
+                    const int64_t p = q + j + u;
+                    if (!coeff) {
+                        const int fb = __ldg(bin + p);
+                        if (fb >= 0 && fb < F) add4(mine[fb * CV + cg], d);
+                    } else {
+                        for (int t = 0; t < T; ++t) {
+                            const int fb = __ldg(bin + p * T + t);
+                            if (fb >= 0 && fb < F) fma4s(mine[fb * CV + cg], __ldg(coeff + p * T + t), d);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    float4* out = partial + (int64_t)blockIdx.x * F * CV;
+    for (int i = threadIdx.x; i < F * CV; i += blockDim.x) {
+        float4 s4 = acc4[i];
+        for (int k = 1; k < SUB; ++k) add4(s4, acc4[(size_t)k * F * CV + i]);
+        out[i] = s4;
+    }
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 // the vector kernels: depth multiplier 1, channels a multiple of 4 and at most 1024 (one group of lanes per point),
 // and a filter table that leaves room in shared memory for at least one accumulator copy
@@ -243,6 +530,50 @@ static int vec_sub_groups(int F, int C) {
     while (sub > 1 && (size_t)sub * F * C * 4 > 96 * 1024) --sub;
     return sub;
 }
+
+// groups of a filter-gradient block: as many accumulator copies as fit 56 KB (four blocks on an SM), whole warps
+static int coop_sub_groups(int F, int C) {
+    const int CV = C / 4, step = 32 / CV, most = 256 / CV;
+    int sub = (int)((56 * 1024) / ((size_t)F * C * 4)) / step * step;
+    return sub < step ? step : sub > most ? most : sub;
+}
+static bool coop_ok(int F, int C) {
+    return (C == 32 || C == 64 || C == 128) && (size_t)coop_sub_groups(F, C) * F * C * 4 <= 200 * 1024;
+}
+
+template <int TT, int CV>
+static int launch_fwd_coop(int64_t Np, int64_t Mp, int F, int T, const float* input, const float* filter, const int32_t* nnCount,
+                           const int32_t* nnIndex, const int32_t* bin, const float* coeff, const int32_t* rowptr,
+                           const int32_t* members, float* output, cudaStream_t stream) {
+    PB_LAUNCH("pcloud_conv_fwd", (conv_fwd_coop_kernel<TT, CV>), persistent_blocks(Mp * CV, 256, 8), 256, sizeof(float4) * F * CV,
+              stream, Np, Mp, F, T, (const float4*)input, (const float4*)filter, nnCount, nnIndex, bin, coeff, rowptr, members,
+              (float4*)output);
+    return PB200_OK;
+}
+
+template <int TT, int CV>
+static int launch_bwd_coop(int64_t Np, int64_t Mp, int64_t Nout, int nb, int F, int T, const float* input, const float* filter,
+                           const float* gout, const int32_t* nnCount, const int32_t* nnIndex, const int32_t* bin,
+                           const float* coeff, const int32_t* rowptr, const int32_t* members, float* gin, float* partial,
+                           cudaStream_t stream) {
+    if (Np > 0)
+        PB_LAUNCH("pcloud_conv_bwd_input", (conv_bwd_input_coop_kernel<TT, CV>), persistent_blocks(Np * CV, 256, 8), 256,
+                  sizeof(float4) * F * CV, stream, Np, Mp, F, T, (const float4*)gout, (const float4*)filter, nnCount, nnIndex, bin,
+                  coeff, rowptr, members, (float4*)gin);
+    const int sub = coop_sub_groups(F, 4 * CV);
+    const size_t smem = sizeof(float4) * (size_t)sub * F * CV;
+    PB_CUDA(cudaFuncSetAttribute(conv_bwd_filter_coop_kernel<TT, CV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    PB_LAUNCH("pcloud_conv_bwd_filter", (conv_bwd_filter_coop_kernel<TT, CV>), nb, sub * CV, smem, stream, Np, Mp, Nout,
+              VEC_PAIRS_PER_BLOCK, sub, F, T, (const float4*)input, (const float4*)gout, nnCount, nnIndex, bin, coeff,
+              (float4*)partial);
+    return PB200_OK;
+}
+
+// the kernels are built for CV of 8, 16, 32 and for one bin per pair, three weighted bins, or any T
+#define PB_COOP_DISPATCH(FN, ...)                                                                                  \
+    (tt == 1 ? (CV == 8 ? FN<1, 8>(__VA_ARGS__) : CV == 16 ? FN<1, 16>(__VA_ARGS__) : FN<1, 32>(__VA_ARGS__))      \
+     : tt == 3 ? (CV == 8 ? FN<3, 8>(__VA_ARGS__) : CV == 16 ? FN<3, 16>(__VA_ARGS__) : FN<3, 32>(__VA_ARGS__))    \
+               : (CV == 8 ? FN<0, 8>(__VA_ARGS__) : CV == 16 ? FN<0, 16>(__VA_ARGS__) : FN<0, 32>(__VA_ARGS__)))
 
 static int filter_blocks(int64_t Nout) {
     int64_t b = ceil_div(Nout > 0 ? Nout : 1, 256);         // at least 256 pairs per block
@@ -269,6 +600,11 @@ int pb200_pcloud_conv3d_forward(int64_t Np, int64_t Mp, int64_t Nout, int F, int
                PB200_EINVAL, "pcloud_conv3d_forward: null pointer");
     if (vec_ok(F, C, r) && aligned16(input) && aligned16(filter) && aligned16(output)) {
         const int CV = C / 4;
+        if (coop_ok(F, C)) {
+            const int tt = !binCoeff ? 1 : T == 3 ? 3 : 0;
+            return PB_COOP_DISPATCH(launch_fwd_coop, Np, Mp, F, T, input, filter, nnCount, nnIndex, binIndex, binCoeff, rowptr_out,
+                                    members_out, output, stream);
+        }
         PB_LAUNCH("pcloud_conv_fwd", conv_fwd_vec_kernel, persistent_blocks(Mp * CV, 256, 8), 256, sizeof(float) * F * C, stream,
                   Np, Mp, F, CV, T, (const float4*)input, (const float4*)filter, nnCount, nnIndex, binIndex, binCoeff, rowptr_out,
                   members_out, (float4*)output);
@@ -301,6 +637,14 @@ int pb200_pcloud_conv3d_backward(int64_t Np, int64_t Mp, int64_t Nout, int F, in
     if (vec_ok(F, C, r) && aligned16(input) && aligned16(filter) && aligned16(gradOutput) && aligned16(gradInput) &&
         aligned16(workspace)) {
         const int CV = C / 4;
+        if (coop_ok(F, C)) {
+            const int nbc = vec_filter_blocks(Nout);
+            const int tt = !binCoeff ? 1 : T == 3 ? 3 : 0;
+            const int rc = PB_COOP_DISPATCH(launch_bwd_coop, Np, Mp, Nout, nbc, F, T, input, filter, gradOutput, nnCount, nnIndex,
+                                            binIndex, binCoeff, rowptr_in, members_in, gradInput, (float*)workspace, stream);
+            if (rc != PB200_OK) return rc;
+            return reduce_partials((const float*)workspace, nbc, (int64_t)F * C, gradFilter, stream);
+        }
         if (Np > 0)
             PB_LAUNCH("pcloud_conv_bwd_input", conv_bwd_input_vec_kernel, persistent_blocks(Np * CV, 256, 8), 256,
                       sizeof(float) * F * C, stream, Np, Mp, F, CV, T, (const float4*)gradOutput, (const float4*)filter, nnCount,

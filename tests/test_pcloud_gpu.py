@@ -20,6 +20,9 @@ CASES = [
     (3000, 1000, 24, 33, 64, 1, 3, True),
     (4000, 4000, 16, 17, 128, 1, 0, False),
     (64, 16, 40, 5, 3, 3, 2, True),
+    (2500, 700, 20, 51, 32, 1, 3, True),       # eight lanes per point: four points to a warp
+    (900, 300, 37, 25, 12, 1, 0, True),        # four channels per lane without the warp-cooperative walk
+    (700, 200, 70, 140, 128, 1, 3, False),     # runs longer than a warp; a filter table the cooperative kernels decline
 ]
 
 
