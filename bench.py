@@ -999,12 +999,14 @@ def aux_cases(cfg, dev, impl):
         from picassoplus_b200.mesh.pi_modules import pool3d, unpool3d
         from picassoplus_b200.point.pi_modules import conv3d as pconv
         from picassoplus_b200 import topology
-        mx, idx = pool3d.max_forward(x, rep, vmap, vout)
+        mx, idx, clusters = pool3d.max_forward(x, rep, vmap, vout, return_clusters=True)
         L = cfg["L"]
         vt = torch.arange(nv_in, dtype=torch.int32, device=dev)
         cases = [
             ("mesh_max_pool_fwd", lambda: pool3d.max_forward(x, rep, vmap, vout), 4 * C * nv_in + 8 * C * nv_out),
-            ("mesh_max_pool_bwd", lambda: pool3d.max_backward(xc, x, idx), 8 * C * nv_out + 4 * C * nv_in),
+            ("mesh_max_pool_bwd", lambda: pool3d.max_backward(xc, x, idx, clusters), 8 * C * nv_out + 4 * C * nv_in),
+            ("mesh_max_pool_bwd (reference's signature: zero fill + scatter)", lambda: pool3d.max_backward(xc, x, idx),
+             8 * C * nv_out + 4 * C * nv_in),
             ("mesh_avg_pool_fwd", lambda: pool3d.avg_forward(x, rep, vmap, vout), 4 * C * nv_in + 4 * C * nv_out),
             ("mesh_avg_pool_bwd", lambda: pool3d.avg_backward(xc, x, rep, vmap), 4 * C * nv_out + 4 * C * nv_in),
             ("mesh_unpool_fwd", lambda: unpool3d.forward(xc, rep, vmap), 4 * C * nv_out + 4 * C * nv_in),

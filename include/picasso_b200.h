@@ -313,6 +313,13 @@ int pb200_mesh_max_pool_forward(int64_t NvIn, int64_t NvOut, int C, const float*
  * (mesh_pool3d_gpu.cu:93-105,171-177; binding MeshMaxPool3dGrad). */
 int pb200_mesh_max_pool_backward(int64_t NvIn, int64_t NvOut, int C, const int32_t* maxIndex, const float* gradOutput,
                                  float* gradInput, void* stream);
+/* The same gradient for a caller that holds the cluster structures of pb200_build_cluster_csr (key, rowptr) and a
+ * maxIndex made by pb200_mesh_max_pool_forward over them: every row of gradInput is written once by a gather
+ * (row v takes gradOutput[key[v],c] where maxIndex[key[v],c] == v), no zero fill and no scattered stores; identical
+ * result, members-less coarse vertices included (their gradient goes to vertex 0 as in the scatter). */
+int pb200_mesh_max_pool_backward_clusters(int64_t NvIn, int64_t NvOut, int C, const int32_t* maxIndex,
+                                          const float* gradOutput, const int32_t* key, const int32_t* rowptr,
+                                          float* gradInput, void* stream);
 /* output[vo,c] = sum over members of input[v,c] / (vtReplace[representative] + 1).  Replaces
  * avgPool3dLauncher (mesh_pool3d_gpu.cu:112-132,179-185; binding MeshAvgPool3d). */
 int pb200_mesh_avg_pool_forward(int64_t NvIn, int64_t NvOut, int C, const float* input, const int32_t* vtReplace,

@@ -71,6 +71,7 @@ SIGNATURES = {
     "pb200_build_cluster_csr": (i32, [i64, i64, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_mesh_max_pool_forward": (i32, [i64, i64, i32, vp, vp, vp, vp, vp, vp]),
     "pb200_mesh_max_pool_backward": (i32, [i64, i64, i32, vp, vp, vp, vp]),
+    "pb200_mesh_max_pool_backward_clusters": (i32, [i64, i64, i32, vp, vp, vp, vp, vp, vp]),
     "pb200_mesh_avg_pool_forward": (i32, [i64, i64, i32, vp, vp, vp, vp, vp, vp]),
     "pb200_mesh_avg_pool_backward": (i32, [i64, i64, i32, vp, vp, vp, vp, vp]),
     "pb200_mesh_unpool_forward": (i32, [i64, i64, i32, vp, vp, vp, vp]),

@@ -88,6 +88,51 @@ __global__ void max_pool_bwd_kernel(int64_t NvIn, int64_t NvOut, int C, const in
     }
 }
 
+// The same gradient as a gather, for callers that hold the cluster structures: fine vertex v of cluster vo takes
+// gradOutput[vo,c] where maxIndex[vo,c] == v, else 0. Whole rows are written once, in order, instead of a zero fill
+// followed by 4-byte stores scattered over rows that have left the L2 (each of those is a read-modify-write of a
+// sector in DRAM).
+template <int VEC>
+__global__ void max_pool_bwd_gather_kernel(int64_t NvIn, int CVn, const int32_t* __restrict__ max_index,
+                                           const float* __restrict__ gout, const int32_t* __restrict__ key,
+                                           float* __restrict__ gin) {
+    const int64_t total = NvIn * CVn;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t v = i / CVn;
+        const int c = (int)(i - v * CVn);
+        const int vo = key[v];
+        if (VEC == 4) {
+            float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (vo >= 0) {
+                const int4 m = __ldg(reinterpret_cast<const int4*>(max_index) + (int64_t)vo * CVn + c);
+                const float4 g = __ldg(reinterpret_cast<const float4*>(gout) + (int64_t)vo * CVn + c);
+                r.x = m.x == v ? g.x : 0.f;
+                r.y = m.y == v ? g.y : 0.f;
+                r.z = m.z == v ? g.z : 0.f;
+                r.w = m.w == v ? g.w : 0.f;
+            }
+            reinterpret_cast<float4*>(gin)[i] = r;
+        } else {
+            float r = 0.f;
+            if (vo >= 0 && max_index[(int64_t)vo * CVn + c] == v) r = gout[(int64_t)vo * CVn + c];
+            gin[i] = r;
+        }
+    }
+}
+
+// A coarse vertex without members records index 0 and the scatter hands its gradient to vertex 0: the gather
+// cannot see it (no fine vertex has it as key), so those rows are stored afterwards.
+__global__ void max_pool_bwd_empty_kernel(int64_t NvIn, int64_t NvOut, int C, const int32_t* __restrict__ rowptr,
+                                          const int32_t* __restrict__ max_index, const float* __restrict__ gout,
+                                          float* __restrict__ gin) {
+    const int64_t vo = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vo >= NvOut || rowptr[vo] != rowptr[vo + 1]) return;
+    for (int c = 0; c < C; ++c) {
+        const int vi = max_index[vo * C + c];
+        if (vi >= 0 && vi < NvIn) gin[(int64_t)vi * C + c] = gout[vo * C + c];
+    }
+}
+
 // output[vo] = sum over members of input[m] / count, count = vtReplace[representative] + 1, terms
 // added in ascending member order (reference: avg_pool3d_forward, mesh_pool3d_gpu.cu:112-132,
 // which divides each term before its atomic add)
@@ -220,6 +265,24 @@ int pb200_mesh_max_pool_backward(int64_t NvIn, int64_t NvOut, int C, const int32
     if (NvOut == 0) return PB200_OK;
     PB_LAUNCH("mesh_max_pool_bwd", max_pool_bwd_kernel, persistent_blocks(NvOut * C, 256, 16), 256, 0, stream, NvIn, NvOut, C,
               maxIndex, gradOutput, gradInput);
+    return PB200_OK;
+}
+
+int pb200_mesh_max_pool_backward_clusters(int64_t NvIn, int64_t NvOut, int C, const int32_t* maxIndex,
+                                          const float* gradOutput, const int32_t* key, const int32_t* rowptr,
+                                          float* gradInput, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(sizes_ok(NvIn, NvOut, C), PB200_EINVAL, "mesh_max_pool_backward_clusters: bad sizes");
+    if (NvIn == 0) return PB200_OK;
+    PB_REQUIRE(gradInput && key && rowptr && (NvOut == 0 || (maxIndex && gradOutput)), PB200_EINVAL,
+               "mesh_max_pool_backward_clusters: null pointer");
+    const bool vec = C % 4 == 0 && aligned16(gradOutput) && aligned16(gradInput) && aligned16(maxIndex);
+    const int CVn = vec ? C / 4 : C;
+    PB_POOL_LAUNCH("mesh_max_pool_bwd", max_pool_bwd_gather_kernel, NvIn * CVn, vec, NvIn, CVn, maxIndex, gradOutput, key,
+                   gradInput);
+    if (NvOut > 0)
+        PB_LAUNCH("mesh_max_pool_bwd_empty", max_pool_bwd_empty_kernel, (unsigned)ceil_div(NvOut, 256), 256, 0, stream, NvIn,
+                  NvOut, C, rowptr, maxIndex, gradOutput, gradInput);
     return PB200_OK;
 }
 

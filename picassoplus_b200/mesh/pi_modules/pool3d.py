@@ -25,7 +25,7 @@ def _pool_checks(input, vt_replace, vt_map, vt_out):
         raise RuntimeError("vt_replace and vt_map must have one entry per input vertex")
 
 
-def max_forward(input, vt_replace, vt_map, vt_out):
+def max_forward(input, vt_replace, vt_map, vt_out, return_clusters=False):
     _pool_checks(input, vt_replace, vt_map, vt_out)
     nv_in, C = input.shape
     nv_out = vt_out.shape[0]
@@ -36,10 +36,14 @@ def max_forward(input, vt_replace, vt_map, vt_out):
         max_index = torch.empty(nv_out, C, dtype=torch.int32, device=dev)
         _lib.call("pb200_mesh_max_pool_forward", nv_in, nv_out, C, ptr(input), ptr(cl.rowptr), ptr(cl.members),
                   ptr(out), ptr(max_index), stream_ptr(dev))
+    if return_clusters:
+        return out, max_index, cl
     return out, max_index
 
 
-def max_backward(grad_output, input, max_index):
+def max_backward(grad_output, input, max_index, clusters=None):
+    """clusters: the ClusterCSR the forward pooled over (the autograd function keeps it); with it the gradient is a
+    gather over the fine vertices instead of a zero fill and a scatter. Same result."""
     _check(grad_output, "grad_output", 2, torch.float32)
     _check(input, "input", 2, torch.float32)
     _check(max_index, "max_index", 2, torch.int32)
@@ -50,8 +54,12 @@ def max_backward(grad_output, input, max_index):
     dev = input.device
     with torch.cuda.device(dev):
         gin = torch.empty(nv_in, C, dtype=input.dtype, device=dev)
-        _lib.call("pb200_mesh_max_pool_backward", nv_in, nv_out, C, ptr(max_index), ptr(grad_output), ptr(gin),
-                  stream_ptr(dev))
+        if clusters is not None and clusters.rowptr.shape[0] == nv_out + 1 and clusters.key.shape[0] >= nv_in:
+            _lib.call("pb200_mesh_max_pool_backward_clusters", nv_in, nv_out, C, ptr(max_index), ptr(grad_output),
+                      ptr(clusters.key), ptr(clusters.rowptr), ptr(gin), stream_ptr(dev))
+        else:
+            _lib.call("pb200_mesh_max_pool_backward", nv_in, nv_out, C, ptr(max_index), ptr(grad_output), ptr(gin),
+                      stream_ptr(dev))
     return gin
 
 
@@ -90,7 +98,7 @@ class MaxPoolFunction(torch.autograd.Function):
         vt_replace.requires_grad = False
         vt_map.requires_grad = False
         vt_out.requires_grad = False
-        output, max_index = max_forward(input, vt_replace, vt_map, vt_out)
+        output, max_index, ctx.clusters = max_forward(input, vt_replace, vt_map, vt_out, return_clusters=True)
         variables = [input, max_index]
         ctx.save_for_backward(*variables)
         return output
@@ -98,7 +106,7 @@ class MaxPoolFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         input, max_index = ctx.saved_tensors
-        grad_input = max_backward(grad_output.contiguous(), input, max_index)
+        grad_input = max_backward(grad_output.contiguous(), input, max_index, ctx.clusters)
         return grad_input, None, None, None
 
 

@@ -45,6 +45,8 @@ def test_pool_and_unpool_match_oracle_and_reference(mods, nv_in, nv_out, C, ties
     assert torch.equal(out.cpu(), w_out) and torch.equal(idx.cpu(), w_idx)
     gin = pool3d.max_backward(c["g_coarse"], c["x"], idx)
     assert torch.equal(gin.cpu(), mo.mesh_max_pool_backward(d["g_coarse"], nv_in, w_idx))
+    _, _, clusters = pool3d.max_forward(c["x"], c["vt_replace"], c["vt_map"], vt_out, return_clusters=True)
+    assert torch.equal(pool3d.max_backward(c["g_coarse"], c["x"], idx, clusters), gin)     # the gather form
     avg = pool3d.avg_forward(c["x"], c["vt_replace"], c["vt_map"], vt_out)
     assert rel_err(avg, mo.mesh_avg_pool_forward(d["x"].double(), d["vt_replace"], d["vt_map"], nv_out)) <= 1e-6
     avg_b = pool3d.avg_backward(c["g_coarse"], c["x"], c["vt_replace"], c["vt_map"])
@@ -110,6 +112,25 @@ def test_autograd_through_pool_layers(mods):
     xc = c["x_coarse"].clone().requires_grad_()
     Unpool3d()(xc, c["vt_replace"], c["vt_map"]).backward(c["g_fine"])
     assert rel_err(xc.grad, mo.mesh_unpool_backward(d["g_fine"].double(), 250, d["vt_replace"], d["vt_map"])) <= 1e-6
+
+
+def test_max_pool_gradient_with_memberless_coarse_vertices(mods):
+    """More output rows than clusters: the extra coarse vertices have no members, record index 0 and hand their
+    gradient to vertex 0 (picasso/mesh/pi_modules/source/mesh_pool3d_gpu.cu:93-105); the gather form does the same.
+    Vertex 0 belongs to no cluster here, so no two writers meet there."""
+    pool3d, _, mo, _ = mods
+    d = cluster_inputs(400, 120, 8, seed=7)
+    assert int(d["vt_map"][0]) < 0 and int(d["vt_replace"][0]) == 0       # this seed leaves vertex 0 outside every cluster
+    c = _dev(d)
+    nv_out = 121
+    vt_out = torch.zeros(nv_out, 3, device="cuda")
+    g = torch.randn(nv_out, 8, device="cuda")
+    out, idx, clusters = pool3d.max_forward(c["x"], c["vt_replace"], c["vt_map"], vt_out, return_clusters=True)
+    assert torch.all(out[120] == 0) and torch.all(idx[120] == 0)
+    scatter = pool3d.max_backward(g, c["x"], idx)
+    gather = pool3d.max_backward(g, c["x"], idx, clusters)
+    assert torch.equal(scatter, gather) and torch.equal(gather[0], g[120])
+    assert torch.equal(gather.cpu(), mo.mesh_max_pool_backward(g.cpu(), 400, idx.cpu()))
 
 
 def test_bad_cluster_indices_are_reported(mods):
