@@ -223,6 +223,9 @@ def kernel_models(d):
     by kernel label: every operand read once, every result written once; fp32 / int32."""
     Nv, Nf, NiK, Ci, Co, K = d["Nv"], d["Nf"], d["NiK"], d["cin"], d["cout"], d["K"]
     Q = K * Ci
+    # sample rows that facet2facet itself sees: one per face when the block folds the repetition of the face rows
+    # into per-face mean weights (face_mean_rows), every sample when the block runs as written
+    Ns = d.get("f2f_samples", NiK)
     m = {
         "v2f_fwd": dict(bytes=4 * Ci * Nv + 12 * Nf + 4 * Ci * Nf),
         "v2f_bwd": dict(bytes=4 * Ci * Nf + 8 * Ci * Nv + 12 * Nf + 4 * Nv),
@@ -239,12 +242,13 @@ def kernel_models(d):
         "f2f_gA_sgemm": dict(bytes=4 * Q * Nf + 4 * Co * Nf, flops=2 * Q * Co * Nf),
         "f2f_gin_from_gA": dict(bytes=4 * Q * Nf + 4 * K * NiK + 4 * Ci * NiK),
         # fused tensor-core path of facet2facet
-        "f2f_fwd_tc": dict(bytes=4 * Ci * NiK + 4 * K * NiK + 4 * Nf + 4 * Co * Nf,
-                           flops=2 * Q * NiK + 2 * Q * Co * Nf),
-        "f2f_bwd_gin_tc": dict(bytes=4 * Co * Nf + 4 * K * NiK + 4 * Nf + 4 * Ci * NiK,
-                               flops=2 * Q * NiK + 2 * Q * Co * Nf),
-        "f2f_bwd_gfilter_tc": dict(bytes=4 * Ci * NiK + 4 * K * NiK + 4 * Nf + 4 * Co * Nf,
-                                   flops=2 * Q * NiK + 2 * Q * Co * Nf),
+        "f2f_fwd_tc": dict(bytes=4 * Ci * Ns + 4 * K * Ns + 4 * Nf + 4 * Co * Nf,
+                           flops=2 * Q * Ns + 2 * Q * Co * Nf),
+        "f2f_bwd_gin_tc": dict(bytes=4 * Co * Nf + 4 * K * Ns + 4 * Nf + 4 * Ci * Ns,
+                               flops=2 * Q * Ns + 2 * Q * Co * Nf),
+        "f2f_bwd_gfilter_tc": dict(bytes=4 * Ci * Ns + 4 * K * Ns + 4 * Nf + 4 * Co * Nf,
+                                   flops=2 * Q * Ns + 2 * Q * Co * Nf),
+        "face_mean_rows": dict(bytes=4 * K * NiK + 4 * Nf + 4 * K * Nf),
     }
     return m
 
@@ -313,7 +317,7 @@ def roofline_from_profile(records, steps, dims):
 def run_ours(args):
     import torch.distributed as dist
     from picassoplus_b200 import _lib
-    from picassoplus_b200.block import conv_block
+    from picassoplus_b200.block import conv_block, conv_block_expanded
     from picassoplus_b200.math_utils import sph_harm_coeff
     from picassoplus_b200.mesh import utils as mesh_utils
     from picassoplus_b200.mesh.pi_modules import conv3d
@@ -357,11 +361,13 @@ def run_ours(args):
     nfc, coeff, bary_sh = prepare()
     xd = d["x"].requires_grad_()
 
+    block_fn = [conv_block]            # the variants swap in the block as written
+
     def step_resident():
         for p in params:
             p.grad = None
         xd.grad = None
-        o = conv_block(xd, params[0], params[1], params[2], d["face"], d["cum"], bary_sh, coeff, nfc, vt_map, sh_eye)
+        o = block_fn[0](xd, params[0], params[1], params[2], d["face"], d["cum"], bary_sh, coeff, nfc, vt_map, sh_eye)
         o.backward(G)
         allreduce()
 
@@ -466,7 +472,8 @@ def run_ours(args):
     _lib.prof_enable(False)
     records = _lib.prof_read(64)
     _lib.prof_reset()
-    dims = dict(Nv=h["Nv"], Nf=h["Nf"], NiK=h["NiK"], cin=cfg["cin"], cout=cfg["cout"], K=K, config=args.config)
+    dims = dict(Nv=h["Nv"], Nf=h["Nf"], NiK=h["NiK"], f2f_samples=h["Nf"], cin=cfg["cin"], cout=cfg["cout"], K=K,
+                config=args.config)
     roof, table = roofline_from_profile(records, prof_steps, dims)
 
     # per-batch preparation, reported apart (amortised over the convolutions of a level): nfCount,
@@ -477,13 +484,14 @@ def run_ours(args):
         torch.cuda.synchronize()
         p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         p0.record()
-        prepare()
+        _, _, bsh = prepare()
         topology.vertex_csr(d["face"], vt_map, h["Nv"], h["Nv"])
+        topology.face_means(bsh, d["cum"])
         p1.record()
         torch.cuda.synchronize()
         prep_ms.append(p0.elapsed_time(p1))
     prep = dict(ms=sorted(prep_ms)[1], includes="count_vertex_adjface, triangle geometry, SH_L(normals), "
-                "SH_L(texture barycentrics), vertex CSR build + index validation; not part of `value` "
+                "SH_L(texture barycentrics) and its per-face means, vertex CSR build + index validation; not part of `value` "
                 "(cached per topology), part of `e2e`")
 
     # the single-MMA operand variants of the facet2facet contraction, same step, same inputs
@@ -501,6 +509,15 @@ def run_ours(args):
             variants[vname] = dict(value=faces_total / (vms / vsteps / 1e3), unit=UNIT, ms_per_step=vms / vsteps,
                                    note=notes[vname])
         conv3d.set_f2f_precision(args.precision)
+        block_fn[0] = conv_block_expanded
+        for _ in range(2):
+            step_resident()
+        vms, _ = timed(step_resident, vsteps)
+        block_fn[0] = conv_block
+        variants["block_as_written"] = dict(
+            value=faces_total / (vms / vsteps / 1e3), unit=UNIT, ms_per_step=vms / vsteps,
+            note="the face rows written once per sample (expand_rows) and the general facet2facet over every sample, "
+                 "instead of per-face mean weights and one sample per face; same result")
 
     # accuracy of the timed precision mode on this batch's first mesh (outside every timed region):
     # the whole block in the timed mode against the library's fp32 FFMA path on identical inputs
@@ -511,19 +528,21 @@ def run_ours(args):
         sl = dict(x=d["x"][:nv0].detach(), face=d["face"][:mf0], cum=d["cum"][:mf0], bary=bary_sh[:nik0],
                   coeff=coeff[:mf0], nfc=nfc[:nv0], vt=vt_map[:nv0], G=G[:nv0])
 
-        def one_mesh(mode):
+        def one_mesh(mode, block):
             conv3d.set_f2f_precision(mode)
             x0 = sl["x"].clone().requires_grad_()
             ws = [p.detach().clone().requires_grad_() for p in params]
-            o = conv_block(x0, ws[0], ws[1], ws[2], sl["face"], sl["cum"], sl["bary"], sl["coeff"], sl["nfc"], sl["vt"],
-                           sh_eye)
+            o = block(x0, ws[0], ws[1], ws[2], sl["face"], sl["cum"], sl["bary"], sl["coeff"], sl["nfc"], sl["vt"],
+                      sh_eye)
             o.backward(sl["G"])
             return [o.detach(), x0.grad] + [w.grad for w in ws]
 
-        got, want = one_mesh(args.precision), one_mesh("fp32_ffma")
+        got, want = one_mesh(args.precision, conv_block), one_mesh("fp32_ffma", conv_block_expanded)
         conv3d.set_f2f_precision(args.precision)
         names = ["out", "grad_x", "grad_Wv", "grad_Wf", "grad_Wo"]
-        parity = {"mode": args.precision, "against": "fp32_ffma path of the same library, same inputs",
+        parity = {"mode": args.precision,
+                  "against": "the block as written (face rows expanded per sample, general facet2facet) on the fp32_ffma "
+                             "path of the same library, same inputs",
                   "sample": f"first mesh of the batch ({mf0} faces)", "gate_max_rel": GATES[args.precision]}
         for n, a, b in zip(names, got, want):
             diff = (a.double() - b.double())
@@ -532,15 +551,15 @@ def run_ours(args):
         # the filter gradients sum over every face of the batch: check them on the rank's whole batch too
         # (a sum that long is where an accumulator that truncates would show)
 
-        def whole_batch(mode):
+        def whole_batch(mode, block):
             conv3d.set_f2f_precision(mode)
             ws = [p.detach().clone().requires_grad_() for p in params]
             x0 = d["x"].detach().clone().requires_grad_()
-            o = conv_block(x0, ws[0], ws[1], ws[2], d["face"], d["cum"], bary_sh, coeff, nfc, vt_map, sh_eye)
+            o = block(x0, ws[0], ws[1], ws[2], d["face"], d["cum"], bary_sh, coeff, nfc, vt_map, sh_eye)
             o.backward(G)
             return [w.grad for w in ws]
 
-        got_b, want_b = whole_batch(args.precision), whole_batch("fp32_ffma")
+        got_b, want_b = whole_batch(args.precision, conv_block), whole_batch("fp32_ffma", conv_block_expanded)
         conv3d.set_f2f_precision(args.precision)
         parity["whole_batch"] = {"sample": f"the rank's whole batch ({h['Nf']} faces)"}
         for n, a, b in zip(names[2:], got_b, want_b):
@@ -611,6 +630,9 @@ def run_ours(args):
             "workload_detail": {"faces": int(faces_total), "vertices": int(nf_all[1].item()),
                                 "texture_samples": int(nf_all[2].item()), "f2f_precision": args.precision,
                                 "parallelism": f"mesh-dp{world}", "meshes_per_gpu": count,
+                                "block": "V2F -> F2F -> F2V with the repetition of the face rows folded into facet2facet "
+                                         "(per-face mean sample weights, one sample per face); variants.block_as_written "
+                                         "times the row expansion + general facet2facet",
                                 "l2_policy": "inputs larger than L2 (no flush)" if h["Nf"] * cfg["cin"] * 4 > 256e6
                                 else "inputs smaller than L2, no flush"},
             "parity": parity, "grad_checksum": checksum,

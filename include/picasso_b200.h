@@ -411,6 +411,16 @@ int pb200_expand_rows_forward(int64_t Nf, int64_t NiK, int C, const float* in, c
 int pb200_expand_rows_backward(int64_t Nf, int64_t NiK, int C, const float* gradOut, const int32_t* numInterior,
                                float* gradIn, void* stream);
 
+/* out[f,:] = mean over the samples k of face f of rows[k,:], added in ascending order; 0 for a face without
+ * samples.  With one input row per face shared by all its samples (the block's repeat_interleave followed by
+ * facet2facet), the face operand of facet2facet factorises:
+ *   (1/T_f) sum_k bary[k,d] * in[f,ci] = mean_k(bary[k,d]) * in[f,ci],
+ * so facet2facet over (in (Nf,Cin), mean rows (Nf,F), numInterior = 1, 2, ..., Nf) gives the same output and the
+ * same gradients as the expanded call (the input gradient already summed per face), without the expanded rows.
+ * No counterpart inside the reference's extension. */
+int pb200_face_mean_rows(int64_t Nf, int64_t NiK, int C, const float* rows, const int32_t* numInterior, float* out,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

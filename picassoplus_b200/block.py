@@ -5,6 +5,12 @@ The reference has no such composite module; the block is defined as
     tex = y[f] repeated once per texture sample of face f
     z   = facet2facet(tex, Wf (Cout,Cin,K), SH(barycentrics), running sample count)
     o   = facet2vertex(z, Wo (K,Cout,1), SH(face normals), face, nfCount, vtMap)
+
+conv_block_expanded runs it as written (row expansion, then the general facet2facet).  conv_block folds the
+repetition into the operator: all samples of a face carry the same row, so the face operand of facet2facet,
+(1/T_f) sum_k bary[k,d] tex[k,ci], is mean_k(bary[k,d]) * y[f,ci]; facet2facet over (y, per-face mean rows, one sample
+per face) gives the same z and the same gradients for y and Wf, without writing or reading the expanded rows and
+with one product per operand element instead of one multiply-add per sample.
 """
 from __future__ import annotations
 
@@ -12,7 +18,7 @@ import torch
 
 from . import _lib
 from .mesh.pi_modules import conv3d
-from .topology import ptr, stream_ptr
+from .topology import face_means, ptr, stream_ptr
 
 
 class _ExpandRows(torch.autograd.Function):
@@ -47,10 +53,24 @@ def expand_rows(inp, cum, n_samples):
     return _ExpandRows.apply(inp, cum, n_samples)
 
 
-def conv_block(x, Wv, Wf, Wo, face, cum, bary_sh, coeff, nf_count, vt_map, sh_eye):
+def conv_block_expanded(x, Wv, Wf, Wo, face, cum, bary_sh, coeff, nf_count, vt_map, sh_eye):
     cin = x.shape[1]
     spatial = (sh_eye @ Wv).reshape(3, cin, 1)
     y = conv3d.vertex2facet(x, spatial, face)
     tex = expand_rows(y, cum, bary_sh.shape[0])
     z = conv3d.facet2facet(tex, Wf, bary_sh, cum)
+    return conv3d.facet2vertex(z, Wo, coeff, face, nf_count, vt_map)
+
+
+def facet2facet_shared_rows(face_rows, filter, bary_sh, cum):
+    """facet2facet(repeat_interleave(face_rows, samples per face), filter, bary_sh, cum) without the expanded rows."""
+    fm = face_means(bary_sh, cum)
+    return conv3d.facet2facet(face_rows, filter, fm.rows, fm.one_each)
+
+
+def conv_block(x, Wv, Wf, Wo, face, cum, bary_sh, coeff, nf_count, vt_map, sh_eye):
+    cin = x.shape[1]
+    spatial = (sh_eye @ Wv).reshape(3, cin, 1)
+    y = conv3d.vertex2facet(x, spatial, face)
+    z = facet2facet_shared_rows(y, Wf, bary_sh, cum)
     return conv3d.facet2vertex(z, Wo, coeff, face, nf_count, vt_map)

@@ -295,6 +295,32 @@ __global__ void copy_counts_kernel(int64_t n, const int32_t* __restrict__ src, i
 }
 
 // ------------------------------------------------------------------------ row expansion
+// out[f] = mean of the rows of face f's samples, added in ascending order (0 for a face without samples)
+template <int VEC>
+__global__ void face_mean_rows_kernel(int64_t Nf, int64_t NiK, int CVn, const float* __restrict__ rows,
+                                      const int32_t* __restrict__ cum, float* __restrict__ out) {
+    int64_t total = Nf * CVn;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t f = i / CVn;
+        int c = (int)(i - f * CVn);
+        int k0 = f > 0 ? __ldg(cum + f - 1) : 0, k1 = __ldg(cum + f);
+        if (k0 < 0) k0 = 0;
+        if (k1 > NiK) k1 = (int)NiK;
+        const float inv = k1 > k0 ? 1.f / (float)(k1 - k0) : 0.f;
+        if (VEC == 4) {
+            float4 acc = zero4();
+            for (int k = k0; k < k1; ++k) add4(acc, __ldg(reinterpret_cast<const float4*>(rows) + (int64_t)k * CVn + c));
+            reinterpret_cast<float4*>(out)[i] = scale4(acc, inv);
+        } else {
+            float acc = 0.f;
+            for (int k = k0; k < k1; ++k) acc += __ldg(rows + (int64_t)k * CVn + c);
+            out[i] = acc * inv;
+        }
+    }
+}
+
+
 // The samples of face f are rows cum[f-1] .. cum[f]-1 (cum = inclusive running count).
 // forward: one item per (face, channel group); the face's row is read once and written to
 // each of its samples (rows k0..k1-1, contiguous in the output)
@@ -573,6 +599,19 @@ int pb200_check_num_interior(int64_t Nf, int64_t NiK, const int32_t* numInterior
     if (Nf == 0) return PB200_OK;
     PB_LAUNCH("check_running_count", check_running_count_kernel, persistent_blocks(Nf, 256, 8), 256, 0, stream,
               Nf, NiK, numInterior, status);
+    return PB200_OK;
+}
+
+int pb200_face_mean_rows(int64_t Nf, int64_t NiK, int C, const float* rows, const int32_t* cum, float* out, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(Nf >= 0 && NiK >= 0 && C > 0, PB200_EINVAL, "face_mean_rows: bad sizes");
+    if (Nf == 0) return PB200_OK;
+    PB_REQUIRE(cum && out && (NiK == 0 || rows), PB200_EINVAL, "face_mean_rows: null pointer");
+    bool vec = (C % 4 == 0) && aligned16(rows) && aligned16(out);
+    int CVn = vec ? C / 4 : C;
+    int grid = persistent_blocks(Nf * CVn, 256, 16);
+    if (vec) PB_LAUNCH("face_mean_rows", face_mean_rows_kernel<4>, grid, 256, 0, stream, Nf, NiK, CVn, rows, cum, out);
+    else     PB_LAUNCH("face_mean_rows", face_mean_rows_kernel<1>, grid, 256, 0, stream, Nf, NiK, CVn, rows, cum, out);
     return PB200_OK;
 }
 

@@ -24,6 +24,7 @@
 // All waits are bounded (tc_ptx.cuh); on a time-out the block unwinds, frees its TMEM and
 // raises the library's asynchronous error word.
 #include "common.cuh"
+#include <type_traits>
 #include "tc_ptx.cuh"
 #include "tc_runtime.cuh"
 
@@ -255,19 +256,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
             __syncwarp();
             const float invT = T > 0 ? 1.f / (float)T : 0.f;
             const int kloc = valid ? k0 - kw0 : 0;            // row of the face's first sample in wb
-            if (!slow) {
+            // the lean path for TR sample slots per face (TR = 1 when no face of the warp has a second sample:
+            // one product per operand element instead of TREG multiply-adds)
+            auto lean = [&](auto trc) {
+                constexpr int TR = decltype(trc)::value;
                 // rows of the face's samples; unused slots point at a valid row and meet x == 0
-                uint32_t bp[TREG];
+                uint32_t bp[TR];
 #pragma unroll
-                for (int t = 0; t < TREG; ++t) {
+                for (int t = 0; t < TR; ++t) {
                     int row = kloc + (t < T ? t : (T > 0 ? T - 1 : 0));
                     if (row >= p.smaxw) row = 0;
                     bp[t] = wb32 + (uint32_t)(row * FP) * 4u;
                 }
                 for (int c16 = 0; c16 < Cin / KS && alive; ++c16) {
-                    float4 x[TREG][2];
+                    float4 x[TR][2];
 #pragma unroll
-                    for (int t = 0; t < TREG; ++t) {
+                    for (int t = 0; t < TR; ++t) {
                         if (t < T) {
                             const float4* src =
                                 reinterpret_cast<const float4*>(p.in + (int64_t)(k0 + t) * Cin + c16 * KS + h * 8);
@@ -278,22 +282,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                         }
                     }
                     for (int d4 = 0; d4 < F && alive; d4 += 4) {
-                        float4 b[TREG];
+                        float4 b[TR];
 #pragma unroll
-                        for (int t = 0; t < TREG; ++t) b[t] = lds_f4(bp[t] + (uint32_t)d4 * 4u);
+                        for (int t = 0; t < TR; ++t) b[t] = lds_f4(bp[t] + (uint32_t)d4 * 4u);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             if (d4 + j < F) {
                                 // packed f32x2 FMAs: half the instructions of the scalar form
                                 float2 s0 = make_float2(0.f, 0.f), s1 = s0, s2 = s0, s3 = s0;
 #pragma unroll
-                                for (int t = 0; t < TREG; ++t) {
+                                for (int t = 0; t < TR; ++t) {
                                     const float bj = j == 0 ? b[t].x : (j == 1 ? b[t].y : (j == 2 ? b[t].z : b[t].w));
                                     const float2 b2 = make_float2(bj, bj);
-                                    s0 = __ffma2_rn(b2, make_float2(x[t][0].x, x[t][0].y), s0);
-                                    s1 = __ffma2_rn(b2, make_float2(x[t][0].z, x[t][0].w), s1);
-                                    s2 = __ffma2_rn(b2, make_float2(x[t][1].x, x[t][1].y), s2);
-                                    s3 = __ffma2_rn(b2, make_float2(x[t][1].z, x[t][1].w), s3);
+                                    if (TR == 1) {
+                                        s0 = __fmul2_rn(b2, make_float2(x[t][0].x, x[t][0].y));
+                                        s1 = __fmul2_rn(b2, make_float2(x[t][0].z, x[t][0].w));
+                                        s2 = __fmul2_rn(b2, make_float2(x[t][1].x, x[t][1].y));
+                                        s3 = __fmul2_rn(b2, make_float2(x[t][1].z, x[t][1].w));
+                                    } else {
+                                        s0 = __ffma2_rn(b2, make_float2(x[t][0].x, x[t][0].y), s0);
+                                        s1 = __ffma2_rn(b2, make_float2(x[t][0].z, x[t][0].w), s1);
+                                        s2 = __ffma2_rn(b2, make_float2(x[t][1].x, x[t][1].y), s2);
+                                        s3 = __ffma2_rn(b2, make_float2(x[t][1].z, x[t][1].w), s3);
+                                    }
                                 }
                                 const float4 a0 = make_float4(s0.x, s0.y, s1.x, s1.y), a1 = make_float4(s2.x, s2.y, s3.x, s3.y);
                                 if (!publish(a0, a1, d4 + j)) { alive = false; break; }
@@ -301,6 +312,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_fwd_tc_kernel(FwdParams p) {
                         }
                     }
                 }
+            };
+            if (!slow) {
+                if (__any_sync(0xffffffffu, T > 1)) lean(std::integral_constant<int, TREG>{});
+                else lean(std::integral_constant<int, 1>{});
             } else {
                 for (int c16 = 0; c16 < Cin / KS && alive; ++c16) {
                     for (int d = 0; d < F; ++d) {

@@ -30,6 +30,7 @@
 // partial[chunk] (final gradFilter layout); a second kernel adds the chunks in order, so the result
 // is deterministic.
 // Modes: 1 split (bf16 or tf32 operands) or 2 splits (bf16 or tf32 hi+lo, three MMAs per k-step).
+#include <type_traits>
 #include "common.cuh"
 #include "tc_ptx.cuh"
 #include "tc_runtime.cuh"
@@ -292,7 +293,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             const int slow = __any_sync(0xffffffffu, (T > TREG) || (kloc + T > ns)) ? 1 : 0;
             if (warp == REC_WARP) {
                 if (lane < KF) sts_i4(rb32 + RAW_REC_OFF + lane * 16, kloc, T, __float_as_int(T > 0 ? 1.f / (float)T : 0.f), cv);
-                if (lane == KF) sts_i4(rb32 + RAW_REC_OFF + KF * 16, slow, 0, ks0, ns);
+                const int one = __any_sync(0xffffffffu, T > 1) ? 0 : 1;          // no face of the stage has a second sample
+                if (lane == KF) sts_i4(rb32 + RAW_REC_OFF + KF * 16, slow, one, ks0, ns);
                 __syncwarp();
                 if (lane == 0) {
                     // the stage's bary rows: one bulk copy (rows are 16-byte multiples)
@@ -381,19 +383,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
             const float invT = __int_as_float(rec.z);
             if (!warp_wait(&empty[si], sph ^ 1u, abort_flag, lane)) { alive = false; break; }
             const uint32_t sb32 = stages32 + (uint32_t)si * (uint32_t)stage_bytes;
-            if (has_unit && !slow) {
-                // fast path: every face of the stage has at most TREG samples, all of them staged.
-                // (Rows behind a face's last sample belong to other faces or are stale: their weight
-                // is zero, so they only matter if the input holds non-finite values.)
-                float2 x[TREG][4];
-                float4 b[TREG];
+            // fast path: every face of the stage has at most TR samples (TR = 1: one product per operand element
+            // instead of TREG multiply-adds), all of them staged.
+            // (Rows behind a face's last sample belong to other faces or are stale: their weight
+            // is zero, so they only matter if the input holds non-finite values.)
+            auto fast = [&](auto trc) {
+                constexpr int TR = decltype(trc)::value;
+                float2 x[TR][4];
+                float4 b[TR];
                 {
                     const uint32_t xa = rb32 + RAW_X_OFF + (uint32_t)fl * (TREG * RAW_X_SLOT);
                     const uint32_t qu = 2u * (uint32_t)half + (sw >> 4);            // 16-byte quarter held first
                     const uint32_t xu = xa + ((qu ^ (uint32_t)(fl & 7)) << 4), xw = xa + (((qu ^ 1u) ^ (uint32_t)(fl & 7)) << 4);
                     const uint32_t ba = rb32 + RAW_B_OFF + (uint32_t)(kloc * p.Fp + 4 * warp) * 4u;
 #pragma unroll
-                    for (int t = 0; t < TREG; ++t) {
+                    for (int t = 0; t < TR; ++t) {
                         const float4 u = lds_f4(xu + t * RAW_X_SLOT), w = lds_f4(xw + t * RAW_X_SLOT);
                         b[t] = lds_f4(ba + (uint32_t)(t * p.Fp) * 4u);
                         const float wt = t < T ? invT : 0.f;
@@ -408,15 +412,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gfilter_tc_kernel(Params 
 #pragma unroll
                         for (int j = 0; j < 4; ++j) a[j] = make_float2(0.f, 0.f);
 #pragma unroll
-                        for (int t = 0; t < TREG; ++t) {
+                        for (int t = 0; t < TR; ++t) {
                             const float bv = dd == 0 ? b[t].x : dd == 1 ? b[t].y : dd == 2 ? b[t].z : b[t].w;
                             const float2 b2 = make_float2(bv, bv);
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) a[j] = __ffma2_rn(b2, x[t][j], a[j]);
+                            for (int j = 0; j < 4; ++j) a[j] = TR == 1 ? __fmul2_rn(b2, x[t][j]) : __ffma2_rn(b2, x[t][j], a[j]);
                         }
                         put_a(sb32, dd, make_float4(a[0].x, a[0].y, a[1].x, a[1].y), make_float4(a[2].x, a[2].y, a[3].x, a[3].y));
                     }
                 }
+            };
+            if (has_unit && !slow) {
+                if (lds_i32(rb32 + RAW_REC_OFF + KF * 16 + 4)) fast(std::integral_constant<int, 1>{});
+                else fast(std::integral_constant<int, TREG>{});
             } else if (has_unit) {
                 // generic path, straight from global memory (halves swapped where sw is set)
                 const int k0 = rec.w, jsw = (int)(sw >> 2);

@@ -320,6 +320,40 @@ def pair_csr(nn_index: torch.Tensor, column: int, n_rows: int) -> PairCSR:
     return csr
 
 
+class FaceMeans:
+    """Per-face mean of the sample rows of a batch (Nf, F) and the running count 1, 2, ..., Nf that says
+    'one sample per face'."""
+
+    def __init__(self, rows, one_each, keep, versions):
+        self.rows = rows
+        self.one_each = one_each
+        self._keep = keep
+        self._versions = versions
+        self.nbytes = 4 * (rows.numel() + one_each.numel())
+
+
+def face_means(sample_rows: torch.Tensor, num_interior: torch.Tensor) -> FaceMeans:
+    """Cached mean over every face's samples of sample_rows (NiK, F) (num_interior = inclusive running sample
+    count, as facet2facet takes it); same cache and budget as vertex_csr.  Forward and backward of a step share it."""
+    nf, nik = num_interior.shape[0], sample_rows.shape[0]
+    slot = ("face_means", sample_rows.device.index, sample_rows.data_ptr(), num_interior.data_ptr(), nik, nf,
+            sample_rows.shape[1])
+    versions = (sample_rows._version, num_interior._version)
+    hit = _lookup(slot, versions)
+    if hit is not None:
+        return hit
+    dev = sample_rows.device
+    with torch.cuda.device(dev):
+        check_num_interior(num_interior, nik)
+        rows = torch.empty(nf, sample_rows.shape[1], dtype=torch.float32, device=dev)
+        _lib.call("pb200_face_mean_rows", nf, nik, sample_rows.shape[1], ptr(sample_rows), ptr(num_interior), ptr(rows),
+                  stream_ptr(dev))
+        one_each = torch.arange(1, nf + 1, dtype=torch.int32, device=dev)
+    fm = FaceMeans(rows, one_each, (sample_rows, num_interior), versions)
+    _store(slot, fm)
+    return fm
+
+
 def check_num_interior(num_interior: torch.Tensor, nik: int) -> None:
     """Validates a running sample count (non-decreasing, inside [0, nik], ends at nik) on the
     device: raises in 'sync' mode, queues the status word in 'deferred' mode.  The facet2facet

@@ -224,6 +224,65 @@ def test_baseline_config_c1_block_exact(mods):
             assert rel_err(b, t) <= TOL, ("reference vs fp64", n, rel_err(b, t))
 
 
+@pytest.mark.parametrize("precision", ["fp32", "bf16", "fp32_ffma"])
+def test_block_with_folded_repetition_equals_the_expanded_block(mods, precision):
+    """conv_block folds 'repeat the face row once per sample' into facet2facet (per-face mean of the sample
+    weights, one sample per face); conv_block_expanded runs the block as written.  Same output and gradients
+    within the mode's gate; a face without samples gives 0 in both; two runs give identical bits."""
+    conv3d, _, mo, _ = mods
+    from picassoplus_b200 import synth, topology
+    from picassoplus_b200.block import conv_block, conv_block_expanded
+    L, cin, cout = 4, 32, 48
+    K = (L + 1) ** 2
+    mb = synth.concat_meshes([synth.heightfield(40, 7), synth.icosphere(3), synth.heightfield(33, 9)])
+    nf, nv = mb.face.shape[0], mb.vertex.shape[0]
+    counts_np, _ = synth.texture_samples(nf, seed=55)
+    counts_np[5::29] = 6                                    # more samples than the kernels keep in registers
+    counts_np[::17] = 0                                     # faces without a sample
+    rng = np.random.default_rng(56)
+    nik = int(counts_np.sum())
+    bary = rng.dirichlet((1.0, 1.0, 1.0), size=nik).astype(np.float32)
+    g = torch.Generator().manual_seed(57)
+    dev = "cuda"
+    x = torch.randn(nv, cin, generator=g).to(dev)
+    Wv = torch.from_numpy(synth.xavier_normal((K, cin), rng)).to(dev)
+    Wf = torch.from_numpy(synth.xavier_normal((cout, cin, K), rng)).to(dev)
+    Wo = torch.from_numpy(synth.xavier_normal((K, cout, 1), rng)).to(dev)
+    G = torch.randn(nv, cout, generator=g).to(dev)
+    vertex, face = torch.from_numpy(mb.vertex), torch.from_numpy(mb.face)
+    cum = torch.cumsum(torch.from_numpy(counts_np), 0, dtype=torch.int32).to(dev)
+    vt_map = torch.arange(nv, dtype=torch.int32)
+    nfc = mo.count_vertex_adjface(face, vt_map, nv).to(dev)
+    coeff = mo.sph_harm_coeff(L, mo.triangle_geometry(vertex, face)[:, :3]).to(dev)
+    bary_sh = mo.sph_harm_coeff(L, torch.from_numpy(bary)).to(dev)
+    sh_eye = mo.sph_harm_coeff(L, torch.eye(3)).to(dev)
+    face, vt_map = face.to(dev), vt_map.to(dev)
+
+    fm = topology.face_means(bary_sh, cum)
+    seg = torch.repeat_interleave(torch.arange(nf, device=dev), torch.from_numpy(counts_np).to(dev).long())
+    want = torch.zeros(nf, K, dtype=torch.float64, device=dev).index_add_(0, seg, bary_sh.double())
+    want = want / torch.from_numpy(counts_np).to(dev).clamp(min=1)[:, None]
+    assert rel_err(fm.rows, want) <= 1e-6 and torch.all(fm.rows[::17] == 0)
+    assert torch.equal(fm.one_each.cpu(), torch.arange(1, nf + 1, dtype=torch.int32))
+
+    def run(block):
+        xd = x.clone().requires_grad_()
+        wd = [w.clone().requires_grad_() for w in (Wv, Wf, Wo)]
+        o = block(xd, wd[0], wd[1], wd[2], face, cum, bary_sh, coeff, nfc, vt_map, sh_eye)
+        o.backward(G)
+        return [o.detach(), xd.grad] + [w.grad for w in wd]
+
+    conv3d.set_f2f_precision(precision)
+    try:
+        folded, expanded, again = run(conv_block), run(conv_block_expanded), run(conv_block)
+    finally:
+        conv3d.set_f2f_precision("fp32")
+    gate = {"fp32": TOL, "fp32_ffma": 2e-5, "bf16": 2e-2}[precision]
+    for n, a, b, c in zip(["out", "grad_x", "grad_Wv", "grad_Wf", "grad_Wo"], folded, expanded, again):
+        assert rel_err(a, b) <= gate, (n, rel_err(a, b))
+        assert torch.equal(a, c), n
+
+
 def test_one_benchmark_mesh_against_fp64(mods):
     """One 360 x 360 heightfield mesh of the headline configuration (128 -> 128 channels, L = 4,
     ~232 k faces): facet2facet forward and backward in every tensor-core mode against the fp64
