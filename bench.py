@@ -249,6 +249,8 @@ def kernel_models(d):
         "f2f_bwd_gfilter_tc": dict(bytes=4 * Ci * Ns + 4 * K * Ns + 4 * Nf + 4 * Co * Nf,
                                    flops=2 * Q * Ns + 2 * Q * Co * Nf),
         "face_mean_rows": dict(bytes=4 * K * NiK + 4 * Nf + 4 * K * Nf),
+        # forward for one sample per face: a plain product over the input rows, the sum over the bases in the epilogue
+        "f2f_fwd_one_sample_tc": dict(bytes=4 * Ci * Nf + 4 * K * Nf + 4 * Co * Nf, flops=2 * Q * Co * Nf + 2 * K * Co * Nf),
     }
     return m
 
@@ -257,9 +259,12 @@ def kernel_models(d):
 # capture on a 2-mesh case of the same shapes, divided by its face count; traffic grows in
 # proportion to the faces).  Source: the summaries under profiles/.
 MEASURED_DRAM_BYTES_PER_FACE = {
+    # the block with the repetition of the face rows folded in (one sample per face reaches facet2facet)
+    ("c5", "f2f_fwd_one_sample_tc"): 1041.0,
+    ("c5", "f2f_bwd_gin_tc"): 1043.0,
+    ("c5", "f2f_bwd_gfilter_tc"): 1858.0,
+    # the general forward kernel over every sample (variants.block_as_written)
     ("c5", "f2f_fwd_tc"): 2001.0,
-    ("c5", "f2f_bwd_gin_tc"): 1998.0,
-    ("c5", "f2f_bwd_gfilter_tc"): 2150.0,
 }
 
 

@@ -243,6 +243,19 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
                               float* output, int precision,
                               void* workspace, size_t workspace_bytes, void* stream);
 
+/* facet2facet forward for faces that have exactly one sample each (numInterior = 1, 2, ..., Nf is implied):
+ *   output[f,co] = sum_d weights[f,d] * sum_ci input[f,ci]*filter[co,ci,d],
+ * input (Nf,Cin), weights (Nf,F), filter (Cout,Cin,F), output (Nf,Cout).  Same result as pb200_facet2facet_forward
+ * with that numInterior; on the tensor cores it runs as a plain product over the input rows with the weighted sum
+ * over d in the epilogue (the input-gradient kernel with the channel roles exchanged), which needs no face operand
+ * of F*Cin products.  With pb200_face_mean_rows this is the forward pass of "one row per face shared by its
+ * samples"; the matching backward is pb200_facet2facet_backward over (input, weights, numInterior = 1..Nf).
+ * No counterpart inside the reference's extension. */
+size_t pb200_facet2facet_one_sample_forward_workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision);
+int pb200_facet2facet_one_sample_forward(int64_t Nf, int Cin, int Cout, int F, const float* input, const float* filter,
+                                         const float* weights, float* output, int precision, void* workspace,
+                                         size_t workspace_bytes, void* stream);
+
 /* gradInput[k,ci] = (1/T_f) sum_d bary[k,d] * sum_co gradOutput[f,co]*filter[co,ci,d];
  * gradFilter[co,ci,d] = sum_f gradOutput[f,co]*A[f,d,ci]
  * Replaces facet2facetConv3dGradLauncher (mesh_conv3d_gpu.cu:45-135,144-168; binding

@@ -64,6 +64,8 @@ SIGNATURES = {
                                                    vp, sz, vp]),
     "pb200_facet2facet_forward_workspace_bytes": (sz, [i64, i64, i32, i32, i32, i32]),
     "pb200_facet2facet_forward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
+    "pb200_facet2facet_one_sample_forward_workspace_bytes": (sz, [i64, i32, i32, i32, i32]),
+    "pb200_facet2facet_one_sample_forward": (i32, [i64, i32, i32, i32, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_facet2facet_backward_workspace_bytes": (sz, [i64, i64, i32, i32, i32, i32]),
     "pb200_facet2facet_backward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_level_prepare": (i32, [i64, i64, i64, i32, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),

@@ -62,10 +62,52 @@ def conv_block_expanded(x, Wv, Wf, Wo, face, cum, bary_sh, coeff, nf_count, vt_m
     return conv3d.facet2vertex(z, Wo, coeff, face, nf_count, vt_map)
 
 
+def one_sample_forward(face_rows, filter, weights):
+    """facet2facet forward for exactly one sample per face: (Nf, Cin) rows, (Cout, Cin, F) filter, (Nf, F) weights."""
+    conv3d._check(face_rows, "input", 2, torch.float32)
+    conv3d._check(filter, "filter", 3, torch.float32)
+    conv3d._check(weights, "weights", 2, torch.float32)
+    Nf, Cin = face_rows.shape
+    Cout, _, F = filter.shape
+    if filter.shape[1] != Cin:
+        raise RuntimeError("input Channel size error of the filter.")
+    if F > 50:
+        raise RuntimeError("A maximum of 50 filters are supported in face2face convolution.")
+    if tuple(weights.shape) != (Nf, F):
+        raise RuntimeError("weights must have shape (NfIn, number of filters)")
+    face_rows, weights = conv3d._aligned16(face_rows), conv3d._aligned16(weights)
+    dev = face_rows.device
+    precision = conv3d._f2f_precision
+    with torch.cuda.device(dev):
+        out = torch.empty(Nf, Cout, dtype=face_rows.dtype, device=dev)
+        nb = _lib.query("pb200_facet2facet_one_sample_forward_workspace_bytes", Nf, Cin, Cout, F, precision)
+        ws = conv3d._ws(nb, dev)
+        _lib.call("pb200_facet2facet_one_sample_forward", Nf, Cin, Cout, F, ptr(face_rows), ptr(filter), ptr(weights),
+                  ptr(out), precision, ptr(ws), nb, stream_ptr(dev))
+    return out
+
+
+class _SharedRowsF2F(torch.autograd.Function):
+    """facet2facet over one row per face shared by the face's samples: forward through the one-sample entry,
+    backward through the general operator's backward over (rows, per-face mean weights, one sample per face)."""
+
+    @staticmethod
+    def forward(ctx, face_rows, filter, weights, one_each):
+        face_rows, filter = face_rows.contiguous(), filter.contiguous()
+        ctx.save_for_backward(face_rows, filter, weights, one_each)
+        return one_sample_forward(face_rows, filter, weights)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        face_rows, filter, weights, one_each = ctx.saved_tensors
+        gin, gf = conv3d.facet2facet_backward(grad_output.contiguous(), face_rows, filter, weights, one_each)
+        return gin, gf, None, None
+
+
 def facet2facet_shared_rows(face_rows, filter, bary_sh, cum):
     """facet2facet(repeat_interleave(face_rows, samples per face), filter, bary_sh, cum) without the expanded rows."""
     fm = face_means(bary_sh, cum)
-    return conv3d.facet2facet(face_rows, filter, fm.rows, fm.one_each)
+    return _SharedRowsF2F.apply(face_rows, filter, fm.rows, fm.one_each)
 
 
 def conv_block(x, Wv, Wf, Wo, face, cum, bary_sh, coeff, nf_count, vt_map, sh_eye):

@@ -22,7 +22,7 @@ bool fits(int Cin, int Cout, int F, int precision);
 size_t workspace_bytes(int Cin, int Cout, int F, int precision);
 int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* filter, const float* bary,
                    const float* bary_p, int Fp, const int32_t* cum, float* gin, int precision, void* ws,
-                   cudaStream_t stream);
+                   cudaStream_t stream, bool transposed);
 }  // namespace gin
 namespace gfilter {
 bool supported(int Cin, int Cout, int F);
@@ -88,6 +88,57 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
     return f2f_simt_forward(Nf, NiK, Cin, Cout, F, input, filter, bary, numInterior, output, workspace, stream);
 }
 
+// One sample per face: output[f,co] = sum_d weights[f,d] * (sum_ci input[f,ci] * filter[co,ci,d]).  The inner
+// sum is a plain GEMM over the input rows (no face operand of F * Cin products to build, split and store) and
+// the outer one an epilogue over the accumulator: the input-gradient kernel with the channel roles exchanged.
+static bool one_sample_on_gin(int Cin, int Cout, int F, int precision) { return use_tc_gin(Cout, Cin, F, precision); }
+
+size_t pb200_facet2facet_one_sample_forward_workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision) {
+    if (!f2f_sizes_ok(Nf, Nf, Cin, Cout, F)) return 0;
+    if (one_sample_on_gin(Cin, Cout, F, precision))
+        return tc::gin::workspace_bytes(Cout, Cin, F, precision) + tc::padded_bary_bytes(Nf, F);
+    return align_up(sizeof(int32_t) * (size_t)(Nf > 0 ? Nf : 1), 256) +
+           pb200_facet2facet_forward_workspace_bytes(Nf, Nf, Cin, Cout, F, precision);
+}
+
+__global__ void count_up_kernel(int64_t n, int32_t* out) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = (int32_t)(i + 1);
+}
+
+int pb200_facet2facet_one_sample_forward(int64_t Nf, int Cin, int Cout, int F, const float* input, const float* filter,
+                                         const float* weights, float* output, int precision, void* workspace,
+                                         size_t workspace_bytes, void* stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PB_REQUIRE(f2f_sizes_ok(Nf, Nf, Cin, Cout, F), PB200_EINVAL, "facet2facet_one_sample_forward: bad sizes (F must be in 1..50)");
+    PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_TF32X3, PB200_EINVAL,
+               "facet2facet_one_sample_forward: unknown precision %d", precision);
+    if (Nf == 0) return PB200_OK;
+    PB_REQUIRE(input && filter && weights && output, PB200_EINVAL, "facet2facet_one_sample_forward: null pointer");
+    PB_REQUIRE(workspace && workspace_bytes >= pb200_facet2facet_one_sample_forward_workspace_bytes(Nf, Cin, Cout, F, precision),
+               PB200_EWORKSPACE, "facet2facet_one_sample_forward: workspace too small");
+    char* w = (char*)workspace;
+    if (one_sample_on_gin(Cin, Cout, F, precision)) {
+        PB_REQUIRE(aligned16(input) && aligned16(weights) && aligned16(workspace), PB200_EINVAL,
+                   "facet2facet_one_sample_forward: input, weights and workspace must be 16-byte aligned");
+        const float* wp = weights;
+        const int Fp = tc::padded_F(F);
+        if (F % 4 != 0) {
+            float* dst = (float*)(w + tc::gin::workspace_bytes(Cout, Cin, F, precision));
+            int rc = tc::pad_bary(Nf, F, weights, dst, stream);
+            if (rc) return rc;
+            wp = dst;
+        }
+        return tc::gin::backward_input(Nf, Cout, Cin, F, input, filter, weights, wp, Fp, nullptr, output, precision, w,
+                                       stream, true);
+    }
+    int32_t* one_each = (int32_t*)w;
+    w += align_up(sizeof(int32_t) * (size_t)Nf, 256);
+    PB_LAUNCH("count_up", count_up_kernel, persistent_blocks(Nf, 256, 8), 256, 0, stream, Nf, one_each);
+    return pb200_facet2facet_forward(Nf, Nf, Cin, Cout, F, input, filter, weights, one_each, output, precision, w,
+                                     workspace_bytes - (size_t)(w - (char*)workspace), stream_);
+}
+
 size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, int precision) {
     if (!f2f_sizes_ok(Nf, NiK, Cin, Cout, F)) return 0;
     const bool tg = use_tc_gin(Cin, Cout, F, precision), tf = use_tc_gf(Nf, Cin, Cout, F, precision);
@@ -137,7 +188,7 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
     if (tg) {
         if (NiK > 0) {
             int rc = tc::gin::backward_input(Nf, Cin, Cout, F, gradOutput, filter, bary, bary_p, Fp, numInterior,
-                                             gradInput, precision, w, stream);
+                                             gradInput, precision, w, stream, false);
             if (rc) return rc;
         }
         w += tc::gin::workspace_bytes(Cin, Cout, F, precision);

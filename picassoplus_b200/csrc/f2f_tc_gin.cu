@@ -92,7 +92,10 @@ __device__ __forceinline__ void tmem_ld_row(uint32_t taddr, float* v) {
 // ---- filter image: Wimg[slice][kst][split][row 0..255][16 floats, 64B-swizzled];
 //      row = cil*F + d, element (row, kk) = filter[co = kst*16 + kk][ci = slice*NQ + cil][d]
 //      (co counts from the chunk's first output channel co0)
+//      The filter element (co, ci, d) is read at filter[co * s_co + ci * s_ci + d]: (Cin * F, F) for the operator's
+//      (Cout, Cin, F) filter, (F, Cin_of_the_filter * F) when the two channel roles are exchanged.
 __global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int co0, int Cout, int nq, int nslices, int kst, int nsplit,
+                                              int64_t s_co, int64_t s_ci,
                                               const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
     int64_t total = (int64_t)nslices * kst * NCOLS * 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -108,7 +111,7 @@ __global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int co0, int Cout,
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             int co = ks * KS + c * 4 + j;
-            float v = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)(co0 + co) * Cin + ci) * F + d) : 0.f;
+            float v = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + (int64_t)(co0 + co) * s_co + (int64_t)ci * s_ci + d) : 0.f;
             if (nsplit == 1) { hi[j] = to_tf32_rna(v); lo[j] = 0.f; }
             else { hi[j] = tf32_hi(v); lo[j] = v - hi[j]; }
         }
@@ -123,8 +126,8 @@ __global__ void f2f_tc_gin_prep_filter_kernel(int F, int Cin, int co0, int Cout,
 // ---- bf16 filter image: Wimg[slice][kst][split][row 0..255][32 bf16, 64B-swizzled];
 //      row = cil*F + d, element (row, kk) = filter[co = kst*32 + kk][ci = slice*NQ + cil][d]
 __global__ void f2f_tc_gin_prep_filter_bf16_kernel(int F, int Cin, int co0, int Cout, int nq, int nslices, int kst,
-                                                   int nsplit, const float* __restrict__ filter,
-                                                   uint8_t* __restrict__ wimg) {
+                                                   int nsplit, int64_t s_co, int64_t s_ci,
+                                                   const float* __restrict__ filter, uint8_t* __restrict__ wimg) {
     int64_t total = (int64_t)nslices * kst * NCOLS * 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -142,7 +145,7 @@ __global__ void f2f_tc_gin_prep_filter_bf16_kernel(int F, int Cin, int co0, int 
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 int co = ks * 32 + c * 8 + 2 * j + e;
-                v[e] = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + ((int64_t)(co0 + co) * Cin + ci) * F + d) : 0.f;
+                v[e] = (cil < nq && ci < Cin && co < Cout) ? __ldg(filter + (int64_t)(co0 + co) * s_co + (int64_t)ci * s_ci + d) : 0.f;
             }
             if (nsplit == 1) { hi[j] = pack_bf16x2(v[0], v[1]); lo[j] = 0u; }
             else split_bf16x2(v[0], v[1], hi[j], lo[j]);
@@ -153,6 +156,9 @@ __global__ void f2f_tc_gin_prep_filter_bf16_kernel(int F, int Cin, int co0, int 
         if (nsplit == 2) *reinterpret_cast<uint4*>(base + W_STAGE_BYTES + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
     }
 }
+
+// running sample count after face f; a null array stands for one sample per face
+__device__ __forceinline__ int cum_at(const int32_t* cum, int64_t f) { return cum ? __ldg(cum + f) : (int)(f + 1); }
 
 struct Params {
     int64_t Nf;
@@ -236,7 +242,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
         int k0n = 0, k1n = 0;
         {
             const int64_t f = (int64_t)blockIdx.x * TILE_M + r;
-            if (f < p.Nf) { k0n = f > 0 ? __ldg(p.cum + f - 1) : 0; k1n = __ldg(p.cum + f); }
+            if (f < p.Nf) { k0n = f > 0 ? cum_at(p.cum, f - 1) : 0; k1n = cum_at(p.cum, f); }
         }
         for (int64_t tile = blockIdx.x; tile < ntiles && alive; tile += gridDim.x, ++tcount) {
             const int64_t f0 = tile * TILE_M;
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             {
                 const int64_t fn = f + (int64_t)gridDim.x * TILE_M;
                 k0n = 0; k1n = 0;
-                if (fn < p.Nf) { k0n = __ldg(p.cum + fn - 1); k1n = __ldg(p.cum + fn); }
+                if (fn < p.Nf) { k0n = cum_at(p.cum, fn - 1); k1n = cum_at(p.cum, fn); }
             }
             const int T = k1 - k0;
             const float invT = T > 0 ? 1.f / (float)T : 0.f;
@@ -254,8 +260,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) f2f_bwd_gin_tc_kernel(Params p) {
             int kt0 = 0, kt1 = 0;
             {
                 int64_t fl = f0 + TILE_M < p.Nf ? f0 + TILE_M : p.Nf;
-                kt0 = f0 > 0 ? __ldg(p.cum + f0 - 1) : 0;
-                kt1 = __ldg(p.cum + fl - 1);
+                kt0 = f0 > 0 ? cum_at(p.cum, f0 - 1) : 0;
+                kt1 = cum_at(p.cum, fl - 1);
             }
             int nrows = kt1 - kt0;
             if (nrows > p.bary_rows) nrows = p.bary_rows;
@@ -642,28 +648,34 @@ size_t workspace_bytes(int Cin, int Cout, int F, int precision) {
 }
 
 template <int NSPLIT, int F, bool BF>
-static int launch(const Params& p, int grid, size_t smem, cudaStream_t stream) {
+static int launch(const char* label, const Params& p, int grid, size_t smem, cudaStream_t stream) {
     PB_CUDA(cudaFuncSetAttribute(f2f_bwd_gin_tc_kernel<NSPLIT, F, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem));
-    PB_LAUNCH("f2f_bwd_gin_tc", (f2f_bwd_gin_tc_kernel<NSPLIT, F, BF>), grid, NTHREADS, smem, stream, p);
+    PB_LAUNCH(label, (f2f_bwd_gin_tc_kernel<NSPLIT, F, BF>), grid, NTHREADS, smem, stream, p);
     return PB200_OK;
 }
 
 template <int NSPLIT, bool BF>
-static int launch_f(int F, const Params& p, int grid, size_t smem, cudaStream_t stream) {
+static int launch_f(const char* label, int F, const Params& p, int grid, size_t smem, cudaStream_t stream) {
     switch (F) {
-        case 4: return launch<NSPLIT, 4, BF>(p, grid, smem, stream);
-        case 9: return launch<NSPLIT, 9, BF>(p, grid, smem, stream);
-        case 16: return launch<NSPLIT, 16, BF>(p, grid, smem, stream);
-        case 25: return launch<NSPLIT, 25, BF>(p, grid, smem, stream);
-        default: return launch<NSPLIT, 36, BF>(p, grid, smem, stream);
+        case 4: return launch<NSPLIT, 4, BF>(label, p, grid, smem, stream);
+        case 9: return launch<NSPLIT, 9, BF>(label, p, grid, smem, stream);
+        case 16: return launch<NSPLIT, 16, BF>(label, p, grid, smem, stream);
+        case 25: return launch<NSPLIT, 25, BF>(label, p, grid, smem, stream);
+        default: return launch<NSPLIT, 36, BF>(label, p, grid, smem, stream);
     }
 }
 
+// transposed = false: the operator's input gradient (filter (Cout, Cin, F)).
+// transposed = true: the same contraction with the channel roles exchanged, for the forward pass of faces that have
+// one sample each (cum null): "gout" is the operator's input (Nf, Cout_here), "Cin" counts the operator's output
+// channels, the filter is the operator's (Cin_here, Cout_here, F) array, and gin receives the output.
 int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, const float* filter, const float* bary,
                    const float* bary_p, int Fp, const int32_t* cum, float* gin, int precision, void* ws,
-                   cudaStream_t stream) {
-    int rc = check_async_error("facet2facet_backward");
+                   cudaStream_t stream, bool transposed) {
+    const char* label = transposed ? "f2f_fwd_one_sample_tc" : "f2f_bwd_gin_tc";
+    const int64_t s_co = transposed ? (int64_t)F : (int64_t)Cin * F, s_ci = transposed ? (int64_t)Cout * F : (int64_t)F;
+    int rc = check_async_error(transposed ? "facet2facet_forward" : "facet2facet_backward");
     if (rc) return rc;
     Plan pl = plan(Cin, Cout, F, precision);
     uint8_t* wimg = (uint8_t*)ws;
@@ -675,10 +687,10 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
         const int64_t items = (int64_t)pl.nslices * kst * NCOLS * 4;
         if (pl.bf) {
             PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_bf16_kernel, persistent_blocks(items, 256, 8), 256, 0,
-                      stream, F, Cin, co0, cchunk, pl.nq, pl.nslices, kst, pl.nsplit, filter, wimg);
+                      stream, F, Cin, co0, cchunk, pl.nq, pl.nslices, kst, pl.nsplit, s_co, s_ci, filter, wimg);
         } else {
             PB_LAUNCH("f2f_tc_gin_prep_filter", f2f_tc_gin_prep_filter_kernel, persistent_blocks(items, 256, 8), 256, 0,
-                      stream, F, Cin, co0, cchunk, pl.nq, pl.nslices, kst, pl.nsplit, filter, wimg);
+                      stream, F, Cin, co0, cchunk, pl.nq, pl.nslices, kst, pl.nsplit, s_co, s_ci, filter, wimg);
         }
         Params p;
         p.Nf = Nf; p.Cin = Cin; p.Cout = cchunk;
@@ -688,8 +700,8 @@ int backward_input(int64_t Nf, int Cin, int Cout, int F, const float* gout, cons
         p.bary = bary; p.bary_p = bary_p; p.Fp = Fp; p.cum = cum; p.wimg = wimg; p.gin = gin;
         p.async_err = async_error_word();
         p.wait_budget = wait_budget_kclocks();
-        if (pl.bf) rc = pl.nsplit == 2 ? launch_f<2, true>(F, p, grid, pl.smem, stream) : launch_f<1, true>(F, p, grid, pl.smem, stream);
-        else rc = pl.nsplit == 2 ? launch_f<2, false>(F, p, grid, pl.smem, stream) : launch_f<1, false>(F, p, grid, pl.smem, stream);
+        if (pl.bf) rc = pl.nsplit == 2 ? launch_f<2, true>(label, F, p, grid, pl.smem, stream) : launch_f<1, true>(label, F, p, grid, pl.smem, stream);
+        else rc = pl.nsplit == 2 ? launch_f<2, false>(label, F, p, grid, pl.smem, stream) : launch_f<1, false>(label, F, p, grid, pl.smem, stream);
         if (rc) return rc;
     }
     return PB200_OK;

@@ -283,6 +283,33 @@ def test_block_with_folded_repetition_equals_the_expanded_block(mods, precision)
         assert torch.equal(a, c), n
 
 
+@pytest.mark.parametrize("nf,cin,cout,F", [(3000, 64, 64, 25), (1234, 128, 96, 16), (777, 32, 300, 9), (500, 3, 32, 16),
+                                            (650, 48, 40, 7), (129, 272, 64, 4)])
+@pytest.mark.parametrize("precision", ["fp32", "bf16", "tf32", "fp32_ffma"])
+def test_one_sample_forward_equals_the_general_forward(mods, nf, cin, cout, F, precision):
+    """pb200_facet2facet_one_sample_forward against pb200_facet2facet_forward with numInterior = 1..Nf and against
+    the fp64 formula; shapes on the exchanged-roles tensor-core kernel, on its chunked form (more than 256 input
+    channels), and on the fallbacks (F = 7, fp32_ffma)."""
+    conv3d, _, mo, _ = mods
+    from picassoplus_b200.block import one_sample_forward
+    g = torch.Generator().manual_seed(nf + cin)
+    x = torch.randn(nf, cin, generator=g).cuda()
+    w = (torch.randn(cout, cin, F, generator=g) / (cin * F) ** 0.5).cuda()
+    b = torch.randn(nf, F, generator=g).cuda()
+    one_each = torch.arange(1, nf + 1, dtype=torch.int32, device="cuda")
+    truth = torch.einsum("fd,fc,ocd->fo", b.double(), x.double(), w.double())
+    conv3d.set_f2f_precision(precision)
+    try:
+        got = one_sample_forward(x, w, b)
+        general = conv3d.facet2facet_forward(x, w, b, one_each)
+        again = one_sample_forward(x, w, b)
+    finally:
+        conv3d.set_f2f_precision("fp32")
+    gate = {"fp32": TOL, "fp32_ffma": 2e-5, "bf16": 2e-2, "tf32": 2e-3}[precision]
+    assert rel_err(got, truth) <= gate and rel_err(general, truth) <= gate, (rel_err(got, truth), rel_err(general, truth))
+    assert torch.equal(got, again)
+
+
 def test_one_benchmark_mesh_against_fp64(mods):
     """One 360 x 360 heightfield mesh of the headline configuration (128 -> 128 channels, L = 4,
     ~232 k faces): facet2facet forward and backward in every tensor-core mode against the fp64
