@@ -60,6 +60,8 @@ def parse_args():
                          "0 = one group per 256 MB of host input, at most 4")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-variants", action="store_true")
+    ap.add_argument("--no-cpu-binding", action="store_true",
+                    help="multi-GPU runs: leave the ranks' CPU affinity alone (default: bind each rank to the cores near its GPU)")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--hierarchy", default="decimate", choices=["decimate", "grid"],
                     help="config c4: mesh levels by the library's quadric-error decimation (stride 4 per level) or by "
@@ -326,7 +328,7 @@ def run_ours(args):
     from picassoplus_b200.math_utils import sph_harm_coeff
     from picassoplus_b200.mesh import utils as mesh_utils
     from picassoplus_b200.mesh.pi_modules import conv3d
-    from picassoplus_b200.parallel import FilterGradAllReduce, HostBatchFeed, partition_meshes
+    from picassoplus_b200.parallel import FilterGradAllReduce, HostBatchFeed, bind_to_gpu_cpus, partition_meshes
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -335,6 +337,8 @@ def run_ours(args):
         raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for --impl ours)")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # several ranks on one host: keep each rank's pinned staging buffers on the socket of its GPU
+    near_cpus = bind_to_gpu_cpus(local) if world > 1 and not args.no_cpu_binding else 0
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus or world == 1, f"WORLD_SIZE={world} but --gpus {args.gpus}"
@@ -635,6 +639,7 @@ def run_ours(args):
             "workload_detail": {"faces": int(faces_total), "vertices": int(nf_all[1].item()),
                                 "texture_samples": int(nf_all[2].item()), "f2f_precision": args.precision,
                                 "parallelism": f"mesh-dp{world}", "meshes_per_gpu": count,
+                                "cpus_bound_near_gpu": near_cpus,
                                 "block": "V2F -> F2F -> F2V with the repetition of the face rows folded into facet2facet "
                                          "(per-face mean sample weights, one sample per face); variants.block_as_written "
                                          "times the row expansion + general facet2facet",

@@ -50,6 +50,42 @@ def shard_batch(vertex: torch.Tensor, face: torch.Tensor, nv: torch.Tensor, mf: 
     return vertex[v0:v1], (face[f0:f1] - v0).to(face.dtype), nv[first:first + count], mf[first:first + count], (v0, v1, f0, f1)
 
 
+def bind_to_gpu_cpus(device_index: int) -> int:
+    """Restricts the calling process to the CPU cores that NVML reports as near GPU `device_index`, so that host
+    buffers allocated afterwards (pinned staging memory above all) come from that socket's memory and a rank's
+    host-to-device copies do not cross the socket link.  Read-only towards the GPU (no setting is changed); returns the
+    number of cores bound to, or 0 when NVML or the affinity call is not available (the process then keeps its
+    affinity)."""
+    import os
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = device_index
+            if visible:
+                entry = visible.split(",")[device_index].strip()
+                if entry.isdigit():
+                    index = int(entry)
+                    handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+                else:
+                    handle = pynvml.nvmlDeviceGetHandleByUUID(entry.encode() if isinstance(entry, str) else entry)
+            else:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            words = (os.cpu_count() + 63) // 64
+            mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        finally:
+            pynvml.nvmlShutdown()
+        cpus = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (int(word) >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if not cpus:
+            return 0
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return 0
+
+
 class FilterGradAllReduce:
     """Sums the gradients of a fixed list of (filter) parameters over the process group in
     one collective on a flat buffer that is allocated once."""
