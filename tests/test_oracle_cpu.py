@@ -178,3 +178,33 @@ def test_triangle_geometry():
     geo = mo.triangle_geometry(d["vertex"], d["face"])
     assert max_abs(geo, co.triangle_geometry(d["vertex"].numpy(), d["face"].numpy())) <= 1e-6
     assert torch.allclose(geo[:, :3].norm(dim=1), torch.ones(geo.shape[0]), atol=1e-5)
+
+
+def test_repeated_face_rows_fold_into_mean_weights():
+    """The identity behind block.conv_block: facet2facet over rows repeated once per sample equals facet2facet over
+    one row per face with the per-face mean of the sample weights and one sample per face -- output, filter gradient,
+    and the input gradient summed over each face's samples (the backward of the repetition).  fp64, the oracle's own
+    restatement of mesh_conv3d_gpu.cu:6-135; faces without samples included."""
+    import numpy as np
+    from oracle import mesh_oracle as mo
+    rng = np.random.default_rng(3)
+    nf, cin, cout, F = 57, 5, 4, 9
+    counts = torch.from_numpy(rng.integers(0, 5, size=nf).astype(np.int64))
+    cum = torch.cumsum(counts, 0).to(torch.int32)
+    nik = int(counts.sum())
+    y = torch.from_numpy(rng.standard_normal((nf, cin)))
+    bary = torch.from_numpy(rng.standard_normal((nik, F)))
+    w = torch.from_numpy(rng.standard_normal((cout, cin, F)))
+    g = torch.from_numpy(rng.standard_normal((nf, cout)))
+    seg = torch.repeat_interleave(torch.arange(nf), counts)
+    tex = y[seg]
+    out = mo.facet2facet_forward(tex, w, bary, cum)
+    gin, gf = mo.facet2facet_backward(g, tex, w, bary, cum)
+    gy = torch.zeros_like(y).index_add_(0, seg, gin)
+    mean = torch.zeros(nf, F, dtype=torch.float64).index_add_(0, seg, bary) / counts.clamp(min=1)[:, None]
+    one_each = torch.arange(1, nf + 1, dtype=torch.int32)
+    out1 = mo.facet2facet_forward(y, w, mean, one_each)
+    gy1, gf1 = mo.facet2facet_backward(g, y, w, mean, one_each)
+    for a, b in ((out1, out), (gy1, gy), (gf1, gf)):
+        assert float((a - b).abs().max()) <= 1e-12 * max(1.0, float(b.abs().max()))
+    assert torch.all(out[counts == 0] == 0) and torch.all(out1[counts == 0] == 0)
