@@ -417,7 +417,8 @@ def run_ours(args):
             # nfCount, face normals, their SH coefficients and the vertex CSR in one library call
             lvl = topology.prepare_level(b["vertex"], b["face"], vt, nv, L, want_geometry=False)
             nfc_, coeff_ = lvl["nf_count"], lvl["coeff"]
-            bary_ = sph_harm_coeff(L, b["bary_xyz"])
+            # SH components of the texture samples, averaged per face in the same kernel (all the folded block needs)
+            bary_ = topology.face_means_sph_harm(L, b["bary_xyz"], b["cum"])
             xe = b["x"].detach().requires_grad_()
             o = conv_block(xe, params[0], params[1], params[2], b["face"], b["cum"], bary_, coeff_, nfc_, vt, sh_eye)
             loss = (o * group_G[gi]).sum()

@@ -433,6 +433,11 @@ int pb200_expand_rows_backward(int64_t Nf, int64_t NiK, int C, const float* grad
  * No counterpart inside the reference's extension. */
 int pb200_face_mean_rows(int64_t Nf, int64_t NiK, int C, const float* rows, const int32_t* numInterior, float* out,
                          void* stream);
+/* The same per-face mean for rows that are the spherical-harmonic components of sample positions: out[f,:] =
+ * mean over the samples k of face f of pb200_sph_harm_coeff(xyz[k]) (identical bits), without the (NiK,(L+1)^2) array
+ * in between.  xyz (NiK,3), out (Nf,(L+1)^2), L <= 5. */
+int pb200_face_mean_sph_harm(int64_t Nf, int64_t NiK, int L, const float* xyz, const int32_t* numInterior, float* out,
+                             void* stream);
 
 #ifdef __cplusplus
 }

@@ -97,6 +97,7 @@ SIGNATURES = {
     "pb200_expand_rows_forward": (i32, [i64, i64, i32, vp, vp, vp, vp]),
     "pb200_expand_rows_backward": (i32, [i64, i64, i32, vp, vp, vp, vp]),
     "pb200_face_mean_rows": (i32, [i64, i64, i32, vp, vp, vp, vp]),
+    "pb200_face_mean_sph_harm": (i32, [i64, i64, i32, vp, vp, vp, vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

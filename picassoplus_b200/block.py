@@ -18,7 +18,7 @@ import torch
 
 from . import _lib
 from .mesh.pi_modules import conv3d
-from .topology import face_means, ptr, stream_ptr
+from .topology import FaceMeans, face_means, ptr, stream_ptr
 
 
 class _ExpandRows(torch.autograd.Function):
@@ -105,8 +105,10 @@ class _SharedRowsF2F(torch.autograd.Function):
 
 
 def facet2facet_shared_rows(face_rows, filter, bary_sh, cum):
-    """facet2facet(repeat_interleave(face_rows, samples per face), filter, bary_sh, cum) without the expanded rows."""
-    fm = face_means(bary_sh, cum)
+    """facet2facet(repeat_interleave(face_rows, samples per face), filter, bary_sh, cum) without the expanded rows.
+    bary_sh: the (NiK, F) sample weights, or their per-face means as topology.face_means / face_means_sph_harm
+    return them (then cum is not looked at)."""
+    fm = bary_sh if isinstance(bary_sh, FaceMeans) else face_means(bary_sh, cum)
     return _SharedRowsF2F.apply(face_rows, filter, fm.rows, fm.one_each)
 
 

@@ -354,6 +354,28 @@ def face_means(sample_rows: torch.Tensor, num_interior: torch.Tensor) -> FaceMea
     return fm
 
 
+def face_means_sph_harm(L: int, sample_xyz: torch.Tensor, num_interior: torch.Tensor) -> FaceMeans:
+    """face_means(sph_harm_coeff(L, sample_xyz), num_interior) in one kernel (identical bits), without the
+    (NiK, (L+1)^2) array; cached the same way."""
+    nf, nik = num_interior.shape[0], sample_xyz.shape[0]
+    slot = ("face_means_sh", sample_xyz.device.index, sample_xyz.data_ptr(), num_interior.data_ptr(), nik, nf, int(L))
+    versions = (sample_xyz._version, num_interior._version)
+    hit = _lookup(slot, versions)
+    if hit is not None:
+        return hit
+    if sample_xyz.dim() != 2 or sample_xyz.shape[1] != 3 or sample_xyz.dtype != torch.float32 or not sample_xyz.is_contiguous():
+        raise RuntimeError("sample_xyz must be a contiguous float32 tensor of shape (NiK, 3)")
+    dev = sample_xyz.device
+    with torch.cuda.device(dev):
+        check_num_interior(num_interior, nik)
+        rows = torch.empty(nf, (L + 1) ** 2, dtype=torch.float32, device=dev)
+        _lib.call("pb200_face_mean_sph_harm", nf, nik, int(L), ptr(sample_xyz), ptr(num_interior), ptr(rows), stream_ptr(dev))
+        one_each = torch.arange(1, nf + 1, dtype=torch.int32, device=dev)
+    fm = FaceMeans(rows, one_each, (sample_xyz, num_interior), versions)
+    _store(slot, fm)
+    return fm
+
+
 def check_num_interior(num_interior: torch.Tensor, nik: int) -> None:
     """Validates a running sample count (non-decreasing, inside [0, nik], ends at nik) on the
     device: raises in 'sync' mode, queues the status word in 'deferred' mode.  The facet2facet

@@ -310,6 +310,30 @@ def test_one_sample_forward_equals_the_general_forward(mods, nf, cin, cout, F, p
     assert torch.equal(got, again)
 
 
+@pytest.mark.parametrize("L", [0, 2, 3, 4, 5])
+def test_face_means_of_sh_components_in_one_kernel(mods, L):
+    """pb200_face_mean_sph_harm against pb200_sph_harm_coeff followed by pb200_face_mean_rows (same bits) and against the
+    fp64 oracle; faces without samples, a long run of samples on one face, and the conv_block call that takes the means."""
+    _, _, mo, _ = mods
+    from picassoplus_b200 import topology
+    from picassoplus_b200.math_utils import sph_harm_coeff
+    rng = np.random.default_rng(70 + L)
+    nf = 1000
+    counts = rng.integers(0, 5, size=nf)
+    counts[123] = 37
+    nik = int(counts.sum())
+    xyz = torch.from_numpy(rng.dirichlet((1.0, 1.0, 1.0), size=nik).astype(np.float32)).cuda()
+    cum = torch.cumsum(torch.from_numpy(counts), 0, dtype=torch.int32).cuda()
+    fused = topology.face_means_sph_harm(L, xyz, cum)
+    two_step = topology.face_means(sph_harm_coeff(L, xyz), cum)
+    assert torch.equal(fused.rows, two_step.rows) and torch.equal(fused.one_each, two_step.one_each)
+    sh = mo.sph_harm_coeff(L, xyz.cpu()).double()
+    seg = torch.repeat_interleave(torch.arange(nf), torch.from_numpy(counts))
+    want = torch.zeros(nf, (L + 1) ** 2, dtype=torch.float64).index_add_(0, seg, sh) / torch.from_numpy(counts).clamp(min=1)[:, None]
+    assert max_abs(fused.rows, want) <= 5e-6
+    assert torch.all(fused.rows[torch.from_numpy(counts == 0).cuda()] == 0)
+
+
 def test_one_benchmark_mesh_against_fp64(mods):
     """One 360 x 360 heightfield mesh of the headline configuration (128 -> 128 channels, L = 4,
     ~232 k faces): facet2facet forward and backward in every tensor-core mode against the fp64
