@@ -250,11 +250,12 @@ int pb200_facet2facet_forward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F,
  * over d in the epilogue (the input-gradient kernel with the channel roles exchanged), which needs no face operand
  * of F*Cin products.  With pb200_face_mean_rows this is the forward pass of "one row per face shared by its
  * samples"; the matching backward is pb200_facet2facet_backward over (input, weights, numInterior = 1..Nf).
+ * weightsPadded (may be NULL): the pb200_pad_rows copy of weights; given, the call does not pad weights itself.
  * No counterpart inside the reference's extension. */
 size_t pb200_facet2facet_one_sample_forward_workspace_bytes(int64_t Nf, int Cin, int Cout, int F, int precision);
 int pb200_facet2facet_one_sample_forward(int64_t Nf, int Cin, int Cout, int F, const float* input, const float* filter,
-                                         const float* weights, float* output, int precision, void* workspace,
-                                         size_t workspace_bytes, void* stream);
+                                         const float* weights, const float* weightsPadded, float* output, int precision,
+                                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* gradInput[k,ci] = (1/T_f) sum_d bary[k,d] * sum_co gradOutput[f,co]*filter[co,ci,d];
  * gradFilter[co,ci,d] = sum_f gradOutput[f,co]*A[f,d,ci]
@@ -268,6 +269,18 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
                                const float* input, const float* filter, const float* bary,
                                const int32_t* numInterior, float* gradInput, float* gradFilter,
                                int precision, void* workspace, size_t workspace_bytes, void* stream);
+
+/* The tensor-core kernels read the rows of bary 16 bytes at a time; when F is not a multiple of 4 they work on a copy
+ * with rows padded to pb200_padded_row_floats(F) floats (pad columns zero) that every call makes in its workspace.  A
+ * caller that uses the same bary for several calls (forward and backward of a step, several steps) can make the copy once
+ * with pb200_pad_rows (out: (N, pb200_padded_row_floats(F)), 16-byte aligned) and pass it as baryPadded; NULL = pad
+ * inside the call as pb200_facet2facet_backward does.  Same results bit for bit. */
+int pb200_padded_row_floats(int F);
+int pb200_pad_rows(int64_t N, int F, const float* rows, float* out, void* stream);
+int pb200_facet2facet_backward_padded(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
+                                      const float* input, const float* filter, const float* bary, const float* baryPadded,
+                                      const int32_t* numInterior, float* gradInput, float* gradFilter,
+                                      int precision, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- spherical-harmonic basis and triangle geometry -----------------------------------
  * out[i, 0..(L+1)^2) = real/imaginary spherical-harmonic components of xyz[i] projected

@@ -65,9 +65,12 @@ SIGNATURES = {
     "pb200_facet2facet_forward_workspace_bytes": (sz, [i64, i64, i32, i32, i32, i32]),
     "pb200_facet2facet_forward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_facet2facet_one_sample_forward_workspace_bytes": (sz, [i64, i32, i32, i32, i32]),
-    "pb200_facet2facet_one_sample_forward": (i32, [i64, i32, i32, i32, vp, vp, vp, vp, i32, vp, sz, vp]),
+    "pb200_facet2facet_one_sample_forward": (i32, [i64, i32, i32, i32, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
+    "pb200_padded_row_floats": (i32, [i32]),
+    "pb200_pad_rows": (i32, [i64, i32, vp, vp, vp]),
     "pb200_facet2facet_backward_workspace_bytes": (sz, [i64, i64, i32, i32, i32, i32]),
     "pb200_facet2facet_backward": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
+    "pb200_facet2facet_backward_padded": (i32, [i64, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, sz, vp]),
     "pb200_level_prepare": (i32, [i64, i64, i64, i32, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "pb200_cluster_csr_workspace_bytes": (sz, [i64, i64]),
     "pb200_build_cluster_csr": (i32, [i64, i64, vp, vp, vp, vp, vp, vp, vp, sz, vp]),

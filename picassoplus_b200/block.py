@@ -62,8 +62,9 @@ def conv_block_expanded(x, Wv, Wf, Wo, face, cum, bary_sh, coeff, nf_count, vt_m
     return conv3d.facet2vertex(z, Wo, coeff, face, nf_count, vt_map)
 
 
-def one_sample_forward(face_rows, filter, weights):
-    """facet2facet forward for exactly one sample per face: (Nf, Cin) rows, (Cout, Cin, F) filter, (Nf, F) weights."""
+def one_sample_forward(face_rows, filter, weights, weights_padded=None):
+    """facet2facet forward for exactly one sample per face: (Nf, Cin) rows, (Cout, Cin, F) filter, (Nf, F) weights;
+    weights_padded: topology.pad_rows(weights) when the caller keeps it (saves the copy inside the call)."""
     conv3d._check(face_rows, "input", 2, torch.float32)
     conv3d._check(filter, "filter", 3, torch.float32)
     conv3d._check(weights, "weights", 2, torch.float32)
@@ -76,6 +77,8 @@ def one_sample_forward(face_rows, filter, weights):
     if tuple(weights.shape) != (Nf, F):
         raise RuntimeError("weights must have shape (NfIn, number of filters)")
     face_rows, weights = conv3d._aligned16(face_rows), conv3d._aligned16(weights)
+    if weights_padded is not None and tuple(weights_padded.shape) != (Nf, _lib.query("pb200_padded_row_floats", F)):
+        raise RuntimeError("weights_padded must have shape (NfIn, padded row length)")
     dev = face_rows.device
     precision = conv3d._f2f_precision
     with torch.cuda.device(dev):
@@ -83,7 +86,7 @@ def one_sample_forward(face_rows, filter, weights):
         nb = _lib.query("pb200_facet2facet_one_sample_forward_workspace_bytes", Nf, Cin, Cout, F, precision)
         ws = conv3d._ws(nb, dev)
         _lib.call("pb200_facet2facet_one_sample_forward", Nf, Cin, Cout, F, ptr(face_rows), ptr(filter), ptr(weights),
-                  ptr(out), precision, ptr(ws), nb, stream_ptr(dev))
+                  ptr(weights_padded), ptr(out), precision, ptr(ws), nb, stream_ptr(dev))
     return out
 
 
@@ -92,16 +95,18 @@ class _SharedRowsF2F(torch.autograd.Function):
     backward through the general operator's backward over (rows, per-face mean weights, one sample per face)."""
 
     @staticmethod
-    def forward(ctx, face_rows, filter, weights, one_each):
+    def forward(ctx, face_rows, filter, weights, one_each, weights_padded):
         face_rows, filter = face_rows.contiguous(), filter.contiguous()
         ctx.save_for_backward(face_rows, filter, weights, one_each)
-        return one_sample_forward(face_rows, filter, weights)
+        ctx.weights_padded = weights_padded
+        return one_sample_forward(face_rows, filter, weights, weights_padded)
 
     @staticmethod
     def backward(ctx, grad_output):
         face_rows, filter, weights, one_each = ctx.saved_tensors
-        gin, gf = conv3d.facet2facet_backward(grad_output.contiguous(), face_rows, filter, weights, one_each)
-        return gin, gf, None, None
+        gin, gf = conv3d.facet2facet_backward(grad_output.contiguous(), face_rows, filter, weights, one_each,
+                                              baryPadded=ctx.weights_padded)
+        return gin, gf, None, None, None
 
 
 def facet2facet_shared_rows(face_rows, filter, bary_sh, cum):
@@ -109,7 +114,7 @@ def facet2facet_shared_rows(face_rows, filter, bary_sh, cum):
     bary_sh: the (NiK, F) sample weights, or their per-face means as topology.face_means / face_means_sph_harm
     return them (then cum is not looked at)."""
     fm = bary_sh if isinstance(bary_sh, FaceMeans) else face_means(bary_sh, cum)
-    return _SharedRowsF2F.apply(face_rows, filter, fm.rows, fm.one_each)
+    return _SharedRowsF2F.apply(face_rows, filter, fm.rows, fm.one_each, fm.rows_padded)
 
 
 def conv_block(x, Wv, Wf, Wo, face, cum, bary_sh, coeff, nf_count, vt_map, sh_eye):

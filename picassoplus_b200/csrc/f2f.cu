@@ -107,8 +107,8 @@ __global__ void count_up_kernel(int64_t n, int32_t* out) {
 }
 
 int pb200_facet2facet_one_sample_forward(int64_t Nf, int Cin, int Cout, int F, const float* input, const float* filter,
-                                         const float* weights, float* output, int precision, void* workspace,
-                                         size_t workspace_bytes, void* stream_) {
+                                         const float* weights, const float* weightsPadded, float* output, int precision,
+                                         void* workspace, size_t workspace_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     PB_REQUIRE(f2f_sizes_ok(Nf, Nf, Cin, Cout, F), PB200_EINVAL, "facet2facet_one_sample_forward: bad sizes (F must be in 1..50)");
     PB_REQUIRE(precision >= PB200_PREC_FP32 && precision <= PB200_PREC_FP32_TF32X3, PB200_EINVAL,
@@ -123,7 +123,11 @@ int pb200_facet2facet_one_sample_forward(int64_t Nf, int Cin, int Cout, int F, c
                    "facet2facet_one_sample_forward: input, weights and workspace must be 16-byte aligned");
         const float* wp = weights;
         const int Fp = tc::padded_F(F);
-        if (F % 4 != 0) {
+        if (F % 4 != 0 && weightsPadded) {
+            PB_REQUIRE(aligned16(weightsPadded), PB200_EINVAL,
+                       "facet2facet_one_sample_forward: weightsPadded must be 16-byte aligned");
+            wp = weightsPadded;
+        } else if (F % 4 != 0) {
             float* dst = (float*)(w + tc::gin::workspace_bytes(Cout, Cin, F, precision));
             int rc = tc::pad_bary(Nf, F, weights, dst, stream);
             if (rc) return rc;
@@ -150,10 +154,14 @@ size_t pb200_facet2facet_backward_workspace_bytes(int64_t Nf, int64_t NiK, int C
     return n;
 }
 
-int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
-                               const float* input, const float* filter, const float* bary,
-                               const int32_t* numInterior, float* gradInput, float* gradFilter, int precision,
-                               void* workspace, size_t workspace_bytes, void* stream_) {
+}  // extern "C"
+
+// baryPadded: optional copy of bary with rows padded to padded_F(F) floats (pad columns zero), as pb200_pad_rows
+// makes it; given, the tensor-core kernels read it instead of padding bary into the workspace on every call
+static int f2f_backward_impl(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
+                             const float* input, const float* filter, const float* bary, const float* baryPadded,
+                             const int32_t* numInterior, float* gradInput, float* gradFilter, int precision,
+                             void* workspace, size_t workspace_bytes, void* stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     PB_REQUIRE(f2f_sizes_ok(Nf, NiK, Cin, Cout, F), PB200_EINVAL,
                "facet2facet_backward: bad sizes (F must be in 1..50)");
@@ -179,11 +187,16 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
     const float* bary_p = bary;
     const int Fp = tc::padded_F(F);
     if ((tg || tf) && F % 4 != 0 && NiK > 0) {
-        char* wp = w + (tg ? tc::gin::workspace_bytes(Cin, Cout, F, precision) : 0) +
-                   (tf ? tc::gfilter::workspace_bytes(Nf, Cin, Cout, F, precision) : 0);
-        int rc = tc::pad_bary(NiK, F, bary, (float*)wp, stream);
-        if (rc) return rc;
-        bary_p = (const float*)wp;
+        if (baryPadded) {
+            PB_REQUIRE(aligned16(baryPadded), PB200_EINVAL, "facet2facet_backward: baryPadded must be 16-byte aligned");
+            bary_p = baryPadded;
+        } else {
+            char* wp = w + (tg ? tc::gin::workspace_bytes(Cin, Cout, F, precision) : 0) +
+                       (tf ? tc::gfilter::workspace_bytes(Nf, Cin, Cout, F, precision) : 0);
+            int rc = tc::pad_bary(NiK, F, bary, (float*)wp, stream);
+            if (rc) return rc;
+            bary_p = (const float*)wp;
+        }
     }
     if (tg) {
         if (NiK > 0) {
@@ -211,6 +224,34 @@ int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F
     if (tg && tf) return PB200_OK;
     return f2f_simt_backward(Nf, NiK, Cin, Cout, F, gradOutput, input, filter, bary, numInterior, gradInput,
                              gradFilter, simt_ws, stream, !tg, !tf);
+}
+
+extern "C" {
+
+int pb200_facet2facet_backward(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
+                               const float* input, const float* filter, const float* bary,
+                               const int32_t* numInterior, float* gradInput, float* gradFilter, int precision,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    return f2f_backward_impl(Nf, NiK, Cin, Cout, F, gradOutput, input, filter, bary, nullptr, numInterior, gradInput,
+                             gradFilter, precision, workspace, workspace_bytes, stream);
+}
+
+int pb200_facet2facet_backward_padded(int64_t Nf, int64_t NiK, int Cin, int Cout, int F, const float* gradOutput,
+                                      const float* input, const float* filter, const float* bary, const float* baryPadded,
+                                      const int32_t* numInterior, float* gradInput, float* gradFilter, int precision,
+                                      void* workspace, size_t workspace_bytes, void* stream) {
+    return f2f_backward_impl(Nf, NiK, Cin, Cout, F, gradOutput, input, filter, bary, baryPadded, numInterior, gradInput,
+                             gradFilter, precision, workspace, workspace_bytes, stream);
+}
+
+int pb200_padded_row_floats(int F) { return F > 0 ? tc::padded_F(F) : 0; }
+
+int pb200_pad_rows(int64_t N, int F, const float* rows, float* out, void* stream) {
+    PB_REQUIRE(N >= 0 && F > 0, PB200_EINVAL, "pad_rows: bad sizes");
+    if (N == 0) return PB200_OK;
+    PB_REQUIRE(rows && out, PB200_EINVAL, "pad_rows: null pointer");
+    PB_REQUIRE(aligned16(out), PB200_EINVAL, "pad_rows: out must be 16-byte aligned");
+    return tc::pad_bary(N, F, rows, out, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -77,7 +77,8 @@ def facet2facet_forward(textureIn, filter, baryCoeff, numTexture):
     return out
 
 
-def facet2facet_backward(grad_output, textureIn, filter, baryCoeff, numTexture):
+def facet2facet_backward(grad_output, textureIn, filter, baryCoeff, numTexture, baryPadded=None):
+    """baryPadded (not in the reference's signature): topology.pad_rows(baryCoeff), for callers that keep it."""
     _check(textureIn, "input", 2, torch.float32)
     _check(filter, "filter", 3, torch.float32)
     _check(grad_output, "grad_output", 2, torch.float32)
@@ -101,8 +102,11 @@ def facet2facet_backward(grad_output, textureIn, filter, baryCoeff, numTexture):
         gf = torch.empty(Cout, Cin, F, dtype=textureIn.dtype, device=dev)
         nb = _lib.query("pb200_facet2facet_backward_workspace_bytes", Nf, NiK, Cin, Cout, F, _f2f_precision)
         ws = _ws(nb, dev)
-        _lib.call("pb200_facet2facet_backward", Nf, NiK, Cin, Cout, F, ptr(grad_output), ptr(textureIn), ptr(filter),
-                  ptr(baryCoeff), ptr(numTexture), ptr(gin), ptr(gf), _f2f_precision, ptr(ws), nb, stream_ptr(dev))
+        if baryPadded is not None and tuple(baryPadded.shape) != (NiK, _lib.query("pb200_padded_row_floats", F)):
+            raise RuntimeError("baryPadded must have shape (NiK, padded row length)")
+        _lib.call("pb200_facet2facet_backward_padded", Nf, NiK, Cin, Cout, F, ptr(grad_output), ptr(textureIn), ptr(filter),
+                  ptr(baryCoeff), ptr(baryPadded), ptr(numTexture), ptr(gin), ptr(gf), _f2f_precision, ptr(ws), nb,
+                  stream_ptr(dev))
     return gin, gf
 
 

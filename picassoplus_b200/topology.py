@@ -327,9 +327,25 @@ class FaceMeans:
     def __init__(self, rows, one_each, keep, versions):
         self.rows = rows
         self.one_each = one_each
+        # the copy with rows padded to a multiple of four floats that the tensor-core kernels read (None when the row
+        # length is such a multiple already): made once here instead of in every forward and backward call
+        self.rows_padded = pad_rows(rows)
         self._keep = keep
         self._versions = versions
-        self.nbytes = 4 * (rows.numel() + one_each.numel())
+        self.nbytes = 4 * (rows.numel() + one_each.numel() + (0 if self.rows_padded is None else self.rows_padded.numel()))
+
+
+def pad_rows(rows: torch.Tensor):
+    """(N, F) float32 rows -> (N, F rounded up to 4) with zero pad columns, or None when F % 4 == 0."""
+    n, F = rows.shape
+    if F % 4 == 0 or n == 0:
+        return None
+    Fp = _lib.query("pb200_padded_row_floats", F)
+    dev = rows.device
+    with torch.cuda.device(dev):
+        out = torch.empty(n, Fp, dtype=torch.float32, device=dev)
+        _lib.call("pb200_pad_rows", n, F, ptr(rows), ptr(out), stream_ptr(dev))
+    return out
 
 
 def face_means(sample_rows: torch.Tensor, num_interior: torch.Tensor) -> FaceMeans:

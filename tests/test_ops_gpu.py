@@ -300,14 +300,22 @@ def test_one_sample_forward_equals_the_general_forward(mods, nf, cin, cout, F, p
     truth = torch.einsum("fd,fc,ocd->fo", b.double(), x.double(), w.double())
     conv3d.set_f2f_precision(precision)
     try:
+        from picassoplus_b200 import topology
         got = one_sample_forward(x, w, b)
         general = conv3d.facet2facet_forward(x, w, b, one_each)
         again = one_sample_forward(x, w, b)
+        # the caller-kept padded copy of the weight rows changes nothing but the work done per call
+        bp = topology.pad_rows(b)
+        assert (bp is None) == (F % 4 == 0)
+        kept = one_sample_forward(x, w, b, bp)
+        go = torch.randn(nf, cout, generator=g).cuda()
+        back, back_kept = conv3d.facet2facet_backward(go, x, w, b, one_each), conv3d.facet2facet_backward(go, x, w, b, one_each, bp)
     finally:
         conv3d.set_f2f_precision("fp32")
     gate = {"fp32": TOL, "fp32_ffma": 2e-5, "bf16": 2e-2, "tf32": 2e-3}[precision]
     assert rel_err(got, truth) <= gate and rel_err(general, truth) <= gate, (rel_err(got, truth), rel_err(general, truth))
-    assert torch.equal(got, again)
+    assert torch.equal(got, again) and torch.equal(got, kept)
+    assert torch.equal(back[0], back_kept[0]) and torch.equal(back[1], back_kept[1])
 
 
 @pytest.mark.parametrize("L", [0, 2, 3, 4, 5])
