@@ -511,3 +511,49 @@ def test_error_behaviour(mods):
         conv3d.vertex2facet_backward(d["g_v2f"], d["x_v"], d["filt_v2f"], bad)
     # the context is still usable afterwards
     assert torch.isfinite(conv3d.vertex2facet(d["x_v"], d["filt_v2f"], d["face"])).all()
+
+
+def test_error_behaviour_of_the_shared_rows_entries(mods):
+    """Bad arguments to the one-sample forward, the padded-copy arguments, the per-face means and the cluster form of the
+    max-pool gradient are answered with an error (RuntimeError from the wrappers, an error code from the C ABI), and the
+    context keeps working."""
+    conv3d, _, _, _ = mods
+    from picassoplus_b200 import _lib, topology
+    from picassoplus_b200.block import one_sample_forward
+    from picassoplus_b200.topology import ptr, stream_ptr
+    nf, cin, cout, F = 300, 32, 16, 25
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(nf, cin, generator=g).cuda()
+    w = torch.randn(cout, cin, F, generator=g).cuda()
+    b = torch.randn(nf, F, generator=g).cuda()
+    with pytest.raises(RuntimeError):
+        one_sample_forward(x, w[:, :8].contiguous(), b)                        # filter input channels
+    with pytest.raises(RuntimeError):
+        one_sample_forward(x, w, b[:-1].contiguous())                           # one weight row per face
+    with pytest.raises(RuntimeError):
+        one_sample_forward(x, w, b, torch.zeros(nf, 27, device="cuda"))         # padded copy of the wrong width
+    with pytest.raises(RuntimeError):
+        one_sample_forward(x.cpu(), w, b)                                       # not CUDA
+    with pytest.raises(RuntimeError):
+        conv3d.facet2facet_backward(torch.zeros(nf, cout, device="cuda"), x, w, b,
+                                    torch.arange(1, nf + 1, dtype=torch.int32, device="cuda"), torch.zeros(nf, 24, device="cuda"))
+    with pytest.raises(RuntimeError):
+        topology.face_means_sph_harm(4, torch.zeros(10, 2, device="cuda"), torch.arange(1, 11, dtype=torch.int32, device="cuda"))
+    # straight at the C ABI: a workspace that is too small, an unknown precision, a degree above 5
+    out = torch.empty(nf, cout, device="cuda")
+    ws = torch.empty(16, dtype=torch.uint8, device="cuda")
+    need = _lib.query("pb200_facet2facet_one_sample_forward_workspace_bytes", nf, cin, cout, F, _lib.PREC_FP32)
+    assert need > 16
+    with pytest.raises(RuntimeError, match="workspace"):
+        _lib.call("pb200_facet2facet_one_sample_forward", nf, cin, cout, F, ptr(x), ptr(w), ptr(b), None, ptr(out), _lib.PREC_FP32,
+                  ptr(ws), 16, stream_ptr(x.device))
+    big = torch.empty(need, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="precision"):
+        _lib.call("pb200_facet2facet_one_sample_forward", nf, cin, cout, F, ptr(x), ptr(w), ptr(b), None, ptr(out), 99, ptr(big), need,
+                  stream_ptr(x.device))
+    with pytest.raises(RuntimeError, match="degree"):
+        _lib.call("pb200_face_mean_sph_harm", 10, 10, 6, ptr(x), ptr(torch.arange(1, 11, dtype=torch.int32, device="cuda")), ptr(out),
+                  stream_ptr(x.device))
+    assert _lib.query("pb200_padded_row_floats", 25) == 28 and _lib.query("pb200_padded_row_floats", 16) == 16
+    # nothing of the above has left the device in a bad state
+    assert torch.isfinite(one_sample_forward(x, w, b)).all()
