@@ -432,9 +432,10 @@ def run_ours(args):
             bary_ = topology.face_means_sph_harm(L, b["bary_xyz"], b["cum"])
             xe = b["x"].detach().requires_grad_()
             o = conv_block(xe, params[0], params[1], params[2], b["face"], b["cum"], bary_, coeff_, nfc_, vt, sh_eye)
-            loss = (o * group_G[gi]).sum()
-            loss.backward()
-            total = total + loss.detach()
+            # loss = sum(o * G): its value by one dot product, its gradient with respect to o is G itself
+            with torch.no_grad():
+                total = total + torch.dot(o.reshape(-1), group_G[gi].reshape(-1))
+            o.backward(group_G[gi])
         allreduce()
         out = float(total.item())
         topology.check_deferred()
